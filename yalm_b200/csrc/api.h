@@ -1,0 +1,59 @@
+// C interface of the sm_100a kernel library.  Every function launches on the
+// given stream and returns 0, a cudaError_t of the launch, or a negative code
+// for arguments it refuses (a size the kernel does not take).  Pointers are
+// device pointers unless said otherwise.  dtype codes: 0 = float32, 1 = bfloat16.
+#pragma once
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int yalm_embed(const int* tokens, const void* table, int table_dtype, float* x, int n_tokens,
+               int dim, int vocab, int* status, cudaStream_t stream);
+
+int yalm_rmsnorm(float* x, const float* partials, int n_partials, long long partial_stride,
+                 const int* rows, const float* weight, void* out, int out_dtype, int n_rows,
+                 int dim, float eps, cudaStream_t stream);
+
+int yalm_silu_mul(const float* gu, int n_partials, long long partial_stride, void* out,
+                  int out_dtype, int rows, int F, cudaStream_t stream);
+
+int yalm_rope_store(const float* qkv, int n_partials, long long partial_stride,
+                    const float* inv_freq, const int* token_seq, const int* q_start,
+                    const int* seq_slot, const int* slot_pos, void* q_out, void* kv_step,
+                    void* k_cache, void* v_cache, int dtype, int n_tokens, int H, int G, int hd,
+                    int capacity, int write_cache, cudaStream_t stream);
+
+int yalm_advance(const int* q_start, const int* seq_slot, int* slot_pos, int n_seqs,
+                 cudaStream_t stream);
+
+int yalm_attention(const void* q, const void* kv_step, const void* k_cache, const void* v_cache,
+                   const int* token_seq, const int* q_start, const int* seq_slot,
+                   const int* slot_pos, void* out, float* part_o, float* part_ml, int dtype,
+                   int n_tokens, int H, int G, int hd, int capacity, int window, int nsplit,
+                   cudaStream_t stream);
+
+int yalm_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* out,
+                   int out_dtype, int M, int N, int K, int accumulate, cudaStream_t stream);
+
+int yalm_sample(const float* logits, int n_rows, int vocab, float temperature,
+                unsigned long long seed, const int* row_key, const int* seq_slot,
+                const int* slot_pos, int* out_tokens, cudaStream_t stream);
+
+float yalm_uniform01(unsigned long long seed, unsigned key, unsigned counter);
+
+// tcgen05 / TMA matrix product (bfloat16 operands, 32-bit accumulation in TMEM):
+//   mode 0: out[M,N]  = A W^T             (out_dtype 0 or 1)
+//   mode 1: out[M,N] += A W^T             (out float32: the residual stream)
+//   mode 2: out[M,N/2] = silu(A Wg^T) * (A Wu^T), W = [Wg; Wu] with N rows in all
+//   mode 3: out[s][M,N] = partial products of `splits` slices of K (float32 scratch)
+// status: a device int that receives ERR_WAIT_TIMEOUT if a bounded wait gave up.
+int yalm_gemm_tc(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
+                 int mode, int splits, int* status, cudaStream_t stream);
+// 0 if the driver's tensor-map encoder was found (host-side set-up of yalm_gemm_tc).
+int yalm_gemm_tc_available(void);
+
+#ifdef __cplusplus
+}
+#endif

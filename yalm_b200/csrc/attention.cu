@@ -1,0 +1,265 @@
+// Causal grouped-query attention over the cache, one query token per block
+// column, for prefill and decode alike, in 32-bit arithmetic on bfloat16 or
+// 32-bit storage.
+//
+// The reference computes the same thing for one token of one sequence with
+// three kernels (attn_dot infer.cu:339-362, attn_softmax infer.cu:364-396,
+// att_mix infer.cu:398-523): scores (q.k)/sqrt(hd) over kv_len keys, a
+// max-subtracted softmax, the weighted sum of values.  Here one kernel does
+// all three with an online softmax; the query heads that share a kv head
+// share its loads; the keys of one query can be split over several blocks
+// (split-KV) whose partial results a second kernel merges.
+//
+// Where a key lives: position j of a sequence is in this step's own buffer
+// (kv_step) when j >= past (the sequence's length before the step), else in
+// the cache ring at row j % capacity.  A prompt longer than the ring therefore
+// still sees all of its own keys during prefill.
+#include "api.h"
+#include "common.cuh"
+
+namespace yalm {
+
+constexpr int ATT_RT = 4;        // query heads per block (of those sharing one kv head)
+constexpr int ATT_WARPS = 4;
+constexpr int ATT_EPL = 8;       // elements of a head that one lane owns
+
+template <typename T> struct Vec8;
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 v = __bfloat1622float2(h[i]);
+      f[2 * i] = v.x;
+      f[2 * i + 1] = v.y;
+    }
+  }
+};
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+};
+
+// LPK lanes share one key (LPK*8 >= hd); a warp handles 32/LPK keys at a time.
+template <typename T, int LPK>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_token_kernel(const T* __restrict__ q, const T* __restrict__ kv_step,
+                  const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                  const int* __restrict__ token_seq, const int* __restrict__ q_start,
+                  const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
+                  T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                  int H, int G, int hd, int capacity, int window, int nsplit, float scale, int t0) {
+  constexpr int KPW = 32 / LPK;                 // keys per warp per iteration
+  constexpr int GROUPS = ATT_WARPS * KPW;       // key groups per block
+  __shared__ float m_s[GROUPS][ATT_RT];
+  __shared__ float l_s[GROUPS][ATT_RT];
+  __shared__ float o_s[ATT_RT * GROUPS * LPK * ATT_EPL];   // [RT][GROUPS][LPK*8]
+
+  const int R = H / G;
+  const int nchunks = (R + ATT_RT - 1) / ATT_RT;
+  const int g = blockIdx.y / nchunks;
+  const int chunk = blockIdx.y % nchunks;
+  const int h0 = g * R + chunk * ATT_RT;
+  const int nh = min(ATT_RT, R - chunk * ATT_RT);
+  const int t = t0 + blockIdx.z;
+  const int split = blockIdx.x;
+
+  const int b = token_seq[t];
+  const int slot = seq_slot[b];
+  const int past = slot_pos[slot];
+  const int qs = q_start[b];
+  const int pos = past + (t - qs);
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int nkeys = pos - lo + 1;
+  const int per = (nkeys + nsplit - 1) / nsplit;
+  const int s_lo = lo + split * per;
+  const int s_hi = min(lo + (split + 1) * per, pos + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane % LPK, kg = lane / LPK;
+  const int e0 = sub * ATT_EPL;
+  const bool lane_on = e0 < hd;
+
+  float qreg[ATT_RT][ATT_EPL];
+#pragma unroll
+  for (int r = 0; r < ATT_RT; ++r) {
+    if (r < nh && lane_on) {
+      Vec8<T>::load(q + ((size_t)t * H + h0 + r) * hd + e0, qreg[r]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < ATT_EPL; ++e) qreg[r][e] = 0.f;
+    }
+  }
+  float m[ATT_RT], l[ATT_RT], o[ATT_RT][ATT_EPL];
+#pragma unroll
+  for (int r = 0; r < ATT_RT; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int e = 0; e < ATT_EPL; ++e) o[r][e] = 0.f;
+  }
+
+  const size_t step_row = (size_t)2 * G * hd;
+  const T* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
+  const T* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
+
+  for (int base = s_lo + warp * KPW; base < s_hi; base += GROUPS) {
+    const int key = base + kg;
+    const bool valid = key < s_hi;
+    float kf[ATT_EPL], vf[ATT_EPL];
+    if (valid && lane_on) {
+      const T *kp, *vp;
+      if (key >= past) {
+        kp = kv_step + (size_t)(qs + key - past) * step_row + (size_t)g * hd + e0;
+        vp = kp + (size_t)G * hd;
+      } else {
+        const size_t row = (size_t)(key % capacity) * hd + e0;
+        kp = kc + row;
+        vp = vc + row;
+      }
+      Vec8<T>::load(kp, kf);
+      Vec8<T>::load(vp, vf);
+    } else {
+#pragma unroll
+      for (int e = 0; e < ATT_EPL; ++e) { kf[e] = 0.f; vf[e] = 0.f; }
+    }
+    float s[ATT_RT];
+#pragma unroll
+    for (int r = 0; r < ATT_RT; ++r) {
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < ATT_EPL; ++e) d = fmaf(qreg[r][e], kf[e], d);
+#pragma unroll
+      for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+      s[r] = d * scale;
+    }
+    if (valid) {
+#pragma unroll
+      for (int r = 0; r < ATT_RT; ++r) {
+        const float mn = fmaxf(m[r], s[r]);
+        const float corr = expf(m[r] - mn);     // exp(-inf) = 0 on the first key
+        const float p = expf(s[r] - mn);
+        l[r] = l[r] * corr + p;
+#pragma unroll
+        for (int e = 0; e < ATT_EPL; ++e) o[r][e] = fmaf(p, vf[e], o[r][e] * corr);
+        m[r] = mn;
+      }
+    }
+  }
+
+  // merge the key groups of the block
+  const int grp = warp * KPW + kg;
+#pragma unroll
+  for (int r = 0; r < ATT_RT; ++r) {
+    if (sub == 0) { m_s[grp][r] = m[r]; l_s[grp][r] = l[r]; }
+#pragma unroll
+    for (int e = 0; e < ATT_EPL; ++e)
+      o_s[((size_t)r * GROUPS + grp) * (LPK * ATT_EPL) + e0 + e] = o[r][e];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
+    const int r = idx / hd, d = idx % hd;
+    float M = -INFINITY;
+    for (int gi = 0; gi < GROUPS; ++gi) M = fmaxf(M, m_s[gi][r]);
+    float L = 0.f, O = 0.f;
+    if (M > -INFINITY) {
+      for (int gi = 0; gi < GROUPS; ++gi) {
+        const float w = expf(m_s[gi][r] - M);
+        L += l_s[gi][r] * w;
+        O += o_s[((size_t)r * GROUPS + gi) * (LPK * ATT_EPL) + d] * w;
+      }
+    }
+    const int h = h0 + r;
+    if (nsplit == 1) {
+      out[((size_t)t * H + h) * hd + d] = from_float<T>(O / L);
+    } else {
+      const size_t pi = ((size_t)t * H + h) * nsplit + split;
+      part_o[pi * hd + d] = O;
+      if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+    }
+  }
+}
+
+// Merges the nsplit partial results of one (token, head): block per (token, head).
+template <typename T>
+__global__ void attn_merge_kernel(const float* __restrict__ part_o,
+                                  const float* __restrict__ part_ml, T* __restrict__ out, int hd,
+                                  int nsplit) {
+  const size_t th = blockIdx.x;
+  const float* ml = part_ml + th * nsplit * 2;
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml[2 * s]);
+  float L = 0.f;
+  for (int s = 0; s < nsplit; ++s)
+    if (ml[2 * s] > -INFINITY) L += ml[2 * s + 1] * expf(ml[2 * s] - M);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float O = 0.f;
+    for (int s = 0; s < nsplit; ++s)
+      if (ml[2 * s] > -INFINITY) O += part_o[(th * nsplit + s) * hd + d] * expf(ml[2 * s] - M);
+    out[th * hd + d] = from_float<T>(O / L);
+  }
+}
+
+template <typename T>
+static int launch_attention(const void* q, const void* kv_step, const void* k_cache,
+                            const void* v_cache, const int* token_seq, const int* q_start,
+                            const int* seq_slot, const int* slot_pos, void* out, float* part_o,
+                            float* part_ml, int n_tokens, int H, int G, int hd, int capacity,
+                            int window, int nsplit, cudaStream_t stream) {
+  const int R = H / G;
+  const int nchunks = (R + ATT_RT - 1) / ATT_RT;
+  const dim3 block(ATT_WARPS * 32);
+  const float scale = 1.0f / sqrtf((float)hd);
+  // gridDim.z is limited to 65535: tokens run in slices
+  for (int t0 = 0; t0 < n_tokens; t0 += 65535) {
+  const dim3 grid(nsplit, G * nchunks, n_tokens - t0 < 65535 ? n_tokens - t0 : 65535);
+#define YALM_ATT_CASE(LPK)                                                                      \
+  attn_token_kernel<T, LPK><<<grid, block, 0, stream>>>(                                        \
+      (const T*)q, (const T*)kv_step, (const T*)k_cache, (const T*)v_cache, token_seq, q_start, \
+      seq_slot, slot_pos, (T*)out, part_o, part_ml, H, G, hd, capacity, window, nsplit, scale, t0)
+  if (hd <= 16) YALM_ATT_CASE(2);
+  else if (hd <= 32) YALM_ATT_CASE(4);
+  else if (hd <= 64) YALM_ATT_CASE(8);
+  else if (hd <= 128) YALM_ATT_CASE(16);
+  else YALM_ATT_CASE(32);
+#undef YALM_ATT_CASE
+  YALM_LAUNCH_CHECK();
+  }
+  if (nsplit > 1) {
+    const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
+    attn_merge_kernel<T><<<n_tokens * H, threads, 0, stream>>>(part_o, part_ml, (T*)out, hd,
+                                                               nsplit);
+    YALM_LAUNCH_CHECK();
+  }
+  return 0;
+}
+
+}  // namespace yalm
+
+using namespace yalm;
+
+// part_o: [n_tokens, H, nsplit, hd] floats, part_ml: [n_tokens, H, nsplit, 2]
+// floats; both are needed only when nsplit > 1.
+extern "C" int yalm_attention(const void* q, const void* kv_step, const void* k_cache,
+                              const void* v_cache, const int* token_seq, const int* q_start,
+                              const int* seq_slot, const int* slot_pos, void* out, float* part_o,
+                              float* part_ml, int dtype, int n_tokens, int H, int G, int hd,
+                              int capacity, int window, int nsplit, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (hd % 8 != 0 || hd > 256 || hd <= 0) return -2;     // head sizes: multiples of 8 up to 256
+  if (G <= 0 || H % G != 0) return -3;
+  if (nsplit < 1 || nsplit > 65535) return -4;
+  if ((size_t)G * ((H / G + ATT_RT - 1) / ATT_RT) > 65535) return -5;
+  if (dtype == DT_F32)
+    return launch_attention<float>(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot,
+                                   slot_pos, out, part_o, part_ml, n_tokens, H, G, hd, capacity,
+                                   window, nsplit, stream);
+  return launch_attention<__nv_bfloat16>(q, kv_step, k_cache, v_cache, token_seq, q_start,
+                                         seq_slot, slot_pos, out, part_o, part_ml, n_tokens, H, G,
+                                         hd, capacity, window, nsplit, stream);
+}

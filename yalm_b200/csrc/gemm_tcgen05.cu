@@ -1,0 +1,381 @@
+// out[M,N] = A[M,K] * W[N,K]^T on the Blackwell tensor cores: bfloat16
+// operands brought into shared memory by TMA (128-byte swizzle), tcgen05.mma
+// issued by one thread, 32-bit accumulators in tensor memory (TMEM), read back
+// with tcgen05.ld for a fused epilogue.
+//
+// The WEIGHT tile sits on the 128-row side of the instruction and the tokens on
+// its N side (16..256), so the same kernel serves decode (a handful of tokens:
+// the step is a stream of weights, optionally split over K so that all SMs pull
+// from HBM) and prefill (256 tokens per tile: compute bound).  In TMEM a lane is
+// an output feature and a column is a token.
+//
+// The reference's counterparts are its one-token GEMV kernels: matmul_wide
+// infer.cu:250-268, fused_matmul_add_residuals infer.cu:270-288 (mode 1 here),
+// fused_qkv_matmul_clip infer.cu:290-337, fused_ffn_w1_w3_glu_act
+// infer.cu:610-634 (mode 2 here: two accumulators, gate and up, one epilogue).
+//
+// Every wait on a barrier is bounded: after about two seconds a role gives up,
+// raises ERR_WAIT_TIMEOUT in the status word, and the block frees its TMEM and
+// returns.
+#include <cuda.h>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace yalm {
+
+constexpr int TC_BM = 128;      // weight rows (output features) per tile = UMMA M
+constexpr int TC_BK = 64;       // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int TC_UMMA_K = 16;
+constexpr int TC_THREADS = 192; // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
+constexpr unsigned long long TC_WAIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+// Bounded wait; false after the time limit or once another role has given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((it & 255u) == 255u) {
+      if (*abort_flag) return false;
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > TC_WAIT_NS) { *abort_flag = 1; return false; }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
+// (64 bf16) with the 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address
+  d |= (uint64_t)1 << 16;                                // leading byte offset (unused here)
+  d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset
+  d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
+  return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BT, int NACC> struct TcCfg {
+  static constexpr int W_BYTES = TC_BM * TC_BK * 2;              // 16 KiB per weight tile
+  static constexpr int A_BYTES = BT * TC_BK * 2;
+  static constexpr int STAGE_BYTES = NACC * W_BYTES + A_BYTES;
+  static constexpr int BUDGET = BT <= 32 ? 110 * 1024 : 200 * 1024;   // small tiles: 2 blocks/SM
+  static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;       // + slack to align to 1024
+  static constexpr int TMEM_COLS_RAW = NACC * BT;
+  static constexpr int TMEM_COLS = TMEM_COLS_RAW <= 32 ? 32 : (TMEM_COLS_RAW <= 64 ? 64 :
+                                   (TMEM_COLS_RAW <= 128 ? 128 : (TMEM_COLS_RAW <= 256 ? 256 : 512)));
+};
+
+// mode 0: store, 1: add into float32 out, 2: silu(gate)*up (NACC == 2), 3: split-K partials
+template <int BT, int NACC>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+               void* __restrict__ out, int out_dtype, int M, int N, int K, int mode, int splits,
+               int* __restrict__ status) {
+  using Cfg = TcCfg<BT, NACC>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[Cfg::STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[Cfg::STAGES];
+  __shared__ __align__(8) uint64_t acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int n_out = mode == 2 ? N / 2 : N;                   // features this grid covers
+  const int feat0 = blockIdx.x * TC_BM;
+  const int tok0 = blockIdx.y * BT;
+  const int nkb = (K + TC_BK - 1) / TC_BK;
+  const int per = (nkb + splits - 1) / splits;
+  const int kb_lo = blockIdx.z * per;
+  const int kb_hi = min(nkb, kb_lo + per);
+  const int nk = max(0, kb_hi - kb_lo);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(&acc_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abort_p = &abort_flag;
+
+  if (warp == 0) {
+    // ---------------- TMA producer
+    if (lane == 0 && nk > 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+      for (int it = 0; it < nk; ++it) {
+        const int s = it % Cfg::STAGES;
+        const uint32_t phase = (it / Cfg::STAGES) & 1;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u, abort_p)) break;
+        const uint32_t stage = tiles + s * Cfg::STAGE_BYTES;
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        mbar_expect_tx(bar, Cfg::STAGE_BYTES);
+        const int kx = (kb_lo + it) * TC_BK;
+        tma_load_2d(stage, &map_w, kx, feat0, bar);
+        if (NACC == 2) tma_load_2d(stage + Cfg::W_BYTES, &map_w, kx, n_out + feat0, bar);
+        tma_load_2d(stage + NACC * Cfg::W_BYTES, &map_a, kx, tok0, bar);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0 && nk > 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BT >> 3) << 17) |
+                             ((uint32_t)(TC_BM >> 4) << 24);
+      bool ok = true;
+      for (int it = 0; it < nk && ok; ++it) {
+        const int s = it % Cfg::STAGES;
+        const uint32_t phase = (it / Cfg::STAGES) & 1;
+        ok = mbar_wait(smem_u32(&full_bar[s]), phase, abort_p);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t stage = tiles + s * Cfg::STAGE_BYTES;
+        const uint64_t wdesc = umma_desc_k_sw128(stage);
+        const uint64_t adesc = umma_desc_k_sw128(stage + NACC * Cfg::W_BYTES);
+#pragma unroll
+        for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
+          const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+          const uint64_t koff = (uint64_t)((k * TC_UMMA_K * 2) >> 4);   // 32 bytes per k-step
+          umma_bf16(tmem_base, wdesc + koff, adesc + koff, idesc, acc);
+          if (NACC == 2) {
+            const uint64_t w2 = umma_desc_k_sw128(stage + Cfg::W_BYTES);
+            umma_bf16(tmem_base + BT, w2 + koff, adesc + koff, idesc, acc);
+          }
+        }
+        umma_commit(smem_u32(&empty_bar[s]));     // frees the stage once these MMAs are done
+      }
+      if (ok) umma_commit(smem_u32(&acc_bar));    // accumulators complete
+    }
+  } else {
+    // ---------------- epilogue: TMEM -> registers -> global
+    const int quarter = warp & 3;                 // the TMEM lanes this warp may read
+    const int f = feat0 + quarter * 32 + lane;    // output feature of this thread
+    bool ok = true;
+    if (nk > 0) ok = mbar_wait(smem_u32(&acc_bar), 0, abort_p);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      float* outf = reinterpret_cast<float*>(out);
+      __nv_bfloat16* outh = reinterpret_cast<__nv_bfloat16*>(out);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BT; c0 += 16) {
+        if (tok0 + c0 >= M) break;                // uniform over the warp
+        float v[16];
+        if (nk > 0) {
+          tmem_ld16(taddr + c0, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+        if (NACC == 2) {
+          float u[16];
+          tmem_ld16(taddr + BT + c0, u);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + expf(-v[j])) * u[j];
+        }
+        if (f < n_out) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int tok = tok0 + c0 + j;
+            if (tok < M) {
+              if (mode == 3) {
+                outf[((size_t)blockIdx.z * M + tok) * n_out + f] = v[j];
+              } else if (mode == 1) {
+                outf[(size_t)tok * n_out + f] += v[j];
+              } else if (out_dtype == DT_F32) {
+                outf[(size_t)tok * n_out + f] = v[j];
+              } else {
+                outh[(size_t)tok * n_out + f] = __float2bfloat16_rn(v[j]);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (abort_flag) {
+    // a wait ran out: let copies in flight land before the block leaves
+    if (threadIdx.x == 0) atomicOr(status, ERR_WAIT_TIMEOUT);
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                 ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// rows x K bfloat16, row-major; box = box_rows x 64 with the 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -10;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -11;
+}
+
+template <int BT, int NACC>
+static int launch_tc(const CUtensorMap& mw, const void* A, void* out, int out_dtype, int M, int N,
+                     int K, int mode, int splits, int* status, cudaStream_t stream) {
+  using Cfg = TcCfg<BT, NACC>;
+  static_assert(Cfg::STAGES >= 2, "pipeline needs two stages");
+  CUtensorMap ma;
+  int rc = make_map(&ma, A, M, K, BT);
+  if (rc) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BT, NACC>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int n_out = mode == 2 ? N / 2 : N;
+  const dim3 grid((n_out + TC_BM - 1) / TC_BM, (M + BT - 1) / BT, splits);
+  if (grid.y > 65535 || grid.z > 65535) return -4;
+  gemm_tc_kernel<BT, NACC><<<grid, TC_THREADS, Cfg::SMEM, stream>>>(mw, ma, out, out_dtype, M, N,
+                                                                   K, mode, splits, status);
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace yalm
+
+using namespace yalm;
+
+extern "C" int yalm_gemm_tc_available(void) { return encode_fn() ? 0 : -10; }
+
+extern "C" int yalm_gemm_tc(const void* A, const void* W, void* out, int out_dtype, int M, int N,
+                            int K, int mode, int splits, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 != 0) return -2;               // TMA: rows must be 16-byte multiples
+  if (((uintptr_t)A | (uintptr_t)W) & 15) return -6; // TMA: 16-byte aligned bases
+  if (mode < 0 || mode > 3) return -3;
+  if (mode == 2 && (N % 2 != 0)) return -3;
+  if ((mode == 1 || mode == 3) && out_dtype != DT_F32) return -3;
+  const int nkb = (K + TC_BK - 1) / TC_BK;
+  if (mode != 3) splits = 1;
+  if (splits < 1 || splits > nkb) return -5;
+  {
+    const int per = (nkb + splits - 1) / splits;
+    if ((splits - 1) * per >= nkb) return -5;        // no empty slice of K
+  }
+  CUtensorMap mw;
+  int rc = make_map(&mw, W, N, K, TC_BM);
+  if (rc) return rc;
+#define YALM_TC(BT, NACC) \
+  return launch_tc<BT, NACC>(mw, A, out, out_dtype, M, N, K, mode, splits, status, stream)
+  if (mode == 2) {
+    if (M <= 16) YALM_TC(16, 2);
+    if (M <= 32) YALM_TC(32, 2);
+    if (M <= 64) YALM_TC(64, 2);
+    if (M <= 128) YALM_TC(128, 2);
+    YALM_TC(256, 2);
+  }
+  if (M <= 16) YALM_TC(16, 1);
+  if (M <= 32) YALM_TC(32, 1);
+  if (M <= 64) YALM_TC(64, 1);
+  if (M <= 128) YALM_TC(128, 1);
+  YALM_TC(256, 1);
+#undef YALM_TC
+}

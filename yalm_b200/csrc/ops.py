@@ -1,0 +1,238 @@
+"""Thin typed wrappers around the kernel library's C interface.
+
+Arguments are CUDA tensors (their ``data_ptr`` is handed over) and plain
+numbers; every call runs on torch's current stream, so the calls can be
+captured into a CUDA graph.  A non-zero return code raises ``KernelError``:
+there is no fallback to another implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+
+ERR_TOKEN_RANGE, ERR_WAIT_TIMEOUT, ERR_SLOT_RANGE = 1, 2, 4
+
+_REFUSALS = {
+    -2: "a size that this kernel does not take",
+    -3: "an unsupported combination of types or modes",
+    -4: "a launch grid beyond the device limits",
+    -5: "a bad split count",
+    -6: "a pointer that is not 16-byte aligned",
+    -10: "cuTensorMapEncodeTiled was not found in the driver",
+    -11: "cuTensorMapEncodeTiled refused the tensor",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"the kernels take float32 and bfloat16 tensors, not {dt}")
+
+
+_c = ctypes
+_vp, _i, _ll, _f, _ull = _c.c_void_p, _c.c_int, _c.c_longlong, _c.c_float, _c.c_ulonglong
+_SIGNATURES = {
+    "yalm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp],
+    "yalm_rmsnorm": [_vp, _vp, _i, _ll, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+    "yalm_silu_mul": [_vp, _i, _ll, _vp, _i, _i, _i, _vp],
+    "yalm_rope_store": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
+                        _i, _i, _i, _vp],
+    "yalm_advance": [_vp, _vp, _vp, _i, _vp],
+    "yalm_attention": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+                       _i, _i, _i, _vp],
+    "yalm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
+    "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp],
+    "yalm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "yalm_gemm_tc_available": [],
+}
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        l = build.load()
+        for name, args in _SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.argtypes = args
+            fn.restype = _c.c_int
+        l.yalm_uniform01.argtypes = [_ull, _c.c_uint, _c.c_uint]
+        l.yalm_uniform01.restype = _c.c_float
+        _lib = l
+    return _lib
+
+
+def loaded_library_path() -> str:
+    lib()
+    return build.library_path()
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc < 0:
+        raise KernelError(f"{what}: refused, {_REFUSALS.get(rc, f'code {rc}')}")
+    raise KernelError(f"{what}: CUDA error {rc} at launch "
+                      f"({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+# --------------------------------------------------------------------------
+def embed(tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor, status: torch.Tensor) -> None:
+    n, dim = x.shape
+    _need(tokens.dtype == torch.int32 and tokens.numel() >= n, "embed: tokens must be int32 [n]")
+    _need(table.shape[1] == dim and x.dtype == torch.float32 and x.is_contiguous()
+          and table.is_contiguous(), "embed: shapes")
+    _check(lib().yalm_embed(_p(tokens), _p(table), dtype_code(table.dtype), _p(x), n, dim,
+                            table.shape[0], _p(status), _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+            partials: Optional[torch.Tensor] = None, n_partials: int = 0,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = norm(x[rows[r]] + sum of partials) * weight; with partials and no
+    ``rows`` the sum is written back to x.  partials: float32 [n_partials, N, dim]."""
+    dim = x.shape[1]
+    n_rows = out.shape[0]
+    _need(x.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == dim
+          and out.shape[1] == dim and x.is_contiguous() and out.is_contiguous(), "rmsnorm: shapes")
+    stride = 0
+    if n_partials:
+        _need(partials is not None and partials.dtype == torch.float32
+              and partials.shape[-1] == dim and partials.shape[-2] == x.shape[0],
+              "rmsnorm: partials must be float32 [s, N, dim]")
+        stride = x.shape[0] * dim
+    if rows is None:
+        _need(n_rows == x.shape[0], "rmsnorm: out rows")
+    else:
+        _need(rows.dtype == torch.int32 and rows.numel() >= n_rows, "rmsnorm: rows int32")
+    _check(lib().yalm_rmsnorm(_p(x), _p(partials) if n_partials else None, n_partials, stride,
+                              _p(rows), _p(weight), _p(out), dtype_code(out.dtype), n_rows, dim,
+                              float(eps), _stream()), "rmsnorm")
+
+
+def silu_mul(gu: torch.Tensor, out: torch.Tensor, n_partials: int = 1) -> None:
+    """gu: float32 [(n_partials,) rows, 2F] (gate | up); out: [rows, F]."""
+    rows, F = out.shape
+    _need(gu.dtype == torch.float32 and gu.shape[-1] == 2 * F and gu.shape[-2] == rows
+          and gu.is_contiguous() and out.is_contiguous(), "silu_mul: shapes")
+    _check(lib().yalm_silu_mul(_p(gu), n_partials, rows * 2 * F, _p(out), dtype_code(out.dtype),
+                               rows, F, _stream()), "silu_mul")
+
+
+def rope_store(qkv: torch.Tensor, n_partials: int, inv_freq: torch.Tensor, batch,
+               q_out: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
+               v_cache: torch.Tensor, slot_pos: torch.Tensor, H: int, G: int, hd: int,
+               capacity: int, write_cache: bool = True) -> None:
+    n = q_out.shape[0]
+    _need(qkv.dtype == torch.float32 and qkv.shape[-1] == (H + 2 * G) * hd
+          and qkv.shape[-2] == n and qkv.is_contiguous(), "rope_store: qkv float32 [(s,) N, (H+2G)hd]")
+    _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == hd // 2, "rope_store: inv_freq")
+    _need(q_out.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype, "rope_store: dtypes")
+    _need(q_out.is_contiguous() and kv_step.is_contiguous() and k_cache.is_contiguous()
+          and v_cache.is_contiguous(), "rope_store: contiguity")
+    _check(lib().yalm_rope_store(_p(qkv), n_partials, n * (H + 2 * G) * hd, _p(inv_freq),
+                                 _p(batch.token_seq), _p(batch.q_start), _p(batch.seq_slot),
+                                 _p(slot_pos), _p(q_out), _p(kv_step), _p(k_cache), _p(v_cache),
+                                 dtype_code(q_out.dtype), n, H, G, hd, capacity,
+                                 1 if write_cache else 0, _stream()), "rope_store")
+
+
+def advance(batch, slot_pos: torch.Tensor) -> None:
+    _check(lib().yalm_advance(_p(batch.q_start), _p(batch.seq_slot), _p(slot_pos), batch.n_seqs,
+                              _stream()), "advance")
+
+
+def attention(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              batch, slot_pos: torch.Tensor, out: torch.Tensor, H: int, G: int, hd: int,
+              capacity: int, window: Optional[int], nsplit: int = 1,
+              part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> None:
+    n = q.shape[0]
+    _need(q.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == out.dtype,
+          "attention: dtypes")
+    _need(hd % 8 == 0 and 0 < hd <= 256,
+          f"attention: head size {hd} is not supported (multiples of 8 up to 256)")
+    if nsplit > 1:
+        _need(part_o is not None and part_ml is not None
+              and part_o.numel() >= n * H * nsplit * hd and part_ml.numel() >= n * H * nsplit * 2
+              and part_o.dtype == torch.float32 and part_ml.dtype == torch.float32,
+              "attention: split scratch")
+    _check(lib().yalm_attention(_p(q), _p(kv_step), _p(k_cache), _p(v_cache), _p(batch.token_seq),
+                                _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos), _p(out),
+                                _p(part_o), _p(part_ml), dtype_code(q.dtype), n, H, G, hd,
+                                capacity, int(window or 0), nsplit, _stream()), "attention")
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    M, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and tuple(out.shape) == (M, N) and a.is_contiguous()
+          and w.is_contiguous() and out.is_contiguous(), "gemm_simt: shapes")
+    _need(not accumulate or out.dtype == torch.float32, "gemm_simt: accumulate needs float32 out")
+    _check(lib().yalm_gemm_simt(_p(a), dtype_code(a.dtype), _p(w), dtype_code(w.dtype), _p(out),
+                                dtype_code(out.dtype), M, N, K, 1 if accumulate else 0, _stream()),
+           "gemm_simt")
+
+
+GEMM_STORE, GEMM_ADD, GEMM_SILU_MUL, GEMM_SPLIT = 0, 1, 2, 3
+
+
+def gemm_tc_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, status: torch.Tensor,
+            splits: int = 1) -> None:
+    M, K = a.shape
+    N = w.shape[0]
+    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+          and a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "gemm_tc: operands")
+    if mode == GEMM_SILU_MUL:
+        _need(tuple(out.shape) == (M, N // 2), "gemm_tc: silu-mul out is [M, N/2]")
+    elif mode == GEMM_SPLIT:
+        _need(out.dtype == torch.float32 and out.numel() >= splits * M * N, "gemm_tc: split scratch")
+    else:
+        _need(tuple(out.shape) == (M, N), "gemm_tc: out is [M, N]")
+    _check(lib().yalm_gemm_tc(_p(a), _p(w), _p(out), dtype_code(out.dtype), M, N, K, mode, splits,
+                              _p(status), _stream()), "gemm_tc")
+
+
+def sample(logits: torch.Tensor, temperature: float, seed: int, row_key: torch.Tensor,
+           seq_slot: torch.Tensor, slot_pos: torch.Tensor, out_tokens: torch.Tensor) -> None:
+    rows, vocab = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous() and out_tokens.dtype == torch.int32
+          and row_key.dtype == torch.int32, "sample: types")
+    _check(lib().yalm_sample(_p(logits), rows, vocab, float(temperature), int(seed) & (2 ** 64 - 1),
+                             _p(row_key), _p(seq_slot), _p(slot_pos), _p(out_tokens), _stream()),
+           "sample")
+
+
+def uniform01(seed: int, key: int, counter: int) -> float:
+    return float(lib().yalm_uniform01(int(seed) & (2 ** 64 - 1), int(key) & 0xffffffff,
+                                      int(counter) & 0xffffffff))

@@ -1,0 +1,187 @@
+"""The Python entry point: a model folder (or a configuration and a seed) in,
+logits or generated tokens out.
+
+    lm = LM.from_pretrained("model_dir", dtype="bfloat16", max_context=4096, max_batch=8)
+    out = lm.generate([[1, 5, 9], [1, 7]], max_new_tokens=32, temperature=0.0)
+    out[0].tokens, out[0].finish_reason
+
+The reference has no Python interface; its C++ ``main`` is the counterpart
+(main.cpp:54-148), mirrored by ``python -m yalm_b200``.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import time
+from typing import Any, Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..config import config_from_dict, load_config
+from ..csrc import ops
+from ..parts import Model, Runtime
+from ..weights import load_checkpoint, random_tensors, write_model_dir
+from .generate import Completion, run_generation
+from .step import Engine, StepError
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def _dtype(d) -> torch.dtype:
+    if d not in _DTYPES:
+        raise ValueError(f"dtype must be 'bfloat16' or 'float32', got {d!r}")
+    return _DTYPES[d]
+
+
+class LM:
+    def __init__(self, config: Any, tensors: Dict[str, torch.Tensor], dtype="bfloat16",
+                 max_context: Optional[int] = None, max_batch: int = 8, device="cuda:0",
+                 gemm: str = "auto"):
+        self.config = config
+        self.spec = config.to_spec()
+        self.rt = Runtime(_dtype(dtype), device, gemm=gemm)
+        self.model = Model(self.spec, self.rt)
+        self.model.bind(tensors)
+        context = self.spec.max_positions if not max_context else min(int(max_context),
+                                                                     self.spec.max_positions)
+        self.engine = Engine(self.model, max_batch, context)
+        self._next_key = 0
+
+    # -- construction ----------------------------------------------------------
+    @classmethod
+    def from_pretrained(cls, model_dir: str, **kw) -> "LM":
+        config = load_config(model_dir)
+        return cls(config, load_checkpoint(model_dir), **kw)
+
+    @classmethod
+    def from_random(cls, config: Union[dict, Any], seed: int = 0, dtype="bfloat16",
+                    std: float = 0.02, norm_jitter: float = 0.02, device="cuda:0", **kw) -> "LM":
+        """Random weights drawn on the device (no model folder is written)."""
+        if isinstance(config, dict):
+            config = config_from_dict(config)
+        dt = _dtype(dtype)
+        tensors = random_tensors(tensor_needs_of(config), seed, dtype=dt, std=std,
+                                 norm_jitter=norm_jitter, device=device)
+        return cls(config, tensors, dtype=dtype, device=device, **kw)
+
+    @staticmethod
+    def write_random_model(out_dir: str, config: Union[dict, Any], seed: int = 0,
+                           dtype="bfloat16", std: float = 0.02, norm_jitter: float = 0.02) -> None:
+        """Random-weights mode: writes config.json and model.safetensors."""
+        if isinstance(config, dict):
+            config = config_from_dict(config)
+        write_model_dir(out_dir, config, tensor_needs_of(config), seed, dtype=_dtype(dtype),
+                        std=std, norm_jitter=norm_jitter)
+
+    # -- the step function -----------------------------------------------------
+    @property
+    def context(self) -> int:
+        return self.engine.context
+
+    @property
+    def max_batch(self) -> int:
+        return self.engine.cache.n_slots
+
+    def acquire(self, n: int) -> List[int]:
+        return self.engine.acquire(n)
+
+    def release(self, slots: Sequence[int]) -> None:
+        self.engine.release(slots)
+
+    def step(self, token_lists, slots, want) -> Optional[torch.Tensor]:
+        return self.engine.step(token_lists, slots, want)
+
+    # -- generation ------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 256,
+                 temperature: float = 1.0, seed: int = 0, stop_ids: Optional[Sequence[int]] = None,
+                 ignore_eos: bool = False, on_token=None) -> List[Completion]:
+        """Continues every prompt.  ``temperature == 0`` is greedy.  Stop tokens
+        default to the configuration's eos ids; the stop token is part of the
+        output.  Requests beyond ``max_batch`` run as further batches."""
+        if stop_ids is None:
+            stop_ids = [] if ignore_eos else list(self.spec.stop_token_ids)
+        backend = _DeviceBackend(self, float(temperature), int(seed))
+        t0 = time.perf_counter()
+        out = run_generation(backend, prompts, max_new_tokens, stop_ids, on_token=on_token)
+        self.rt.check_status()
+        self.last_stats = {"seconds": time.perf_counter() - t0,
+                           "prefill_seconds": backend.prefill_seconds,
+                           "prompt_tokens": sum(len(p) for p in prompts),
+                           "new_tokens": sum(len(c.tokens) for c in out),
+                           "decode_steps": backend.decode_steps}
+        return out
+
+    def perplexity(self, tokens: Sequence[int]):
+        """exp(-mean log p(next token)) over one sequence and its error
+        estimate, as the reference's perplexity mode (main.cpp:201-218)."""
+        if len(tokens) < 2:
+            raise ValueError("perplexity needs at least two tokens")
+        if len(tokens) > self.context:
+            raise ValueError(f"{len(tokens)} tokens exceed the context {self.context}")
+        slot = self.acquire(1)
+        try:
+            logits = self.step([list(tokens)], slot, [list(range(len(tokens) - 1))])
+        finally:
+            self.release(slot)
+        lp = torch.log_softmax(logits.double(), -1)
+        nxt = torch.tensor(list(tokens[1:]), device=lp.device)
+        vals = lp.gather(1, nxt[:, None])[:, 0]
+        n = vals.numel()
+        s, ss = vals.sum().item(), (vals * vals).sum().item()
+        ppl = math.exp(-s / n)
+        return ppl, ppl * math.sqrt(max(0.0, (ss - s * s / n) / n / n))
+
+
+def tensor_needs_of(config) -> dict:
+    """The tensors a configuration's model declares (no device needed)."""
+    return Model(config.to_spec(), Runtime.shapes_only()).tensor_needs()
+
+
+class _DeviceBackend:
+    """The generation loop's view of the engine (see generate.py)."""
+
+    def __init__(self, lm: LM, temperature: float, seed: int):
+        self.lm = lm
+        self.engine = lm.engine
+        self.temperature = temperature
+        self.seed = seed
+        self.max_batch = lm.max_batch
+        self.context = lm.context
+        self.prefill_seconds = 0.0
+        self.decode_steps = 0
+
+    def begin(self, prompts, keys):
+        eng = self.engine
+        slots = eng.acquire(len(prompts))
+        try:
+            t0 = time.perf_counter()
+            logits = eng.step(prompts, slots, [[len(p) - 1] for p in prompts])
+            B = len(prompts)
+            d = eng._decode_buffers()
+            # sample the first token of every sequence into the decode token buffer
+            eng.set_decode_batch([0] * B, slots, keys)
+            ops.sample(logits, self.temperature, self.seed, d["row_key"][:B], d["seq_slot"][:B],
+                       eng.cache.slot_pos, d["tokens"][:B])
+            first = eng.read_decode_tokens(B)
+            self.prefill_seconds += time.perf_counter() - t0
+        except Exception:
+            eng.release(slots)
+            raise
+        handle = {"slots": slots, "keys": list(keys), "active": list(range(len(prompts)))}
+        return handle, first
+
+    def decode(self, handle, active, tokens):
+        eng = self.engine
+        if active != handle["active"]:
+            # the batch shrank: put the survivors' tokens, slots and keys on the device
+            eng.set_decode_batch(tokens, [handle["slots"][j] for j in active],
+                                 [handle["keys"][j] for j in active])
+            handle["active"] = list(active)
+        eng.decode_step(len(active), self.temperature, self.seed)
+        self.decode_steps += 1
+        return eng.read_decode_tokens(len(active))
+
+    def end(self, handle):
+        self.engine.release(handle["slots"])

@@ -1,0 +1,173 @@
+"""The step function: one batch of sequences, only the tokens it is given,
+from the cache that earlier steps left, logits at the wanted places.
+
+The reference's step is ``Model::forward(state, token, pos, mode)``: one token
+of one sequence, logits or none (model.h:260, infer.cu:1103-1207).  Here a
+step takes a ragged batch: all prompts of a batch at once, then one token per
+sequence; a sequence's position lives in the cache's per-slot record on the
+device and is advanced by the step itself.
+
+Decode steps of a fixed set of sequences are captured once into a CUDA graph
+(embedding to sampling) and replayed; the sampled token is written where the
+next step's embedding reads it, so the device can decode on its own while the
+host only reads tokens back.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache import Cache
+from ..csrc import ops
+from ..parts import Model
+from .batch import StepBatch, build_batch
+
+
+class StepError(RuntimeError):
+    pass
+
+
+class Engine:
+    def __init__(self, model: Model, n_slots: int, context: int):
+        self.model = model
+        self.rt = model.rt
+        self.context = int(context)
+        if self.context > model.spec.max_positions:
+            raise StepError(f"context {context} exceeds the model's {model.spec.max_positions} positions")
+        self.cache = Cache(model.cache_needs(), n_slots, self.context, self.rt.dtype, self.rt.device)
+        self.vocab = model.spec.vocab_size
+        self._graphs: Dict[tuple, dict] = {}
+        self._dec: Optional[dict] = None
+        self.use_graphs = True
+
+    # -- slots -----------------------------------------------------------------
+    def acquire(self, n: int) -> List[int]:
+        return self.cache.acquire(n)
+
+    def release(self, slots: Sequence[int]) -> None:
+        self.cache.release(slots)
+
+    # -- the step --------------------------------------------------------------
+    def step(self, token_lists: Sequence[Sequence[int]], slots: Sequence[int],
+             want: Sequence[Sequence[int]]) -> Optional[torch.Tensor]:
+        """Runs ``token_lists[b]`` as the next tokens of the sequence in
+        ``slots[b]``; returns float32 logits [sum(len(want[b])), vocab] in the
+        order of the sequences and of ``want`` (None if nothing is wanted)."""
+        if not (len(token_lists) == len(slots) == len(want)):
+            raise StepError("token_lists, slots and want must have one entry per sequence")
+        if len(set(slots)) != len(slots):
+            raise StepError(f"a slot appears twice in one step: {list(slots)}")
+        held = set(self.cache.slots.held)
+        past = []
+        for b, (toks, s) in enumerate(zip(token_lists, slots)):
+            if s not in held:
+                raise StepError(f"slot {s} is not held by a live sequence")
+            if len(toks) == 0:
+                raise StepError(f"sequence {b} brings no tokens")
+            if self.cache.host_pos[s] + len(toks) > self.context:
+                raise StepError(
+                    f"sequence {b} would reach {self.cache.host_pos[s] + len(toks)} positions; "
+                    f"the context is {self.context}")
+            for t in toks:
+                if not 0 <= int(t) < self.vocab:
+                    raise StepError(f"sequence {b}: token {t} is outside the vocabulary "
+                                    f"(0..{self.vocab - 1})")
+            past.append(self.cache.host_pos[s])
+        batch = build_batch(token_lists, slots, past, want, self.rt.device)
+        logits = self.model.forward(batch, self.cache, batch.want_rows, batch.n_want)
+        ops.advance(batch, self.cache.slot_pos)
+        for s, toks in zip(slots, token_lists):
+            self.cache.host_pos[s] += len(toks)
+        self.rt.check_status()
+        return logits
+
+    # -- decode steps that stay on the device ----------------------------------
+    def _decode_buffers(self) -> dict:
+        if self._dec is None:
+            n = self.cache.n_slots
+            dev = self.rt.device
+            self._dec = {
+                "tokens": torch.zeros(n, dtype=torch.int32, device=dev),
+                "seq_slot": torch.zeros(n, dtype=torch.int32, device=dev),
+                "row_key": torch.zeros(n, dtype=torch.int32, device=dev),
+                "arange": torch.arange(n + 1, dtype=torch.int32, device=dev),
+                "logits": torch.empty((n, self.vocab), dtype=torch.float32, device=dev),
+                "host": torch.zeros(3 * n, dtype=torch.int32).pin_memory(),
+                "host_out": torch.zeros(n, dtype=torch.int32).pin_memory(),
+            }
+        return self._dec
+
+    def set_decode_batch(self, tokens: Sequence[int], slots: Sequence[int],
+                         keys: Sequence[int]) -> None:
+        """Puts the next tokens, slots and request keys of the decoding
+        sequences on the device (one copy from pinned memory)."""
+        d = self._decode_buffers()
+        B = len(tokens)
+        n = self.cache.n_slots
+        h = d["host"]
+        h[0:B] = torch.tensor(list(tokens), dtype=torch.int32)
+        h[n:n + B] = torch.tensor(list(slots), dtype=torch.int32)
+        h[2 * n:2 * n + B] = torch.tensor(list(keys), dtype=torch.int32)
+        d["tokens"][:B].copy_(h[0:B], non_blocking=True)
+        d["seq_slot"][:B].copy_(h[n:n + B], non_blocking=True)
+        d["row_key"][:B].copy_(h[2 * n:2 * n + B], non_blocking=True)
+        d["slots_host"] = list(slots)
+
+    def _decode_batch(self, B: int) -> StepBatch:
+        d = self._decode_buffers()
+        slots = d["slots_host"]
+        return StepBatch(n_tokens=B, n_seqs=B, q_lens=[1] * B, slots=list(slots),
+                         past=[self.cache.host_pos[s] for s in slots], tokens=d["tokens"][:B],
+                         token_seq=d["arange"][:B], q_start=d["arange"][:B + 1],
+                         seq_slot=d["seq_slot"][:B], want_rows=d["arange"][:B], n_want=B)
+
+    def _decode_body(self, B: int, temperature: float, seed: int) -> None:
+        d = self._decode_buffers()
+        batch = self._decode_batch(B)
+        logits = self.model.forward(batch, self.cache, batch.want_rows, B, logits_out=d["logits"][:B])
+        ops.advance(batch, self.cache.slot_pos)
+        # the new token goes where the next step's embedding reads it
+        ops.sample(logits, temperature, seed, d["row_key"][:B], batch.seq_slot,
+                   self.cache.slot_pos, d["tokens"][:B])
+
+    def decode_step(self, B: int, temperature: float, seed: int) -> None:
+        """One decode step of the B sequences set by ``set_decode_batch``: their
+        tokens are read from, and their sampled successors written to, the
+        device token buffer.  Nothing crosses to the host."""
+        d = self._decode_buffers()
+        for s in d["slots_host"][:B]:
+            if self.cache.host_pos[s] + 1 > self.context:
+                raise StepError(f"the sequence in slot {s} is at the context's end ({self.context})")
+        if not self.use_graphs:
+            self._decode_body(B, temperature, seed)
+        else:
+            key = (B, float(temperature), int(seed))
+            g = self._graphs.get(key)
+            if g is not None and g["generation"] != self.rt.buffer_generation:
+                g = None                      # a scratch buffer moved since the capture
+            if g is None:
+                # the first step of this shape runs eagerly (every scratch buffer gets
+                # its final size); then the same launches are captured for replays
+                self._decode_body(B, temperature, seed)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                self.rt.frozen = True
+                try:
+                    with torch.cuda.graph(graph):
+                        self._decode_body(B, temperature, seed)
+                finally:
+                    self.rt.frozen = False
+                self._graphs[key] = {"graph": graph, "generation": self.rt.buffer_generation}
+            else:
+                g["graph"].replay()
+        for s in d["slots_host"][:B]:
+            self.cache.host_pos[s] += 1
+
+    def read_decode_tokens(self, B: int) -> List[int]:
+        d = self._decode_buffers()
+        d["host_out"][:B].copy_(d["tokens"][:B], non_blocking=False)
+        return d["host_out"][:B].tolist()
+
+    def decode_logits(self, B: int) -> torch.Tensor:
+        return self._decode_buffers()["logits"][:B]

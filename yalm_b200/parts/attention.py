@@ -1,0 +1,90 @@
+"""Grouped-query causal attention with an optional sliding window.
+
+q = Wq h, k = Wk h, v = Wv h (one product over the stacked matrix); position
+encoding on q and k; k, v into the cache; softmax((q.k)/sqrt(hd)) v over the
+visible keys with head h reading kv head h // (H/G); x += Wo o.  The formulas
+are the reference's (infer.cpp:278-338, infer.cu:730-920); the window
+(keys p-W+1..p) is the checkpoint's ``sliding_window``, which the reference
+does not read.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..cache import CacheNeed
+from ..csrc import ops
+from ..weights import TensorNeed
+from .base import POSITIONS, make_part, register_mixer
+from .linear import matmul_partials
+
+
+@register_mixer("gqa_attention")
+class GQAAttention:
+    def __init__(self, params: dict, rt):
+        self.rt = rt
+        self.D = int(params["hidden_size"])
+        self.H = int(params["num_heads"])
+        self.G = int(params["num_kv_heads"])
+        self.hd = int(params["head_dim"])
+        self.window: Optional[int] = params.get("window")
+        if self.H % self.G:
+            raise ValueError(f"{self.H} heads do not divide into {self.G} kv heads")
+        if self.hd % 8 or not 0 < self.hd <= 256:
+            raise ValueError(f"head size {self.hd} is not supported by the attention kernel "
+                             f"(multiples of 8 up to 256)")
+        self.position = make_part(POSITIONS, params["position"], rt)
+        self.w_qkv = None
+        self.w_o = None
+
+    def tensor_needs(self):
+        return {"q": TensorNeed((self.H * self.hd, self.D)),
+                "k": TensorNeed((self.G * self.hd, self.D)),
+                "v": TensorNeed((self.G * self.hd, self.D)),
+                "o": TensorNeed((self.D, self.H * self.hd))}
+
+    def bind(self, tensors) -> None:
+        parts = [tensors["q"], tensors["k"], tensors["v"]]
+        if any(p.dtype == torch.float32 for p in parts):
+            parts = [p.to(torch.float32) for p in parts]
+        self.w_qkv = self.rt.matrix(torch.cat(parts, 0))
+        self.w_o = self.rt.matrix(tensors["o"])
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=self.window)
+
+    def split_count(self, batch, capacity: int) -> int:
+        """Key slices per query, so that a few decoding sequences still fill the
+        device; fixed by the batch's shape, not by the current lengths."""
+        if not batch.is_decode:
+            return 1
+        R = self.H // self.G
+        blocks = batch.n_tokens * self.G * -(-R // 4)
+        want = -(-2 * self.rt.sm_count // blocks)
+        return max(1, min(want, 32, capacity // 256))
+
+    def forward(self, h, batch, stream, view, shared: bool = False) -> None:
+        rt, H, G, hd = self.rt, self.H, self.G, self.hd
+        n = batch.n_tokens
+        qkv, S = matmul_partials(rt, h, self.w_qkv, "qkv")
+        q = rt.buffer("q_rot", (n, H * hd), rt.dtype)
+        # a layer whose cache another run entry reads keeps its step keys apart
+        kv_step = view.kv_step if getattr(view, "kv_step", None) is not None else \
+            rt.buffer("kv_step", (n, 2, G, hd), rt.dtype)
+        if shared:
+            # this run reads the owner's keys and values: rotate q only
+            scratch = rt.buffer("kv_step_unused", (n, 2, G, hd), rt.dtype)
+            self.position.rotate_and_store(qkv, S, batch, view, q, scratch, H, G,
+                                           write_cache=False)
+        else:
+            self.position.rotate_and_store(qkv, S, batch, view, q, kv_step, H, G)
+        o = rt.buffer("attn_out", (n, H * hd), rt.dtype)
+        nsplit = self.split_count(batch, view.capacity)
+        part_o = part_ml = None
+        if nsplit > 1:
+            part_o = rt.buffer("attn_part_o", (n, H, nsplit, hd), torch.float32)
+            part_ml = rt.buffer("attn_part_ml", (n, H, nsplit, 2), torch.float32)
+        ops.attention(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
+                      view.capacity, self.window, nsplit, part_o, part_ml)
+        stream.add_linear(o, self.w_o)

@@ -1,0 +1,105 @@
+"""Matrix products of the parts: which kernel, which epilogue, how many K
+slices.
+
+bfloat16 operands go to the tcgen05 kernel.  When the token count is small the
+grid of 128-row weight tiles is too small to pull from HBM with every SM, so K
+is split and each slice writes a 32-bit partial product; the consumer (norm,
+rotary or SiLU kernel) sums the slices while it reads them.  With many tokens
+the epilogue is fused instead (store, residual add, SiLU*up).  32-bit operands,
+mixed operands (a matrix stored in 32 bits under bfloat16 compute) and shapes
+TMA cannot address go to the FMA kernel.
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+
+from ..csrc import ops
+
+
+def _token_tile(M: int) -> int:
+    for bt in (16, 32, 64, 128):
+        if M <= bt:
+            return bt
+    return 256
+
+
+def plan_splits(M: int, N: int, K: int, sm_count: int = 148) -> int:
+    """Number of K slices for a small-M product: trade idle SMs against the
+    traffic of the partial sums (written once, read once, 4 bytes each)."""
+    bt = _token_tile(M)
+    tiles = -(-N // 128) * -(-M // bt)
+    nkb = -(-K // 64)
+    weight_bytes = 2.0 * N * K
+    best, best_cost = 1, None
+    for s in (1, 2, 3, 4, 5, 6, 8, 10, 12, 16):
+        if s > nkb:
+            break
+        per = -(-nkb // s)
+        if (s - 1) * per >= nkb:
+            continue                       # would leave an empty slice
+        busy = min(1.0, tiles * s / float(sm_count))
+        cost = weight_bytes / busy + 2.0 * s * M * N * 4.0
+        if best_cost is None or cost < best_cost * 0.97:
+            best, best_cost = s, cost
+    return best
+
+
+def _use_tc(rt, a: torch.Tensor, w: torch.Tensor) -> bool:
+    return rt.gemm != "simt" and ops.gemm_tc_usable(a, w)
+
+
+def _small(rt, M: int, N: int) -> bool:
+    return -(-N // 128) * -(-M // _token_tile(M)) < rt.sm_count and M <= 128
+
+
+def matmul_partials(rt, a: torch.Tensor, w: torch.Tensor, name: str) -> Tuple[torch.Tensor, int]:
+    """a @ w.T as S 32-bit slices [S, M, N] whose sum is the product."""
+    M, K = a.shape
+    N = w.shape[0]
+    if _use_tc(rt, a, w):
+        S = plan_splits(M, N, K, rt.sm_count) if _small(rt, M, N) else 1
+        buf = rt.buffer(name, (S, M, N), torch.float32)
+        ops.gemm_tc(a, w, buf, ops.GEMM_SPLIT, rt.status, splits=S)
+        return buf, S
+    buf = rt.buffer(name, (1, M, N), torch.float32)
+    ops.gemm_simt(a, w, buf[0])
+    return buf, 1
+
+
+def matmul_store(rt, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out = a @ w.T (out float32 or the compute type)."""
+    if _use_tc(rt, a, w):
+        ops.gemm_tc(a, w, out, ops.GEMM_STORE, rt.status)
+    else:
+        ops.gemm_simt(a, w, out)
+
+
+def matmul_into_stream(rt, a: torch.Tensor, w: torch.Tensor, stream) -> None:
+    """stream.x += a @ w.T, directly or as pending partial sums."""
+    M, K = a.shape
+    N = w.shape[0]
+    if stream.n_pending:
+        stream.resolve()
+    if _use_tc(rt, a, w):
+        if _small(rt, M, N):
+            S = plan_splits(M, N, K, rt.sm_count)
+            buf = rt.buffer("stream_partials", (S, M, N), torch.float32)
+            ops.gemm_tc(a, w, buf, ops.GEMM_SPLIT, rt.status, splits=S)
+            stream.pending, stream.n_pending = buf, S
+        else:
+            ops.gemm_tc(a, w, stream.x, ops.GEMM_ADD, rt.status)
+    else:
+        ops.gemm_simt(a, w, stream.x, accumulate=True)
+
+
+def matmul_silu_mul(rt, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(a @ Wg.T) * (a @ Wu.T), w_gate_up = [Wg; Wu]."""
+    M, K = a.shape
+    N2 = w_gate_up.shape[0]
+    if _use_tc(rt, a, w_gate_up) and not _small(rt, M, N2 // 2):
+        ops.gemm_tc(a, w_gate_up, out, ops.GEMM_SILU_MUL, rt.status)
+        return
+    buf, S = matmul_partials(rt, a, w_gate_up, "gate_up")
+    ops.silu_mul(buf, out, n_partials=S)
