@@ -1,0 +1,80 @@
+"""The cache's bookkeeping on the host: no slot lost, held twice or freed twice (no GPU)."""
+import random
+
+import pytest
+import torch
+
+from yalm_b200.cache import Cache, CacheNeed, SlotAllocator, SlotError
+
+
+def test_slots_are_handed_out_once_and_come_back():
+    a = SlotAllocator(4)
+    s = a.acquire(3)
+    assert sorted(s) == [0, 1, 2] and a.free_count == 1
+    with pytest.raises(SlotError, match="only 1 of 4"):
+        a.acquire(2)
+    a.release([s[1]])
+    assert a.free_count == 2 and a.held == [0, 2]
+    again = a.acquire(2)
+    assert sorted(again) == [1, 3]
+    a.check()
+
+
+def test_double_free_and_foreign_slots_raise():
+    a = SlotAllocator(3)
+    s = a.acquire(2)
+    a.release([s[0]])
+    with pytest.raises(SlotError, match="not held"):
+        a.release([s[0]])
+    with pytest.raises(SlotError, match="does not exist"):
+        a.release([7])
+    with pytest.raises(SlotError, match="twice"):
+        a.release([s[1], s[1]])
+    assert a.held == [s[1]]                      # the failed call released nothing
+    with pytest.raises(SlotError):
+        SlotAllocator(0)
+
+
+def test_random_traffic_never_loses_or_duplicates_a_slot():
+    rng = random.Random(0)
+    a = SlotAllocator(9)
+    mine = []
+    for _ in range(2000):
+        if mine and (rng.random() < 0.5 or a.free_count == 0):
+            k = rng.randint(1, len(mine))
+            out = [mine.pop(rng.randrange(len(mine))) for _ in range(k)]
+            a.release(out)
+        else:
+            got = a.acquire(rng.randint(1, a.free_count))
+            assert not set(got) & set(mine)
+            mine.extend(got)
+        a.check()
+        assert sorted(mine) == a.held and a.free_count == 9 - len(mine)
+
+
+def test_groups_have_storage_of_their_own_and_state_is_zeroed():
+    needs = {0: CacheNeed("kv", kv_heads=2, head_dim=16),
+             1: CacheNeed("kv", kv_heads=2, head_dim=16, window=8),
+             2: CacheNeed("kv", kv_heads=2, head_dim=16),
+             3: CacheNeed("state", state_shape=(4, 3))}
+    c = Cache(needs, n_slots=3, context=32, dtype=torch.float32, device="cpu")
+    assert len(c.groups) == 3
+    full, ring, state = c.view(0), c.view(1), c.view(3)
+    assert full.k.shape == (3, 2, 32, 16) and ring.k.shape == (3, 2, 8, 16)
+    assert full.capacity == 32 and ring.capacity == 8
+    assert c.view(2).k.data_ptr() != full.k.data_ptr()          # same group, own layer plane
+    assert state.state.shape == (3, 4, 3)
+    assert c.bytes() == Cache.bytes_needed(needs, 3, 32, torch.float32)
+    s = c.acquire(2)
+    state.state[s[0]] += 5.0
+    c.slot_pos[s[0]] = 17
+    c.host_pos[s[0]] = 17
+    c.release(s)
+    t = c.acquire(3)                                            # slots come back, reset
+    assert sorted(t) == [0, 1, 2]
+    assert c.slot_pos.tolist() == [0, 0, 0] and c.host_pos == [0, 0, 0]
+    assert float(c.view(3).state.abs().sum()) == 0.0
+    with pytest.raises(SlotError):
+        c.acquire(1)
+    with pytest.raises(KeyError):
+        Cache({0: needs[0]}, 1, 8, torch.float32, "cpu").view(5)

@@ -1,0 +1,241 @@
+"""The engine against the plain implementation on a GPU: every request alone
+and whole; with the last 32 tokens one by one; in batches of unequal lengths
+whose shorter requests end earlier, batch after batch so that slots are used
+again; in 32-bit and in bfloat16; through bin/trace_run and through the Python
+entry point."""
+import os
+
+import pytest
+import torch
+
+from helpers import CONFIGS, TOL, make_weights, random_tokens, write_model
+from plain_model import plain_forward, plain_generate_greedy, plain_perplexity
+from trace_tools import Trace, add_batches, add_tail, add_whole, compare, run_in_process, run_trace_run
+
+pytestmark = pytest.mark.gpu
+
+# request lengths and prompt lengths per configuration (contexts 128 / 96 / 160)
+REQUESTS = {
+    "tiny_a": {"lens": {"r0": 21, "r1": 33, "r2": 47, "r3": 100, "r4": 128, "r5": 2},
+               "prompts": {"r0": 5, "r1": 17, "r2": 31, "r3": 64, "r4": 96, "r5": 1},
+               "batches": [["r0", "r1", "r2"], ["r3", "r5", "r4"], ["r2", "r0"]]},
+    "tiny_b": {"lens": {"r0": 21, "r1": 29, "r2": 60, "r3": 90, "r4": 96, "r5": 34},
+               "prompts": {"r0": 1, "r1": 9, "r2": 40, "r3": 70, "r4": 33, "r5": 32},
+               "batches": [["r0", "r1", "r2", "r3"], ["r4", "r5"], ["r3", "r0", "r1"]]},
+    "tiny_c": {"lens": {"r0": 7, "r1": 45, "r2": 81, "r3": 160},
+               "prompts": {"r0": 3, "r1": 41, "r2": 39, "r3": 100},
+               "batches": [["r0", "r1", "r2"], ["r3", "r0"]]},
+}
+
+
+def _setup(name):
+    cfg, seed = CONFIGS[name]
+    w = make_weights(cfg, seed)
+    reqs = {rid: random_tokens(n, cfg["vocab_size"], 100 + i)
+            for i, (rid, n) in enumerate(REQUESTS[name]["lens"].items())}
+    refs = {rid: plain_forward(cfg, w, t) for rid, t in reqs.items()}
+    tr = Trace()
+    add_whole(tr, reqs)
+    add_tail(tr, reqs, tail=32)
+    add_batches(tr, reqs, REQUESTS[name]["batches"], REQUESTS[name]["prompts"])
+    return cfg, w, reqs, refs, tr
+
+
+_cache = {}
+
+
+def setup(name):
+    if name not in _cache:
+        _cache[name] = _setup(name)
+    return _cache[name]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_trace_run_matches_plain_model(name, dtype, tmp_path):
+    cfg, w, reqs, refs, tr = setup(name)
+    model_dir = write_model(str(tmp_path / "model"), cfg, w)
+    got = run_trace_run(model_dir, dtype, tr, str(tmp_path / "out"))
+    compare(tr, got, refs, cfg["vocab_size"], TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+def test_step_function_matches_plain_model(name, dtype):
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, w, reqs, refs, tr = setup(name)
+    lm = LM(config_from_dict(cfg), dict(w), dtype=dtype, max_batch=max(1, tr.max_tokens // 64))
+    got = run_in_process(lm, tr)
+    compare(tr, got, refs, cfg["vocab_size"], TOL[dtype])
+    assert lm.engine.cache.slots.free_count == lm.max_batch
+
+
+def test_the_two_ways_of_cutting_agree_beyond_the_plain_models_tolerance():
+    """32-bit logits at a position are the same to rounding whether the position
+    was part of a whole prompt, decoded alone, or decoded inside a batch."""
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, w, reqs, refs, tr = setup("tiny_b")
+    lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=max(1, tr.max_tokens // 64))
+    got = run_in_process(lm, tr)
+    seen = {}
+    for step, rows in tr.rows.items():
+        g = got[step].reshape(-1, cfg["vocab_size"])
+        for i, key in enumerate(rows):
+            if key in seen:
+                assert float((g[i] - seen[key]).abs().max()) <= 2e-5 * float(refs[key[0]].abs().max())
+            else:
+                seen[key] = g[i]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_past_the_window(dtype):
+    """300 tokens decoded one by one through a ring of 32 rows."""
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg = dict(CONFIGS["tiny_b"][0], max_position_embeddings=512)
+    w = make_weights(cfg, 7)
+    toks = random_tokens(330, cfg["vocab_size"], 5)
+    ref = plain_forward(cfg, w, toks)
+    lm = LM(config_from_dict(cfg), dict(w), dtype=dtype, max_batch=1)
+    s = lm.acquire(1)
+    lg = lm.step([toks[:30]], s, [[29]])
+    worst = float((lg[0].cpu() - ref[29]).abs().max() / ref.abs().max())
+    for p in range(30, 330):
+        lg = lm.step([[toks[p]]], s, [[0]])
+        worst = max(worst, float((lg[0].cpu() - ref[p]).abs().max() / ref.abs().max()))
+    lm.release(s)
+    assert worst <= TOL[dtype], worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_first_tokens_of_a_sequence(dtype):
+    """A prompt of one token, then positions 1, 2, 3 alone; and steps that want nothing."""
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, seed = CONFIGS["tiny_a"]
+    w = make_weights(cfg, seed)
+    toks = random_tokens(6, cfg["vocab_size"], 9)
+    ref = plain_forward(cfg, w, toks)
+    lm = LM(config_from_dict(cfg), dict(w), dtype=dtype, max_batch=2)
+    s = lm.acquire(1)
+    assert lm.step([[toks[0]]], s, [[]]) is None               # nothing wanted: no logits
+    for p in range(1, 6):
+        lg = lm.step([[toks[p]]], s, [[0]])
+        assert float((lg[0].cpu() - ref[p]).abs().max() / ref.abs().max()) <= TOL[dtype], p
+    lm.release(s)
+
+
+def test_greedy_generation_through_the_entry_point():
+    """Unequal prompts, a stop token, more requests than slots; 32-bit tokens
+    equal the plain model's, step for step."""
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    for name in ("tiny_a", "tiny_b"):
+        cfg, seed = CONFIGS[name]
+        w = make_weights(cfg, seed)
+        prompts = [random_tokens(n, cfg["vocab_size"], 40 + n) for n in (5, 17, 31, 2, 9)]
+        lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=2)
+        free = plain_generate_greedy(cfg, w, prompts[0], 12)
+        stop = [free[5]]
+        want = [plain_generate_greedy(cfg, w, p, 12, stop=stop) for p in prompts]
+        got = lm.generate(prompts, max_new_tokens=12, temperature=0.0, stop_ids=stop)
+        assert [c.tokens for c in got] == want
+        assert got[0].finish_reason == "stop" and got[0].tokens[-1] == stop[0]
+        assert all(c.finish_reason in ("stop", "length") for c in got)
+        assert lm.engine.cache.slots.free_count == 2
+        # the same through replayed graphs a second time, and without graphs
+        again = lm.generate(prompts, max_new_tokens=12, temperature=0.0, stop_ids=stop)
+        assert [c.tokens for c in again] == want
+        lm.engine.use_graphs = False
+        assert [c.tokens for c in lm.generate(prompts, 12, 0.0, stop_ids=stop)] == want
+
+
+def test_greedy_generation_in_bfloat16_picks_near_maximal_tokens():
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, seed = CONFIGS["tiny_a"]
+    w = make_weights(cfg, seed)
+    prompts = [random_tokens(n, cfg["vocab_size"], 70 + n) for n in (5, 17, 31)]
+    lm = LM(config_from_dict(cfg), dict(w), dtype="bfloat16", max_batch=4)
+    for p, c in zip(prompts, lm.generate(prompts, max_new_tokens=10, temperature=0.0, ignore_eos=True)):
+        logits = plain_forward(cfg, w, p + c.tokens)
+        for i, t in enumerate(c.tokens):
+            row = logits[len(p) - 1 + i]
+            assert float(row.max() - row[t]) <= 2 * TOL["bfloat16"] * float(logits.abs().max())
+
+
+def test_temperature_sampling_is_per_request_and_reproducible():
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, seed = CONFIGS["tiny_a"]
+    w = make_weights(cfg, seed)
+    prompts = [random_tokens(n, cfg["vocab_size"], 80 + n) for n in (6, 11, 3)]
+    lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=4)
+    a = lm.generate(prompts, max_new_tokens=8, temperature=1.0, seed=3, ignore_eos=True)
+    b = lm.generate(prompts, max_new_tokens=8, temperature=1.0, seed=3, ignore_eos=True)
+    c = lm.generate(prompts, max_new_tokens=8, temperature=1.0, seed=4, ignore_eos=True)
+    assert [x.tokens for x in a] == [x.tokens for x in b]
+    assert [x.tokens for x in a] != [x.tokens for x in c]
+    # request 0 alone draws the same tokens as request 0 inside the batch
+    alone = lm.generate(prompts[:1], max_new_tokens=8, temperature=1.0, seed=3, ignore_eos=True)
+    assert alone[0].tokens == a[0].tokens
+
+
+def test_perplexity_matches_plain_model():
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, seed = CONFIGS["tiny_b"]
+    w = make_weights(cfg, seed)
+    toks = random_tokens(60, cfg["vocab_size"], 2)
+    lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=1)
+    ppl, err = lm.perplexity(toks)
+    rp, re = plain_perplexity(cfg, w, toks)
+    assert abs(ppl - rp) / rp < 1e-4 and abs(err - re) / re < 1e-3
+
+
+def test_slots_do_not_leak_into_each_other():
+    """Two sequences decoded in turn in neighbouring slots, then a third that
+    takes over a used slot: each equals its own whole-prompt logits."""
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, seed = CONFIGS["tiny_a"]
+    w = make_weights(cfg, seed)
+    V = cfg["vocab_size"]
+    ta, tb, tc = (random_tokens(n, V, 200 + n) for n in (40, 23, 31))
+    ra, rb, rc = (plain_forward(cfg, w, t) for t in (ta, tb, tc))
+    lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=2)
+    sa, sb = lm.acquire(2)
+    lm.step([ta[:10]], [sa], [[]])
+    lm.step([tb[:20]], [sb], [[]])
+    lm.step([ta[10:11]], [sa], [[]])
+    # b alone, then a alone, with lengths 20 vs 11: a row of b must not show up in a
+    lg = lm.step([tb[20:23]], [sb], [[2]])
+    assert float((lg[0].cpu() - rb[22]).abs().max() / rb.abs().max()) <= TOL["float32"]
+    lm.release([sb])
+    (sc,) = lm.acquire(1)
+    assert sc == sb                                           # the slot is used again
+    lg = lm.step([tc, ta[11:40]], [sc, sa], [[30], [28]])
+    assert float((lg[0].cpu() - rc[30]).abs().max() / rc.abs().max()) <= TOL["float32"]
+    assert float((lg[1].cpu() - ra[39]).abs().max() / ra.abs().max()) <= TOL["float32"]
+
+
+def test_step_refuses_bad_requests():
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    from yalm_b200.engine.step import StepError
+    cfg, seed = CONFIGS["tiny_a"]
+    lm = LM(config_from_dict(cfg), make_weights(cfg, seed), dtype="float32", max_batch=2)
+    (s,) = lm.acquire(1)
+    with pytest.raises(StepError, match="vocabulary"):
+        lm.step([[1, 999]], [s], [[]])
+    with pytest.raises(StepError, match="context"):
+        lm.step([[1] * 129], [s], [[]])
+    with pytest.raises(StepError, match="not held"):
+        lm.step([[1]], [1 - s], [[]])
+    with pytest.raises(StepError, match="twice"):
+        lm.step([[1], [2]], [s, s], [[], []])
+    with pytest.raises(IndexError):
+        lm.step([[1, 2]], [s], [[2]])
+    lm.step([[1, 2]], [s], [[1]])                               # still usable afterwards

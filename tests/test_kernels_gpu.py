@@ -1,0 +1,283 @@
+"""Each kernel alone against a plain 32-bit reference of the same operation, at
+sizes other than the engine's tiny configurations, with inputs built so that a
+fault shows: a far key among hundreds, a window's edge, a wrapped ring, a slot."""
+import math
+
+import pytest
+import torch
+
+from plain_model import plain_argmax, plain_attention, plain_inv_freq, plain_rmsnorm, plain_rope
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from yalm_b200.csrc import ops as o
+    o.lib()
+    return o
+
+
+class B:
+    """The index arrays of a ragged batch."""
+
+    def __init__(self, q_lens, slots):
+        qs = [0]
+        for q in q_lens:
+            qs.append(qs[-1] + q)
+        self.n_seqs, self.n_tokens, self.q_lens, self.slots = len(q_lens), qs[-1], q_lens, slots
+        self.q_start = torch.tensor(qs, dtype=torch.int32, device=DEV)
+        self.seq_slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
+        self.token_seq = torch.tensor(sum([[i] * q for i, q in enumerate(q_lens)], []),
+                                      dtype=torch.int32, device=DEV)
+
+
+def test_embedding_gathers_rows_and_flags_bad_ids(ops):
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for dt in (torch.float32, torch.bfloat16):
+        table = torch.randn(1000, 200, device=DEV).to(dt)
+        tok = torch.randint(0, 1000, (77,), device=DEV, dtype=torch.int32)
+        x = torch.empty(77, 200, device=DEV)
+        ops.embed(tok, table, x, status)
+        assert torch.equal(x, table.float()[tok.long()]) and status.item() == 0
+    tok[3] = 1000
+    ops.embed(tok, table, x, status)
+    assert status.item() == ops.ERR_TOKEN_RANGE
+
+
+@pytest.mark.parametrize("dim", [40, 200, 1000, 4096, 5000])
+def test_rmsnorm_with_partials_and_gather(ops, dim):
+    x = torch.randn(23, dim, device=DEV) * 3
+    w = torch.randn(dim, device=DEV)
+    parts = torch.randn(4, 23, dim, device=DEV)
+    ref = plain_rmsnorm(x.cpu(), w.cpu(), 1e-6)
+    out = torch.empty(23, dim, device=DEV)
+    xc = x.clone()
+    ops.rmsnorm(xc, w, out, 1e-6)
+    assert torch.equal(xc, x)
+    assert (out.cpu() - ref).abs().max() <= 2e-6 * ref.abs().max()
+    xs = x + parts.sum(0)
+    ref = plain_rmsnorm(xs.cpu(), w.cpu(), 1e-6)
+    ops.rmsnorm(xc, w, out, 1e-6, partials=parts, n_partials=4)
+    assert (out.cpu() - ref).abs().max() <= 4e-6 * ref.abs().max()
+    assert (xc - xs).abs().max() <= 1e-5                        # the residual sum was written back
+    rows = torch.tensor([22, 0, 7, 7], dtype=torch.int32, device=DEV)
+    outg = torch.empty(4, dim, device=DEV, dtype=torch.bfloat16)
+    xc = x.clone()
+    ops.rmsnorm(xc, w, outg, 1e-6, partials=parts, n_partials=4, rows=rows)
+    assert torch.equal(xc, x)                                   # a gather leaves x alone
+    assert (outg.float().cpu() - ref[rows.long().cpu()]).abs().max() <= 1e-2 * ref.abs().max()
+
+
+def test_silu_mul_sums_partials(ops):
+    gu = torch.randn(3, 11, 2 * 333, device=DEV) * 2
+    out = torch.empty(11, 333, device=DEV)
+    ops.silu_mul(gu, out, n_partials=3)
+    s = gu.sum(0).cpu()
+    g, u = s[:, :333], s[:, 333:]
+    ref = g / (1 + torch.exp(-g)) * u
+    assert (out.cpu() - ref).abs().max() <= 1e-5 * ref.abs().max()
+
+
+@pytest.mark.parametrize("shape", [(1, 70, 50), (65, 129, 17), (300, 520, 260)])
+def test_fma_matrix_product_is_true_32_bit(ops, shape):
+    M, N, K = shape
+    a, w = torch.randn(M, K, device=DEV), torch.randn(N, K, device=DEV)
+    ref = (a.double() @ w.double().T)
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm_simt(a, w, out)
+    # 32-bit accumulation: error ~ sqrt(K) * 2^-24 * |a||w|; a 10-bit mantissa mode would give 1e-3
+    assert (out.double() - ref).abs().max() <= 3e-6 * math.sqrt(K) * ref.abs().max()
+    ops.gemm_simt(a, w, out, accumulate=True)
+    assert (out.double() - 2 * ref).abs().max() <= 6e-6 * math.sqrt(K) * ref.abs().max()
+    # a row's result does not depend on the other rows of the batch
+    one = torch.empty(1, N, device=DEV)
+    ops.gemm_simt(a[M // 2:M // 2 + 1].contiguous(), w, one)
+    ops.gemm_simt(a, w, out)
+    assert torch.equal(one[0], out[M // 2])
+    # mixed storage: bfloat16 activations on a matrix kept in 32 bits
+    ah = a.to(torch.bfloat16)
+    ops.gemm_simt(ah, w, out)
+    assert (out.double() - ah.double() @ w.double().T).abs().max() <= 3e-6 * math.sqrt(K) * ref.abs().max()
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 64), (3, 200, 72), (16, 384, 512), (40, 1000, 320),
+                                   (64, 2048, 1024), (130, 300, 88), (256, 512, 256), (700, 640, 448)])
+def test_tcgen05_matrix_product_all_epilogues(ops, shape):
+    M, N, K = shape
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    a = (torch.randn(M, K, device=DEV) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.5).to(torch.bfloat16)
+    ref = a.double() @ w.double().T
+    tol = 2e-6 * math.sqrt(K) * ref.abs().max()
+    out = torch.full((M, N), 7.0, device=DEV)
+    ops.gemm_tc(a, w, out, ops.GEMM_STORE, status)
+    assert (out.double() - ref).abs().max() <= tol
+    ops.gemm_tc(a, w, out, ops.GEMM_ADD, status)
+    assert (out.double() - 2 * ref).abs().max() <= 2 * tol
+    outh = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tc(a, w, outh, ops.GEMM_STORE, status)
+    assert (outh.double() - ref).abs().max() <= 2 ** -8 * ref.abs().max()
+    nkb = -(-K // 64)
+    for S in sorted({1, min(2, nkb), min(5, nkb)}):
+        per = -(-nkb // S)
+        if (S - 1) * per >= nkb:
+            continue
+        part = torch.full((S, M, N), 3.0, device=DEV)
+        ops.gemm_tc(a, w, part, ops.GEMM_SPLIT, status, splits=S)
+        assert (part.sum(0).double() - ref).abs().max() <= tol, S
+    g, u = ref[:, :N // 2], ref[:, N // 2:]
+    r2 = g / (1 + torch.exp(-g)) * u
+    o2 = torch.zeros(M, N // 2, device=DEV)
+    ops.gemm_tc(a, w, o2, ops.GEMM_SILU_MUL, status)
+    assert (o2.double() - r2).abs().max() <= 4e-6 * math.sqrt(K) * max(1.0, r2.abs().max())
+    assert status.item() == 0
+
+
+def test_tcgen05_refuses_what_tma_cannot_address(ops):
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    a = torch.zeros(4, 36, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(128, 36, device=DEV, dtype=torch.bfloat16)
+    assert not ops.gemm_tc_usable(a, w)
+    with pytest.raises(ops.KernelError, match="refused"):
+        ops.gemm_tc(a, w, torch.zeros(4, 128, device=DEV), ops.GEMM_STORE, status)
+    with pytest.raises(ops.KernelError, match="split"):
+        ops.gemm_tc(torch.zeros(4, 64, device=DEV, dtype=torch.bfloat16),
+                    torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16),
+                    torch.zeros(2, 4, 128, device=DEV), ops.GEMM_SPLIT, status, splits=2)
+
+
+def _rope_attend(ops, dt, H, G, hd, cap, window, q_lens, slots, n_slots, steps, nsplit_decode):
+    """Drives rope_store + attention over several steps and returns the largest
+    error against plain_rope + plain_attention on the whole sequences."""
+    inv = plain_inv_freq(hd, 10000.0, None).to(DEV)
+    slot_pos = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+    kc = torch.zeros(n_slots, G, cap, hd, device=DEV, dtype=dt)
+    vc = torch.zeros_like(kc)
+    hist = {s: [] for s in slots}
+    worst = 0.0
+    for step in range(steps):
+        lens = q_lens if step == 0 else [1] * len(slots)
+        b = B(lens, slots)
+        N = b.n_tokens
+        qkv = torch.randn(N, (H + 2 * G) * hd, device=DEV)
+        q_out = torch.empty(N, H * hd, device=DEV, dtype=dt)
+        kv_step = torch.empty(N, 2, G, hd, device=DEV, dtype=dt)
+        ops.rope_store(qkv, 1, inv, b, q_out, kv_step, kc, vc, slot_pos, H, G, hd, cap)
+        out = torch.empty(N, H * hd, device=DEV, dtype=dt)
+        ns = 1 if step == 0 else nsplit_decode
+        po = torch.empty(N * H * ns * hd, device=DEV)
+        pml = torch.empty(N * H * ns * 2, device=DEV)
+        ops.attention(q_out, kv_step, kc, vc, b, slot_pos, out, H, G, hd, cap, window, ns, po, pml)
+        qs = b.q_start.tolist()
+        for i, s in enumerate(slots):
+            hist[s].append(qkv[qs[i]:qs[i + 1]].cpu().view(-1, H + 2 * G, hd))
+            allt = torch.cat(hist[s])
+            T = allt.shape[0]
+            pos = torch.arange(T)
+            q = plain_rope(allt[:, :H], pos, inv.cpu()).to(dt).float()
+            k = plain_rope(allt[:, H:H + G], pos, inv.cpu()).to(dt).float()
+            v = allt[:, H + G:].to(dt).float()
+            ref = plain_attention(q, k, v, window)[T - lens[i]:]
+            got = out[qs[i]:qs[i + 1]].float().cpu().view(-1, H, hd)
+            worst = max(worst, float((got - ref).abs().max()))
+        ops.advance(b, slot_pos)
+    return worst
+
+
+@pytest.mark.parametrize("dt, tol", [(torch.float32, 3e-6), (torch.bfloat16, 1.6e-2)])
+@pytest.mark.parametrize("H, G, hd, cap, window", [
+    (8, 8, 16, 96, None),      # no grouping
+    (10, 2, 80, 96, None),     # 5 query heads per kv head, head size 80
+    (16, 1, 64, 24, 24),       # one kv head, a ring of 24 rows shorter than the prompt
+    (4, 4, 256, 96, 50),       # the largest head, window inside a larger ring
+    (6, 3, 112, 40, 40),
+])
+def test_rotary_cache_write_and_attention(ops, dt, tol, H, G, hd, cap, window):
+    err = _rope_attend(ops, dt, H, G, hd, cap, window, q_lens=[33, 1, 60], slots=[4, 0, 2],
+                       n_slots=5, steps=10, nsplit_decode=3)
+    assert err <= tol, err
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_attention_finds_a_far_key_a_window_edge_and_a_wrapped_row(ops, dt):
+    """Keys are one-hot, queries 1e3 times a one-hot: the output is the value
+    of exactly one position.  Position 3 among 700; the oldest key inside a
+    window; the key just outside it; a ring row that has been overwritten."""
+    H = G = 1
+    hd = 64
+    for window, cap, T, targets in [(None, 1024, 700, [3, 0, 699, 350]),
+                                    (64, 64, 700, [699, 636, 650])]:
+        n_slots = 3
+        slot = 1
+        kc = torch.zeros(n_slots, G, cap, hd, device=DEV, dtype=dt)
+        vc = torch.zeros_like(kc)
+        # keys: position p has key e_{p % 64} scaled by (1 + p/1000) so that equal directions differ
+        pos = torch.arange(T)
+        keys = torch.zeros(T, hd)
+        keys[pos, pos % hd] = 1.0
+        vals = torch.zeros(T, hd)
+        vals[pos, (pos * 7) % hd] = 1.0 + pos.float() / 1024.0
+        live = pos if window is None else pos[T - window:]
+        kc[slot, 0, live % cap] = keys[live].to(dt).to(DEV)
+        vc[slot, 0, live % cap] = vals[live].to(dt).to(DEV)
+        slot_pos = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+        slot_pos[slot] = T - 1                       # the query is the token at position T-1
+        b = B([1], [slot])
+        kv_step = torch.zeros(1, 2, G, hd, device=DEV, dtype=dt)
+        kv_step[0, 0, 0] = keys[T - 1].to(dt)
+        kv_step[0, 1, 0] = vals[T - 1].to(dt)
+        for tgt in targets:
+            # a bias towards late positions that only the one-hot match can beat
+            q = torch.zeros(1, hd, device=DEV)
+            q[0, tgt % hd] = 1000.0
+            lo = 0 if window is None else T - window
+            cands = [p for p in range(lo, T) if p % hd == tgt % hd]
+            for ns in (1, 4):
+                out = torch.empty(1, hd, device=DEV, dtype=dt)
+                po = torch.empty(ns * hd, device=DEV)
+                pml = torch.empty(ns * 2, device=DEV)
+                ops.attention(q.to(dt), kv_step, kc, vc, b, slot_pos, out, H, G, hd, cap, window,
+                              ns, po, pml)
+                ref = torch.stack([vals[p] for p in cands]).mean(0)
+                assert (out[0].float().cpu() - ref.to(dt).float()).abs().max() < 2e-2, (window, tgt, ns)
+        if window is not None:
+            # the key just outside the window (position T-1-window) must not be seen
+            outside = T - 1 - window
+            assert outside % hd == (T - 1) % hd       # same direction as the newest key
+            q = torch.zeros(1, hd, device=DEV)
+            q[0, outside % hd] = 1000.0
+            out = torch.empty(1, hd, device=DEV, dtype=dt)
+            ops.attention(q.to(dt), kv_step, kc, vc, b, slot_pos, out, H, G, hd, cap, window, 1)
+            assert abs(out[0, ((T - 1) * 7) % hd].item() - vals[T - 1].max().item()) < 2e-2
+
+
+def test_sampling_greedy_and_temperature(ops):
+    V = 5003
+    logits = torch.randn(6, V, device=DEV) * 4
+    logits[2, 17] = logits[2, 4000] = 60.0                      # a tie: the first index wins
+    slot_pos = torch.tensor([5, 6, 7, 8, 9, 10], dtype=torch.int32, device=DEV)
+    seq_slot = torch.arange(6, dtype=torch.int32, device=DEV)
+    keys = torch.arange(6, dtype=torch.int32, device=DEV) + 100
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.sample(logits, 0.0, 1, keys, seq_slot, slot_pos, out)
+    assert out.tolist() == [plain_argmax(r) for r in logits.cpu()] and out[2].item() == 17
+    for temp in (1.0, 0.3, 2.5):
+        for seed in range(4):
+            ops.sample(logits, temp, seed, keys, seq_slot, slot_pos, out)
+            for r in range(6):
+                u = ops.uniform01(seed, 100 + r, 5 + r)
+                assert 0.0 <= u < 1.0
+                c = torch.softmax(logits[r].double().cpu() / temp, 0).cumsum(0)
+                t = out[r].item()
+                lo = 0.0 if t == 0 else c[t - 1].item()
+                assert lo - 1e-5 <= u <= c[t].item() + 1e-5, (temp, seed, r)
+    # the draw depends on (seed, key, position) only, not on the row it sits in
+    ops.sample(logits[3:4].contiguous(), 1.0, 2, keys[3:4].contiguous(), seq_slot[:1].contiguous(),
+               slot_pos[3:4].contiguous(), out[:1])
+    one = out[0].item()
+    ops.sample(logits, 1.0, 2, keys, seq_slot, slot_pos, out)
+    assert out[3].item() == one
+    us = [ops.uniform01(9, 1, i) for i in range(2000)]
+    assert 0.45 < sum(us) / len(us) < 0.55 and len(set(us)) > 1990

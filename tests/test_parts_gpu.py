@@ -1,0 +1,282 @@
+"""Each part alone against its plain function, and a toy mixer with state of
+its own that is registered, built and stepped without touching the library."""
+import dataclasses
+import math
+
+import pytest
+import torch
+
+from helpers import TINY_A, TINY_C, TOL, make_weights, random_tokens
+from plain_model import (plain_attention, plain_block, plain_embedding, plain_forward,
+                         plain_inv_freq, plain_rmsnorm, plain_rope, plain_swiglu)
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rt(dtype):
+    from yalm_b200.parts import Runtime
+    return Runtime(dtype, DEV)
+
+
+def _prefill_batch(n):
+    from yalm_b200.engine.batch import build_batch
+    return build_batch([[0] * n], [0], [0], [[]], DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from yalm_b200.parts import NORMS, ResidualStream
+    rt = _rt(dtype)
+    norm = NORMS["rmsnorm"]({"size": 200, "eps": 1e-4}, rt)
+    assert norm.tensor_needs()["weight"].shape == (200,)
+    w = torch.randn(200)
+    norm.bind({"weight": w})
+    x = torch.randn(9, 200, device=DEV)
+    h = norm(ResidualStream(rt, x.clone()))
+    ref = plain_rmsnorm(x.cpu(), w, 1e-4)
+    tol = 2e-6 if dtype == torch.float32 else 2 ** -8
+    assert h.dtype == dtype and (h.float().cpu() - ref).abs().max() <= tol * ref.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    from yalm_b200.parts import FEED_FORWARDS, ResidualStream
+    rt = _rt(dtype)
+    ffn = FEED_FORWARDS["swiglu"]({"hidden_size": 88, "intermediate_size": 200}, rt)
+    w = {k: (0.1 * torch.randn(s)).to(torch.bfloat16)
+         for k, s in (("gate", (200, 88)), ("up", (200, 88)), ("down", (88, 200)))}
+    ffn.bind(w)
+    for n in (3, 150):                                          # few tokens (split K) and many
+        h = torch.randn(n, 88).to(dtype)
+        stream = ResidualStream(rt, torch.ones(n, 88, device=DEV))
+        ffn.forward(h.to(DEV), _prefill_batch(n), stream)
+        got = stream.resolve().cpu()
+        ref = 1.0 + plain_swiglu(h.float(), w["gate"], w["up"], w["down"])
+        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        assert (got - ref).abs().max() <= tol * ref.abs().max(), n
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 20])
+def test_attention_part_with_its_position_encoding(dtype, window):
+    from yalm_b200.cache import Cache
+    from yalm_b200.config import PartSpec
+    from yalm_b200.parts import MIXERS, ResidualStream
+    rt = _rt(dtype)
+    D, H, G, hd, T = 88, 6, 2, 48, 70
+    scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+               "high_freq_factor": 4.0, "original_max_position_embeddings": 32}
+    mixer = MIXERS["gqa_attention"]({
+        "hidden_size": D, "num_heads": H, "num_kv_heads": G, "head_dim": hd, "window": window,
+        "position": PartSpec("rope", {"head_dim": hd, "theta": 5000.0, "scaling": scaling})}, rt)
+    w = {k: (0.1 * torch.randn(s)).to(torch.bfloat16)
+         for k, s in (("q", (H * hd, D)), ("k", (G * hd, D)), ("v", (G * hd, D)), ("o", (D, H * hd)))}
+    mixer.bind(w)
+    need = mixer.cache_need()
+    assert (need.kind, need.kv_heads, need.head_dim, need.window) == ("kv", G, hd, window)
+    cache = Cache({0: need}, n_slots=1, context=96, dtype=dtype, device=DEV)
+    cache.acquire(1)
+    h = torch.randn(T, D).to(dtype)
+    stream = ResidualStream(rt, torch.zeros(T, D, device=DEV))
+    mixer.forward(h.to(DEV), _prefill_batch(T), stream, cache.view(0))
+    got = stream.resolve().cpu()
+    hf = h.float()
+    inv = plain_inv_freq(hd, 5000.0, scaling)
+    pos = torch.arange(T)
+    q = plain_rope((hf @ w["q"].float().T).view(T, H, hd), pos, inv)
+    k = plain_rope((hf @ w["k"].float().T).view(T, G, hd), pos, inv)
+    v = (hf @ w["v"].float().T).view(T, G, hd)
+    ref = plain_attention(q, k, v, window).reshape(T, H * hd) @ w["o"].float().T
+    tol = 1e-5 if dtype == torch.float32 else 1.5e-2
+    assert (got - ref).abs().max() <= tol * ref.abs().max()
+    # the ring holds the last `capacity` rotated keys at row pos % capacity
+    cap = cache.view(0).capacity
+    p = T - 1
+    assert (cache.view(0).k[0, 1, p % cap].float().cpu() - k[p, 1]).abs().max() <= (
+        1e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_block_embedding_and_head(dtype):
+    from yalm_b200.cache import Cache
+    from yalm_b200.config import config_from_dict
+    from yalm_b200.parts import BLOCKS, EMBEDDINGS, HEADS, ResidualStream
+    rt = _rt(dtype)
+    cfg = TINY_C
+    spec = config_from_dict(cfg).to_spec()
+    w = make_weights(cfg, 3)
+    toks = random_tokens(50, cfg["vocab_size"], 1)
+    emb = EMBEDDINGS["embedding"](spec.embedding.params, rt)
+    emb.bind({"weight": w["model.embed_tokens.weight"]})
+    from yalm_b200.engine.batch import build_batch
+    batch = build_batch([toks], [0], [0], [[]], DEV)
+    x = emb.forward(batch)
+    assert torch.equal(x.cpu(), plain_embedding(w["model.embed_tokens.weight"], toks))
+    block = BLOCKS["prenorm"](spec.layers[1], rt)
+    for part, pspec in block.parts():
+        part.bind({k: w[pspec.tensors[k]] for k in part.tensor_needs()})
+    cache = Cache({0: block.mixer.cache_need()}, 1, 160, dtype, DEV)
+    cache.acquire(1)
+    stream = ResidualStream(rt, x)
+    block.forward(stream, batch, cache.view(0))
+    ref = plain_block(plain_embedding(w["model.embed_tokens.weight"], toks), cfg, w, 1,
+                      torch.arange(50))
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    got = stream.resolve().cpu()
+    assert (got - ref).abs().max() <= tol * ref.abs().max()
+    head = HEADS["linear_head"](spec.head.params, rt)
+    head.bind({"weight": w["lm_head.weight"]})
+    hh = torch.randn(5, cfg["hidden_size"]).to(dtype)
+    out = head.forward(hh.to(DEV), torch.empty(5, cfg["vocab_size"], device=DEV))
+    ref = hh.float() @ w["lm_head.weight"].float().T
+    assert (out.cpu() - ref).abs().max() <= (1e-5 if dtype == torch.float32 else 1e-5) * ref.abs().max()
+
+
+def test_a_matrix_stored_in_32_bits_stays_32_bit_under_bfloat16():
+    from yalm_b200.parts import HEADS
+    rt = _rt(torch.bfloat16)
+    head = HEADS["linear_head"]({"vocab_size": 300, "size": 88}, rt)
+    w = torch.randn(300, 88) * (1 + 2 ** -12)                   # not representable in bfloat16
+    head.bind({"weight": w})
+    assert head.weight.dtype == torch.float32
+    h = torch.randn(4, 88).to(torch.bfloat16)
+    out = head.forward(h.to(DEV), torch.empty(4, 300, device=DEV))
+    ref = h.double() @ w.double().T
+    assert (out.double().cpu() - ref).abs().max() <= 1e-5 * ref.abs().max()
+
+
+# ---------------------------------------------------------------------------
+# A toy mixer with state of its own, defined here: s <- decay * s + h_t per
+# sequence, output W s.  It is registered, built into a model next to an
+# attention layer, and stepped, without a change to the library's files.
+
+def _register_toy():
+    from yalm_b200.cache import CacheNeed
+    from yalm_b200.config import LlamaConfig, PartSpec, register_architecture
+    from yalm_b200.parts import MIXERS, register_mixer
+    from yalm_b200.weights import TensorNeed
+    if "toy_decay" in MIXERS:
+        return
+
+    @register_mixer("toy_decay")
+    class ToyDecay:
+        def __init__(self, params, rt):
+            self.rt, self.D, self.decay = rt, int(params["size"]), float(params["decay"])
+
+        def tensor_needs(self):
+            return {"w": TensorNeed((self.D, self.D))}
+
+        def bind(self, tensors):
+            self.w = tensors["w"].to(self.rt.device, torch.float32)
+
+        def cache_need(self):
+            return CacheNeed("state", state_shape=(self.D,), state_dtype=torch.float32)
+
+        def forward(self, h, batch, stream, view, shared=False):
+            out = torch.empty(batch.n_tokens, self.D, device=self.rt.device)
+            t = 0
+            for slot, n in zip(batch.slots, batch.q_lens):
+                s = view.state[slot]
+                for i in range(n):
+                    s = self.decay * s + h[t].float()
+                    out[t] = self.w @ s
+                    t += 1
+                view.state[slot] = s
+            stream.add_tensor(out)
+
+    class ToyConfig(LlamaConfig):
+        def to_spec(self):
+            spec = super().to_spec()
+            toy = PartSpec("toy_decay", {"size": self.hidden_size, "decay": 0.5},
+                           {"w": "model.layers.0.toy.weight"})
+            layers = [dataclasses.replace(spec.layers[0], mixer=toy)] + spec.layers[1:]
+            return dataclasses.replace(spec, layers=layers)
+
+    register_architecture("ToyForCausalLM", ToyConfig)
+
+
+def _plain_toy_forward(cfg, w, toks):
+    T = len(toks)
+    x = plain_embedding(w["model.embed_tokens.weight"], toks)
+    h = plain_rmsnorm(x, w["model.layers.0.input_layernorm.weight"], cfg["rms_norm_eps"])
+    s = torch.zeros(cfg["hidden_size"])
+    y = torch.zeros_like(x)
+    for t in range(T):
+        s = 0.5 * s + h[t]
+        y[t] = w["model.layers.0.toy.weight"].float() @ s
+    x = x + y
+    h = plain_rmsnorm(x, w["model.layers.0.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+    x = x + plain_swiglu(h, w["model.layers.0.mlp.gate_proj.weight"],
+                         w["model.layers.0.mlp.up_proj.weight"], w["model.layers.0.mlp.down_proj.weight"])
+    x = plain_block(x, cfg, w, 1, torch.arange(T))
+    x = plain_rmsnorm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+    return x @ w["lm_head.weight"].float().T
+
+
+def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped():
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    _register_toy()
+    cfg = dict(TINY_A, architectures=["ToyForCausalLM"])
+    w = make_weights(cfg, 4)
+    for k in ("q_proj", "k_proj", "v_proj", "o_proj"):
+        del w[f"model.layers.0.self_attn.{k}.weight"]
+    w["model.layers.0.toy.weight"] = (0.05 * torch.randn(64, 64)).to(torch.bfloat16)
+    lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=2)
+    kinds = sorted(g["need"].kind for g in lm.engine.cache.groups)
+    assert kinds == ["kv", "state"]                             # two groups, storage of their own
+    ta, tb = random_tokens(30, 256, 1), random_tokens(12, 256, 2)
+    ra, rb = _plain_toy_forward(cfg, w, ta), _plain_toy_forward(cfg, w, tb)
+    sa, sb = lm.acquire(2)
+    lg = lm.step([ta[:20], tb[:5]], [sa, sb], [[19], [4]])
+    assert (lg[0].cpu() - ra[19]).abs().max() <= 1e-5 * ra.abs().max()
+    assert (lg[1].cpu() - rb[4]).abs().max() <= 1e-5 * rb.abs().max()
+    for p in range(5, 12):                                      # token by token, state carried
+        lg = lm.step([[ta[15 + p]], [tb[p]]], [sa, sb], [[0], [0]])
+        assert (lg[0].cpu() - ra[15 + p]).abs().max() <= 1e-5 * ra.abs().max()
+        assert (lg[1].cpu() - rb[p]).abs().max() <= 1e-5 * rb.abs().max()
+    lm.release([sa, sb])
+    (sc,) = lm.acquire(1)                                       # a used slot: its state starts at zero
+    lg = lm.step([tb], [sc], [[11]])
+    assert (lg[0].cpu() - rb[11]).abs().max() <= 1e-5 * rb.abs().max()
+
+
+def test_a_layer_named_twice_and_a_layer_reading_anothers_cache():
+    """run_order [0, 1, 0]: layer 0 runs twice with a cache per run; then
+    [0, 1, 1<-reads 1]: the third run reuses the second run's keys and values."""
+    from yalm_b200.cache import Cache
+    from yalm_b200.config import RunEntry, config_from_dict
+    from yalm_b200.engine.step import Engine
+    from yalm_b200.parts import Model, Runtime
+    cfg = TINY_A
+    w = make_weights(cfg, 0)
+    toks = random_tokens(40, 256, 3)
+    spec = config_from_dict(cfg).to_spec()
+    rt = Runtime(torch.float32, DEV)
+    m = Model(dataclasses.replace(spec, run_order=[RunEntry(0), RunEntry(1), RunEntry(0)]), rt)
+    m.bind(dict(w))
+    assert sorted(m.cache_needs()) == [0, 1, 2]
+    eng = Engine(m, 1, 128)
+    s = eng.acquire(1)
+    ref = plain_forward(cfg, w, toks, run_order=[0, 1, 0])
+    lg = eng.step([toks[:25]], s, [[24]])
+    assert (lg[0].cpu() - ref[24]).abs().max() <= 1e-5 * ref.abs().max()
+    for p in range(25, 40):
+        lg = eng.step([[toks[p]]], s, [[0]])
+        assert (lg[0].cpu() - ref[p]).abs().max() <= 1e-5 * ref.abs().max(), p
+    # sharing: the reader's keys/values are the owner's, so its own k/v projections are unused
+    m2 = Model(dataclasses.replace(spec, run_order=[RunEntry(0), RunEntry(1), RunEntry(1, 1)]), rt)
+    m2.bind(dict(w))
+    assert sorted(m2.cache_needs()) == [0, 1]
+    eng2 = Engine(m2, 1, 128)
+    s = eng2.acquire(1)
+    whole = eng2.step([toks], s, [list(range(40))]).cpu()
+    eng2.release(s)
+    s = eng2.acquire(1)
+    cut = eng2.step([toks[:30]], s, [[29]]).cpu()
+    assert (cut[0] - whole[29]).abs().max() <= 1e-5 * whole.abs().max()
+    for p in range(30, 40):
+        lg = eng2.step([[toks[p]]], s, [[0]]).cpu()
+        assert (lg[0] - whole[p]).abs().max() <= 1e-5 * whole.abs().max(), p
+    assert (whole - plain_forward(cfg, w, toks, run_order=[0, 1, 1])).abs().max() > 1e-3

@@ -78,8 +78,8 @@ class LlamaConfig:
     torch_dtype: Optional[str] = None
 
     # ---- reading ---------------------------------------------------------
-    @staticmethod
-    def from_dict(d: Dict[str, Any]) -> "LlamaConfig":
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "LlamaConfig":
         missing = [k for k in _REQUIRED if k not in d]
         if missing:
             raise ConfigError(f"config.json lacks the keys {missing}")
@@ -110,7 +110,7 @@ class LlamaConfig:
         else:
             eos_ids = [int(eos)]
         window = d.get("sliding_window")
-        cfg = LlamaConfig(
+        cfg = cls(
             architecture=str(archs[0]),
             hidden_size=hidden,
             intermediate_size=int(d["intermediate_size"]),
