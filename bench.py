@@ -1,0 +1,296 @@
+#!/usr/bin/env python3
+"""Benchmark of the serving step on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default run: Mistral-7B-v0.2 layer sizes with random weights (bfloat16), a batch
+of 8 sequences with prompt lengths drawn uniformly from [64, 2048] inside a
+context of 4096.  A "step" is one decode step of the batch.  One JSON line:
+
+  value        decoded tokens per second, K steps timed on the device (CUDA events)
+  e2e          the same through LM.generate: every step the host's tokens go down
+               from pinned memory and the sampled tokens come back
+  prefill      one prompt of 2,048 tokens: tokens/s, ms, fraction of the bf16 peak
+  roofline     bytes the decode step must read (weights once + live cache) / time
+  points       decode tokens/s at batch 1 and 64
+  clocks       SM clocks and throttle reasons sampled during the timed region
+  gpu_launches kernels of this library launched inside the timed region
+
+Inputs are far larger than L2 (a decode step streams all weights), so no L2
+flush is needed between timed iterations.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MISTRAL_7B = {
+    "architectures": ["MistralForCausalLM"],
+    "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+    "vocab_size": 32000, "max_position_embeddings": 32768, "rms_norm_eps": 1e-5,
+    "rope_theta": 1000000.0, "sliding_window": None, "tie_word_embeddings": False,
+    "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
+}
+CONTEXT = 4096
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            p = [x.strip() for x in l.split(",")]
+            if len(p) < 6:
+                continue
+            try:
+                mhz.append(float(p[0]))
+                mx = float(p[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, p[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def prompt_lengths(n, lo, hi, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(lo, hi + 1, (n,), generator=g).tolist()
+
+
+def random_prompts(lengths, vocab, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
+
+
+def decode_bytes(lm, contexts):
+    """Bytes one decode step has to read: every weight once (the embedding
+    table only one row per sequence) plus the keys and values of the live
+    sequences."""
+    cfg = lm.config
+    esz = 2
+    D, F, V, L = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
+    H, G, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    per_layer = ((H + 2 * G) * hd * D + D * H * hd + 3 * F * D) * esz + 2 * D * 4
+    weights = L * per_layer + V * D * esz + D * 4 + len(contexts) * D * esz
+    kv = sum(contexts) * L * 2 * G * hd * esz
+    return weights + kv
+
+
+def prefill_flops(cfg, T):
+    D, F, V, L = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
+    H, G, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    linear = 2.0 * T * L * ((H + 2 * G) * hd * D + D * H * hd + 3 * F * D) + 2.0 * V * D
+    attn = L * 2.0 * 2.0 * H * hd * (T * (T + 1) / 2.0)
+    return linear + attn
+
+
+def prefill_batch(lm, prompts, group=8):
+    """Prefills all prompts (in groups, to bound scratch memory) and leaves them
+    ready to decode; returns slots and the first sampled tokens."""
+    import torch
+    slots = lm.acquire(len(prompts))
+    first = []
+    for i in range(0, len(prompts), group):
+        ps, ss = prompts[i:i + group], slots[i:i + group]
+        logits = lm.step(ps, ss, [[len(p) - 1] for p in ps])
+        first += logits.argmax(-1).tolist()
+    torch.cuda.synchronize()
+    return slots, first
+
+
+def time_decode(lm, batch, steps, warmup, seed, sampler=None):
+    """Device-timed decode steps of a batch with prompt lengths U[64, 2048]."""
+    import torch
+    from yalm_b200.csrc import ops
+    lens = prompt_lengths(batch, 64, 2048, seed)
+    prompts = random_prompts(lens, lm.config.vocab_size, seed + 1)
+    slots, first = prefill_batch(lm, prompts)
+    eng = lm.engine
+    eng.set_decode_batch(first, slots, list(range(batch)))
+    for _ in range(max(warmup, 3)):
+        eng.decode_step(batch, 0.0, 0)
+    torch.cuda.synchronize()
+    ctx0 = [eng.cache.host_pos[s] for s in slots]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sampler:
+        sampler.start()
+    l0 = ops.LAUNCHES
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        eng.decode_step(batch, 0.0, 0)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    clocks = sampler.stop() if sampler else None
+    launches = ops.LAUNCHES - l0
+    ctx_mid = [c + steps // 2 for c in ctx0]
+    lm.rt.check_status()
+    lm.release(slots)
+    return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launches,
+            "contexts": ctx_mid, "clocks": clocks, "prompt_lens": lens}
+
+
+def time_e2e(lm, batch, steps, seed):
+    lens = prompt_lengths(batch, 64, 2048, seed)
+    prompts = random_prompts(lens, lm.config.vocab_size, seed + 1)
+    lm.generate(prompts, max_new_tokens=4, temperature=0.0, ignore_eos=True)     # warm-up
+    lm.generate(prompts, max_new_tokens=steps + 1, temperature=0.0, ignore_eos=True)
+    st = lm.last_stats
+    n = st["decode_steps"]
+    return {"value": batch * n / st["decode_seconds"], "unit": "tokens/s",
+            "h2d_bytes_per_step": st["h2d_bytes"] / n, "d2h_bytes_per_step": st["d2h_bytes"] / n,
+            "steps": n}
+
+
+def time_prefill(lm, T, reps, pk):
+    import torch
+    prompt = random_prompts([T], lm.config.vocab_size, 99)[0]
+    times = []
+    for i in range(reps + 2):
+        s = lm.acquire(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        lm.step([prompt], s, [[T - 1]])
+        b.record()
+        torch.cuda.synchronize()
+        lm.release(s)
+        if i >= 2:
+            times.append(a.elapsed_time(b))
+    ms = sorted(times)[len(times) // 2]
+    fl = prefill_flops(lm.config, T)
+    return {"value": T / (ms / 1e3), "tokens": T, "ms": ms,
+            "frac": fl / (ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=MISTRAL_7B["num_hidden_layers"])
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1/64 and prefill")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference has no setup.py or pyproject.toml: pip cannot install it "
+                          "offline, and it ships no sm_100 build of its CUDA kernels"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+
+    import torch
+    from yalm_b200 import LM
+    pk = peaks()
+    cfg = dict(MISTRAL_7B, num_hidden_layers=args.layers)
+    t0 = time.time()
+    lm = LM.from_random(cfg, seed=0, dtype="bfloat16", std=0.02, norm_jitter=0.0,
+                        max_context=CONTEXT, max_batch=max(64, args.batch))
+    torch.cuda.synchronize()
+    print(f"[bench] model ready in {time.time() - t0:.0f} s "
+          f"({lm.model.weight_bytes() / 1e9:.1f} GB weights, {lm.engine.cache.bytes() / 1e9:.1f} GB cache)",
+          file=sys.stderr, flush=True)
+
+    W = max(3, args.warmup)
+    main_run = time_decode(lm, args.batch, args.steps, W, seed=1, sampler=ClockSampler())
+    by = decode_bytes(lm, main_run["contexts"])
+    achieved = by / (main_run["ms_per_step"] / 1e3) / 1e9
+    e2e = time_e2e(lm, args.batch, args.steps, seed=1)
+    out = {
+        "metric": "decode tokens/s at batch 8 (Mistral-7B-v0.2 shapes, context 4096)",
+        "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": W, "ms_per_step": main_run["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {
+            "model": "mistral-7b-v0.2-shapes-random", "layers": args.layers,
+            "layers_of_config": MISTRAL_7B["num_hidden_layers"], "hidden": 4096, "ffn": 14336,
+            "heads": 32, "kv_heads": 8, "head_dim": 128, "vocab": 32000, "global_batch": args.batch,
+            "seq_len": CONTEXT, "prompt_lens": "uniform[64,2048]",
+            "mean_context": sum(main_run["contexts"]) / len(main_run["contexts"]),
+            "parallelism": "single-gpu", "l2": "inputs larger than L2 (weights streamed each step)",
+            "peaks": pk["source"], "weights": "random N(0,0.02), norms 1",
+        },
+        "e2e": e2e,
+        "gpu_launches": main_run["launches"],
+        "clocks": main_run["clocks"],
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": by,
+                     "of": pk["source"]},
+    }
+    if not args.no_points:
+        out["prefill"] = time_prefill(lm, 2048, 5, pk)
+        pts = {}
+        for b in (1, 64):
+            r = time_decode(lm, b, max(16, args.steps // 2), W, seed=10 + b)
+            pts[f"decode_b{b}"] = r["tok_s"]
+            pts[f"decode_b{b}_ms"] = r["ms_per_step"]
+            bb = decode_bytes(lm, r["contexts"])
+            pts[f"decode_b{b}_hbm_frac"] = bb / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"]
+        out["points"] = pts
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

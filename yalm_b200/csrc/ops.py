@@ -80,8 +80,13 @@ def loaded_library_path() -> str:
     return build.library_path()
 
 
-def _check(rc: int, what: str) -> None:
+LAUNCHES = 0     # kernels launched through this module (a graph replay adds its captured count)
+
+
+def _check(rc: int, what: str, kernels: int = 1) -> None:
+    global LAUNCHES
     if rc == 0:
+        LAUNCHES += kernels
         return
     if rc < 0:
         raise KernelError(f"{what}: refused, {_REFUSALS.get(rc, f'code {rc}')}")
@@ -185,7 +190,8 @@ def attention(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor, v_c
     _check(lib().yalm_attention(_p(q), _p(kv_step), _p(k_cache), _p(v_cache), _p(batch.token_seq),
                                 _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos), _p(out),
                                 _p(part_o), _p(part_ml), dtype_code(q.dtype), n, H, G, hd,
-                                capacity, int(window or 0), nsplit, _stream()), "attention")
+                                capacity, int(window or 0), nsplit, _stream()), "attention",
+           kernels=2 if nsplit > 1 else 1)
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

@@ -110,7 +110,9 @@ class LM:
                            "prefill_seconds": backend.prefill_seconds,
                            "prompt_tokens": sum(len(p) for p in prompts),
                            "new_tokens": sum(len(c.tokens) for c in out),
-                           "decode_steps": backend.decode_steps}
+                           "decode_steps": backend.decode_steps,
+                           "decode_seconds": backend.decode_seconds,
+                           "h2d_bytes": backend.h2d_bytes, "d2h_bytes": backend.d2h_bytes}
         return out
 
     def perplexity(self, tokens: Sequence[int]):
@@ -150,7 +152,10 @@ class _DeviceBackend:
         self.max_batch = lm.max_batch
         self.context = lm.context
         self.prefill_seconds = 0.0
+        self.decode_seconds = 0.0
         self.decode_steps = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
 
     def begin(self, prompts, keys):
         eng = self.engine
@@ -173,15 +178,25 @@ class _DeviceBackend:
         return handle, first
 
     def decode(self, handle, active, tokens):
+        """One step: the host's tokens go down (pinned memory), the sampled
+        tokens come back; slots and keys go down only when the batch shrank."""
         eng = self.engine
+        t0 = time.perf_counter()
+        B = len(active)
         if active != handle["active"]:
-            # the batch shrank: put the survivors' tokens, slots and keys on the device
             eng.set_decode_batch(tokens, [handle["slots"][j] for j in active],
                                  [handle["keys"][j] for j in active])
             handle["active"] = list(active)
-        eng.decode_step(len(active), self.temperature, self.seed)
+            self.h2d_bytes += 12 * B
+        else:
+            eng.set_decode_tokens(tokens)
+            self.h2d_bytes += 4 * B
+        eng.decode_step(B, self.temperature, self.seed)
+        out = eng.read_decode_tokens(B)
+        self.d2h_bytes += 4 * B
         self.decode_steps += 1
-        return eng.read_decode_tokens(len(active))
+        self.decode_seconds += time.perf_counter() - t0
+        return out
 
     def end(self, handle):
         self.engine.release(handle["slots"])

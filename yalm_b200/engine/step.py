@@ -114,6 +114,14 @@ class Engine:
         d["row_key"][:B].copy_(h[2 * n:2 * n + B], non_blocking=True)
         d["slots_host"] = list(slots)
 
+    def set_decode_tokens(self, tokens: Sequence[int]) -> None:
+        """Only the next tokens (the decoding sequences are unchanged)."""
+        d = self._decode_buffers()
+        B = len(tokens)
+        h = d["host"]
+        h[0:B] = torch.tensor(list(tokens), dtype=torch.int32)
+        d["tokens"][:B].copy_(h[0:B], non_blocking=True)
+
     def _decode_batch(self, B: int) -> StepBatch:
         d = self._decode_buffers()
         slots = d["slots_host"]
@@ -153,14 +161,19 @@ class Engine:
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
                 self.rt.frozen = True
+                before = ops.LAUNCHES
                 try:
                     with torch.cuda.graph(graph):
                         self._decode_body(B, temperature, seed)
                 finally:
                     self.rt.frozen = False
-                self._graphs[key] = {"graph": graph, "generation": self.rt.buffer_generation}
+                captured = ops.LAUNCHES - before
+                ops.LAUNCHES = before             # capturing launches nothing
+                self._graphs[key] = {"graph": graph, "generation": self.rt.buffer_generation,
+                                     "kernels": captured}
             else:
                 g["graph"].replay()
+                ops.LAUNCHES += g["kernels"]
         for s in d["slots_host"][:B]:
             self.cache.host_pos[s] += 1
 
