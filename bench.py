@@ -228,6 +228,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=MISTRAL_7B["num_hidden_layers"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1/64 and prefill")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (profiling)")
+    ap.add_argument("--no-graphs", action="store_true",
+                    help="launch decode kernels one by one instead of replaying a CUDA graph")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -251,11 +254,13 @@ def main():
           f"({lm.model.weight_bytes() / 1e9:.1f} GB weights, {lm.engine.cache.bytes() / 1e9:.1f} GB cache)",
           file=sys.stderr, flush=True)
 
+    if args.no_graphs:
+        lm.engine.use_graphs = False
     W = max(3, args.warmup)
     main_run = time_decode(lm, args.batch, args.steps, W, seed=1, sampler=ClockSampler())
     by = decode_bytes(lm, main_run["contexts"])
     achieved = by / (main_run["ms_per_step"] / 1e3) / 1e9
-    e2e = time_e2e(lm, args.batch, args.steps, seed=1)
+    e2e = None if args.no_e2e else time_e2e(lm, args.batch, args.steps, seed=1)
     out = {
         "metric": "decode tokens/s at batch 8 (Mistral-7B-v0.2 shapes, context 4096)",
         "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,

@@ -22,11 +22,16 @@ namespace yalm {
 constexpr int ATT_RT = 4;        // query heads per block (of those sharing one kv head)
 constexpr int ATT_WARPS = 4;
 constexpr int ATT_EPL = 8;       // elements of a head that one lane owns
+constexpr int ATT_U = 4;         // keys in flight per lane group
 
 template <typename T> struct Vec8;
 template <> struct Vec8<__nv_bfloat16> {
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
-    const uint4 u = *reinterpret_cast<const uint4*>(p);
+  typedef uint4 Raw;
+  static __device__ __forceinline__ Raw zero() { return make_uint4(0u, 0u, 0u, 0u); }
+  static __device__ __forceinline__ Raw load_raw(const __nv_bfloat16* p) {
+    return *reinterpret_cast<const uint4*>(p);
+  }
+  static __device__ __forceinline__ void unpack(const Raw& u, float* f) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -35,14 +40,29 @@ template <> struct Vec8<__nv_bfloat16> {
       f[2 * i + 1] = v.y;
     }
   }
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    unpack(load_raw(p), f);
+  }
 };
 template <> struct Vec8<float> {
-  static __device__ __forceinline__ void load(const float* p, float* f) {
-    const float4 a = *reinterpret_cast<const float4*>(p);
-    const float4 b = *reinterpret_cast<const float4*>(p + 4);
-    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
-    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  struct Raw { float4 a, b; };
+  static __device__ __forceinline__ Raw zero() {
+    Raw r;
+    r.a = make_float4(0.f, 0.f, 0.f, 0.f);
+    r.b = r.a;
+    return r;
   }
+  static __device__ __forceinline__ Raw load_raw(const float* p) {
+    Raw r;
+    r.a = *reinterpret_cast<const float4*>(p);
+    r.b = *reinterpret_cast<const float4*>(p + 4);
+    return r;
+  }
+  static __device__ __forceinline__ void unpack(const Raw& r, float* f) {
+    f[0] = r.a.x; f[1] = r.a.y; f[2] = r.a.z; f[3] = r.a.w;
+    f[4] = r.b.x; f[5] = r.b.y; f[6] = r.b.z; f[7] = r.b.w;
+  }
+  static __device__ __forceinline__ void load(const float* p, float* f) { unpack(load_raw(p), f); }
 };
 
 // LPK lanes share one key (LPK*8 >= hd); a warp handles 32/LPK keys at a time.
@@ -108,46 +128,72 @@ attn_token_kernel(const T* __restrict__ q, const T* __restrict__ kv_step,
   const T* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
   const T* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
 
-  for (int base = s_lo + warp * KPW; base < s_hi; base += GROUPS) {
-    const int key = base + kg;
-    const bool valid = key < s_hi;
-    float kf[ATT_EPL], vf[ATT_EPL];
-    if (valid && lane_on) {
-      const T *kp, *vp;
-      if (key >= past) {
-        kp = kv_step + (size_t)(qs + key - past) * step_row + (size_t)g * hd + e0;
-        vp = kp + (size_t)G * hd;
+  // ATT_U keys per lane group are loaded before any is used: the loop is a
+  // stream of independent 16-byte loads, which is what hides HBM latency
+  for (int base = s_lo + warp * KPW; base < s_hi; base += GROUPS * ATT_U) {
+    typename Vec8<T>::Raw kraw[ATT_U], vraw[ATT_U];
+    bool valid[ATT_U];
+#pragma unroll
+    for (int u = 0; u < ATT_U; ++u) {
+      const int key = base + u * GROUPS + kg;
+      valid[u] = key < s_hi;
+      if (valid[u] && lane_on) {
+        const T *kp, *vp;
+        if (key >= past) {
+          kp = kv_step + (size_t)(qs + key - past) * step_row + (size_t)g * hd + e0;
+          vp = kp + (size_t)G * hd;
+        } else {
+          const size_t row = (size_t)(key % capacity) * hd + e0;
+          kp = kc + row;
+          vp = vc + row;
+        }
+        kraw[u] = Vec8<T>::load_raw(kp);
+        vraw[u] = Vec8<T>::load_raw(vp);
       } else {
-        const size_t row = (size_t)(key % capacity) * hd + e0;
-        kp = kc + row;
-        vp = vc + row;
+        kraw[u] = Vec8<T>::zero();
+        vraw[u] = Vec8<T>::zero();
       }
-      Vec8<T>::load(kp, kf);
-      Vec8<T>::load(vp, vf);
-    } else {
-#pragma unroll
-      for (int e = 0; e < ATT_EPL; ++e) { kf[e] = 0.f; vf[e] = 0.f; }
     }
-    float s[ATT_RT];
+    float s[ATT_U][ATT_RT];
 #pragma unroll
-    for (int r = 0; r < ATT_RT; ++r) {
-      float d = 0.f;
-#pragma unroll
-      for (int e = 0; e < ATT_EPL; ++e) d = fmaf(qreg[r][e], kf[e], d);
-#pragma unroll
-      for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-      s[r] = d * scale;
-    }
-    if (valid) {
+    for (int u = 0; u < ATT_U; ++u) {
+      float kf[ATT_EPL];
+      Vec8<T>::unpack(kraw[u], kf);
 #pragma unroll
       for (int r = 0; r < ATT_RT; ++r) {
-        const float mn = fmaxf(m[r], s[r]);
-        const float corr = expf(m[r] - mn);     // exp(-inf) = 0 on the first key
-        const float p = expf(s[r] - mn);
-        l[r] = l[r] * corr + p;
+        float d = 0.f;
 #pragma unroll
-        for (int e = 0; e < ATT_EPL; ++e) o[r][e] = fmaf(p, vf[e], o[r][e] * corr);
-        m[r] = mn;
+        for (int e = 0; e < ATT_EPL; ++e) d = fmaf(qreg[r][e], kf[e], d);
+#pragma unroll
+        for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+        s[u][r] = valid[u] ? d * scale : -INFINITY;
+      }
+    }
+    float mn[ATT_RT], corr[ATT_RT];
+#pragma unroll
+    for (int r = 0; r < ATT_RT; ++r) {
+      float x = m[r];
+#pragma unroll
+      for (int u = 0; u < ATT_U; ++u) x = fmaxf(x, s[u][r]);
+      mn[r] = x;
+      corr[r] = x > -INFINITY ? expf(m[r] - x) : 1.f;     // exp(-inf) = 0 on the first key
+      l[r] *= corr[r];
+#pragma unroll
+      for (int e = 0; e < ATT_EPL; ++e) o[r][e] *= corr[r];
+      m[r] = x;
+    }
+#pragma unroll
+    for (int u = 0; u < ATT_U; ++u) {
+      if (valid[u]) {
+        float vf[ATT_EPL];
+        Vec8<T>::unpack(vraw[u], vf);
+#pragma unroll
+        for (int r = 0; r < ATT_RT; ++r) {
+          const float p = expf(s[u][r] - mn[r]);
+          l[r] += p;
+#pragma unroll
+          for (int e = 0; e < ATT_EPL; ++e) o[r][e] = fmaf(p, vf[e], o[r][e]);
+        }
       }
     }
   }

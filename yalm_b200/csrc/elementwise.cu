@@ -61,6 +61,70 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
   }
 }
 
+// The same with the row held in registers as VPT float4 vectors per thread:
+// every load of a pass is in flight at once, which is what a decode step's
+// handful of rows needs (the kernel is a chain of memory round trips).
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<unsigned*>(&lo);
+  u.y = *reinterpret_cast<unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TO, int VPT>
+__global__ void rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partials,
+                                   int n_partials, long long partial_stride,
+                                   const int* __restrict__ rows, const float* __restrict__ weight,
+                                   TO* __restrict__ out, int dim, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  const int nvec = dim >> 2;
+  float4* xr = reinterpret_cast<float4*>(x + (size_t)src * dim);
+  float4 v[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    v[k] = c < nvec ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int s = 0; s < n_partials; ++s) {
+    const float4* pr = reinterpret_cast<const float4*>(partials + (size_t)s * partial_stride +
+                                                       (size_t)src * dim);
+    float4 p[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int c = threadIdx.x + k * blockDim.x;
+      p[k] = c < nvec ? pr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      v[k].x += p[k].x; v[k].y += p[k].y; v[k].z += p[k].z; v[k].w += p[k].w;
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (n_partials > 0 && rows == nullptr && c < nvec) xr[c] = v[k];
+    ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+  const float4* wr = reinterpret_cast<const float4*>(weight);
+  TO* o = out + (size_t)r * dim;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < nvec) {
+      const float4 w = wr[c];
+      store4(o + 4 * c, make_float4(v[k].x * scale * w.x, v[k].y * scale * w.y,
+                                    v[k].z * scale * w.z, v[k].w * scale * w.w));
+    }
+  }
+}
+
 // ---------------------------------------------------------------- silu * up
 // gu: [rows, 2F] (gate | up) in 32-bit, possibly as n_partials split-K slices.
 template <typename TO>
@@ -81,12 +145,13 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, int n_partials,
 }
 
 // ------------------------------------------------- rotary + cache write
-// One block per token.  qkv: [N, (H+2G)*hd] in 32-bit (n_partials slices are
-// summed).  Pair (i, i+hd/2) of every q and k head is rotated by the angle
-// pos * inv_freq[i], all in 32-bit.  Rotated q goes to q_out [N, H*hd]; rotated
-// k and plain v go to kv_step [N, 2, G, hd] (this step's keys and values in
-// token order) and, for the positions that the ring keeps, to the cache
-// [slots, G, capacity, hd] at row pos % capacity.
+// One block per (token, group of heads); one thread per (head, rotary pair).
+// qkv: [N, (H+2G)*hd] in 32-bit (n_partials slices are summed).  Pair
+// (i, i+hd/2) of every q and k head is rotated by the angle pos * inv_freq[i],
+// all in 32-bit.  Rotated q goes to q_out [N, H*hd]; rotated k and plain v go
+// to kv_step [N, 2, G, hd] (this step's keys and values in token order) and,
+// for the positions that the ring keeps, to the cache [slots, G, capacity, hd]
+// at row pos % capacity.
 template <typename T>
 __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
                                   long long partial_stride, const float* __restrict__ inv_freq,
@@ -94,58 +159,49 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
                                   const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
                                   T* __restrict__ q_out, T* __restrict__ kv_step,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G,
-                                  int hd, int capacity, int write_cache) {
+                                  int hd, int capacity, int write_cache, int heads_per_block) {
   const int t = blockIdx.x;
+  const int half = hd >> 1;
+  const int i = threadIdx.x % half;
+  const int head = blockIdx.y * heads_per_block + threadIdx.x / half;
+  if (head >= H + 2 * G) return;
   const int b = token_seq[t];
   const int slot = seq_slot[b];
   const int past = slot_pos[slot];
-  const int pos = past + (t - q_start[b]);
-  const int end = past + (q_start[b + 1] - q_start[b]);   // positions after this step
+  const int qs = q_start[b];
+  const int pos = past + (t - qs);
+  const int end = past + (q_start[b + 1] - qs);            // positions after this step
   const bool keep = write_cache && pos >= end - capacity;
-  const int half = hd >> 1;
-  const int i = threadIdx.x % half;
-  const int group = threadIdx.x / half;
-  const int ngroups = blockDim.x / half;
-  if (group >= ngroups) return;
-  const float ang = (float)pos * inv_freq[i];
-  const float c = cosf(ang), s = sinf(ang);
   const int row_elems = (H + 2 * G) * hd;
-  const float* src = qkv + (size_t)t * row_elems;
-  const int ring = pos % capacity;
-  for (int head = group; head < H + 2 * G; head += ngroups) {
-    float a = 0.f, bb = 0.f;
-    for (int p = 0; p < n_partials; ++p) {
-      const float* sp = src + (size_t)p * partial_stride + head * hd;
-      a += sp[i];
-      bb += sp[i + half];
-    }
-    if (head < H) {
-      T* o = q_out + (size_t)t * H * hd + head * hd;
-      o[i] = from_float<T>(a * c - bb * s);
-      o[i + half] = from_float<T>(a * s + bb * c);
-    } else if (head < H + G) {
-      const int g = head - H;
-      const T r0 = from_float<T>(a * c - bb * s), r1 = from_float<T>(a * s + bb * c);
-      T* o = kv_step + ((size_t)t * 2 * G + g) * hd;
-      o[i] = r0;
-      o[i + half] = r1;
-      if (keep) {
-        T* kc = k_cache + (((size_t)slot * G + g) * capacity + ring) * hd;
-        kc[i] = r0;
-        kc[i + half] = r1;
-      }
-    } else {
-      const int g = head - H - G;
-      const T r0 = from_float<T>(a), r1 = from_float<T>(bb);
-      T* o = kv_step + ((size_t)t * 2 * G + G + g) * hd;
-      o[i] = r0;
-      o[i + half] = r1;
-      if (keep) {
-        T* vc = v_cache + (((size_t)slot * G + g) * capacity + ring) * hd;
-        vc[i] = r0;
-        vc[i + half] = r1;
-      }
-    }
+  const float* sp = qkv + (size_t)t * row_elems + head * hd + i;
+  float a = 0.f, bb = 0.f;
+  for (int p = 0; p < n_partials; ++p) {
+    a += sp[(size_t)p * partial_stride];
+    bb += sp[(size_t)p * partial_stride + half];
+  }
+  if (head < H + G) {
+    const float ang = (float)pos * inv_freq[i];
+    const float c = cosf(ang), s = sinf(ang);
+    const float r0 = a * c - bb * s, r1 = a * s + bb * c;
+    a = r0;
+    bb = r1;
+  }
+  const T o0 = from_float<T>(a), o1 = from_float<T>(bb);
+  if (head < H) {
+    T* o = q_out + ((size_t)t * H + head) * hd;
+    o[i] = o0;
+    o[i + half] = o1;
+    return;
+  }
+  const bool is_v = head >= H + G;
+  const int g = head - H - (is_v ? G : 0);
+  T* o = kv_step + ((size_t)t * 2 * G + (is_v ? G : 0) + g) * hd;
+  o[i] = o0;
+  o[i + half] = o1;
+  if (keep) {
+    T* c = (is_v ? v_cache : k_cache) + (((size_t)slot * G + g) * capacity + pos % capacity) * hd;
+    c[i] = o0;
+    c[i + half] = o1;
   }
 }
 
@@ -173,18 +229,44 @@ extern "C" int yalm_embed(const int* tokens, const void* table, int table_dtype,
   return 0;
 }
 
+template <typename TO>
+static void launch_rmsnorm(float* x, const float* partials, int n_partials,
+                           long long partial_stride, const int* rows, const float* weight, TO* out,
+                           int n_rows, int dim, float eps, cudaStream_t stream) {
+  const bool vec = dim % 4 == 0 && partial_stride % 4 == 0 &&
+                   ((((uintptr_t)x) | ((uintptr_t)partials) | ((uintptr_t)weight) |
+                     ((uintptr_t)out)) & 15) == 0;
+  const int nvec = dim / 4;
+  if (vec && nvec <= 8 * 512) {
+    const int threads = nvec <= 128 ? 128 : (nvec <= 1024 ? 256 : 512);
+    const int vpt = (nvec + threads - 1) / threads;
+#define YALM_RMS(V)                                                                          \
+  rmsnorm_vec_kernel<TO, V><<<n_rows, threads, 0, stream>>>(x, partials, n_partials,          \
+                                                           partial_stride, rows, weight, out, \
+                                                           dim, eps)
+    if (vpt <= 1) YALM_RMS(1);
+    else if (vpt <= 2) YALM_RMS(2);
+    else if (vpt <= 4) YALM_RMS(4);
+    else YALM_RMS(8);
+#undef YALM_RMS
+    return;
+  }
+  const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+  rmsnorm_kernel<TO><<<n_rows, threads, 0, stream>>>(x, partials, n_partials, partial_stride, rows,
+                                                     weight, out, dim, eps);
+}
+
 extern "C" int yalm_rmsnorm(float* x, const float* partials, int n_partials,
                             long long partial_stride, const int* rows, const float* weight,
                             void* out, int out_dtype, int n_rows, int dim, float eps,
                             cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
   if (out_dtype == DT_F32)
-    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, partials, n_partials, partial_stride,
-                                                          rows, weight, (float*)out, dim, eps);
+    launch_rmsnorm<float>(x, partials, n_partials, partial_stride, rows, weight, (float*)out,
+                          n_rows, dim, eps, stream);
   else
-    rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
-        x, partials, n_partials, partial_stride, rows, weight, (__nv_bfloat16*)out, dim, eps);
+    launch_rmsnorm<__nv_bfloat16>(x, partials, n_partials, partial_stride, rows, weight,
+                                  (__nv_bfloat16*)out, n_rows, dim, eps, stream);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -213,20 +295,24 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
                                int n_tokens, int H, int G, int hd, int capacity, int write_cache,
                                cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (hd % 2 != 0 || hd / 2 > 256) return -2;
+  if (hd % 2 != 0 || hd / 2 > 512 || hd <= 0) return -2;
   const int half = hd / 2;
-  int threads = 128;
-  if (threads < half) threads = 256;
+  int hpb = 1024 / half;                       // heads per block
+  if (hpb > 8) hpb = 8;
+  if (hpb > H + 2 * G) hpb = H + 2 * G;
+  const dim3 grid(n_tokens, (H + 2 * G + hpb - 1) / hpb);
+  const int threads = half * hpb;
+  if (grid.y > 65535) return -4;
   if (dtype == DT_F32)
-    rope_store_kernel<float><<<n_tokens, threads, 0, stream>>>(
+    rope_store_kernel<float><<<grid, threads, 0, stream>>>(
         qkv, n_partials, partial_stride, inv_freq, token_seq, q_start, seq_slot, slot_pos,
         (float*)q_out, (float*)kv_step, (float*)k_cache, (float*)v_cache, H, G, hd, capacity,
-        write_cache);
+        write_cache, hpb);
   else
-    rope_store_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+    rope_store_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         qkv, n_partials, partial_stride, inv_freq, token_seq, q_start, seq_slot, slot_pos,
         (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_step, (__nv_bfloat16*)k_cache,
-        (__nv_bfloat16*)v_cache, H, G, hd, capacity, write_cache);
+        (__nv_bfloat16*)v_cache, H, G, hd, capacity, write_cache, hpb);
   YALM_LAUNCH_CHECK();
   return 0;
 }

@@ -244,15 +244,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + expf(-v[j])) * u[j];
         }
-        if (f < n_out) {
+        if (f < n_out && mode == 1) {
+          // residual add: all 16 loads are issued before the first store
+          float old[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int tok = tok0 + c0 + j;
+            old[j] = tok < M ? outf[(size_t)tok * n_out + f] : 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int tok = tok0 + c0 + j;
+            if (tok < M) outf[(size_t)tok * n_out + f] = old[j] + v[j];
+          }
+        } else if (f < n_out) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int tok = tok0 + c0 + j;
             if (tok < M) {
               if (mode == 3) {
                 outf[((size_t)blockIdx.z * M + tok) * n_out + f] = v[j];
-              } else if (mode == 1) {
-                outf[(size_t)tok * n_out + f] += v[j];
               } else if (out_dtype == DT_F32) {
                 outf[(size_t)tok * n_out + f] = v[j];
               } else {

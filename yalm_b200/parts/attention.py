@@ -61,8 +61,8 @@ class GQAAttention:
             return 1
         R = self.H // self.G
         blocks = batch.n_tokens * self.G * -(-R // 4)
-        want = -(-2 * self.rt.sm_count // blocks)
-        return max(1, min(want, 32, capacity // 256))
+        want = -(-4 * self.rt.sm_count // blocks)
+        return max(1, min(want, 32, capacity // 128))
 
     def forward(self, h, batch, stream, view, shared: bool = False) -> None:
         rt, H, G, hd = self.rt, self.H, self.G, self.hd
