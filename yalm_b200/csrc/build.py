@@ -24,7 +24,7 @@ from typing import List, Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ["elementwise.cu", "attention.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "sampling.cu"]
-HEADERS = ["api.h", "common.cuh"]
+HEADERS = ["api.h", "common.cuh", "no_alloc.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 
@@ -114,6 +114,13 @@ def build(verbose_ptxas: bool = False, force: bool = False) -> str:
     if r.returncode != 0:
         raise BuildError(f"linking failed:\n{' '.join(cmd)}\n{r.stdout}")
     os.replace(tmp, path)
+    for name in os.listdir(out_dir):           # older builds of other source states
+        if name.startswith("libyalm_b200_") and name.endswith(".so") and \
+                os.path.join(out_dir, name) != path:
+            try:
+                os.remove(os.path.join(out_dir, name))
+            except OSError:
+                pass
     for o in objs:
         try:
             os.remove(o)
