@@ -16,6 +16,7 @@
 // still sees all of its own keys during prefill.
 #include "api.h"
 #include "common.cuh"
+#include "no_alloc.h"
 
 namespace yalm {
 
@@ -308,4 +309,70 @@ extern "C" int yalm_attention(const void* q, const void* kv_step, const void* k_
   return launch_attention<__nv_bfloat16>(q, kv_step, k_cache, v_cache, token_seq, q_start,
                                          seq_slot, slot_pos, out, part_o, part_ml, n_tokens, H, G,
                                          hd, capacity, window, nsplit, stream);
+}
+
+// ---------------------------------------------------------------------------
+// yalm_attention_no_alloc: the same attention for callers that cannot allocate.
+// (Declared in no_alloc.h; the reference has nothing like it.)
+//
+// Split-KV attention needs scratch for the partial results of each key slice.
+// yalm_attention takes that scratch from its caller.  Some callers have no way
+// to provide it: a host program that gave all device memory to an arena of its
+// own at start-up, or code running inside another runtime's callback where
+// cudaMalloc is off limits because it synchronises the whole device.  For them
+// the scratch lives in the array below, which is part of the loaded library
+// image: every GPU that loads the library holds these 8 MiB until the process
+// exits, whether or not this entry point is ever called.
+//
+// Rules of use:
+//  * n_tokens * H * nsplit * (hd + 2) floats must fit into the array; a larger
+//    request is refused with -7 and nothing is launched.
+//  * The first call on a device looks up the array's device address
+//    (cudaGetSymbolAddress, with that device current) and remembers it; make
+//    that first call outside any stream capture.
+//  * All calls share the one array, and it keeps whatever the last call left.
+//    Nothing in it has to start at zero: every slice that is read was written
+//    by the same call (an empty slice writes max = -inf, sum = 0).  Two calls
+//    that overlap on the GPU (different streams) race on it; keep calls on one
+//    stream or order them with events.
+//  * No cudaMalloc, cudaFree or other allocating routine is called.
+namespace yalm {
+constexpr size_t NO_ALLOC_SCRATCH_FLOATS = (size_t)2 * 1024 * 1024;      // 8 MiB
+static __device__ __align__(256) float g_attention_scratch[NO_ALLOC_SCRATCH_FLOATS];
+constexpr int NO_ALLOC_MAX_DEVICES = 64;
+static float* g_attention_scratch_addr[NO_ALLOC_MAX_DEVICES];            // per device, host side
+}  // namespace yalm
+
+extern "C" long long yalm_attention_no_alloc_capacity(void) {
+  return (long long)yalm::NO_ALLOC_SCRATCH_FLOATS;
+}
+
+extern "C" int yalm_attention_no_alloc(const void* q, const void* kv_step, const void* k_cache,
+                                       const void* v_cache, const int* token_seq,
+                                       const int* q_start, const int* seq_slot,
+                                       const int* slot_pos, void* out, int dtype, int n_tokens,
+                                       int H, int G, int hd, int capacity, int window, int nsplit,
+                                       cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (nsplit < 1 || H <= 0 || hd <= 0) return -4;
+  const size_t need = (size_t)n_tokens * H * nsplit * ((size_t)hd + 2);
+  if (nsplit > 1 && need > yalm::NO_ALLOC_SCRATCH_FLOATS) return -7;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= yalm::NO_ALLOC_MAX_DEVICES) return -8;
+  if (yalm::g_attention_scratch_addr[dev] == nullptr) {
+    // the array's name is a host-side handle here, not a device address
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, yalm::g_attention_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (p == nullptr) return -9;
+    yalm::g_attention_scratch_addr[dev] = p;
+  }
+  float* base = yalm::g_attention_scratch_addr[dev];
+  float* part_o = base;                                              // [tokens, H, nsplit, hd]
+  float* part_ml = base + (size_t)n_tokens * H * nsplit * hd;        // [tokens, H, nsplit, 2]
+  return yalm_attention(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot, slot_pos, out,
+                        part_o, part_ml, dtype, n_tokens, H, G, hd, capacity, window, nsplit,
+                        stream);
 }
