@@ -239,3 +239,32 @@ def test_step_refuses_bad_requests():
     with pytest.raises(IndexError):
         lm.step([[1, 2]], [s], [[2]])
     lm.step([[1, 2]], [s], [[1]])                               # still usable afterwards
+
+
+def test_command_line_completion_and_perplexity(tmp_path):
+    """python -m yalm_b200 with token-id prompts on a random model folder that
+    the random-weights mode wrote."""
+    import json
+    import subprocess
+    import sys
+    from trace_tools import ROOT
+    cfg, _ = CONFIGS["tiny_a"]
+    (tmp_path / "cfg.json").write_text(json.dumps(cfg))
+    model = str(tmp_path / "model")
+    base = [sys.executable, "-m", "yalm_b200", model, "--dtype", "float32"]
+    r = subprocess.run(base + ["--random-weights", str(tmp_path / "cfg.json"), "--seed", "3",
+                               "--tokens", "5,6,7;9,10", "-n", "5", "-t", "0"],
+                       capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert os.path.isfile(os.path.join(model, "model.safetensors"))
+    lines = [l for l in r.stdout.splitlines() if l.startswith("tokens:")]
+    assert len(lines) == 2 and "throughput" in r.stdout
+    from yalm_b200.weights import load_checkpoint
+    w = load_checkpoint(model)
+    want = plain_generate_greedy(cfg, w, [5, 6, 7], 5, stop=[2])
+    assert [int(t) for t in lines[0].split("(")[0].split()[1:]] == want
+    r = subprocess.run(base + ["-m", "perp", "--tokens", ",".join(map(str, range(3, 40)))],
+                       capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    ppl = float(r.stdout.split("perplexity:")[1].split()[0])
+    assert abs(ppl - plain_perplexity(cfg, w, list(range(3, 40)))[0]) / ppl < 1e-3
