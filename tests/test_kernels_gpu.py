@@ -281,3 +281,56 @@ def test_sampling_greedy_and_temperature(ops):
     assert out[3].item() == one
     us = [ops.uniform01(9, 1, i) for i in range(2000)]
     assert 0.45 < sum(us) / len(us) < 0.55 and len(set(us)) > 1990
+
+
+@pytest.mark.parametrize("dt, tol", [(torch.float32, 3e-6), (torch.bfloat16, 1.6e-2)])
+@pytest.mark.parametrize("H, G, hd, cap, window, chunk", [
+    (8, 2, 128, 700, None, 64),     # chunks of 64 keys, the last one ragged
+    (6, 3, 48, 40, 40, 32),         # a ring that wraps inside a chunk
+    (5, 5, 16, 300, 100, 128),      # window inside a larger ring, one chunk
+    (16, 2, 64, 512, None, 32),     # 8 query heads per kv head: two head groups
+])
+def test_decode_attention_from_staged_chunks(ops, dt, tol, H, G, hd, cap, window, chunk):
+    """attention_decode (bulk copies into shared memory, chunks merged by the
+    last block) against the plain attention over each sequence's visible keys,
+    twice in a row (the counters must come back to zero)."""
+    g = torch.Generator(device=DEV).manual_seed(hd + cap)
+    lens = [1, 37, cap - 1, cap, 3 * cap + 5] if window else [1, 37, 200, cap - 1, cap]
+    B, n_slots = len(lens), len(lens) + 3
+    slots = [5, 0, 3, 7, 2][:B]
+    kc = torch.randn(n_slots, G, cap, hd, device=DEV, generator=g).to(dt)
+    vc = torch.randn(n_slots, G, cap, hd, device=DEV, generator=g).to(dt)
+    q = torch.randn(B, H * hd, device=DEV, generator=g).to(dt)
+    slot_pos = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+    for s, n in zip(slots, lens):
+        slot_pos[s] = n - 1                                     # the query is the last position
+    seq_slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    bound = max(lens)
+    visible = min(bound, window) if window else bound
+    mc = -(-visible // chunk)
+    part_o = torch.empty(B * H * mc * hd, device=DEV)
+    part_ml = torch.empty(B * H * mc * 2, device=DEV)
+    counters = torch.zeros(B * G * -(-(H // G) // 4), dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for rep in range(2):
+        out = torch.zeros(B, H * hd, device=DEV, dtype=dt)
+        ops.attention_decode(q, kc, vc, seq_slot, slot_pos, out, part_o, part_ml, counters, status,
+                             H, G, hd, cap, window, chunk, bound)
+        torch.cuda.synchronize()
+        assert status.item() == 0 and int(counters.abs().sum()) == 0
+        for b, (s, n) in enumerate(zip(slots, lens)):
+            lo = 0 if window is None else max(0, n - window)
+            rows = torch.tensor([p % cap for p in range(lo, n)])
+            k = kc[s][:, rows].permute(1, 0, 2).float().cpu()   # [keys, G, hd]
+            v = vc[s][:, rows].permute(1, 0, 2).float().cpu()
+            qq = torch.zeros(len(rows), H, hd)
+            qq[-1] = q[b].float().cpu().view(H, hd)
+            ref = plain_attention(qq, k, v, None)[-1]
+            got = out[b].float().cpu().view(H, hd)
+            assert (got - ref).abs().max().item() <= tol, (rep, b, n)
+    # a bound that is too small is reported, not silently wrong
+    ops.attention_decode(q, kc, vc, seq_slot, slot_pos, out, part_o, part_ml, counters, status,
+                         H, G, hd, cap, window, chunk, 1)
+    torch.cuda.synchronize()
+    need = max(-(-(min(n, window) if window else n) // chunk) for n in lens)
+    assert status.item() == (ops.ERR_CONTEXT_RANGE if need > 1 else 0)

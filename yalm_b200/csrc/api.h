@@ -34,6 +34,12 @@ int yalm_attention(const void* q, const void* kv_step, const void* k_cache, cons
                    int n_tokens, int H, int G, int hd, int capacity, int window, int nsplit,
                    cudaStream_t stream);
 
+int yalm_attention_decode(const void* q, const void* k_cache, const void* v_cache,
+                          const int* seq_slot, const int* slot_pos, void* out, float* part_o,
+                          float* part_ml, int* counters, int* status, int dtype, int n_seqs, int H,
+                          int G, int hd, int capacity, int window, int chunk, int max_context,
+                          cudaStream_t stream);
+
 int yalm_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* out,
                    int out_dtype, int M, int N, int K, int accumulate, cudaStream_t stream);
 
@@ -53,6 +59,16 @@ int yalm_gemm_tc(const void* A, const void* W, void* out, int out_dtype, int M, 
                  int mode, int splits, int* status, cudaStream_t stream);
 // 0 if the driver's tensor-map encoder was found (host-side set-up of yalm_gemm_tc).
 int yalm_gemm_tc_available(void);
+
+// Persistent stream-K variant of the tcgen05 product with the epilogue fused for
+// every token count (mode 0 store, 1 add into float32 out, 2 silu(gate)*up).
+// scratch: float32 workspace of at least yalm_gemm_sk_scratch_floats(M, mode == 2)
+// floats; counters: one int per output tile, zero before the first launch (the
+// kernel leaves them zero).
+long long yalm_gemm_sk_scratch_floats(int M, int dual);
+int yalm_gemm_sk(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
+                 int mode, float* scratch, long long scratch_floats, int* counters,
+                 int n_counters, int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -75,6 +75,8 @@ attn_token_kernel(const T* __restrict__ q, const T* __restrict__ kv_step,
                   const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
                   T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                   int H, int G, int hd, int capacity, int window, int nsplit, float scale, int t0) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int KPW = 32 / LPK;                 // keys per warp per iteration
   constexpr int GROUPS = ATT_WARPS * KPW;       // key groups per block
   __shared__ float m_s[GROUPS][ATT_RT];
@@ -237,6 +239,8 @@ template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o,
                                   const float* __restrict__ part_ml, T* __restrict__ out, int hd,
                                   int nsplit) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t th = blockIdx.x;
   const float* ml = part_ml + th * nsplit * 2;
   float M = -INFINITY;
@@ -249,6 +253,266 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o,
     for (int s = 0; s < nsplit; ++s)
       if (ml[2 * s] > -INFINITY) O += part_o[(th * nsplit + s) * hd + d] * expf(ml[2 * s] - M);
     out[th * hd + d] = from_float<T>(O / L);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Decode attention: one query token per sequence, every key and value in the
+// cache (the step's own row was written by the rotary kernel just before).
+// A block takes one chunk of `chunk` consecutive positions of one (sequence,
+// kv head, group of query heads).  It brings the chunk's K and V rows into
+// shared memory with bulk asynchronous copies (one thread issues at most four:
+// K and V, twice if the chunk wraps around the ring), so the memory system sees
+// few large requests instead of thousands of 16-byte loads, and then computes
+// from shared memory exactly as attn_token_kernel does from global memory.
+// Chunks of one query are merged by the block that finishes last (a counter per
+// query and head group; partial results in scratch, added in chunk order), so
+// there is no second kernel.  Blocks whose chunk lies beyond the sequence's
+// length leave at once.
+template <typename T, int LPK>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
+                   const T* __restrict__ v_cache, const int* __restrict__ seq_slot,
+                   const int* __restrict__ slot_pos, T* __restrict__ out,
+                   float* __restrict__ part_o, float* __restrict__ part_ml,
+                   int* __restrict__ counters, int* __restrict__ status, int H, int G, int hd,
+                   int capacity, int window, int chunk, int max_chunks, float scale) {
+  constexpr int KPW = 32 / LPK;
+  constexpr int GROUPS = ATT_WARPS * KPW;
+  extern __shared__ __align__(128) uint8_t att_smem[];
+  __shared__ float m_s[GROUPS][ATT_RT];
+  __shared__ float l_s[GROUPS][ATT_RT];
+  __shared__ float o_s[ATT_RT * GROUPS * LPK * ATT_EPL];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  __shared__ int last_flag;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  const int R = H / G;
+  const int nchunks = (R + ATT_RT - 1) / ATT_RT;
+  const int g = blockIdx.y / nchunks;
+  const int hchunk = blockIdx.y % nchunks;
+  const int h0 = g * R + hchunk * ATT_RT;
+  const int nh = min(ATT_RT, R - hchunk * ATT_RT);
+  const int t = blockIdx.z;
+  const int c = blockIdx.x;
+
+  const int slot = seq_slot[t];
+  const int pos = slot_pos[slot];                           // the query's position
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int nkeys = pos - lo + 1;
+  const int n_active = (nkeys + chunk - 1) / chunk;
+  if (n_active > max_chunks && c == 0 && threadIdx.x == 0) atomicOr(status, ERR_CONTEXT_RANGE);
+  if (c >= n_active) return;
+  const int k_lo = lo + c * chunk;
+  const int n = min(chunk, pos + 1 - k_lo);
+
+  T* ks = reinterpret_cast<T*>(att_smem);
+  T* vs = ks + (size_t)chunk * hd;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    const size_t row_bytes = (size_t)hd * sizeof(T);
+    const T* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
+    const T* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
+    const int r0 = k_lo % capacity;
+    const int n1 = min(n, capacity - r0);                   // rows before the ring wraps
+    mbar_expect_tx(smem_u32(&bar), (uint32_t)(2 * n * row_bytes));
+    bulk_load(smem_u32(ks), kc + (size_t)r0 * hd, (uint32_t)(n1 * row_bytes), smem_u32(&bar));
+    bulk_load(smem_u32(vs), vc + (size_t)r0 * hd, (uint32_t)(n1 * row_bytes), smem_u32(&bar));
+    if (n1 < n) {
+      bulk_load(smem_u32(ks + (size_t)n1 * hd), kc, (uint32_t)((n - n1) * row_bytes),
+                smem_u32(&bar));
+      bulk_load(smem_u32(vs + (size_t)n1 * hd), vc, (uint32_t)((n - n1) * row_bytes),
+                smem_u32(&bar));
+    }
+  }
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane % LPK, kg = lane / LPK;
+  const int e0 = sub * ATT_EPL;
+  const bool lane_on = e0 < hd;
+  float qreg[ATT_RT][ATT_EPL];
+#pragma unroll
+  for (int r = 0; r < ATT_RT; ++r) {
+    if (r < nh && lane_on) {
+      Vec8<T>::load(q + ((size_t)t * H + h0 + r) * hd + e0, qreg[r]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < ATT_EPL; ++e) qreg[r][e] = 0.f;
+    }
+  }
+  float m[ATT_RT], l[ATT_RT], o[ATT_RT][ATT_EPL];
+#pragma unroll
+  for (int r = 0; r < ATT_RT; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int e = 0; e < ATT_EPL; ++e) o[r][e] = 0.f;
+  }
+  __syncthreads();                                           // the barrier is initialised
+  const bool arrived = mbar_wait(smem_u32(&bar), 0, &abort_flag);
+  if (!arrived) {
+    // never expected: give the copies time to land, report, and leave without a result
+    if (threadIdx.x == 0) atomicOr(status, ERR_WAIT_TIMEOUT);
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+
+  if (arrived) {
+    for (int base = warp * KPW; base < n; base += GROUPS) {
+      const int i = base + kg;
+      const bool valid = i < n;
+      float kf[ATT_EPL], vf[ATT_EPL];
+      if (valid && lane_on) {
+        Vec8<T>::load(ks + (size_t)i * hd + e0, kf);
+        Vec8<T>::load(vs + (size_t)i * hd + e0, vf);
+      } else {
+#pragma unroll
+        for (int e = 0; e < ATT_EPL; ++e) { kf[e] = 0.f; vf[e] = 0.f; }
+      }
+#pragma unroll
+      for (int r = 0; r < ATT_RT; ++r) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < ATT_EPL; ++e) d = fmaf(qreg[r][e], kf[e], d);
+#pragma unroll
+        for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+        if (valid) {
+          const float sc = d * scale;
+          const float mn = fmaxf(m[r], sc);
+          const float corr = expf(m[r] - mn);
+          const float p = expf(sc - mn);
+          l[r] = l[r] * corr + p;
+#pragma unroll
+          for (int e = 0; e < ATT_EPL; ++e) o[r][e] = fmaf(p, vf[e], o[r][e] * corr);
+          m[r] = mn;
+        }
+      }
+    }
+  }
+
+  // merge the key groups of the block
+  const int grp = warp * KPW + kg;
+#pragma unroll
+  for (int r = 0; r < ATT_RT; ++r) {
+    if (sub == 0) { m_s[grp][r] = m[r]; l_s[grp][r] = l[r]; }
+#pragma unroll
+    for (int e = 0; e < ATT_EPL; ++e)
+      o_s[((size_t)r * GROUPS + grp) * (LPK * ATT_EPL) + e0 + e] = o[r][e];
+  }
+  __syncthreads();
+  const size_t qh = (size_t)t * H + h0;                       // first (token, head) of this block
+  for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
+    const int r = idx / hd, d = idx % hd;
+    float M = -INFINITY;
+    for (int gi = 0; gi < GROUPS; ++gi) M = fmaxf(M, m_s[gi][r]);
+    float L = 0.f, O = 0.f;
+    if (M > -INFINITY) {
+      for (int gi = 0; gi < GROUPS; ++gi) {
+        const float w = expf(m_s[gi][r] - M);
+        L += l_s[gi][r] * w;
+        O += o_s[((size_t)r * GROUPS + gi) * (LPK * ATT_EPL) + d] * w;
+      }
+    }
+    if (n_active == 1) {
+      out[(qh + r) * hd + d] = from_float<T>(O / L);
+    } else {
+      const size_t pi = (qh + r) * max_chunks + c;
+      part_o[pi * hd + d] = O;
+      if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+    }
+  }
+  if (n_active == 1) return;
+
+  // the block that arrives last adds the chunks in order
+  __threadfence();
+  __syncthreads();
+  int* counter = counters + (size_t)t * gridDim.y + blockIdx.y;
+  if (threadIdx.x == 0) last_flag = (atomicAdd(counter, 1) == n_active - 1) ? 1 : 0;
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  if (threadIdx.x == 0) *counter = 0;
+  // weights of the chunks first (the small (max, sum) records, spread over all
+  // threads), then the weighted sum of the partial outputs, eight loads in flight
+  float* w_s = o_s;                                          // [n_active][ATT_RT], reuses o_s
+  constexpr int W_CAP = (GROUPS * LPK * ATT_EPL);            // chunks whose weights fit (1024)
+  if (n_active <= W_CAP) {
+    float mloc[ATT_RT], lloc[ATT_RT];
+#pragma unroll
+    for (int r = 0; r < ATT_RT; ++r) {
+      mloc[r] = -INFINITY;
+      if (r < nh) {
+        const float* ml = part_ml + (qh + r) * max_chunks * 2;
+        for (int s2 = threadIdx.x; s2 < n_active; s2 += blockDim.x)
+          mloc[r] = fmaxf(mloc[r], __ldcg(ml + 2 * s2));
+      }
+      mloc[r] = warp_max(mloc[r]);
+      if (lane == 0) m_s[warp][r] = mloc[r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < ATT_RT; ++r) {
+      float M = -INFINITY;
+#pragma unroll
+      for (int wp = 0; wp < ATT_WARPS; ++wp) M = fmaxf(M, m_s[wp][r]);
+      lloc[r] = 0.f;
+      if (r < nh) {
+        const float* ml = part_ml + (qh + r) * max_chunks * 2;
+        for (int s2 = threadIdx.x; s2 < n_active; s2 += blockDim.x) {
+          const float ms = __ldcg(ml + 2 * s2);
+          const float w = ms > -INFINITY ? expf(ms - M) : 0.f;
+          lloc[r] += __ldcg(ml + 2 * s2 + 1) * w;
+          w_s[s2 * ATT_RT + r] = w;
+        }
+      }
+      lloc[r] = warp_sum(lloc[r]);
+      if (lane == 0) l_s[warp][r] = lloc[r];
+    }
+    __syncthreads();
+    if (threadIdx.x < ATT_RT) {
+      float L = 0.f;
+#pragma unroll
+      for (int wp = 0; wp < ATT_WARPS; ++wp) L += l_s[wp][threadIdx.x];
+      m_s[ATT_WARPS][threadIdx.x] = L;                       // GROUPS >= 8 rows: row 4 is free
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
+      const int r = idx / hd, d = idx % hd;
+      const float* po = part_o + (qh + r) * max_chunks * hd + d;
+      float O = 0.f;
+      int s = 0;
+      for (; s + 8 <= n_active; s += 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __ldcg(po + (size_t)(s + j) * hd);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) O = fmaf(v[j], w_s[(s + j) * ATT_RT + r], O);
+      }
+      for (; s < n_active; ++s) O = fmaf(__ldcg(po + (size_t)s * hd), w_s[s * ATT_RT + r], O);
+      out[(qh + r) * hd + d] = from_float<T>(O / m_s[ATT_WARPS][r]);
+    }
+    return;
+  }
+  for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
+    const int r = idx / hd, d = idx % hd;
+    const float* ml = part_ml + (qh + r) * max_chunks * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < n_active; ++s) M = fmaxf(M, __ldcg(ml + 2 * s));
+    float L = 0.f, O = 0.f;
+    for (int s = 0; s < n_active; ++s) {
+      const float ms = __ldcg(ml + 2 * s);
+      if (ms > -INFINITY) {
+        const float w = expf(ms - M);
+        L += __ldcg(ml + 2 * s + 1) * w;
+        O += __ldcg(part_o + ((qh + r) * max_chunks + s) * hd + d) * w;
+      }
+    }
+    out[(qh + r) * hd + d] = from_float<T>(O / L);
   }
 }
 
@@ -266,7 +530,7 @@ static int launch_attention(const void* q, const void* kv_step, const void* k_ca
   for (int t0 = 0; t0 < n_tokens; t0 += 65535) {
   const dim3 grid(nsplit, G * nchunks, n_tokens - t0 < 65535 ? n_tokens - t0 : 65535);
 #define YALM_ATT_CASE(LPK)                                                                      \
-  attn_token_kernel<T, LPK><<<grid, block, 0, stream>>>(                                        \
+  launch_pdl(attn_token_kernel<T, LPK>, dim3(grid), dim3(block), 0, stream,                                         \
       (const T*)q, (const T*)kv_step, (const T*)k_cache, (const T*)v_cache, token_seq, q_start, \
       seq_slot, slot_pos, (T*)out, part_o, part_ml, H, G, hd, capacity, window, nsplit, scale, t0)
   if (hd <= 16) YALM_ATT_CASE(2);
@@ -279,7 +543,7 @@ static int launch_attention(const void* q, const void* kv_step, const void* k_ca
   }
   if (nsplit > 1) {
     const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
-    attn_merge_kernel<T><<<n_tokens * H, threads, 0, stream>>>(part_o, part_ml, (T*)out, hd,
+    launch_pdl(attn_merge_kernel<T>, dim3(n_tokens * H), dim3(threads), 0, stream, part_o, part_ml, (T*)out, hd,
                                                                nsplit);
     YALM_LAUNCH_CHECK();
   }
@@ -309,6 +573,64 @@ extern "C" int yalm_attention(const void* q, const void* kv_step, const void* k_
   return launch_attention<__nv_bfloat16>(q, kv_step, k_cache, v_cache, token_seq, q_start,
                                          seq_slot, slot_pos, out, part_o, part_ml, n_tokens, H, G,
                                          hd, capacity, window, nsplit, stream);
+}
+
+// Decode attention (see attn_decode_kernel).  Every query is the newest token of
+// its sequence and its own key/value row is already in the cache.  chunk: keys
+// per block; max_context: upper bound of any sequence's visible keys in this
+// call (it sizes the grid).  part_o [n, H, max_chunks, hd], part_ml
+// [n, H, max_chunks, 2] floats with max_chunks = ceil(max_context / chunk);
+// counters: n * G * ceil((H/G)/4) ints, zero before the first launch.
+extern "C" int yalm_attention_decode(const void* q, const void* k_cache, const void* v_cache,
+                                     const int* seq_slot, const int* slot_pos, void* out,
+                                     float* part_o, float* part_ml, int* counters, int* status,
+                                     int dtype, int n_seqs, int H, int G, int hd, int capacity,
+                                     int window, int chunk, int max_context,
+                                     cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (hd % 8 != 0 || hd > 256 || hd <= 0) return -2;
+  if (G <= 0 || H % G != 0) return -3;
+  if (chunk <= 0 || max_context <= 0 || n_seqs > 65535) return -4;
+  const size_t esz = dtype == DT_F32 ? 4 : 2;
+  const size_t smem = (size_t)2 * chunk * hd * esz;
+  if (smem > 160 * 1024) return -2;
+  const int R = H / G;
+  const int nchunks = (R + ATT_RT - 1) / ATT_RT;
+  if ((size_t)G * nchunks > 65535) return -4;
+  const int visible = window > 0 && window < max_context ? window : max_context;
+  const int max_chunks = (visible + chunk - 1) / chunk;
+  const dim3 grid(max_chunks, G * nchunks, n_seqs);
+  const dim3 block(ATT_WARPS * 32);
+  const float scale = 1.0f / sqrtf((float)hd);
+#define YALM_DEC_CASE(T, LPK)                                                                  \
+  do {                                                                                         \
+    static size_t attr_smem = 0;                                                               \
+    if (smem > attr_smem) {                                                                    \
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<T, LPK>,                         \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                           (int)smem);                                         \
+      if (e != cudaSuccess) return (int)e;                                                     \
+      attr_smem = smem;                                                                        \
+    }                                                                                          \
+    launch_pdl(attn_decode_kernel<T, LPK>, grid, block, smem, stream, (const T*)q,             \
+               (const T*)k_cache, (const T*)v_cache, seq_slot, slot_pos, (T*)out, part_o,      \
+               part_ml, counters, status, H, G, hd, capacity, window, chunk, max_chunks,       \
+               scale);                                                                         \
+  } while (0)
+#define YALM_DEC_T(T)                                  \
+  do {                                                 \
+    if (hd <= 16) YALM_DEC_CASE(T, 2);                 \
+    else if (hd <= 32) YALM_DEC_CASE(T, 4);            \
+    else if (hd <= 64) YALM_DEC_CASE(T, 8);            \
+    else if (hd <= 128) YALM_DEC_CASE(T, 16);          \
+    else YALM_DEC_CASE(T, 32);                         \
+  } while (0)
+  if (dtype == DT_F32) YALM_DEC_T(float);
+  else YALM_DEC_T(__nv_bfloat16);
+#undef YALM_DEC_T
+#undef YALM_DEC_CASE
+  YALM_LAUNCH_CHECK();
+  return 0;
 }
 
 // ---------------------------------------------------------------------------

@@ -17,6 +17,7 @@ enum : int {
   ERR_TOKEN_RANGE = 1,    // a token id outside the vocabulary
   ERR_WAIT_TIMEOUT = 2,   // a bounded wait on a barrier gave up
   ERR_SLOT_RANGE = 4,     // a slot index outside the cache
+  ERR_CONTEXT_RANGE = 8,  // a sequence longer than the bound the launch was sized for
 };
 
 __device__ __forceinline__ float to_float(float v) { return v; }
@@ -72,6 +73,85 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   }
   __syncthreads();
   return scratch[32];
+}
+
+// ---- shared-memory barriers with bounded waits --------------------------
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+// Bounded wait; false after the time limit or once another role has given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((it & 255u) == 255u) {
+      if (*abort_flag) return false;
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+    }
+  }
+}
+// Plain (untiled) bulk copy global -> shared; both addresses and the size are
+// multiples of 16 bytes.  Completion is counted on the barrier in bytes.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// ---- programmatic dependent launch ---------------------------------------
+// Every kernel of the library is launched so that its blocks may start while
+// the previous kernel of the stream is still draining.  A kernel first lets its
+// own successor do the same (pdl_launch_dependents) and then waits until the
+// previous kernel has completed and its writes are visible (pdl_wait) before it
+// touches anything that kernel may have written or may still read.  Only data
+// that no kernel of a step writes (weights) is read before the wait.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+extern int g_pdl_enabled;     // defined in elementwise.cu; yalm_set_pdl switches it
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_pdl_enabled ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 }  // namespace yalm

@@ -12,10 +12,14 @@
 
 namespace yalm {
 
+int g_pdl_enabled = 1;
+
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                              float* __restrict__ x, int dim, int vocab, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int tok = tokens[t];
   if (tok < 0 || tok >= vocab) {
@@ -36,6 +40,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
                                int n_partials, long long partial_stride,
                                const int* __restrict__ rows, const float* __restrict__ weight,
                                TO* __restrict__ out, int dim, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -78,6 +84,8 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ x, const float* __restric
                                    int n_partials, long long partial_stride,
                                    const int* __restrict__ rows, const float* __restrict__ weight,
                                    TO* __restrict__ out, int dim, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -130,6 +138,8 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ x, const float* __restric
 template <typename TO>
 __global__ void silu_mul_kernel(const float* __restrict__ gu, int n_partials,
                                 long long partial_stride, TO* __restrict__ out, int rows, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t total = (size_t)rows * F;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
@@ -160,6 +170,8 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
                                   T* __restrict__ q_out, T* __restrict__ kv_step,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G,
                                   int hd, int capacity, int write_cache, int heads_per_block) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int half = hd >> 1;
   const int i = threadIdx.x % half;
@@ -207,6 +219,8 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
 
 __global__ void advance_kernel(const int* __restrict__ q_start, const int* __restrict__ seq_slot,
                                int* __restrict__ slot_pos, int n_seqs) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b < n_seqs) slot_pos[seq_slot[b]] += q_start[b + 1] - q_start[b];
 }
@@ -215,15 +229,22 @@ __global__ void advance_kernel(const int* __restrict__ q_start, const int* __res
 
 using namespace yalm;
 
+// Programmatic dependent launch on (1, the default) or off (0: every kernel starts
+// only after the previous one has ended, as a plain stream launch does).
+extern "C" int yalm_set_pdl(int on) {
+  g_pdl_enabled = on ? 1 : 0;
+  return 0;
+}
+
 extern "C" int yalm_embed(const int* tokens, const void* table, int table_dtype, float* x,
                           int n_tokens, int dim, int vocab, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const int threads = dim >= 1024 ? 256 : 128;
   if (table_dtype == DT_F32)
-    embed_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, x, dim,
+    launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, x, dim,
                                                           vocab, status);
   else
-    embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+    launch_pdl(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, 
         tokens, (const __nv_bfloat16*)table, x, dim, vocab, status);
   YALM_LAUNCH_CHECK();
   return 0;
@@ -241,7 +262,7 @@ static void launch_rmsnorm(float* x, const float* partials, int n_partials,
     const int threads = nvec <= 128 ? 128 : (nvec <= 1024 ? 256 : 512);
     const int vpt = (nvec + threads - 1) / threads;
 #define YALM_RMS(V)                                                                          \
-  rmsnorm_vec_kernel<TO, V><<<n_rows, threads, 0, stream>>>(x, partials, n_partials,          \
+  launch_pdl(rmsnorm_vec_kernel<TO, V>, dim3(n_rows), dim3(threads), 0, stream, x, partials, n_partials,          \
                                                            partial_stride, rows, weight, out, \
                                                            dim, eps)
     if (vpt <= 1) YALM_RMS(1);
@@ -252,7 +273,7 @@ static void launch_rmsnorm(float* x, const float* partials, int n_partials,
     return;
   }
   const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
-  rmsnorm_kernel<TO><<<n_rows, threads, 0, stream>>>(x, partials, n_partials, partial_stride, rows,
+  launch_pdl(rmsnorm_kernel<TO>, dim3(n_rows), dim3(threads), 0, stream, x, partials, n_partials, partial_stride, rows,
                                                      weight, out, dim, eps);
 }
 
@@ -279,10 +300,10 @@ extern "C" int yalm_silu_mul(const float* gu, int n_partials, long long partial_
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (out_dtype == DT_F32)
-    silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>(gu, n_partials, partial_stride,
+    launch_pdl(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, gu, n_partials, partial_stride,
                                                                (float*)out, rows, F);
   else
-    silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
+    launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, 
         gu, n_partials, partial_stride, (__nv_bfloat16*)out, rows, F);
   YALM_LAUNCH_CHECK();
   return 0;
@@ -304,12 +325,12 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
   const int threads = half * hpb;
   if (grid.y > 65535) return -4;
   if (dtype == DT_F32)
-    rope_store_kernel<float><<<grid, threads, 0, stream>>>(
+    launch_pdl(rope_store_kernel<float>, dim3(grid), dim3(threads), 0, stream, 
         qkv, n_partials, partial_stride, inv_freq, token_seq, q_start, seq_slot, slot_pos,
         (float*)q_out, (float*)kv_step, (float*)k_cache, (float*)v_cache, H, G, hd, capacity,
         write_cache, hpb);
   else
-    rope_store_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+    launch_pdl(rope_store_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, 
         qkv, n_partials, partial_stride, inv_freq, token_seq, q_start, seq_slot, slot_pos,
         (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_step, (__nv_bfloat16*)k_cache,
         (__nv_bfloat16*)v_cache, H, G, hd, capacity, write_cache, hpb);
@@ -320,7 +341,7 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
 extern "C" int yalm_advance(const int* q_start, const int* seq_slot, int* slot_pos, int n_seqs,
                             cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
-  advance_kernel<<<(n_seqs + 127) / 128, 128, 0, stream>>>(q_start, seq_slot, slot_pos, n_seqs);
+  launch_pdl(advance_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, stream, q_start, seq_slot, slot_pos, n_seqs);
   YALM_LAUNCH_CHECK();
   return 0;
 }

@@ -18,6 +18,8 @@ template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __restrict__ out, int M,
                  int N, int K, int accumulate) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float As[SG_BK][SG_BM + 4];
   __shared__ float Ws[SG_BK][SG_BN + 4];
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
@@ -75,10 +77,10 @@ static int launch_simt(const void* A, const void* W, void* out, int out_dtype, i
   const dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
   if (grid.y > 65535) return -4;
   if (out_dtype == DT_F32)
-    gemm_simt_kernel<TA, TW, float><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W,
+    launch_pdl(gemm_simt_kernel<TA, TW, float>, dim3(grid), dim3(256), 0, stream, (const TA*)A, (const TW*)W,
                                                               (float*)out, M, N, K, accumulate);
   else
-    gemm_simt_kernel<TA, TW, __nv_bfloat16><<<grid, 256, 0, stream>>>(
+    launch_pdl(gemm_simt_kernel<TA, TW, __nv_bfloat16>, dim3(grid), dim3(256), 0, stream, 
         (const TA*)A, (const TW*)W, (__nv_bfloat16*)out, M, N, K, accumulate);
   YALM_LAUNCH_CHECK();
   return 0;

@@ -16,7 +16,7 @@ from . import build
 
 F32, BF16 = 0, 1
 
-ERR_TOKEN_RANGE, ERR_WAIT_TIMEOUT, ERR_SLOT_RANGE = 1, 2, 4
+ERR_TOKEN_RANGE, ERR_WAIT_TIMEOUT, ERR_SLOT_RANGE, ERR_CONTEXT_RANGE = 1, 2, 4, 8
 
 _REFUSALS = {
     -2: "a size that this kernel does not take",
@@ -26,6 +26,8 @@ _REFUSALS = {
     -6: "a pointer that is not 16-byte aligned",
     -10: "cuTensorMapEncodeTiled was not found in the driver",
     -11: "cuTensorMapEncodeTiled refused the tensor",
+    -12: "more output tiles than tile counters",
+    -13: "a scratch buffer that is too small",
 }
 
 
@@ -52,10 +54,13 @@ _SIGNATURES = {
     "yalm_advance": [_vp, _vp, _vp, _i, _vp],
     "yalm_attention": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                        _i, _i, _i, _vp],
+    "yalm_attention_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+                              _i, _i, _i, _i, _vp],
     "yalm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp],
     "yalm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_gemm_tc_available": [],
+    "yalm_gemm_sk": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _ll, _vp, _i, _vp, _vp],
 }
 
 _lib = None
@@ -69,6 +74,8 @@ def lib():
             fn = getattr(l, name)
             fn.argtypes = args
             fn.restype = _c.c_int
+        l.yalm_gemm_sk_scratch_floats.argtypes = [_i, _i]
+        l.yalm_gemm_sk_scratch_floats.restype = _c.c_longlong
         l.yalm_uniform01.argtypes = [_ull, _c.c_uint, _c.c_uint]
         l.yalm_uniform01.restype = _c.c_float
         _lib = l
@@ -194,6 +201,27 @@ def attention(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor, v_c
            kernels=2 if nsplit > 1 else 1)
 
 
+def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     seq_slot: torch.Tensor, slot_pos: torch.Tensor, out: torch.Tensor,
+                     part_o: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
+                     status: torch.Tensor, H: int, G: int, hd: int, capacity: int,
+                     window: Optional[int], chunk: int, max_context: int) -> None:
+    """One query per sequence over the cache (the query's own row included)."""
+    n = q.shape[0]
+    _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype, "attention_decode: dtypes")
+    visible = min(max_context, window) if window else max_context
+    max_chunks = -(-visible // chunk)
+    hc = -(-(H // G) // 4)
+    _need(part_o.numel() >= n * H * max_chunks * hd and part_ml.numel() >= n * H * max_chunks * 2
+          and counters.numel() >= n * G * hc and counters.dtype == torch.int32,
+          "attention_decode: workspace")
+    _check(lib().yalm_attention_decode(_p(q), _p(k_cache), _p(v_cache), _p(seq_slot), _p(slot_pos),
+                                       _p(out), _p(part_o), _p(part_ml), _p(counters), _p(status),
+                                       dtype_code(q.dtype), n, H, G, hd, capacity,
+                                       int(window or 0), chunk, max_context, _stream()),
+           "attention_decode")
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     M, K = a.shape
     N = w.shape[0]
@@ -229,6 +257,25 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, stat
                               _p(status), _stream()), "gemm_tc")
 
 
+def gemm_sk_scratch_floats(M: int, dual: bool) -> int:
+    return int(lib().yalm_gemm_sk_scratch_floats(int(M), 1 if dual else 0))
+
+
+def gemm_sk(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, status: torch.Tensor,
+            scratch: torch.Tensor, counters: torch.Tensor) -> None:
+    """Persistent stream-K tcgen05 product with a fused epilogue (GEMM_STORE,
+    GEMM_ADD or GEMM_SILU_MUL)."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+          and a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "gemm_sk: operands")
+    _need(tuple(out.shape) == ((M, N // 2) if mode == GEMM_SILU_MUL else (M, N)), "gemm_sk: out shape")
+    _need(scratch.dtype == torch.float32 and counters.dtype == torch.int32, "gemm_sk: workspace types")
+    _check(lib().yalm_gemm_sk(_p(a), _p(w), _p(out), dtype_code(out.dtype), M, N, K, mode,
+                              _p(scratch), scratch.numel(), _p(counters), counters.numel(),
+                              _p(status), _stream()), "gemm_sk")
+
+
 def sample(logits: torch.Tensor, temperature: float, seed: int, row_key: torch.Tensor,
            seq_slot: torch.Tensor, slot_pos: torch.Tensor, out_tokens: torch.Tensor) -> None:
     rows, vocab = logits.shape
@@ -237,6 +284,14 @@ def sample(logits: torch.Tensor, temperature: float, seed: int, row_key: torch.T
     _check(lib().yalm_sample(_p(logits), rows, vocab, float(temperature), int(seed) & (2 ** 64 - 1),
                              _p(row_key), _p(seq_slot), _p(slot_pos), _p(out_tokens), _stream()),
            "sample")
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch on (default) or off for all later launches."""
+    l = lib()
+    l.yalm_set_pdl.argtypes = [_i]
+    l.yalm_set_pdl.restype = _c.c_int
+    l.yalm_set_pdl(1 if on else 0)
 
 
 def uniform01(seed: int, key: int, counter: int) -> float:

@@ -31,6 +31,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, float temperature,
               unsigned long long seed, const int* __restrict__ row_key,
               const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
               int* __restrict__ out_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red_v[SAMPLE_THREADS];
   __shared__ int red_i[SAMPLE_THREADS];
   __shared__ float prefix[SAMPLE_THREADS + 1];
@@ -103,7 +105,7 @@ extern "C" int yalm_sample(const float* logits, int n_rows, int vocab, float tem
                            const int* slot_pos, int* out_tokens, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (vocab <= 0 || temperature < 0.f) return -2;
-  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, temperature, seed, row_key,
+  launch_pdl(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, vocab, temperature, seed, row_key,
                                                       seq_slot, slot_pos, out_tokens);
   YALM_LAUNCH_CHECK();
   return 0;

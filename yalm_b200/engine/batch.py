@@ -28,6 +28,7 @@ class StepBatch:
     seq_slot: torch.Tensor
     want_rows: Optional[torch.Tensor] = None   # int32 flat token indices whose logits are wanted
     n_want: int = 0
+    ctx_bound: int = 0                    # no sequence exceeds this many positions after the step
 
     @property
     def is_decode(self) -> bool:
@@ -68,4 +69,5 @@ def build_batch(token_lists: Sequence[Sequence[int]], slots: Sequence[int], past
     want_rows = dev[o:o + len(rows)]
     return StepBatch(n_tokens=N, n_seqs=B, q_lens=q_lens, slots=list(slots), past=list(past),
                      tokens=tokens, token_seq=token_seq, q_start=qs, seq_slot=seq_slot,
-                     want_rows=want_rows, n_want=len(rows))
+                     want_rows=want_rows, n_want=len(rows),
+                     ctx_bound=max(p + q for p, q in zip(past, q_lens)))

@@ -125,10 +125,19 @@ class Engine:
     def _decode_batch(self, B: int) -> StepBatch:
         d = self._decode_buffers()
         slots = d["slots_host"]
-        return StepBatch(n_tokens=B, n_seqs=B, q_lens=[1] * B, slots=list(slots),
-                         past=[self.cache.host_pos[s] for s in slots], tokens=d["tokens"][:B],
-                         token_seq=d["arange"][:B], q_start=d["arange"][:B + 1],
-                         seq_slot=d["seq_slot"][:B], want_rows=d["arange"][:B], n_want=B)
+        past = [self.cache.host_pos[s] for s in slots]
+        return StepBatch(n_tokens=B, n_seqs=B, q_lens=[1] * B, slots=list(slots), past=past,
+                         tokens=d["tokens"][:B], token_seq=d["arange"][:B],
+                         q_start=d["arange"][:B + 1], seq_slot=d["seq_slot"][:B],
+                         want_rows=d["arange"][:B], n_want=B, ctx_bound=self._ctx_bucket(past))
+
+    CTX_BUCKET = 512
+
+    def _ctx_bucket(self, past: Sequence[int]) -> int:
+        """The longest sequence after this step, rounded up: launches sized by it
+        stay valid (and a captured graph reusable) until a sequence crosses it."""
+        longest = max(past) + 1
+        return min(self.context, -(-longest // self.CTX_BUCKET) * self.CTX_BUCKET)
 
     def _decode_body(self, B: int, temperature: float, seed: int) -> None:
         d = self._decode_buffers()
@@ -150,7 +159,8 @@ class Engine:
         if not self.use_graphs:
             self._decode_body(B, temperature, seed)
         else:
-            key = (B, float(temperature), int(seed))
+            key = (B, float(temperature), int(seed),
+                   self._ctx_bucket([self.cache.host_pos[s] for s in d["slots_host"][:B]]))
             g = self._graphs.get(key)
             if g is not None and g["generation"] != self.rt.buffer_generation:
                 g = None                      # a scratch buffer moved since the capture

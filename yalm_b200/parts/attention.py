@@ -54,15 +54,12 @@ class GQAAttention:
     def cache_need(self) -> CacheNeed:
         return CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=self.window)
 
-    def split_count(self, batch, capacity: int) -> int:
-        """Key slices per query, so that a few decoding sequences still fill the
-        device; fixed by the batch's shape, not by the current lengths."""
-        if not batch.is_decode:
-            return 1
-        R = self.H // self.G
-        blocks = batch.n_tokens * self.G * -(-R // 4)
-        want = -(-4 * self.rt.sm_count // blocks)
-        return max(1, min(want, 32, capacity // 128))
+    def decode_chunk(self, batch) -> int:
+        """Keys per block of the decode kernel: 32 KiB of keys and values, so
+        that several blocks share an SM and hide each other's copy latency."""
+        esz = 4 if self.rt.dtype == torch.float32 else 2
+        chunk = (32 * 1024) // (2 * self.hd * esz)
+        return max(8, min(128, chunk))
 
     def forward(self, h, batch, stream, view, shared: bool = False) -> None:
         rt, H, G, hd = self.rt, self.H, self.G, self.hd
@@ -80,11 +77,19 @@ class GQAAttention:
         else:
             self.position.rotate_and_store(qkv, S, batch, view, q, kv_step, H, G)
         o = rt.buffer("attn_out", (n, H * hd), rt.dtype)
-        nsplit = self.split_count(batch, view.capacity)
-        part_o = part_ml = None
-        if nsplit > 1:
-            part_o = rt.buffer("attn_part_o", (n, H, nsplit, hd), torch.float32)
-            part_ml = rt.buffer("attn_part_ml", (n, H, nsplit, 2), torch.float32)
-        ops.attention(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
-                      view.capacity, self.window, nsplit, part_o, part_ml)
+        if batch.is_decode:
+            # one query per sequence, every key in the cache: the bulk-copy kernel
+            chunk = self.decode_chunk(batch)
+            bound = max(1, batch.ctx_bound)
+            visible = min(bound, self.window) if self.window else bound
+            max_chunks = -(-visible // chunk)
+            part_o = rt.buffer("attn_part_o", (n, H, max_chunks, hd), torch.float32)
+            part_ml = rt.buffer("attn_part_ml", (n, H, max_chunks, 2), torch.float32)
+            counters = rt.zeros("attn_counters", n * G * -(-(H // G) // 4))
+            ops.attention_decode(q, view.k, view.v, batch.seq_slot, view.slot_pos, o, part_o,
+                                 part_ml, counters, rt.status, H, G, hd, view.capacity,
+                                 self.window, chunk, bound)
+        else:
+            ops.attention(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
+                          view.capacity, self.window, 1, None, None)
         stream.add_linear(o, self.w_o)

@@ -106,6 +106,20 @@ class Runtime:
             self.buffer_generation += 1       # captured graphs that used the old one are stale
         return buf[:n].view(*shape)
 
+    def zeros(self, name: str, n: int, dtype: torch.dtype = torch.int32) -> torch.Tensor:
+        """A named buffer that starts at zero and that kernels leave at zero
+        (tile and chunk counters)."""
+        key = f"zero:{name}:{dtype}"
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < n:
+            if self.frozen:
+                raise RuntimeError(f"counter buffer {name!r} would grow while a graph holds it")
+            buf = torch.zeros(max(n, 1024 if buf is None else 2 * buf.numel()), dtype=dtype,
+                              device=self.device)
+            self._buffers[key] = buf
+            self.buffer_generation += 1
+        return buf
+
     def matrix(self, t: torch.Tensor, share: bool = False) -> torch.Tensor:
         """A weight matrix in the type it is multiplied in: the compute type,
         except that a matrix stored in 32 bits stays 32-bit.  ``share``: parts
@@ -137,6 +151,8 @@ class Runtime:
                 what.append("a bounded barrier wait ran out inside a kernel")
             if code & ops.ERR_SLOT_RANGE:
                 what.append("a slot index outside the cache")
+            if code & ops.ERR_CONTEXT_RANGE:
+                what.append("a sequence longer than the bound its attention launch was sized for")
             raise ops.KernelError("kernel status: " + "; ".join(what or [f"code {code}"]))
 
 
