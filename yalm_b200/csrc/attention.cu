@@ -269,6 +269,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o,
 // query and head group; partial results in scratch, added in chunk order), so
 // there is no second kernel.  Blocks whose chunk lies beyond the sequence's
 // length leave at once.
+constexpr int ATT_MAX_CHUNK = 128;
+
 template <typename T, int LPK>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
@@ -277,12 +279,14 @@ attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
                    float* __restrict__ part_o, float* __restrict__ part_ml,
                    int* __restrict__ counters, int* __restrict__ status, int H, int G, int hd,
                    int capacity, int window, int chunk, int max_chunks, float scale) {
+  static_assert(ATT_WARPS == ATT_RT, "one warp per query head in the softmax pass");
   constexpr int KPW = 32 / LPK;
   constexpr int GROUPS = ATT_WARPS * KPW;
-  extern __shared__ __align__(128) uint8_t att_smem[];
-  __shared__ float m_s[GROUPS][ATT_RT];
+  extern __shared__ __align__(128) uint8_t att_smem[];      // K rows, V rows; later the o partials
+  __shared__ float sc_s[ATT_RT][ATT_MAX_CHUNK];             // scores, then probabilities
+  __shared__ float m_s[GROUPS][ATT_RT];                     // scratch of the final merge
   __shared__ float l_s[GROUPS][ATT_RT];
-  __shared__ float o_s[ATT_RT * GROUPS * LPK * ATT_EPL];
+  __shared__ float ml_s[2][ATT_RT];                         // this chunk's max and sum per head
   __shared__ __align__(8) uint64_t bar;
   __shared__ int abort_flag;
   __shared__ int last_flag;
@@ -345,85 +349,92 @@ attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
       for (int e = 0; e < ATT_EPL; ++e) qreg[r][e] = 0.f;
     }
   }
-  float m[ATT_RT], l[ATT_RT], o[ATT_RT][ATT_EPL];
-#pragma unroll
-  for (int r = 0; r < ATT_RT; ++r) {
-    m[r] = -INFINITY;
-    l[r] = 0.f;
-#pragma unroll
-    for (int e = 0; e < ATT_EPL; ++e) o[r][e] = 0.f;
-  }
   __syncthreads();                                           // the barrier is initialised
   const bool arrived = mbar_wait(smem_u32(&bar), 0, &abort_flag);
   if (!arrived) {
-    // never expected: give the copies time to land, report, and leave without a result
+    // never expected: give the copies time to land, report, and go on without a result
     if (threadIdx.x == 0) atomicOr(status, ERR_WAIT_TIMEOUT);
     const unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
   }
 
-  if (arrived) {
-    for (int base = warp * KPW; base < n; base += GROUPS) {
-      const int i = base + kg;
-      const bool valid = i < n;
-      float kf[ATT_EPL], vf[ATT_EPL];
-      if (valid && lane_on) {
-        Vec8<T>::load(ks + (size_t)i * hd + e0, kf);
-        Vec8<T>::load(vs + (size_t)i * hd + e0, vf);
-      } else {
+  // pass 1: scores of the chunk's keys
+  for (int base = warp * KPW; base < n; base += GROUPS) {
+    const int i = base + kg;
+    const bool valid = i < n;
+    float kf[ATT_EPL];
+    if (valid && lane_on) {
+      Vec8<T>::load(ks + (size_t)i * hd + e0, kf);
+    } else {
 #pragma unroll
-        for (int e = 0; e < ATT_EPL; ++e) { kf[e] = 0.f; vf[e] = 0.f; }
-      }
+      for (int e = 0; e < ATT_EPL; ++e) kf[e] = 0.f;
+    }
+#pragma unroll
+    for (int r = 0; r < ATT_RT; ++r) {
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < ATT_EPL; ++e) d = fmaf(qreg[r][e], kf[e], d);
+#pragma unroll
+      for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+      if (valid && sub == 0) sc_s[r][i] = d * scale;
+    }
+  }
+  __syncthreads();
+  // softmax numerators of the chunk: warp r owns head r
+  {
+    float mx = -INFINITY;
+    for (int i = lane; i < n; i += 32) mx = fmaxf(mx, sc_s[warp][i]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int i = lane; i < n; i += 32) {
+      const float p = expf(sc_s[warp][i] - mx);
+      sc_s[warp][i] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) { ml_s[0][warp] = mx; ml_s[1][warp] = sum; }
+  }
+  __syncthreads();
+  // pass 2: weighted sum of the values
+  float o[ATT_RT][ATT_EPL];
+#pragma unroll
+  for (int r = 0; r < ATT_RT; ++r)
+#pragma unroll
+    for (int e = 0; e < ATT_EPL; ++e) o[r][e] = 0.f;
+  for (int base = warp * KPW; base < n; base += GROUPS) {
+    const int i = base + kg;
+    if (i < n && lane_on) {
+      float vf[ATT_EPL];
+      Vec8<T>::load(vs + (size_t)i * hd + e0, vf);
 #pragma unroll
       for (int r = 0; r < ATT_RT; ++r) {
-        float d = 0.f;
+        const float p = sc_s[r][i];
 #pragma unroll
-        for (int e = 0; e < ATT_EPL; ++e) d = fmaf(qreg[r][e], kf[e], d);
-#pragma unroll
-        for (int off = LPK / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-        if (valid) {
-          const float sc = d * scale;
-          const float mn = fmaxf(m[r], sc);
-          const float corr = expf(m[r] - mn);
-          const float p = expf(sc - mn);
-          l[r] = l[r] * corr + p;
-#pragma unroll
-          for (int e = 0; e < ATT_EPL; ++e) o[r][e] = fmaf(p, vf[e], o[r][e] * corr);
-          m[r] = mn;
-        }
+        for (int e = 0; e < ATT_EPL; ++e) o[r][e] = fmaf(p, vf[e], o[r][e]);
       }
     }
   }
-
-  // merge the key groups of the block
+  __syncthreads();                                           // K and V are no longer read
+  float* o_s = reinterpret_cast<float*>(att_smem);           // [RT][GROUPS][LPK*8] over the K/V area
   const int grp = warp * KPW + kg;
 #pragma unroll
-  for (int r = 0; r < ATT_RT; ++r) {
-    if (sub == 0) { m_s[grp][r] = m[r]; l_s[grp][r] = l[r]; }
+  for (int r = 0; r < ATT_RT; ++r)
 #pragma unroll
     for (int e = 0; e < ATT_EPL; ++e)
       o_s[((size_t)r * GROUPS + grp) * (LPK * ATT_EPL) + e0 + e] = o[r][e];
-  }
   __syncthreads();
   const size_t qh = (size_t)t * H + h0;                       // first (token, head) of this block
   for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
     const int r = idx / hd, d = idx % hd;
-    float M = -INFINITY;
-    for (int gi = 0; gi < GROUPS; ++gi) M = fmaxf(M, m_s[gi][r]);
-    float L = 0.f, O = 0.f;
-    if (M > -INFINITY) {
-      for (int gi = 0; gi < GROUPS; ++gi) {
-        const float w = expf(m_s[gi][r] - M);
-        L += l_s[gi][r] * w;
-        O += o_s[((size_t)r * GROUPS + gi) * (LPK * ATT_EPL) + d] * w;
-      }
-    }
+    float O = 0.f;
+#pragma unroll
+    for (int gi = 0; gi < GROUPS; ++gi) O += o_s[((size_t)r * GROUPS + gi) * (LPK * ATT_EPL) + d];
     if (n_active == 1) {
-      out[(qh + r) * hd + d] = from_float<T>(O / L);
+      out[(qh + r) * hd + d] = from_float<T>(O / ml_s[1][r]);
     } else {
       const size_t pi = (qh + r) * max_chunks + c;
       part_o[pi * hd + d] = O;
-      if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+      if (d == 0) { part_ml[pi * 2] = ml_s[0][r]; part_ml[pi * 2 + 1] = ml_s[1][r]; }
     }
   }
   if (n_active == 1) return;
@@ -478,7 +489,7 @@ attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
       float L = 0.f;
 #pragma unroll
       for (int wp = 0; wp < ATT_WARPS; ++wp) L += l_s[wp][threadIdx.x];
-      m_s[ATT_WARPS][threadIdx.x] = L;                       // GROUPS >= 8 rows: row 4 is free
+      ml_s[1][threadIdx.x] = L;                              // the total over all chunks
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
@@ -494,7 +505,7 @@ attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
         for (int j = 0; j < 8; ++j) O = fmaf(v[j], w_s[(s + j) * ATT_RT + r], O);
       }
       for (; s < n_active; ++s) O = fmaf(__ldcg(po + (size_t)s * hd), w_s[s * ATT_RT + r], O);
-      out[(qh + r) * hd + d] = from_float<T>(O / m_s[ATT_WARPS][r]);
+      out[(qh + r) * hd + d] = from_float<T>(O / ml_s[1][r]);
     }
     return;
   }
@@ -592,7 +603,9 @@ extern "C" int yalm_attention_decode(const void* q, const void* k_cache, const v
   if (G <= 0 || H % G != 0) return -3;
   if (chunk <= 0 || max_context <= 0 || n_seqs > 65535) return -4;
   const size_t esz = dtype == DT_F32 ? 4 : 2;
-  const size_t smem = (size_t)2 * chunk * hd * esz;
+  if (chunk > ATT_MAX_CHUNK) return -2;
+  size_t smem = (size_t)2 * chunk * hd * esz;
+  if (smem < 16 * 1024) smem = 16 * 1024;                    // the merge reuses it for partials
   if (smem > 160 * 1024) return -2;
   const int R = H / G;
   const int nchunks = (R + ATT_RT - 1) / ATT_RT;

@@ -55,10 +55,10 @@ class GQAAttention:
         return CacheNeed("kv", kv_heads=self.G, head_dim=self.hd, window=self.window)
 
     def decode_chunk(self, batch) -> int:
-        """Keys per block of the decode kernel: 32 KiB of keys and values, so
-        that several blocks share an SM and hide each other's copy latency."""
+        """Keys per block of the decode kernel: 64 KiB of keys and values, so
+        that three blocks share an SM and hide each other's copy latency."""
         esz = 4 if self.rt.dtype == torch.float32 else 2
-        chunk = (32 * 1024) // (2 * self.hd * esz)
+        chunk = (64 * 1024) // (2 * self.hd * esz)
         return max(8, min(128, chunk))
 
     def forward(self, h, batch, stream, view, shared: bool = False) -> None:
