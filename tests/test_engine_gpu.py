@@ -268,3 +268,22 @@ def test_command_line_completion_and_perplexity(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     ppl = float(r.stdout.split("perplexity:")[1].split()[0])
     assert abs(ppl - plain_perplexity(cfg, w, list(range(3, 40)))[0]) / ppl < 1e-3
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_prompt_cut_into_steps_on_a_full_ring(dtype):
+    """Several tokens at once on top of a ring that already wrapped (not a
+    schedule of the generation loop, but the step function takes it): the ring
+    rows are written after the attention has read the keys they replace."""
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, seed = CONFIGS["tiny_b"]                               # window 32, context 96
+    w = make_weights(cfg, seed)
+    toks = random_tokens(96, cfg["vocab_size"], 11)
+    ref = plain_forward(cfg, w, toks)
+    lm = LM(config_from_dict(cfg), dict(w), dtype=dtype, max_batch=1)
+    s = lm.acquire(1)
+    got = [lm.step([toks[a:b]], s, [list(range(b - a))]).cpu()
+           for a, b in ((0, 50), (50, 51), (51, 80), (80, 96))]
+    err = float((torch.cat(got) - ref).abs().max() / ref.abs().max())
+    assert err <= TOL[dtype], err

@@ -334,3 +334,98 @@ def test_decode_attention_from_staged_chunks(ops, dt, tol, H, G, hd, cap, window
     torch.cuda.synchronize()
     need = max(-(-(min(n, window) if window else n) // chunk) for n in lens)
     assert status.item() == (ops.ERR_CONTEXT_RANGE if need > 1 else 0)
+
+
+@pytest.mark.parametrize("H, G, hd, cap, window", [
+    (8, 2, 128, 256, None),
+    (6, 3, 48, 40, 40),         # a ring shorter than the prompts
+    (5, 5, 16, 300, 100),
+    (16, 2, 64, 512, None),
+    (4, 1, 112, 200, 70),
+])
+def test_tensor_core_prefill_attention(ops, H, G, hd, cap, window):
+    """attention_prefill_mma against the plain attention: ragged prompts (one
+    longer than 64-token tiles, one of a single token), then a second chunk of
+    the same sequences on top of the cache (keys from the ring and from the step)."""
+    dt = torch.bfloat16
+    inv = plain_inv_freq(hd, 10000.0, None).to(DEV)
+    n_slots, slots = 4, [2, 0, 3]
+    slot_pos = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+    kc = torch.zeros(n_slots, G, cap, hd, device=DEV, dtype=dt)
+    vc = torch.zeros_like(kc)
+    hist = {s: [] for s in slots}
+    for lens in ([150, 1, 70], [20, 37, 1]):
+        if window is None and max(a + b for a, b in zip([sum(x.shape[0] for x in hist[s]) for s in slots], lens)) > cap:
+            continue
+        b = B(lens, slots)
+        N = b.n_tokens
+        qkv = torch.randn(N, (H + 2 * G) * hd, device=DEV)
+        q_out = torch.empty(N, H * hd, device=DEV, dtype=dt)
+        kv_step = torch.empty(N, 2, G, hd, device=DEV, dtype=dt)
+        # the ring is written after the attention: several tokens on top of a full
+        # ring would otherwise replace keys that the first of them still sees
+        ops.rope_store(qkv, 1, inv, b, q_out, kv_step, kc, vc, slot_pos, H, G, hd, cap,
+                       write_cache=False)
+        out = torch.empty(N, H * hd, device=DEV, dtype=dt)
+        ops.attention_prefill_mma(q_out, kv_step, kc, vc, b, slot_pos, out, H, G, hd, cap, window)
+        ref_simt = torch.empty_like(out)
+        ops.attention(q_out, kv_step, kc, vc, b, slot_pos, ref_simt, H, G, hd, cap, window, 1)
+        ops.rope_store(qkv, 1, inv, b, q_out, kv_step, kc, vc, slot_pos, H, G, hd, cap)
+        qs = b.q_start.tolist()
+        for i, s in enumerate(slots):
+            hist[s].append(qkv[qs[i]:qs[i + 1]].cpu().view(-1, H + 2 * G, hd))
+            allt = torch.cat(hist[s])
+            T = allt.shape[0]
+            pos = torch.arange(T)
+            qq = plain_rope(allt[:, :H], pos, inv.cpu()).to(dt).float()
+            kk = plain_rope(allt[:, H:H + G], pos, inv.cpu()).to(dt).float()
+            vv = allt[:, H + G:].to(dt).float()
+            ref = plain_attention(qq, kk, vv, window)[T - lens[i]:]
+            got = out[qs[i]:qs[i + 1]].float().cpu().view(-1, H, hd)
+            assert (got - ref).abs().max().item() <= 2.5e-2, (lens, i)
+        assert (out.float() - ref_simt.float()).abs().max().item() <= 2.5e-2
+        ops.advance(b, slot_pos)
+
+
+@pytest.mark.parametrize("H, G, hd, cap, window", [
+    (32, 8, 128, 700, None),
+    (6, 3, 48, 40, 40),
+    (40, 2, 64, 300, 100),      # 20 query heads per kv head: two head groups of the tile
+    (3, 1, 32, 1000, None),
+])
+def test_tensor_core_decode_attention(ops, H, G, hd, cap, window):
+    dt = torch.bfloat16
+    g = torch.Generator(device=DEV).manual_seed(hd + cap)
+    lens = [1, 37, cap - 1, cap, 3 * cap + 5] if window else [1, 129, 200, cap - 1, cap]
+    Bn, n_slots = len(lens), len(lens) + 3
+    slots = [5, 0, 3, 7, 2]
+    kc = torch.randn(n_slots, G, cap, hd, device=DEV, generator=g).to(dt)
+    vc = torch.randn(n_slots, G, cap, hd, device=DEV, generator=g).to(dt)
+    q = torch.randn(Bn, H * hd, device=DEV, generator=g).to(dt)
+    slot_pos = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+    for s, n in zip(slots, lens):
+        slot_pos[s] = n - 1
+    seq_slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    bound = max(lens)
+    visible = min(bound, window) if window else bound
+    mc = -(-visible // 128)
+    part_o = torch.empty(Bn * H * mc * hd, device=DEV)
+    part_ml = torch.empty(Bn * H * mc * 2, device=DEV)
+    counters = torch.zeros(Bn * G * -(-(H // G) // 16), dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for rep in range(2):
+        out = torch.zeros(Bn, H * hd, device=DEV, dtype=dt)
+        ops.attention_decode_mma(q, kc, vc, seq_slot, slot_pos, out, part_o, part_ml, counters,
+                                 status, H, G, hd, cap, window, bound)
+        torch.cuda.synchronize()
+        assert status.item() == 0 and int(counters.abs().sum()) == 0
+        for b, (s, n) in enumerate(zip(slots, lens)):
+            lo = 0 if window is None else max(0, n - window)
+            rows = torch.tensor([p % cap for p in range(lo, n)])
+            k = kc[s][:, rows].permute(1, 0, 2).float().cpu()
+            v = vc[s][:, rows].permute(1, 0, 2).float().cpu()
+            qq = torch.zeros(len(rows), H, hd)
+            qq[-1] = q[b].float().cpu().view(H, hd)
+            ref = plain_attention(qq, k, v, None)[-1]
+            got = out[b].float().cpu().view(H, hd)
+            assert (got - ref).abs().max().item() <= 2.5e-2, (rep, b, n)

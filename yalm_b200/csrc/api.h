@@ -40,6 +40,17 @@ int yalm_attention_decode(const void* q, const void* k_cache, const void* v_cach
                           int G, int hd, int capacity, int window, int chunk, int max_context,
                           cudaStream_t stream);
 
+// bfloat16 attention on tensor cores (attention_mma.cu): head sizes in steps of 16 up to 128
+int yalm_attention_prefill_mma(const void* q, const void* kv_step, const void* k_cache,
+                               const void* v_cache, const int* q_start, const int* seq_slot,
+                               const int* slot_pos, void* out, int n_seqs, int max_q_len, int H,
+                               int G, int hd, int capacity, int window, cudaStream_t stream);
+int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
+                              const int* seq_slot, const int* slot_pos, void* out, float* part_o,
+                              float* part_ml, int* counters, int* status, int n_seqs, int H, int G,
+                              int hd, int capacity, int window, int max_context,
+                              cudaStream_t stream);
+
 int yalm_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* out,
                    int out_dtype, int M, int N, int K, int accumulate, cudaStream_t stream);
 

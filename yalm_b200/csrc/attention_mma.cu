@@ -1,0 +1,602 @@
+// Tensor-core attention for bfloat16: prefill (many query tokens per
+// sequence) and decode (one query token per sequence).
+//
+// Same mathematics as attention.cu (and as the reference's attn_dot /
+// attn_softmax / att_mix, infer.cu:339-523): scores (q.k)/sqrt(hd) over the
+// visible keys, max-subtracted softmax in 32-bit, weighted sum of values.  Here
+// Q.K^T and P.V run as m16n8k16 bfloat16 tiles with 32-bit accumulators
+// (mma.sync); keys and values are brought into shared memory with cp.async in a
+// 16-byte-chunk XOR swizzle so that ldmatrix is free of bank conflicts; the
+// softmax is the online form (running max and sum per row), so no score matrix
+// ever leaves registers.
+//
+// Where a key lives: position j of a sequence is in this step's own buffer
+// (kv_step [N, 2, G, hd]) when j >= past, else in the cache ring at row
+// j % capacity -- the same rule as attention.cu.
+#include <cuda_bf16.h>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace yalm {
+
+constexpr int FA_WARPS = 4;
+constexpr int FA_THREADS = FA_WARPS * 32;
+constexpr int FA_BM = 64;          // query rows per block (16 per warp)
+constexpr int FA_BN = 64;          // keys per block iteration
+
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, const uint32_t* b) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// 16-byte asynchronous copy; with pred false the destination is zero-filled
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
+  const int n = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A tile of rows x HDP bfloat16 in shared memory; HDP is a multiple of 64, so a
+// row is a multiple of 128 bytes and the 16-byte chunk index can be XORed with
+// (row & 7) without leaving the row.
+template <int HDP>
+__device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) {
+  return base + (uint32_t)(row * (HDP * 2) + ((chunk ^ (row & 7)) << 4));
+}
+
+// Loads `rows` rows of hd elements each into a swizzled tile.  row_ptr(r) gives the
+// global address of row r, or nullptr for a row that is to be zero.
+template <int HDP, typename RowPtr>
+__device__ __forceinline__ void load_tile(uint32_t base, int rows, int hd,
+                                          const __nv_bfloat16* valid_ptr, RowPtr row_ptr) {
+  const int cpr = hd >> 3;                                    // 16-byte chunks per row
+  for (int idx = threadIdx.x; idx < rows * cpr; idx += FA_THREADS) {
+    const int r = idx / cpr, ch = idx - r * cpr;
+    const __nv_bfloat16* p = row_ptr(r);
+    // a zero-filled chunk still names an address: give it one that exists
+    cp_async16(tile_addr<HDP>(base, r, ch), p ? p + ch * 8 : valid_ptr, p != nullptr);
+  }
+}
+
+// ----------------------------------------------------------------- prefill
+// grid (query tiles of a sequence, heads, sequences); a block takes 64 query
+// tokens of one head.  scale_log2 = log2(e) / sqrt(hd).
+template <int HDP>
+__global__ void __launch_bounds__(FA_THREADS)
+attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv_step,
+                        const __nv_bfloat16* __restrict__ k_cache,
+                        const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ q_start,
+                        const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
+                        __nv_bfloat16* __restrict__ out, int H, int G, int hd, int capacity,
+                        int window, float scale_log2) {
+  constexpr int NKS = HDP / 16, NOT = HDP / 8;
+  extern __shared__ __align__(128) uint8_t fa_smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int g = h / (H / G);
+  const int qs = q_start[b], q_len = q_start[b + 1] - qs;
+  const int m0 = blockIdx.x * FA_BM;
+  if (m0 >= q_len) return;
+  const int slot = seq_slot[b];
+  const int past = slot_pos[slot];
+  const int rows = min(FA_BM, q_len - m0);
+  const int nks = hd >> 4, n_ot = hd >> 3;
+
+  const uint32_t q_s = smem_u32(fa_smem);
+  const uint32_t k_s0 = q_s + FA_BM * HDP * 2;
+  const uint32_t v_s0 = k_s0 + 2 * FA_BN * HDP * 2;           // two K stages, then two V stages
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+
+  // the visible key range of the whole tile: [k_begin, k_end)
+  const int p_first = past + m0, p_last = past + m0 + rows - 1;
+  const int k_end = p_last + 1;
+  const int k_begin = window > 0 ? max(0, p_first - window + 1) : 0;
+  const int kb0 = k_begin / FA_BN, kb1 = (k_end + FA_BN - 1) / FA_BN;
+
+  const size_t step_row = (size_t)2 * G * hd;
+  const __nv_bfloat16* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
+  const __nv_bfloat16* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
+  auto load_kv = [&](int kb, int stage) {
+    const int j0 = kb * FA_BN;
+    load_tile<HDP>(k_s0 + stage * FA_BN * HDP * 2, FA_BN, hd, q, [&](int r) -> const __nv_bfloat16* {
+      const int j = j0 + r;
+      if (j >= k_end) return nullptr;
+      return j >= past ? kv_step + (size_t)(qs + j - past) * step_row + (size_t)g * hd
+                       : kc + (size_t)(j % capacity) * hd;
+    });
+    load_tile<HDP>(v_s0 + stage * FA_BN * HDP * 2, FA_BN, hd, q, [&](int r) -> const __nv_bfloat16* {
+      const int j = j0 + r;
+      if (j >= k_end) return nullptr;
+      return j >= past ? kv_step + (size_t)(qs + j - past) * step_row + (size_t)(G + g) * hd
+                       : vc + (size_t)(j % capacity) * hd;
+    });
+  };
+
+  load_tile<HDP>(q_s, FA_BM, hd, q, [&](int r) -> const __nv_bfloat16* {
+    return r < rows ? q + ((size_t)(qs + m0 + r) * H + h) * hd : nullptr;
+  });
+  load_kv(kb0, 0);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // Q fragments of this warp's 16 rows stay in registers
+  uint32_t qf[NKS][4];
+#pragma unroll
+  for (int ks = 0; ks < NKS; ++ks) {
+    if (ks < nks) {
+      const int row = warp * 16 + (lane & 15);
+      ldsm_x4(qf[ks], tile_addr<HDP>(q_s, row, ks * 2 + (lane >> 4)));
+    }
+  }
+  float o[NOT][4];
+#pragma unroll
+  for (int i = 0; i < NOT; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int p_row[2] = {past + m0 + warp * 16 + gid, past + m0 + warp * 16 + gid + 8};
+
+  for (int kb = kb0; kb < kb1; ++kb) {
+    const int stage = (kb - kb0) & 1;
+    if (kb + 1 < kb1) load_kv(kb + 1, stage ^ 1);             // prefetch the next block
+    cp_async_commit();
+    const uint32_t k_s = k_s0 + stage * FA_BN * HDP * 2, v_s = v_s0 + stage * FA_BN * HDP * 2;
+
+    // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
+    float s[FA_BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < FA_BN / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < NKS; ++ks) {
+      if (ks < nks) {
+#pragma unroll
+        for (int np = 0; np < FA_BN / 16; ++np) {             // two n-tiles per ldmatrix.x4
+          uint32_t kf[4];
+          const int row = np * 16 + (lane & 7) + ((lane >> 4) << 3);
+          ldsm_x4(kf, tile_addr<HDP>(k_s, row, ks * 2 + ((lane >> 3) & 1)));
+          mma_bf16(s[2 * np], qf[ks], kf);
+          mma_bf16(s[2 * np + 1], qf[ks], kf + 2);
+        }
+      }
+    }
+    // mask and online softmax (rows gid and gid + 8 of this warp)
+    const int j_base = kb * FA_BN;
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int i = 0; i < FA_BN / 8; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int key = j_base + i * 8 + tig * 2 + (j & 1);
+        const int pr = p_row[j >> 1];
+        const bool vis = key <= pr && (window <= 0 || key > pr - window);
+        s[i][j] = vis ? s[i][j] * scale_log2 : -INFINITY;
+        m_new[j >> 1] = fmaxf(m_new[j >> 1], s[i][j]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
+      m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
+    }
+    float corr[2], l_add[2] = {0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+      corr[r] = m_new[r] > -INFINITY ? exp2f(m_run[r] - m_new[r]) : 1.f;
+    uint32_t pf[FA_BN / 16][4];
+#pragma unroll
+    for (int i = 0; i < FA_BN / 8; ++i) {
+      float p[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float mr = m_new[j >> 1];
+        p[j] = mr > -INFINITY ? exp2f(s[i][j] - mr) : 0.f;
+        l_add[j >> 1] += p[j];
+      }
+      pf[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
+      pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_run[r] = l_run[r] * corr[r] + l_add[r];
+      m_run[r] = m_new[r];
+    }
+#pragma unroll
+    for (int i = 0; i < NOT; ++i) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0];
+      o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
+    // O += P V: k-steps of 16 keys, n-tiles of 8 head elements (two per ldmatrix.x4.trans)
+#pragma unroll
+    for (int kk = 0; kk < FA_BN / 16; ++kk) {
+#pragma unroll
+      for (int np = 0; np < NOT / 2; ++np) {
+        if (np * 2 < n_ot) {
+          uint32_t vf[4];
+          const int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+          ldsm_x4_t(vf, tile_addr<HDP>(v_s, row, np * 2 + (lane >> 4)));
+          mma_bf16(o[2 * np], pf[kk], vf);
+          mma_bf16(o[2 * np + 1], pf[kk], vf + 2);
+        }
+      }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+  }
+
+  // rows' sums live spread over the four lanes of a quad
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + gid + r * 8;
+    if (row < rows) {
+      const float inv = 1.0f / l_run[r];
+      __nv_bfloat16* op = out + ((size_t)(qs + m0 + row) * H + h) * hd;
+#pragma unroll
+      for (int i = 0; i < NOT; ++i) {
+        if (i < n_ot) {
+          *reinterpret_cast<uint32_t*>(op + i * 8 + tig * 2) =
+              pack_bf16(o[i][r * 2] * inv, o[i][r * 2 + 1] * inv);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ decode
+// One query token per sequence; every key in the cache.  A block takes one chunk
+// of 128 positions of one (sequence, kv head, up to 16 query heads): the rows of
+// the MMA tile are the query heads that share the kv head, each warp takes 32 of
+// the chunk's keys, the four warps' results are merged in shared memory, and the
+// chunks of a query are merged by the block that finishes last (as in
+// attn_decode_kernel).  Maxima are kept in the log2 domain (scores times
+// log2(e)/sqrt(hd)).
+constexpr int FD_CHUNK = 128;
+constexpr int FD_ROWS = 16;
+
+template <int HDP>
+__global__ void __launch_bounds__(FA_THREADS)
+attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                       const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ seq_slot,
+                       const int* __restrict__ slot_pos, __nv_bfloat16* __restrict__ out,
+                       float* __restrict__ part_o, float* __restrict__ part_ml,
+                       int* __restrict__ counters, int* __restrict__ status, int H, int G, int hd,
+                       int capacity, int window, int max_chunks, float scale_log2) {
+  constexpr int NKS = HDP / 16, NOT = HDP / 8;
+  extern __shared__ __align__(128) uint8_t fa_smem[];
+  __shared__ float wm_s[FA_WARPS][FD_ROWS];                  // per warp: row max, row sum
+  __shared__ float wl_s[FA_WARPS][FD_ROWS];
+  __shared__ float row_m[FD_ROWS], row_l[FD_ROWS];
+  __shared__ int last_flag;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  const int R = H / G;
+  const int nhc = (R + FD_ROWS - 1) / FD_ROWS;
+  const int g = blockIdx.y / nhc, hchunk = blockIdx.y % nhc;
+  const int h0 = g * R + hchunk * FD_ROWS;
+  const int nh = min(FD_ROWS, R - hchunk * FD_ROWS);
+  const int t = blockIdx.z, c = blockIdx.x;
+  const int slot = seq_slot[t];
+  const int pos = slot_pos[slot];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int nkeys = pos - lo + 1;
+  const int n_active = (nkeys + FD_CHUNK - 1) / FD_CHUNK;
+  if (n_active > max_chunks && c == 0 && threadIdx.x == 0) atomicOr(status, ERR_CONTEXT_RANGE);
+  if (c >= n_active) return;
+  const int k_lo = lo + c * FD_CHUNK;
+  const int n = min(FD_CHUNK, pos + 1 - k_lo);
+  const int nks = hd >> 4, n_ot = hd >> 3;
+
+  const uint32_t k_s = smem_u32(fa_smem);
+  const uint32_t v_s = k_s + FD_CHUNK * HDP * 2;
+  const uint32_t q_s = v_s + FD_CHUNK * HDP * 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const __nv_bfloat16* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
+  const __nv_bfloat16* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
+  load_tile<HDP>(q_s, FD_ROWS, hd, q, [&](int r) -> const __nv_bfloat16* {
+    return r < nh ? q + ((size_t)t * H + h0 + r) * hd : nullptr;
+  });
+  load_tile<HDP>(k_s, FD_CHUNK, hd, q, [&](int r) -> const __nv_bfloat16* {
+    return r < n ? kc + (size_t)((k_lo + r) % capacity) * hd : nullptr;
+  });
+  load_tile<HDP>(v_s, FD_CHUNK, hd, q, [&](int r) -> const __nv_bfloat16* {
+    return r < n ? vc + (size_t)((k_lo + r) % capacity) * hd : nullptr;
+  });
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // this warp's 32 keys
+  const int key0 = warp * 32;
+  float s[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < NKS; ++ks) {
+    if (ks < nks) {
+      uint32_t qf[4];
+      ldsm_x4(qf, tile_addr<HDP>(q_s, lane & 15, ks * 2 + (lane >> 4)));
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        uint32_t kf[4];
+        const int row = key0 + np * 16 + (lane & 7) + ((lane >> 4) << 3);
+        ldsm_x4(kf, tile_addr<HDP>(k_s, row, ks * 2 + ((lane >> 3) & 1)));
+        mma_bf16(s[2 * np], qf, kf);
+        mma_bf16(s[2 * np + 1], qf, kf + 2);
+      }
+    }
+  }
+  float m_w[2] = {-INFINITY, -INFINITY}, l_w[2] = {0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int key = key0 + i * 8 + tig * 2 + (j & 1);
+      s[i][j] = key < n ? s[i][j] * scale_log2 : -INFINITY;
+      m_w[j >> 1] = fmaxf(m_w[j >> 1], s[i][j]);
+    }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    m_w[r] = fmaxf(m_w[r], __shfl_xor_sync(0xffffffffu, m_w[r], 1));
+    m_w[r] = fmaxf(m_w[r], __shfl_xor_sync(0xffffffffu, m_w[r], 2));
+  }
+  uint32_t pf[2][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float p[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float mr = m_w[j >> 1];
+      p[j] = mr > -INFINITY ? exp2f(s[i][j] - mr) : 0.f;
+      l_w[j >> 1] += p[j];
+    }
+    pf[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
+    pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 1);
+    l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 2);
+  }
+  float o[NOT][4];
+#pragma unroll
+  for (int i = 0; i < NOT; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+    for (int np = 0; np < NOT / 2; ++np) {
+      if (np * 2 < n_ot) {
+        uint32_t vf[4];
+        const int row = key0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        ldsm_x4_t(vf, tile_addr<HDP>(v_s, row, np * 2 + (lane >> 4)));
+        mma_bf16(o[2 * np], pf[kk], vf);
+        mma_bf16(o[2 * np + 1], pf[kk], vf + 2);
+      }
+    }
+  }
+  if (tig == 0) {
+    wm_s[warp][gid] = m_w[0]; wm_s[warp][gid + 8] = m_w[1];
+    wl_s[warp][gid] = l_w[0]; wl_s[warp][gid + 8] = l_w[1];
+  }
+  __syncthreads();                                           // K is no longer read: reuse it
+  float* o_s = reinterpret_cast<float*>(fa_smem);            // [warps][16 rows][hd]
+#pragma unroll
+  for (int i = 0; i < NOT; ++i) {
+    if (i < n_ot) {
+      float* p0 = o_s + ((size_t)warp * FD_ROWS + gid) * hd + i * 8 + tig * 2;
+      float* p1 = o_s + ((size_t)warp * FD_ROWS + gid + 8) * hd + i * 8 + tig * 2;
+      p0[0] = o[i][0]; p0[1] = o[i][1];
+      p1[0] = o[i][2]; p1[1] = o[i][3];
+    }
+  }
+  if (threadIdx.x < FD_ROWS) {
+    const int r = threadIdx.x;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < FA_WARPS; ++w) M = fmaxf(M, wm_s[w][r]);
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < FA_WARPS; ++w) {
+      const float f = wm_s[w][r] > -INFINITY ? exp2f(wm_s[w][r] - M) : 0.f;
+      wm_s[w][r] = f;                                         // now the warp's weight
+      L += wl_s[w][r] * f;
+    }
+    row_m[r] = M;
+    row_l[r] = L;
+  }
+  __syncthreads();
+  const size_t qh = (size_t)t * H + h0;
+  for (int idx = threadIdx.x; idx < nh * hd; idx += FA_THREADS) {
+    const int r = idx / hd, d = idx - r * hd;
+    float O = 0.f;
+#pragma unroll
+    for (int w = 0; w < FA_WARPS; ++w) O += o_s[((size_t)w * FD_ROWS + r) * hd + d] * wm_s[w][r];
+    if (n_active == 1) {
+      out[(qh + r) * hd + d] = __float2bfloat16_rn(O / row_l[r]);
+    } else {
+      const size_t pi = (qh + r) * max_chunks + c;
+      part_o[pi * hd + d] = O;
+      if (d == 0) { part_ml[pi * 2] = row_m[r]; part_ml[pi * 2 + 1] = row_l[r]; }
+    }
+  }
+  if (n_active == 1) return;
+
+  // the block that arrives last adds the chunks in order
+  __threadfence();
+  __syncthreads();
+  int* counter = counters + (size_t)t * gridDim.y + blockIdx.y;
+  if (threadIdx.x == 0) last_flag = (atomicAdd(counter, 1) == n_active - 1) ? 1 : 0;
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  if (threadIdx.x == 0) *counter = 0;
+  float* w_s = reinterpret_cast<float*>(fa_smem);            // [n_active][16 rows]
+  // weights: thread (r, lane group) layout -- 8 threads per row scan the chunks
+  {
+    const int r = threadIdx.x >> 3, part = threadIdx.x & 7;  // 16 rows x 8 threads
+    float M = -INFINITY;
+    if (r < nh)
+      for (int s2 = part; s2 < n_active; s2 += 8)
+        M = fmaxf(M, __ldcg(part_ml + ((qh + r) * max_chunks + s2) * 2));
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    float L = 0.f;
+    if (r < nh)
+      for (int s2 = part; s2 < n_active; s2 += 8) {
+        const float* ml = part_ml + ((qh + r) * max_chunks + s2) * 2;
+        const float ms = __ldcg(ml);
+        const float f = ms > -INFINITY ? exp2f(ms - M) : 0.f;
+        L += __ldcg(ml + 1) * f;
+        w_s[s2 * FD_ROWS + r] = f;
+      }
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+    if (part == 0 && r < nh) row_l[r] = L;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nh * hd; idx += FA_THREADS) {
+    const int r = idx / hd, d = idx - r * hd;
+    const float* po = part_o + (qh + r) * max_chunks * hd + d;
+    float O = 0.f;
+    int s2 = 0;
+    for (; s2 + 8 <= n_active; s2 += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __ldcg(po + (size_t)(s2 + j) * hd);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) O = fmaf(v[j], w_s[(s2 + j) * FD_ROWS + r], O);
+    }
+    for (; s2 < n_active; ++s2) O = fmaf(__ldcg(po + (size_t)s2 * hd), w_s[s2 * FD_ROWS + r], O);
+    out[(qh + r) * hd + d] = __float2bfloat16_rn(O / row_l[r]);
+  }
+}
+
+template <int HDP>
+static int launch_decode_mma(const void* q, const void* k_cache, const void* v_cache,
+                             const int* seq_slot, const int* slot_pos, void* out, float* part_o,
+                             float* part_ml, int* counters, int* status, int n_seqs, int H, int G,
+                             int hd, int capacity, int window, int max_chunks,
+                             cudaStream_t stream) {
+  const size_t smem = (size_t)(2 * FD_CHUNK + FD_ROWS) * HDP * 2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HDP>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int nhc = (H / G + FD_ROWS - 1) / FD_ROWS;
+  const dim3 grid(max_chunks, G * nhc, n_seqs);
+  const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
+  launch_pdl(attn_decode_mma_kernel<HDP>, grid, dim3(FA_THREADS), smem, stream,
+             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+             seq_slot, slot_pos, (__nv_bfloat16*)out, part_o, part_ml, counters, status, H, G, hd,
+             capacity, window, max_chunks, scale_log2);
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+template <int HDP>
+static int launch_prefill(const void* q, const void* kv_step, const void* k_cache,
+                          const void* v_cache, const int* q_start, const int* seq_slot,
+                          const int* slot_pos, void* out, int n_seqs, int max_q_len, int H, int G,
+                          int hd, int capacity, int window, cudaStream_t stream) {
+  const size_t smem = (size_t)(FA_BM + 4 * FA_BN) * HDP * 2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HDP>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const dim3 grid((max_q_len + FA_BM - 1) / FA_BM, H, n_seqs);
+  const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
+  launch_pdl(attn_prefill_mma_kernel<HDP>, grid, dim3(FA_THREADS), smem, stream,
+             (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv_step, (const __nv_bfloat16*)k_cache,
+             (const __nv_bfloat16*)v_cache, q_start, seq_slot, slot_pos, (__nv_bfloat16*)out, H, G,
+             hd, capacity, window, scale_log2);
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace yalm
+
+using namespace yalm;
+
+// Prefill attention on tensor cores (bfloat16).  Sequences are given by q_start
+// [n_seqs + 1]; max_q_len is the longest of them (it sizes the grid).  Head sizes:
+// multiples of 16 up to 128 (others: use yalm_attention).
+extern "C" int yalm_attention_prefill_mma(const void* q, const void* kv_step, const void* k_cache,
+                                          const void* v_cache, const int* q_start,
+                                          const int* seq_slot, const int* slot_pos, void* out,
+                                          int n_seqs, int max_q_len, int H, int G, int hd,
+                                          int capacity, int window, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0) return 0;
+  if (hd % 16 != 0 || hd > 128 || hd <= 0) return -2;
+  if (G <= 0 || H % G != 0) return -3;
+  if (H > 65535 || n_seqs > 65535) return -4;
+  if (hd <= 64)
+    return launch_prefill<64>(q, kv_step, k_cache, v_cache, q_start, seq_slot, slot_pos, out,
+                              n_seqs, max_q_len, H, G, hd, capacity, window, stream);
+  return launch_prefill<128>(q, kv_step, k_cache, v_cache, q_start, seq_slot, slot_pos, out, n_seqs,
+                             max_q_len, H, G, hd, capacity, window, stream);
+}
+
+// Decode attention on tensor cores (bfloat16): one query per sequence over the
+// cache, chunks of 128 positions.  part_o [n, H, max_chunks, hd] and part_ml
+// [n, H, max_chunks, 2] floats with max_chunks = ceil(visible / 128), visible =
+// min(max_context, window); counters: n * G * ceil((H/G)/16) ints, zero before the
+// first launch.  Head sizes: multiples of 16 up to 128.
+extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
+                                         const int* seq_slot, const int* slot_pos, void* out,
+                                         float* part_o, float* part_ml, int* counters, int* status,
+                                         int n_seqs, int H, int G, int hd, int capacity,
+                                         int window, int max_context, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (hd % 16 != 0 || hd > 128 || hd <= 0) return -2;
+  if (G <= 0 || H % G != 0) return -3;
+  if (max_context <= 0 || n_seqs > 65535) return -4;
+  const int visible = window > 0 && window < max_context ? window : max_context;
+  const int max_chunks = (visible + FD_CHUNK - 1) / FD_CHUNK;
+  if ((size_t)G * ((H / G + FD_ROWS - 1) / FD_ROWS) > 65535) return -4;
+  if (hd <= 64)
+    return launch_decode_mma<64>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,
+                                 counters, status, n_seqs, H, G, hd, capacity, window, max_chunks,
+                                 stream);
+  return launch_decode_mma<128>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,
+                                counters, status, n_seqs, H, G, hd, capacity, window, max_chunks,
+                                stream);
+}

@@ -56,6 +56,10 @@ _SIGNATURES = {
                        _i, _i, _i, _vp],
     "yalm_attention_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                               _i, _i, _i, _i, _vp],
+    "yalm_attention_prefill_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                                   _i, _vp],
+    "yalm_attention_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
+                                  _i, _i, _i, _vp],
     "yalm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp],
     "yalm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
@@ -220,6 +224,44 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                                        dtype_code(q.dtype), n, H, G, hd, capacity,
                                        int(window or 0), chunk, max_context, _stream()),
            "attention_decode")
+
+
+def mma_attention_usable(dtype: torch.dtype, hd: int) -> bool:
+    """The tensor-core attention kernels take bfloat16 and head sizes in steps of 16 up to 128."""
+    return dtype == torch.bfloat16 and hd % 16 == 0 and 0 < hd <= 128
+
+
+def attention_prefill_mma(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
+                          v_cache: torch.Tensor, batch, slot_pos: torch.Tensor, out: torch.Tensor,
+                          H: int, G: int, hd: int, capacity: int, window: Optional[int]) -> None:
+    _need(q.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16,
+          "attention_prefill_mma: bfloat16 only")
+    _check(lib().yalm_attention_prefill_mma(_p(q), _p(kv_step), _p(k_cache), _p(v_cache),
+                                            _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos),
+                                            _p(out), batch.n_seqs, max(batch.q_lens), H, G, hd,
+                                            capacity, int(window or 0), _stream()),
+           "attention_prefill_mma")
+
+
+def attention_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                         seq_slot: torch.Tensor, slot_pos: torch.Tensor, out: torch.Tensor,
+                         part_o: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
+                         status: torch.Tensor, H: int, G: int, hd: int, capacity: int,
+                         window: Optional[int], max_context: int) -> None:
+    n = q.shape[0]
+    _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16,
+          "attention_decode_mma: bfloat16 only")
+    visible = min(max_context, window) if window else max_context
+    max_chunks = -(-visible // 128)
+    hc = -(-(H // G) // 16)
+    _need(part_o.numel() >= n * H * max_chunks * hd and part_ml.numel() >= n * H * max_chunks * 2
+          and counters.numel() >= n * G * hc and counters.dtype == torch.int32,
+          "attention_decode_mma: workspace")
+    _check(lib().yalm_attention_decode_mma(_p(q), _p(k_cache), _p(v_cache), _p(seq_slot),
+                                           _p(slot_pos), _p(out), _p(part_o), _p(part_ml),
+                                           _p(counters), _p(status), n, H, G, hd, capacity,
+                                           int(window or 0), max_context, _stream()),
+           "attention_decode_mma")
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

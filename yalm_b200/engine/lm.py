@@ -38,10 +38,10 @@ def _dtype(d) -> torch.dtype:
 class LM:
     def __init__(self, config: Any, tensors: Dict[str, torch.Tensor], dtype="bfloat16",
                  max_context: Optional[int] = None, max_batch: int = 8, device="cuda:0",
-                 gemm: str = "auto"):
+                 gemm: str = "auto", attention: str = "auto"):
         self.config = config
         self.spec = config.to_spec()
-        self.rt = Runtime(_dtype(dtype), device, gemm=gemm)
+        self.rt = Runtime(_dtype(dtype), device, gemm=gemm, attention=attention)
         self.model = Model(self.spec, self.rt)
         self.model.bind(tensors)
         context = self.spec.max_positions if not max_context else min(int(max_context),

@@ -69,27 +69,44 @@ class GQAAttention:
         # a layer whose cache another run entry reads keeps its step keys apart
         kv_step = view.kv_step if getattr(view, "kv_step", None) is not None else \
             rt.buffer("kv_step", (n, 2, G, hd), rt.dtype)
+        # Several tokens on top of a ring that is already full: their rows would
+        # replace keys that the first of them still has to see, so the ring is
+        # written after the attention instead of before it.
+        late_write = (not shared) and any(
+            p > 0 and ql > 1 and p + ql > view.capacity for p, ql in zip(batch.past, batch.q_lens))
         if shared:
             # this run reads the owner's keys and values: rotate q only
             scratch = rt.buffer("kv_step_unused", (n, 2, G, hd), rt.dtype)
             self.position.rotate_and_store(qkv, S, batch, view, q, scratch, H, G,
                                            write_cache=False)
         else:
-            self.position.rotate_and_store(qkv, S, batch, view, q, kv_step, H, G)
+            self.position.rotate_and_store(qkv, S, batch, view, q, kv_step, H, G,
+                                           write_cache=not late_write)
         o = rt.buffer("attn_out", (n, H * hd), rt.dtype)
+        tensor_cores = ops.mma_attention_usable(rt.dtype, hd) and rt.attention != "simt"
         if batch.is_decode:
-            # one query per sequence, every key in the cache: the bulk-copy kernel
-            chunk = self.decode_chunk(batch)
+            # one query per sequence, every key already in the cache
+            chunk = 128 if tensor_cores else self.decode_chunk(batch)
             bound = max(1, batch.ctx_bound)
             visible = min(bound, self.window) if self.window else bound
             max_chunks = -(-visible // chunk)
             part_o = rt.buffer("attn_part_o", (n, H, max_chunks, hd), torch.float32)
             part_ml = rt.buffer("attn_part_ml", (n, H, max_chunks, 2), torch.float32)
             counters = rt.zeros("attn_counters", n * G * -(-(H // G) // 4))
-            ops.attention_decode(q, view.k, view.v, batch.seq_slot, view.slot_pos, o, part_o,
-                                 part_ml, counters, rt.status, H, G, hd, view.capacity,
-                                 self.window, chunk, bound)
+            if tensor_cores:
+                ops.attention_decode_mma(q, view.k, view.v, batch.seq_slot, view.slot_pos, o,
+                                         part_o, part_ml, counters, rt.status, H, G, hd,
+                                         view.capacity, self.window, bound)
+            else:
+                ops.attention_decode(q, view.k, view.v, batch.seq_slot, view.slot_pos, o, part_o,
+                                     part_ml, counters, rt.status, H, G, hd, view.capacity,
+                                     self.window, chunk, bound)
+        elif tensor_cores:
+            ops.attention_prefill_mma(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G,
+                                      hd, view.capacity, self.window)
         else:
             ops.attention(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
                           view.capacity, self.window, 1, None, None)
+        if late_write:
+            self.position.rotate_and_store(qkv, S, batch, view, q, kv_step, H, G, write_cache=True)
         stream.add_linear(o, self.w_o)

@@ -64,7 +64,8 @@ class Runtime:
     named scratch buffers that keep their address from step to step (a captured
     CUDA graph relies on that)."""
 
-    def __init__(self, dtype: torch.dtype, device="cuda:0", gemm: str = "auto"):
+    def __init__(self, dtype: torch.dtype, device="cuda:0", gemm: str = "auto",
+                 attention: str = "auto"):
         if dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"compute type must be float32 or bfloat16, not {dtype}")
         self.dtype = dtype
@@ -74,6 +75,7 @@ class Runtime:
                                "there is no CPU path")
         ops.lib()   # builds/loads the kernels now: a missing library fails here, loudly
         self.gemm = gemm                      # "auto" | "simt" (debugging aid: no tensor cores)
+        self.attention = attention            # "auto" | "simt" (likewise for attention)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._buffers: Dict[str, torch.Tensor] = {}
         self._shared = []
@@ -86,7 +88,7 @@ class Runtime:
         """A runtime without a device: parts can be built and asked for the
         tensors they need (random-weights mode, checks), but not run."""
         rt = cls.__new__(cls)
-        rt.dtype, rt.device, rt.gemm = dtype, torch.device("cpu"), "auto"
+        rt.dtype, rt.device, rt.gemm, rt.attention = dtype, torch.device("cpu"), "auto", "auto"
         rt.status, rt._buffers, rt._shared = None, {}, []
         rt.frozen, rt.sm_count, rt.buffer_generation = True, 148, 0
         return rt
