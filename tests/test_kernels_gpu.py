@@ -407,16 +407,15 @@ def test_tensor_core_decode_attention(ops, H, G, hd, cap, window):
         slot_pos[s] = n - 1
     seq_slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
     bound = max(lens)
-    visible = min(bound, window) if window else bound
-    mc = -(-visible // 128)
-    part_o = torch.empty(Bn * H * mc * hd, device=DEV)
-    part_ml = torch.empty(Bn * H * mc * 2, device=DEV)
     counters = torch.zeros(Bn * G * -(-(H // G) // 16), dtype=torch.int32, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    for rep in range(2):
+    for rep, cpc in enumerate((1, 3, 1000)):                   # merged parts ... one block per query
+        mc = ops.decode_mma_parts(bound, window, cpc)
+        part_o = torch.empty(Bn * H * mc * hd, device=DEV)
+        part_ml = torch.empty(Bn * H * mc * 2, device=DEV)
         out = torch.zeros(Bn, H * hd, device=DEV, dtype=dt)
         ops.attention_decode_mma(q, kc, vc, seq_slot, slot_pos, out, part_o, part_ml, counters,
-                                 status, H, G, hd, cap, window, bound)
+                                 status, H, G, hd, cap, window, bound, cpc)
         torch.cuda.synchronize()
         assert status.item() == 0 and int(counters.abs().sum()) == 0
         for b, (s, n) in enumerate(zip(slots, lens)):

@@ -49,7 +49,7 @@ int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_
                               const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                               float* part_ml, int* counters, int* status, int n_seqs, int H, int G,
                               int hd, int capacity, int window, int max_context,
-                              cudaStream_t stream);
+                              int chunks_per_block, cudaStream_t stream);
 
 int yalm_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* out,
                    int out_dtype, int M, int N, int K, int accumulate, cudaStream_t stream);

@@ -77,6 +77,28 @@ __device__ __forceinline__ void load_tile(uint32_t base, int rows, int hd,
   }
 }
 
+// Loads `n` consecutive positions of a cache ring (rows first_row, first_row + 1, ...
+// modulo capacity) into a swizzled tile and zero-fills rows n..rows-1.  Each thread
+// keeps one 16-byte column and steps through the rows, so the row arithmetic is an
+// add and a compare per copy.
+template <int HDP>
+__device__ __forceinline__ void load_ring_tile(uint32_t base, int rows, int n, int hd,
+                                               const __nv_bfloat16* ring, int first_row,
+                                               int capacity) {
+  const int cpr = hd >> 3;
+  const int rstep = FA_THREADS / cpr;                         // rows covered per pass
+  if ((int)threadIdx.x >= rstep * cpr) return;
+  const int ch = threadIdx.x % cpr;
+  int r = threadIdx.x / cpr;
+  int row = (first_row + r) % capacity;
+  const int wrap = rstep % capacity;
+  for (; r < rows; r += rstep) {
+    cp_async16(tile_addr<HDP>(base, r, ch), ring + (size_t)row * hd + ch * 8, r < n);
+    row += wrap;
+    if (row >= capacity) row -= capacity;
+  }
+}
+
 // ----------------------------------------------------------------- prefill
 // grid (query tiles of a sequence, heads, sequences); a block takes 64 query
 // tokens of one head.  scale_log2 = log2(e) / sqrt(hd).
@@ -271,15 +293,18 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 }
 
 // ------------------------------------------------------------------ decode
-// One query token per sequence; every key in the cache.  A block takes one chunk
-// of 128 positions of one (sequence, kv head, up to 16 query heads): the rows of
-// the MMA tile are the query heads that share the kv head, each warp takes 32 of
-// the chunk's keys, the four warps' results are merged in shared memory, and the
-// chunks of a query are merged by the block that finishes last (as in
-// attn_decode_kernel).  Maxima are kept in the log2 domain (scores times
-// log2(e)/sqrt(hd)).
-constexpr int FD_CHUNK = 128;
+// One query token per sequence; every key in the cache.  The rows of the MMA
+// tile are the (up to 16) query heads that share a kv head.  A block takes a run
+// of `cpc` consecutive chunks of 64 positions of one (sequence, kv head, head
+// group) and walks through them with double-buffered cp.async staging and an
+// online softmax; each warp takes 16 of a chunk's keys.  With few sequences cpc
+// is small, so that many blocks work on one sequence at once and the block that
+// finishes last merges their partial results (as in attn_decode_kernel); with many
+// sequences cpc covers the whole sequence and nothing is merged.  Maxima are
+// kept in the log2 domain (scores times log2(e)/sqrt(hd)).
+constexpr int FD_CHUNK = 64;
 constexpr int FD_ROWS = 16;
+constexpr int FD_STAGES = 3;       // chunks in flight or in use per block
 
 template <int HDP>
 __global__ void __launch_bounds__(FA_THREADS)
@@ -288,8 +313,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                        const int* __restrict__ slot_pos, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ part_o, float* __restrict__ part_ml,
                        int* __restrict__ counters, int* __restrict__ status, int H, int G, int hd,
-                       int capacity, int window, int max_chunks, float scale_log2) {
+                       int capacity, int window, int cpc, int max_parts, float scale_log2) {
   constexpr int NKS = HDP / 16, NOT = HDP / 8;
+  constexpr int STAGE = 2 * FD_CHUNK * HDP * 2;              // K and V of one chunk, bytes
   extern __shared__ __align__(128) uint8_t fa_smem[];
   __shared__ float wm_s[FA_WARPS][FD_ROWS];                  // per warp: row max, row sum
   __shared__ float wl_s[FA_WARPS][FD_ROWS];
@@ -303,115 +329,137 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   const int g = blockIdx.y / nhc, hchunk = blockIdx.y % nhc;
   const int h0 = g * R + hchunk * FD_ROWS;
   const int nh = min(FD_ROWS, R - hchunk * FD_ROWS);
-  const int t = blockIdx.z, c = blockIdx.x;
+  const int t = blockIdx.z, part = blockIdx.x;
   const int slot = seq_slot[t];
   const int pos = slot_pos[slot];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int nkeys = pos - lo + 1;
-  const int n_active = (nkeys + FD_CHUNK - 1) / FD_CHUNK;
-  if (n_active > max_chunks && c == 0 && threadIdx.x == 0) atomicOr(status, ERR_CONTEXT_RANGE);
-  if (c >= n_active) return;
-  const int k_lo = lo + c * FD_CHUNK;
-  const int n = min(FD_CHUNK, pos + 1 - k_lo);
+  const int n_chunks = (nkeys + FD_CHUNK - 1) / FD_CHUNK;
+  const int n_parts = (n_chunks + cpc - 1) / cpc;
+  if (n_parts > max_parts && part == 0 && threadIdx.x == 0) atomicOr(status, ERR_CONTEXT_RANGE);
+  if (part >= n_parts) return;
+  const int c0 = part * cpc, c1 = min(n_chunks, c0 + cpc);
   const int nks = hd >> 4, n_ot = hd >> 3;
 
-  const uint32_t k_s = smem_u32(fa_smem);
-  const uint32_t v_s = k_s + FD_CHUNK * HDP * 2;
-  const uint32_t q_s = v_s + FD_CHUNK * HDP * 2;
+  const uint32_t kv_s = smem_u32(fa_smem);                   // FD_STAGES stages of (K, V)
+  const uint32_t q_s = kv_s + FD_STAGES * STAGE;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
   const __nv_bfloat16* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
   const __nv_bfloat16* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
+  auto load_chunk = [&](int c, int stage) {
+    const int k_lo = lo + c * FD_CHUNK;
+    const int n = min(FD_CHUNK, pos + 1 - k_lo);
+    load_ring_tile<HDP>(kv_s + stage * STAGE, FD_CHUNK, n, hd, kc, k_lo % capacity, capacity);
+    load_ring_tile<HDP>(kv_s + stage * STAGE + FD_CHUNK * HDP * 2, FD_CHUNK, n, hd, vc,
+                        k_lo % capacity, capacity);
+  };
   load_tile<HDP>(q_s, FD_ROWS, hd, q, [&](int r) -> const __nv_bfloat16* {
     return r < nh ? q + ((size_t)t * H + h0 + r) * hd : nullptr;
   });
-  load_tile<HDP>(k_s, FD_CHUNK, hd, q, [&](int r) -> const __nv_bfloat16* {
-    return r < n ? kc + (size_t)((k_lo + r) % capacity) * hd : nullptr;
-  });
-  load_tile<HDP>(v_s, FD_CHUNK, hd, q, [&](int r) -> const __nv_bfloat16* {
-    return r < n ? vc + (size_t)((k_lo + r) % capacity) * hd : nullptr;
-  });
-  cp_async_commit();
-  cp_async_wait<0>();
-  __syncthreads();
+  // FD_STAGES - 1 chunks are requested before the first is used
+#pragma unroll
+  for (int i = 0; i < FD_STAGES - 1; ++i) {
+    if (c0 + i < c1) load_chunk(c0 + i, i);
+    cp_async_commit();
+  }
 
-  // this warp's 32 keys
-  const int key0 = warp * 32;
-  float s[4][4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
-#pragma unroll
-  for (int ks = 0; ks < NKS; ++ks) {
-    if (ks < nks) {
-      uint32_t qf[4];
-      ldsm_x4(qf, tile_addr<HDP>(q_s, lane & 15, ks * 2 + (lane >> 4)));
-#pragma unroll
-      for (int np = 0; np < 2; ++np) {
-        uint32_t kf[4];
-        const int row = key0 + np * 16 + (lane & 7) + ((lane >> 4) << 3);
-        ldsm_x4(kf, tile_addr<HDP>(k_s, row, ks * 2 + ((lane >> 3) & 1)));
-        mma_bf16(s[2 * np], qf, kf);
-        mma_bf16(s[2 * np + 1], qf, kf + 2);
-      }
-    }
-  }
-  float m_w[2] = {-INFINITY, -INFINITY}, l_w[2] = {0.f, 0.f};
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int key = key0 + i * 8 + tig * 2 + (j & 1);
-      s[i][j] = key < n ? s[i][j] * scale_log2 : -INFINITY;
-      m_w[j >> 1] = fmaxf(m_w[j >> 1], s[i][j]);
-    }
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    m_w[r] = fmaxf(m_w[r], __shfl_xor_sync(0xffffffffu, m_w[r], 1));
-    m_w[r] = fmaxf(m_w[r], __shfl_xor_sync(0xffffffffu, m_w[r], 2));
-  }
-  uint32_t pf[2][4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float p[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float mr = m_w[j >> 1];
-      p[j] = mr > -INFINITY ? exp2f(s[i][j] - mr) : 0.f;
-      l_w[j >> 1] += p[j];
-    }
-    pf[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
-    pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
-  }
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 1);
-    l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 2);
-  }
   float o[NOT][4];
 #pragma unroll
   for (int i = 0; i < NOT; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+  float m_w[2] = {-INFINITY, -INFINITY}, l_w[2] = {0.f, 0.f};
+  const int key0 = warp * 16;                                // this warp's keys inside a chunk
+
+  for (int c = c0; c < c1; ++c) {
+    const int stage = (c - c0) % FD_STAGES;
+    cp_async_wait<FD_STAGES - 2>();                          // chunk c (and Q) have landed
+    __syncthreads();                                         // ... and chunk c-1 is no longer read
+    if (c + FD_STAGES - 1 < c1) load_chunk(c + FD_STAGES - 1, (c - c0 + FD_STAGES - 1) % FD_STAGES);
+    cp_async_commit();
+    const uint32_t k_s = kv_s + stage * STAGE, v_s = k_s + FD_CHUNK * HDP * 2;
+    const int n = min(FD_CHUNK, pos + 1 - (lo + c * FD_CHUNK));
+
+    float s[2][4];
 #pragma unroll
-  for (int kk = 0; kk < 2; ++kk) {
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < NKS; ++ks) {
+      if (ks < nks) {
+        uint32_t qf[4], kf[4];
+        ldsm_x4(qf, tile_addr<HDP>(q_s, lane & 15, ks * 2 + (lane >> 4)));
+        const int row = key0 + (lane & 7) + ((lane >> 4) << 3);
+        ldsm_x4(kf, tile_addr<HDP>(k_s, row, ks * 2 + ((lane >> 3) & 1)));
+        mma_bf16(s[0], qf, kf);
+        mma_bf16(s[1], qf, kf + 2);
+      }
+    }
+    float m_new[2] = {m_w[0], m_w[1]};
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int key = key0 + i * 8 + tig * 2 + (j & 1);
+        s[i][j] = key < n ? s[i][j] * scale_log2 : -INFINITY;
+        m_new[j >> 1] = fmaxf(m_new[j >> 1], s[i][j]);
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
+      m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
+    }
+    float corr[2], l_add[2] = {0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) corr[r] = m_new[r] > -INFINITY ? exp2f(m_w[r] - m_new[r]) : 1.f;
+    uint32_t pf[4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float p[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float mr = m_new[j >> 1];
+        p[j] = mr > -INFINITY ? exp2f(s[i][j] - mr) : 0.f;
+        l_add[j >> 1] += p[j];
+      }
+      pf[i * 2 + 0] = pack_bf16(p[0], p[1]);
+      pf[i * 2 + 1] = pack_bf16(p[2], p[3]);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_w[r] = l_w[r] * corr[r] + l_add[r];                  // each lane: its own columns' share
+      m_w[r] = m_new[r];
+    }
+#pragma unroll
+    for (int i = 0; i < NOT; ++i) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0];
+      o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
 #pragma unroll
     for (int np = 0; np < NOT / 2; ++np) {
       if (np * 2 < n_ot) {
         uint32_t vf[4];
-        const int row = key0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        const int row = key0 + (lane & 7) + (((lane >> 3) & 1) << 3);
         ldsm_x4_t(vf, tile_addr<HDP>(v_s, row, np * 2 + (lane >> 4)));
-        mma_bf16(o[2 * np], pf[kk], vf);
-        mma_bf16(o[2 * np + 1], pf[kk], vf + 2);
+        mma_bf16(o[2 * np], pf, vf);
+        mma_bf16(o[2 * np + 1], pf, vf + 2);
       }
     }
+  }
+  cp_async_wait<0>();
+  __syncthreads();                                           // the staging area is free
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 1);
+    l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 2);
   }
   if (tig == 0) {
     wm_s[warp][gid] = m_w[0]; wm_s[warp][gid + 8] = m_w[1];
     wl_s[warp][gid] = l_w[0]; wl_s[warp][gid + 8] = l_w[1];
   }
-  __syncthreads();                                           // K is no longer read: reuse it
+  // merge the four warps (they saw different keys): partial outputs over the staging area
   float* o_s = reinterpret_cast<float*>(fa_smem);            // [warps][16 rows][hd]
 #pragma unroll
   for (int i = 0; i < NOT; ++i) {
@@ -422,6 +470,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
       p1[0] = o[i][2]; p1[1] = o[i][3];
     }
   }
+  __syncthreads();
   if (threadIdx.x < FD_ROWS) {
     const int r = threadIdx.x;
     float M = -INFINITY;
@@ -444,39 +493,38 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     float O = 0.f;
 #pragma unroll
     for (int w = 0; w < FA_WARPS; ++w) O += o_s[((size_t)w * FD_ROWS + r) * hd + d] * wm_s[w][r];
-    if (n_active == 1) {
+    if (n_parts == 1) {
       out[(qh + r) * hd + d] = __float2bfloat16_rn(O / row_l[r]);
     } else {
-      const size_t pi = (qh + r) * max_chunks + c;
+      const size_t pi = (qh + r) * max_parts + part;
       part_o[pi * hd + d] = O;
       if (d == 0) { part_ml[pi * 2] = row_m[r]; part_ml[pi * 2 + 1] = row_l[r]; }
     }
   }
-  if (n_active == 1) return;
+  if (n_parts == 1) return;
 
-  // the block that arrives last adds the chunks in order
+  // the block that arrives last adds the parts in order
   __threadfence();
   __syncthreads();
   int* counter = counters + (size_t)t * gridDim.y + blockIdx.y;
-  if (threadIdx.x == 0) last_flag = (atomicAdd(counter, 1) == n_active - 1) ? 1 : 0;
+  if (threadIdx.x == 0) last_flag = (atomicAdd(counter, 1) == n_parts - 1) ? 1 : 0;
   __syncthreads();
   if (!last_flag) return;
   __threadfence();
   if (threadIdx.x == 0) *counter = 0;
-  float* w_s = reinterpret_cast<float*>(fa_smem);            // [n_active][16 rows]
-  // weights: thread (r, lane group) layout -- 8 threads per row scan the chunks
+  float* w_s = reinterpret_cast<float*>(fa_smem);            // [n_parts][16 rows]
   {
-    const int r = threadIdx.x >> 3, part = threadIdx.x & 7;  // 16 rows x 8 threads
+    const int r = threadIdx.x >> 3, sub = threadIdx.x & 7;   // 16 rows x 8 threads
     float M = -INFINITY;
     if (r < nh)
-      for (int s2 = part; s2 < n_active; s2 += 8)
-        M = fmaxf(M, __ldcg(part_ml + ((qh + r) * max_chunks + s2) * 2));
+      for (int s2 = sub; s2 < n_parts; s2 += 8)
+        M = fmaxf(M, __ldcg(part_ml + ((qh + r) * max_parts + s2) * 2));
 #pragma unroll
     for (int off = 4; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
     float L = 0.f;
     if (r < nh)
-      for (int s2 = part; s2 < n_active; s2 += 8) {
-        const float* ml = part_ml + ((qh + r) * max_chunks + s2) * 2;
+      for (int s2 = sub; s2 < n_parts; s2 += 8) {
+        const float* ml = part_ml + ((qh + r) * max_parts + s2) * 2;
         const float ms = __ldcg(ml);
         const float f = ms > -INFINITY ? exp2f(ms - M) : 0.f;
         L += __ldcg(ml + 1) * f;
@@ -484,22 +532,22 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
       }
 #pragma unroll
     for (int off = 4; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
-    if (part == 0 && r < nh) row_l[r] = L;
+    if (sub == 0 && r < nh) row_l[r] = L;
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < nh * hd; idx += FA_THREADS) {
     const int r = idx / hd, d = idx - r * hd;
-    const float* po = part_o + (qh + r) * max_chunks * hd + d;
+    const float* po = part_o + (qh + r) * max_parts * hd + d;
     float O = 0.f;
     int s2 = 0;
-    for (; s2 + 8 <= n_active; s2 += 8) {
+    for (; s2 + 8 <= n_parts; s2 += 8) {
       float v[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = __ldcg(po + (size_t)(s2 + j) * hd);
 #pragma unroll
       for (int j = 0; j < 8; ++j) O = fmaf(v[j], w_s[(s2 + j) * FD_ROWS + r], O);
     }
-    for (; s2 < n_active; ++s2) O = fmaf(__ldcg(po + (size_t)s2 * hd), w_s[s2 * FD_ROWS + r], O);
+    for (; s2 < n_parts; ++s2) O = fmaf(__ldcg(po + (size_t)s2 * hd), w_s[s2 * FD_ROWS + r], O);
     out[(qh + r) * hd + d] = __float2bfloat16_rn(O / row_l[r]);
   }
 }
@@ -508,23 +556,25 @@ template <int HDP>
 static int launch_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                              const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                              float* part_ml, int* counters, int* status, int n_seqs, int H, int G,
-                             int hd, int capacity, int window, int max_chunks,
+                             int hd, int capacity, int window, int cpc, int max_parts,
                              cudaStream_t stream) {
-  const size_t smem = (size_t)(2 * FD_CHUNK + FD_ROWS) * HDP * 2;
-  static bool attr_set = false;
-  if (!attr_set) {
+  size_t smem = (size_t)(2 * FD_STAGES * FD_CHUNK + FD_ROWS) * HDP * 2;   // (K, V) stages and Q
+  const size_t merge = (size_t)FA_WARPS * FD_ROWS * hd * 4;  // the warps' partial outputs
+  if (smem < merge) smem = merge;
+  static size_t attr_smem = 0;
+  if (smem > attr_smem) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HDP>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+    attr_smem = smem;
   }
   const int nhc = (H / G + FD_ROWS - 1) / FD_ROWS;
-  const dim3 grid(max_chunks, G * nhc, n_seqs);
+  const dim3 grid(max_parts, G * nhc, n_seqs);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
   launch_pdl(attn_decode_mma_kernel<HDP>, grid, dim3(FA_THREADS), smem, stream,
              (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
              seq_slot, slot_pos, (__nv_bfloat16*)out, part_o, part_ml, counters, status, H, G, hd,
-             capacity, window, max_chunks, scale_log2);
+             capacity, window, cpc, max_parts, scale_log2);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -576,27 +626,30 @@ extern "C" int yalm_attention_prefill_mma(const void* q, const void* kv_step, co
 }
 
 // Decode attention on tensor cores (bfloat16): one query per sequence over the
-// cache, chunks of 128 positions.  part_o [n, H, max_chunks, hd] and part_ml
-// [n, H, max_chunks, 2] floats with max_chunks = ceil(visible / 128), visible =
-// min(max_context, window); counters: n * G * ceil((H/G)/16) ints, zero before the
+// cache.  A block walks through `chunks_per_block` chunks of 64 positions; a
+// sequence needs parts = ceil(ceil(visible / 64) / chunks_per_block) blocks, with
+// visible = min(max_context, window).  part_o [n, H, parts, hd] and part_ml
+// [n, H, parts, 2] floats; counters: n * G * ceil((H/G)/16) ints, zero before the
 // first launch.  Head sizes: multiples of 16 up to 128.
 extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                                          const int* seq_slot, const int* slot_pos, void* out,
                                          float* part_o, float* part_ml, int* counters, int* status,
                                          int n_seqs, int H, int G, int hd, int capacity,
-                                         int window, int max_context, cudaStream_t stream) {
+                                         int window, int max_context, int chunks_per_block,
+                                         cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (hd % 16 != 0 || hd > 128 || hd <= 0) return -2;
   if (G <= 0 || H % G != 0) return -3;
-  if (max_context <= 0 || n_seqs > 65535) return -4;
+  if (max_context <= 0 || n_seqs > 65535 || chunks_per_block < 1) return -4;
   const int visible = window > 0 && window < max_context ? window : max_context;
   const int max_chunks = (visible + FD_CHUNK - 1) / FD_CHUNK;
+  const int max_parts = (max_chunks + chunks_per_block - 1) / chunks_per_block;
   if ((size_t)G * ((H / G + FD_ROWS - 1) / FD_ROWS) > 65535) return -4;
   if (hd <= 64)
     return launch_decode_mma<64>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,
-                                 counters, status, n_seqs, H, G, hd, capacity, window, max_chunks,
-                                 stream);
+                                 counters, status, n_seqs, H, G, hd, capacity, window,
+                                 chunks_per_block, max_parts, stream);
   return launch_decode_mma<128>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,
-                                counters, status, n_seqs, H, G, hd, capacity, window, max_chunks,
-                                stream);
+                                counters, status, n_seqs, H, G, hd, capacity, window,
+                                chunks_per_block, max_parts, stream);
 }

@@ -59,7 +59,7 @@ _SIGNATURES = {
     "yalm_attention_prefill_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                    _i, _vp],
     "yalm_attention_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
-                                  _i, _i, _i, _vp],
+                                  _i, _i, _i, _i, _vp],
     "yalm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp],
     "yalm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
@@ -243,24 +243,30 @@ def attention_prefill_mma(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch
            "attention_prefill_mma")
 
 
+def decode_mma_parts(max_context: int, window: Optional[int], chunks_per_block: int) -> int:
+    """Blocks (partial results) per query of attention_decode_mma."""
+    visible = min(max_context, window) if window else max_context
+    return -(-(-(-visible // 64)) // chunks_per_block)
+
+
 def attention_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                          seq_slot: torch.Tensor, slot_pos: torch.Tensor, out: torch.Tensor,
                          part_o: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
                          status: torch.Tensor, H: int, G: int, hd: int, capacity: int,
-                         window: Optional[int], max_context: int) -> None:
+                         window: Optional[int], max_context: int, chunks_per_block: int) -> None:
     n = q.shape[0]
     _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16,
           "attention_decode_mma: bfloat16 only")
-    visible = min(max_context, window) if window else max_context
-    max_chunks = -(-visible // 128)
+    parts = decode_mma_parts(max_context, window, chunks_per_block)
     hc = -(-(H // G) // 16)
-    _need(part_o.numel() >= n * H * max_chunks * hd and part_ml.numel() >= n * H * max_chunks * 2
+    _need(part_o.numel() >= n * H * parts * hd and part_ml.numel() >= n * H * parts * 2
           and counters.numel() >= n * G * hc and counters.dtype == torch.int32,
           "attention_decode_mma: workspace")
     _check(lib().yalm_attention_decode_mma(_p(q), _p(k_cache), _p(v_cache), _p(seq_slot),
                                            _p(slot_pos), _p(out), _p(part_o), _p(part_ml),
                                            _p(counters), _p(status), n, H, G, hd, capacity,
-                                           int(window or 0), max_context, _stream()),
+                                           int(window or 0), max_context, chunks_per_block,
+                                           _stream()),
            "attention_decode_mma")
 
 

@@ -61,6 +61,17 @@ class GQAAttention:
         chunk = (64 * 1024) // (2 * self.hd * esz)
         return max(8, min(128, chunk))
 
+    def decode_chunks_per_block(self, batch, visible: int) -> int:
+        """How many 64-key chunks one block of the tensor-core decode kernel walks
+        through: as few as keeps every block resident at once (two per SM).  A few
+        sequences then get many blocks each and a merge; with many sequences a
+        block takes its whole sequence and nothing is merged."""
+        groups = self.G * -(-(self.H // self.G) // 16)
+        lengths = [min(p + 1, self.window) if self.window else p + 1 for p in batch.past]
+        total = groups * sum(-(-n // 64) for n in lengths)
+        resident = 2 * self.rt.sm_count
+        return max(1, min(-(-visible // 64), -(-total // resident)))
+
     def forward(self, h, batch, stream, view, shared: bool = False) -> None:
         rt, H, G, hd = self.rt, self.H, self.G, self.hd
         n = batch.n_tokens
@@ -86,17 +97,21 @@ class GQAAttention:
         tensor_cores = ops.mma_attention_usable(rt.dtype, hd) and rt.attention != "simt"
         if batch.is_decode:
             # one query per sequence, every key already in the cache
-            chunk = 128 if tensor_cores else self.decode_chunk(batch)
             bound = max(1, batch.ctx_bound)
             visible = min(bound, self.window) if self.window else bound
-            max_chunks = -(-visible // chunk)
-            part_o = rt.buffer("attn_part_o", (n, H, max_chunks, hd), torch.float32)
-            part_ml = rt.buffer("attn_part_ml", (n, H, max_chunks, 2), torch.float32)
+            if tensor_cores:
+                cpc = self.decode_chunks_per_block(batch, visible)
+                parts = ops.decode_mma_parts(bound, self.window, cpc)
+            else:
+                chunk = self.decode_chunk(batch)
+                parts = -(-visible // chunk)
+            part_o = rt.buffer("attn_part_o", (n, H, parts, hd), torch.float32)
+            part_ml = rt.buffer("attn_part_ml", (n, H, parts, 2), torch.float32)
             counters = rt.zeros("attn_counters", n * G * -(-(H // G) // 4))
             if tensor_cores:
                 ops.attention_decode_mma(q, view.k, view.v, batch.seq_slot, view.slot_pos, o,
                                          part_o, part_ml, counters, rt.status, H, G, hd,
-                                         view.capacity, self.window, bound)
+                                         view.capacity, self.window, bound, cpc)
             else:
                 ops.attention_decode(q, view.k, view.v, batch.seq_slot, view.slot_pos, o, part_o,
                                      part_ml, counters, rt.status, H, G, hd, view.capacity,
