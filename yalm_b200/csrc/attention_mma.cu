@@ -21,9 +21,11 @@
 namespace yalm {
 
 constexpr int FA_WARPS = 4;
-constexpr int FA_THREADS = FA_WARPS * 32;
-constexpr int FA_BM = 64;          // query rows per block (16 per warp)
-constexpr int FA_BN = 64;          // keys per block iteration
+constexpr int FA_THREADS = FA_WARPS * 32;        // decode blocks and the tile loaders' default
+constexpr int FP_WARPS = 8;
+constexpr int FP_THREADS = FP_WARPS * 32;        // prefill blocks
+constexpr int FA_BM = FP_WARPS * 16;             // query rows per prefill block (16 per warp)
+constexpr int FA_BN = 64;                        // keys per block iteration
 
 __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, const uint32_t* b) {
   asm volatile(
@@ -65,16 +67,30 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk)
 
 // Loads `rows` rows of hd elements each into a swizzled tile.  row_ptr(r) gives the
 // global address of row r, or nullptr for a row that is to be zero.
-template <int HDP, typename RowPtr>
+template <int HDP, int NT = FA_THREADS, typename RowPtr>
 __device__ __forceinline__ void load_tile(uint32_t base, int rows, int hd,
                                           const __nv_bfloat16* valid_ptr, RowPtr row_ptr) {
   const int cpr = hd >> 3;                                    // 16-byte chunks per row
-  for (int idx = threadIdx.x; idx < rows * cpr; idx += FA_THREADS) {
+  for (int idx = threadIdx.x; idx < rows * cpr; idx += NT) {
     const int r = idx / cpr, ch = idx - r * cpr;
     const __nv_bfloat16* p = row_ptr(r);
     // a zero-filled chunk still names an address: give it one that exists
     cp_async16(tile_addr<HDP>(base, r, ch), p ? p + ch * 8 : valid_ptr, p != nullptr);
   }
+}
+
+// Loads `n` rows that lie `stride` elements apart in global memory (rows of this
+// step's own buffers) and zero-fills rows n..rows-1; one 16-byte column per thread.
+template <int HDP, int NT>
+__device__ __forceinline__ void load_strided_tile(uint32_t base, int rows, int n, int hd,
+                                                  const __nv_bfloat16* first, size_t stride) {
+  const int cpr = hd >> 3;
+  const int rstep = NT / cpr;
+  if ((int)threadIdx.x >= rstep * cpr) return;
+  const int ch = threadIdx.x % cpr;
+  for (int r = threadIdx.x / cpr; r < rows; r += rstep)
+    cp_async16(tile_addr<HDP>(base, r, ch), r < n ? first + (size_t)r * stride + ch * 8 : first,
+               r < n);
 }
 
 // Loads `n` consecutive positions of a cache ring (rows first_row, first_row + 1, ...
@@ -103,7 +119,7 @@ __device__ __forceinline__ void load_ring_tile(uint32_t base, int rows, int n, i
 // grid (query tiles of a sequence, heads, sequences); a block takes 64 query
 // tokens of one head.  scale_log2 = log2(e) / sqrt(hd).
 template <int HDP>
-__global__ void __launch_bounds__(FA_THREADS)
+__global__ void __launch_bounds__(FP_THREADS, 2)
 attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv_step,
                         const __nv_bfloat16* __restrict__ k_cache,
                         const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ q_start,
@@ -117,7 +133,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int b = blockIdx.z, h = blockIdx.y;
   const int g = h / (H / G);
   const int qs = q_start[b], q_len = q_start[b + 1] - qs;
-  const int m0 = blockIdx.x * FA_BM;
+  // the tiles with the most keys (the last tokens) are scheduled first
+  const int m0 = (gridDim.x - 1 - blockIdx.x) * FA_BM;
   if (m0 >= q_len) return;
   const int slot = seq_slot[b];
   const int past = slot_pos[slot];
@@ -141,13 +158,22 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const __nv_bfloat16* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
   auto load_kv = [&](int kb, int stage) {
     const int j0 = kb * FA_BN;
-    load_tile<HDP>(k_s0 + stage * FA_BN * HDP * 2, FA_BN, hd, q, [&](int r) -> const __nv_bfloat16* {
+    const uint32_t kd = k_s0 + stage * FA_BN * HDP * 2, vd = v_s0 + stage * FA_BN * HDP * 2;
+    if (j0 >= past) {
+      // the whole block comes from this step's keys and values: rows a fixed stride apart
+      const int n = min(FA_BN, k_end - j0);
+      const __nv_bfloat16* k0 = kv_step + (size_t)(qs + j0 - past) * step_row + (size_t)g * hd;
+      load_strided_tile<HDP, FP_THREADS>(kd, FA_BN, n, hd, k0, step_row);
+      load_strided_tile<HDP, FP_THREADS>(vd, FA_BN, n, hd, k0 + (size_t)G * hd, step_row);
+      return;
+    }
+    load_tile<HDP, FP_THREADS>(kd, FA_BN, hd, q, [&](int r) -> const __nv_bfloat16* {
       const int j = j0 + r;
       if (j >= k_end) return nullptr;
       return j >= past ? kv_step + (size_t)(qs + j - past) * step_row + (size_t)g * hd
                        : kc + (size_t)(j % capacity) * hd;
     });
-    load_tile<HDP>(v_s0 + stage * FA_BN * HDP * 2, FA_BN, hd, q, [&](int r) -> const __nv_bfloat16* {
+    load_tile<HDP, FP_THREADS>(vd, FA_BN, hd, q, [&](int r) -> const __nv_bfloat16* {
       const int j = j0 + r;
       if (j >= k_end) return nullptr;
       return j >= past ? kv_step + (size_t)(qs + j - past) * step_row + (size_t)(G + g) * hd
@@ -155,23 +181,13 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     });
   };
 
-  load_tile<HDP>(q_s, FA_BM, hd, q, [&](int r) -> const __nv_bfloat16* {
-    return r < rows ? q + ((size_t)(qs + m0 + r) * H + h) * hd : nullptr;
-  });
+  load_strided_tile<HDP, FP_THREADS>(q_s, FA_BM, rows, hd, q + ((size_t)(qs + m0) * H + h) * hd,
+                                     (size_t)H * hd);
   load_kv(kb0, 0);
   cp_async_commit();
   cp_async_wait<0>();
   __syncthreads();
 
-  // Q fragments of this warp's 16 rows stay in registers
-  uint32_t qf[NKS][4];
-#pragma unroll
-  for (int ks = 0; ks < NKS; ++ks) {
-    if (ks < nks) {
-      const int row = warp * 16 + (lane & 15);
-      ldsm_x4(qf[ks], tile_addr<HDP>(q_s, row, ks * 2 + (lane >> 4)));
-    }
-  }
   float o[NOT][4];
 #pragma unroll
   for (int i = 0; i < NOT; ++i)
@@ -179,6 +195,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int p_row[2] = {past + m0 + warp * 16 + gid, past + m0 + warp * 16 + gid + 8};
+  const int w_first = past + m0 + warp * 16, w_last = w_first + 15;
+  const int q_row = warp * 16 + (lane & 15);
 
   for (int kb = kb0; kb < kb1; ++kb) {
     const int stage = (kb - kb0) & 1;
@@ -186,82 +204,99 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     cp_async_commit();
     const uint32_t k_s = k_s0 + stage * FA_BN * HDP * 2, v_s = v_s0 + stage * FA_BN * HDP * 2;
 
-    // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
-    float s[FA_BN / 8][4];
+    // the block's 64 keys in two halves of 32: scores, softmax and P.V per half keep
+    // the register count low enough for two blocks per SM
 #pragma unroll
-    for (int i = 0; i < FA_BN / 8; ++i)
+    for (int half = 0; half < 2; ++half) {
+      const int j_base = kb * FA_BN + half * 32;
+      if (j_base > w_last) break;                             // wholly in this warp's future
+      float s[4][4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int ks = 0; ks < NKS; ++ks) {
-      if (ks < nks) {
+        for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
 #pragma unroll
-        for (int np = 0; np < FA_BN / 16; ++np) {             // two n-tiles per ldmatrix.x4
-          uint32_t kf[4];
-          const int row = np * 16 + (lane & 7) + ((lane >> 4) << 3);
-          ldsm_x4(kf, tile_addr<HDP>(k_s, row, ks * 2 + ((lane >> 3) & 1)));
-          mma_bf16(s[2 * np], qf[ks], kf);
-          mma_bf16(s[2 * np + 1], qf[ks], kf + 2);
+      for (int ks = 0; ks < NKS; ++ks) {
+        if (ks < nks) {
+          uint32_t qf[4];
+          ldsm_x4(qf, tile_addr<HDP>(q_s, q_row, ks * 2 + (lane >> 4)));
+#pragma unroll
+          for (int np = 0; np < 2; ++np) {                    // two n-tiles per ldmatrix.x4
+            uint32_t kf[4];
+            const int row = half * 32 + np * 16 + (lane & 7) + ((lane >> 4) << 3);
+            ldsm_x4(kf, tile_addr<HDP>(k_s, row, ks * 2 + ((lane >> 3) & 1)));
+            mma_bf16(s[2 * np], qf, kf);
+            mma_bf16(s[2 * np + 1], qf, kf + 2);
+          }
         }
       }
-    }
-    // mask and online softmax (rows gid and gid + 8 of this warp)
-    const int j_base = kb * FA_BN;
-    float m_new[2] = {m_run[0], m_run[1]};
+      // mask and online softmax (rows gid and gid + 8 of this warp)
+      float m_new[2] = {m_run[0], m_run[1]};
+      const bool inside = j_base + 31 <= w_first && (window <= 0 || j_base > w_last - window);
+      if (inside) {
 #pragma unroll
-    for (int i = 0; i < FA_BN / 8; ++i) {
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int key = j_base + i * 8 + tig * 2 + (j & 1);
-        const int pr = p_row[j >> 1];
-        const bool vis = key <= pr && (window <= 0 || key > pr - window);
-        s[i][j] = vis ? s[i][j] * scale_log2 : -INFINITY;
-        m_new[j >> 1] = fmaxf(m_new[j >> 1], s[i][j]);
+          for (int j = 0; j < 4; ++j) {
+            s[i][j] *= scale_log2;
+            m_new[j >> 1] = fmaxf(m_new[j >> 1], s[i][j]);
+          }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int key = j_base + i * 8 + tig * 2 + (j & 1);
+            const int pr = p_row[j >> 1];
+            const bool vis = key <= pr && (window <= 0 || key > pr - window);
+            s[i][j] = vis ? s[i][j] * scale_log2 : -INFINITY;
+            m_new[j >> 1] = fmaxf(m_new[j >> 1], s[i][j]);
+          }
       }
-    }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
-      m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
-    }
-    float corr[2], l_add[2] = {0.f, 0.f};
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-      corr[r] = m_new[r] > -INFINITY ? exp2f(m_run[r] - m_new[r]) : 1.f;
-    uint32_t pf[FA_BN / 16][4];
-#pragma unroll
-    for (int i = 0; i < FA_BN / 8; ++i) {
-      float p[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float mr = m_new[j >> 1];
-        p[j] = mr > -INFINITY ? exp2f(s[i][j] - mr) : 0.f;
-        l_add[j >> 1] += p[j];
+      for (int r = 0; r < 2; ++r) {
+        m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
+        m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
       }
-      pf[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
-      pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
-    }
+      float corr[2], l_add[2] = {0.f, 0.f};
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      l_run[r] = l_run[r] * corr[r] + l_add[r];
-      m_run[r] = m_new[r];
-    }
+      for (int r = 0; r < 2; ++r)
+        corr[r] = m_new[r] > -INFINITY ? exp2f(m_run[r] - m_new[r]) : 1.f;
+      uint32_t pf[2][4];
 #pragma unroll
-    for (int i = 0; i < NOT; ++i) {
-      o[i][0] *= corr[0]; o[i][1] *= corr[0];
-      o[i][2] *= corr[1]; o[i][3] *= corr[1];
-    }
-    // O += P V: k-steps of 16 keys, n-tiles of 8 head elements (two per ldmatrix.x4.trans)
+      for (int i = 0; i < 4; ++i) {
+        float p[4];
 #pragma unroll
-    for (int kk = 0; kk < FA_BN / 16; ++kk) {
+        for (int j = 0; j < 4; ++j) {
+          const float mr = m_new[j >> 1];
+          p[j] = mr > -INFINITY ? exp2f(s[i][j] - mr) : 0.f;
+          l_add[j >> 1] += p[j];
+        }
+        pf[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
+        pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+      }
 #pragma unroll
-      for (int np = 0; np < NOT / 2; ++np) {
-        if (np * 2 < n_ot) {
-          uint32_t vf[4];
-          const int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-          ldsm_x4_t(vf, tile_addr<HDP>(v_s, row, np * 2 + (lane >> 4)));
-          mma_bf16(o[2 * np], pf[kk], vf);
-          mma_bf16(o[2 * np + 1], pf[kk], vf + 2);
+      for (int r = 0; r < 2; ++r) {
+        l_run[r] = l_run[r] * corr[r] + l_add[r];
+        m_run[r] = m_new[r];
+      }
+#pragma unroll
+      for (int i = 0; i < NOT; ++i) {
+        o[i][0] *= corr[0]; o[i][1] *= corr[0];
+        o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      }
+      // O += P V: k-steps of 16 keys, n-tiles of 8 head elements (two per ldmatrix.x4.trans)
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+        for (int np = 0; np < NOT / 2; ++np) {
+          if (np * 2 < n_ot) {
+            uint32_t vf[4];
+            const int row = half * 32 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+            ldsm_x4_t(vf, tile_addr<HDP>(v_s, row, np * 2 + (lane >> 4)));
+            mma_bf16(o[2 * np], pf[kk], vf);
+            mma_bf16(o[2 * np + 1], pf[kk], vf + 2);
+          }
         }
       }
     }
@@ -590,11 +625,15 @@ static int launch_prefill(const void* q, const void* kv_step, const void* k_cach
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HDP>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HDP>,
+                             cudaFuncAttributePreferredSharedMemoryCarveout,
+                             (int)cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
   const dim3 grid((max_q_len + FA_BM - 1) / FA_BM, H, n_seqs);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
-  launch_pdl(attn_prefill_mma_kernel<HDP>, grid, dim3(FA_THREADS), smem, stream,
+  launch_pdl(attn_prefill_mma_kernel<HDP>, grid, dim3(FP_THREADS), smem, stream,
              (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv_step, (const __nv_bfloat16*)k_cache,
              (const __nv_bfloat16*)v_cache, q_start, seq_slot, slot_pos, (__nv_bfloat16*)out, H, G,
              hd, capacity, window, scale_log2);

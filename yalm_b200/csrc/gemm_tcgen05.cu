@@ -417,7 +417,8 @@ template <int BT, int NACC>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_sk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                void* __restrict__ out, int out_dtype, int M, int N, int K, int mode,
-               float* __restrict__ scratch, int* __restrict__ counters, int* __restrict__ status) {
+               long long units_per_block, float* __restrict__ scratch, int* __restrict__ counters,
+               int* __restrict__ status) {
   using Cfg = SkCfg<BT, NACC>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[Cfg::STAGES];
@@ -435,7 +436,7 @@ gemm_sk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int n_tok_tiles = (M + BT - 1) / BT;
   const int nkb = (K + TC_BK - 1) / TC_BK;
   const long long U = (long long)n_feat_tiles * n_tok_tiles * nkb;
-  const long long q = (U + gridDim.x - 1) / gridDim.x;
+  const long long q = units_per_block;
   const long long u_lo = min(U, (long long)blockIdx.x * q);
   const long long u_hi = min(U, u_lo + q);
 
@@ -684,8 +685,8 @@ static int sm_count() {
 
 template <int BT, int NACC>
 static int launch_sk(const CUtensorMap& mw, const void* A, void* out, int out_dtype, int M, int N,
-                     int K, int mode, float* scratch, long long scratch_floats, int* counters,
-                     int n_counters, int* status, cudaStream_t stream) {
+                     int K, int mode, int whole_tiles, float* scratch, long long scratch_floats,
+                     int* counters, int n_counters, int* status, cudaStream_t stream) {
   using Cfg = SkCfg<BT, NACC>;
   static_assert(Cfg::STAGES >= 2, "pipeline needs two stages");
   CUtensorMap ma;
@@ -699,14 +700,25 @@ static int launch_sk(const CUtensorMap& mw, const void* A, void* out, int out_dt
     attr_set = true;
   }
   const int n_out = mode == 2 ? N / 2 : N;
+  const long long nkb = (K + TC_BK - 1) / TC_BK;
   const long long tiles = (long long)((n_out + TC_BM - 1) / TC_BM) * ((M + BT - 1) / BT);
-  const long long units = tiles * ((K + TC_BK - 1) / TC_BK);
+  const long long units = tiles * nkb;
   long long blocks = sm_count();
-  if (blocks > units) blocks = units;
+  long long q;
+  if (whole_tiles) {
+    // every block takes whole tiles: no tile is shared, nothing is parked in scratch
+    if (blocks > tiles) blocks = tiles;
+    q = ((tiles + blocks - 1) / blocks) * nkb;
+    blocks = (units + q - 1) / q;
+  } else {
+    if (blocks > units) blocks = units;
+    q = (units + blocks - 1) / blocks;
+    blocks = (units + q - 1) / q;
+    if (blocks * 2 * Cfg::SLOT_FLOATS > scratch_floats) return -13;
+  }
   if (tiles > n_counters) return -12;
-  if (blocks * 2 * Cfg::SLOT_FLOATS > scratch_floats) return -13;
   launch_pdl(gemm_sk_kernel<BT, NACC>, dim3((int)blocks), dim3(TC_THREADS), Cfg::SMEM, stream, 
-      mw, ma, out, out_dtype, M, N, K, mode, scratch, counters, status);
+      mw, ma, out, out_dtype, M, N, K, mode, q, scratch, counters, status);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -759,12 +771,15 @@ extern "C" long long yalm_gemm_sk_scratch_floats(int M, int dual) {
 }
 
 // out = A W^T with a fused epilogue (mode 0 store, 1 add to float32 out, 2 silu(gate)*up).
-// scratch: float32 workspace of at least yalm_gemm_sk_scratch_floats(M, mode == 2);
-// counters: one int per output tile, zero before the first launch (the kernel
-// leaves them zero).
+// whole_tiles 0: blocks share tiles (every SM streams the same number of bytes: for a
+// few tokens); 1: every block takes whole tiles (no partial tiles: for many tokens).
+// scratch: float32 workspace of at least yalm_gemm_sk_scratch_floats(M, mode == 2)
+// (unused with whole_tiles); counters: one int per output tile, zero before the
+// first launch (the kernel leaves them zero).
 extern "C" int yalm_gemm_sk(const void* A, const void* W, void* out, int out_dtype, int M, int N,
-                            int K, int mode, float* scratch, long long scratch_floats,
-                            int* counters, int n_counters, int* status, cudaStream_t stream) {
+                            int K, int mode, int whole_tiles, float* scratch,
+                            long long scratch_floats, int* counters, int n_counters, int* status,
+                            cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0) return -2;
   if (((uintptr_t)A | (uintptr_t)W) & 15) return -6;
@@ -775,8 +790,8 @@ extern "C" int yalm_gemm_sk(const void* A, const void* W, void* out, int out_dty
   int rc = make_map(&mw, W, N, K, TC_BM);
   if (rc) return rc;
 #define YALM_SK(BT, NACC)                                                                      \
-  return launch_sk<BT, NACC>(mw, A, out, out_dtype, M, N, K, mode, scratch, scratch_floats,    \
-                             counters, n_counters, status, stream)
+  return launch_sk<BT, NACC>(mw, A, out, out_dtype, M, N, K, mode, whole_tiles, scratch,        \
+                             scratch_floats, counters, n_counters, status, stream)
   if (mode == 2) {
     if (M <= 16) YALM_SK(16, 2);
     if (M <= 32) YALM_SK(32, 2);

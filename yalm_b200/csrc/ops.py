@@ -64,7 +64,7 @@ _SIGNATURES = {
     "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp],
     "yalm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_gemm_tc_available": [],
-    "yalm_gemm_sk": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _ll, _vp, _i, _vp, _vp],
+    "yalm_gemm_sk": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _ll, _vp, _i, _vp, _vp],
 }
 
 _lib = None
@@ -310,7 +310,7 @@ def gemm_sk_scratch_floats(M: int, dual: bool) -> int:
 
 
 def gemm_sk(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, status: torch.Tensor,
-            scratch: torch.Tensor, counters: torch.Tensor) -> None:
+            scratch: Optional[torch.Tensor], counters: torch.Tensor, whole_tiles: bool = False) -> None:
     """Persistent stream-K tcgen05 product with a fused epilogue (GEMM_STORE,
     GEMM_ADD or GEMM_SILU_MUL)."""
     M, K = a.shape
@@ -318,10 +318,12 @@ def gemm_sk(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, stat
     _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
           and a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "gemm_sk: operands")
     _need(tuple(out.shape) == ((M, N // 2) if mode == GEMM_SILU_MUL else (M, N)), "gemm_sk: out shape")
-    _need(scratch.dtype == torch.float32 and counters.dtype == torch.int32, "gemm_sk: workspace types")
+    _need(counters.dtype == torch.int32 and (whole_tiles or scratch is not None),
+          "gemm_sk: workspace")
     _check(lib().yalm_gemm_sk(_p(a), _p(w), _p(out), dtype_code(out.dtype), M, N, K, mode,
-                              _p(scratch), scratch.numel(), _p(counters), counters.numel(),
-                              _p(status), _stream()), "gemm_sk")
+                              1 if whole_tiles else 0, _p(scratch),
+                              0 if scratch is None else scratch.numel(), _p(counters),
+                              counters.numel(), _p(status), _stream()), "gemm_sk")
 
 
 def sample(logits: torch.Tensor, temperature: float, seed: int, row_key: torch.Tensor,
