@@ -39,6 +39,24 @@ MISTRAL_7B = {
     "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
 }
 CONTEXT = 4096
+LLAMA32_1B = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 2048, "intermediate_size": 8192, "num_hidden_layers": 16,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
+    "vocab_size": 128256, "max_position_embeddings": 131072, "rms_norm_eps": 1e-5,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "sliding_window": None, "tie_word_embeddings": True, "hidden_act": "silu",
+    "bos_token_id": 128000, "eos_token_id": 128001,
+}
+MISTRAL_7B_V01 = dict(MISTRAL_7B, rope_theta=10000.0, sliding_window=4096)
+# name -> (config.json keys, context, default batch, prompt lengths lo..hi)
+WORKLOADS = {
+    "mistral-7b-v0.2": (MISTRAL_7B, 4096, 8, 64, 2048),
+    "llama-3.2-1b": (LLAMA32_1B, 8192, 64, 16, 1024),
+    "mistral-7b-v0.1": (MISTRAL_7B_V01, 8192, 8, 6000, 6000),     # decodes past the 4096 window
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -127,7 +145,8 @@ def decode_bytes(lm, contexts):
     H, G, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     per_layer = ((H + 2 * G) * hd * D + D * H * hd + 3 * F * D) * esz + 2 * D * 4
     weights = L * per_layer + V * D * esz + D * 4 + len(contexts) * D * esz
-    kv = sum(contexts) * L * 2 * G * hd * esz
+    window = cfg.sliding_window
+    kv = sum(min(c, window) if window else c for c in contexts) * L * 2 * G * hd * esz
     return weights + kv
 
 
@@ -153,11 +172,11 @@ def prefill_batch(lm, prompts, group=8):
     return slots, first
 
 
-def time_decode(lm, batch, steps, warmup, seed, sampler=None):
-    """Device-timed decode steps of a batch with prompt lengths U[64, 2048]."""
+def time_decode(lm, batch, steps, warmup, seed, sampler=None, lo=64, hi=2048):
+    """Device-timed decode steps of a batch with prompt lengths U[lo, hi]."""
     import torch
     from yalm_b200.csrc import ops
-    lens = prompt_lengths(batch, 64, 2048, seed)
+    lens = prompt_lengths(batch, lo, hi, seed)
     prompts = random_prompts(lens, lm.config.vocab_size, seed + 1)
     slots, first = prefill_batch(lm, prompts)
     eng = lm.engine
@@ -186,8 +205,8 @@ def time_decode(lm, batch, steps, warmup, seed, sampler=None):
             "contexts": ctx_mid, "clocks": clocks, "prompt_lens": lens}
 
 
-def time_e2e(lm, batch, steps, seed):
-    lens = prompt_lengths(batch, 64, 2048, seed)
+def time_e2e(lm, batch, steps, seed, lo=64, hi=2048):
+    lens = prompt_lengths(batch, lo, hi, seed)
     prompts = random_prompts(lens, lm.config.vocab_size, seed + 1)
     lm.generate(prompts, max_new_tokens=4, temperature=0.0, ignore_eos=True)     # warm-up
     lm.generate(prompts, max_new_tokens=steps + 1, temperature=0.0, ignore_eos=True)
@@ -225,8 +244,10 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=MISTRAL_7B["num_hidden_layers"])
+    ap.add_argument("--workload", default="mistral-7b-v0.2", choices=sorted(WORKLOADS),
+                    help="layer sizes, context and prompt lengths (default: the headline one)")
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1/64 and prefill")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (profiling)")
     ap.add_argument("--no-graphs", action="store_true",
@@ -245,10 +266,15 @@ def main():
     import torch
     from yalm_b200 import LM
     pk = peaks()
-    cfg = dict(MISTRAL_7B, num_hidden_layers=args.layers)
+    base_cfg, context, default_batch, lo, hi = WORKLOADS[args.workload]
+    args.batch = args.batch or default_batch
+    args.layers = args.layers or base_cfg["num_hidden_layers"]
+    headline = args.workload == "mistral-7b-v0.2"
+    cfg = dict(base_cfg, num_hidden_layers=args.layers)
     t0 = time.time()
     lm = LM.from_random(cfg, seed=0, dtype="bfloat16", std=0.02, norm_jitter=0.0,
-                        max_context=CONTEXT, max_batch=max(64, args.batch))
+                        max_context=context,
+                        max_batch=max(64, args.batch) if headline and not args.no_points else args.batch)
     torch.cuda.synchronize()
     print(f"[bench] model ready in {time.time() - t0:.0f} s "
           f"({lm.model.weight_bytes() / 1e9:.1f} GB weights, {lm.engine.cache.bytes() / 1e9:.1f} GB cache)",
@@ -257,21 +283,23 @@ def main():
     if args.no_graphs:
         lm.engine.use_graphs = False
     W = max(3, args.warmup)
-    main_run = time_decode(lm, args.batch, args.steps, W, seed=1, sampler=ClockSampler())
+    main_run = time_decode(lm, args.batch, args.steps, W, seed=1, sampler=ClockSampler(), lo=lo, hi=hi)
     by = decode_bytes(lm, main_run["contexts"])
     achieved = by / (main_run["ms_per_step"] / 1e3) / 1e9
-    e2e = None if args.no_e2e else time_e2e(lm, args.batch, args.steps, seed=1)
+    e2e = None if args.no_e2e else time_e2e(lm, args.batch, args.steps, seed=1, lo=lo, hi=hi)
     out = {
-        "metric": "decode tokens/s at batch 8 (Mistral-7B-v0.2 shapes, context 4096)",
+        "metric": f"decode tokens/s at batch {args.batch} ({args.workload} shapes, context {context})",
         "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": W, "ms_per_step": main_run["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
         "config": {
-            "model": "mistral-7b-v0.2-shapes-random", "layers": args.layers,
-            "layers_of_config": MISTRAL_7B["num_hidden_layers"], "hidden": 4096, "ffn": 14336,
-            "heads": 32, "kv_heads": 8, "head_dim": 128, "vocab": 32000, "global_batch": args.batch,
-            "seq_len": CONTEXT, "prompt_lens": "uniform[64,2048]",
+            "model": f"{args.workload}-shapes-random", "layers": args.layers,
+            "layers_of_config": base_cfg["num_hidden_layers"], "hidden": base_cfg["hidden_size"],
+            "ffn": base_cfg["intermediate_size"], "heads": base_cfg["num_attention_heads"],
+            "kv_heads": base_cfg["num_key_value_heads"], "head_dim": base_cfg["head_dim"],
+            "vocab": base_cfg["vocab_size"], "global_batch": args.batch, "seq_len": context,
+            "window": base_cfg.get("sliding_window"), "prompt_lens": f"uniform[{lo},{hi}]",
             "mean_context": sum(main_run["contexts"]) / len(main_run["contexts"]),
             "parallelism": "single-gpu", "l2": "inputs larger than L2 (weights streamed each step)",
             "peaks": pk["source"], "weights": "random N(0,0.02), norms 1",
@@ -283,7 +311,7 @@ def main():
                      "frac": achieved / pk["hbm_gbs"], "bytes_per_step": by,
                      "of": pk["source"]},
     }
-    if not args.no_points:
+    if not args.no_points and headline:
         out["prefill"] = time_prefill(lm, 2048, 5, pk)
         pts = {}
         for b in (1, 64):
