@@ -42,7 +42,19 @@ TINY_C = {
     "tie_word_embeddings": False, "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
 }
 
-CONFIGS = {"tiny_a": (TINY_A, 0), "tiny_b": (TINY_B, 1), "tiny_c": (TINY_C, 2)}
+# sizes that no kernel likes: width 100 and FFN 150 (rows that are no multiple of 16 bytes, so
+# the TMA-fed matrix product must hand over to the FMA one), 5 heads of 16 that do not add up
+# to the width, vocabulary 301
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 100, "intermediate_size": 150, "num_hidden_layers": 2,
+    "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 16,
+    "vocab_size": 301, "max_position_embeddings": 70, "rms_norm_eps": 1e-5,
+    "rope_theta": 10000.0, "rope_scaling": None, "sliding_window": None,
+    "tie_word_embeddings": True, "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
+}
+
+CONFIGS = {"tiny_a": (TINY_A, 0), "tiny_b": (TINY_B, 1), "tiny_c": (TINY_C, 2), "tiny_d": (TINY_D, 3)}
 
 # Tolerances on logits, relative to the largest reference logit in magnitude.
 # float32: FMA chains in another order than the CPU's.  bfloat16: activations are

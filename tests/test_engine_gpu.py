@@ -25,6 +25,9 @@ REQUESTS = {
     "tiny_c": {"lens": {"r0": 7, "r1": 45, "r2": 81, "r3": 160},
                "prompts": {"r0": 3, "r1": 41, "r2": 39, "r3": 100},
                "batches": [["r0", "r1", "r2"], ["r3", "r0"]]},
+    "tiny_d": {"lens": {"r0": 9, "r1": 70, "r2": 38},
+               "prompts": {"r0": 2, "r1": 50, "r2": 37},
+               "batches": [["r0", "r1", "r2"], ["r2", "r0"]]},
 }
 
 
@@ -60,7 +63,7 @@ def test_trace_run_matches_plain_model(name, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
 def test_step_function_matches_plain_model(name, dtype):
     from yalm_b200 import LM
     from yalm_b200.config import config_from_dict
