@@ -467,3 +467,32 @@ def test_persistent_matrix_product(ops, shape, whole_tiles):
         assert torch.equal(again, first)
         torch.cuda.synchronize()
         assert status.item() == 0 and int(counters.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 64), (130, 300, 88), (256, 256, 64), (300, 512, 128),
+                                   (700, 640, 448), (1500, 1152, 320), (2048, 1024, 1024)])
+def test_two_sm_matrix_product(ops, shape):
+    """gemm_2sm: a cluster of two blocks per 256-feature tile (tcgen05.mma.cta_group::2),
+    every epilogue, sizes that leave the second block of a pair partly or wholly empty."""
+    M, N, K = shape
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    a = (torch.randn(M, K, device=DEV) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.5).to(torch.bfloat16)
+    ref = a.double() @ w.double().T
+    tol = 2e-6 * math.sqrt(K) * ref.abs().max()
+    for rep in range(2):
+        out = torch.full((M, N), 7.0, device=DEV)
+        ops.gemm_2sm(a, w, out, ops.GEMM_STORE, status)
+        assert (out.double() - ref).abs().max() <= tol
+        ops.gemm_2sm(a, w, out, ops.GEMM_ADD, status)
+        assert (out.double() - 2 * ref).abs().max() <= 2 * tol
+        outh = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+        ops.gemm_2sm(a, w, outh, ops.GEMM_STORE, status)
+        assert (outh.double() - ref).abs().max() <= 2 ** -8 * ref.abs().max()
+        g, u = ref[:, :N // 2], ref[:, N // 2:]
+        r2 = g / (1 + torch.exp(-g)) * u
+        o2 = torch.zeros(M, N // 2, device=DEV)
+        ops.gemm_2sm(a, w, o2, ops.GEMM_SILU_MUL, status)
+        assert (o2.double() - r2).abs().max() <= 4e-6 * math.sqrt(K) * max(1.0, r2.abs().max())
+        torch.cuda.synchronize()
+        assert status.item() == 0

@@ -82,6 +82,10 @@ int yalm_gemm_sk(const void* A, const void* W, void* out, int out_dtype, int M, 
                  int mode, int whole_tiles, float* scratch, long long scratch_floats,
                  int* counters, int n_counters, int* status, cudaStream_t stream);
 
+// Two-SM (cta_group::2) variant for many tokens: mode 0 store, 1 add, 2 silu(gate)*up.
+int yalm_gemm_2sm(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
+                  int mode, int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

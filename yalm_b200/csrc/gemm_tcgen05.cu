@@ -723,6 +723,289 @@ static int launch_sk(const CUtensorMap& mw, const void* A, void* out, int out_dt
   return 0;
 }
 
+
+// ===========================================================================
+// The two-SM kernel for many tokens.
+//
+// A cluster of two blocks on neighbouring SMs computes one 256-feature x BT-token
+// tile with tcgen05.mma.cta_group::2: each block brings its own 128 weight rows and
+// its own half of the token tile into its shared memory, the first block's MMA
+// thread issues one instruction that reads both halves, and each block's tensor
+// memory receives its 128 rows of the result.  Per byte that leaves L2 the pair does
+// 1.5 times the arithmetic of two single-SM 128x256 tiles, which is what the
+// single-SM kernels are short of at these sizes.
+//
+// Barriers: the "full" barrier of a stage lives in the first block and counts the
+// bytes of both blocks' TMA loads; "empty" and "accumulator full" barriers live in
+// both blocks and are signalled by multicast commits; "accumulator empty" lives in
+// the first block and counts the epilogue warps of both.  Persistent: a pair walks
+// through tiles pair, pair + n_pairs, ...; two accumulator buffers in TMEM.
+constexpr int G2_STAGE_LIMIT = 196 * 1024;
+
+template <int BT, int NACC> struct G2Cfg {
+  static constexpr int W_BYTES = TC_BM * TC_BK * 2;            // this block's 128 weight rows
+  static constexpr int A_BYTES = (BT / 2) * TC_BK * 2;         // this block's half of the tokens
+  static constexpr int STAGE_BYTES = NACC * W_BYTES + A_BYTES;
+  static constexpr int STAGES_RAW = G2_STAGE_LIMIT / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
+  static constexpr int ACC_COLS = NACC * BT;
+  static constexpr int TMEM_COLS = 512;
+  static_assert(2 * ACC_COLS <= 512, "two accumulator buffers must fit into TMEM");
+  static_assert(BT % 32 == 0 && BT <= 256, "token tile of the pair");
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose completion bytes are counted on a barrier that may live in the peer block
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar_cluster_addr)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at this offset in both blocks once the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+      " [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];"
+               ::"r"(bar_cluster_addr) : "memory");
+}
+
+// mode 0: store, 1: add into float32 out, 2: silu(gate)*up (NACC == 2)
+template <int BT, int NACC>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS)
+gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                void* __restrict__ out, int out_dtype, int M, int N, int K, int mode,
+                int* __restrict__ status) {
+  using Cfg = G2Cfg<BT, NACC>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[Cfg::STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[Cfg::STAGES];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  const uint32_t tiles_smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int n_out = mode == 2 ? N / 2 : N;
+  const int n_feat_tiles = (n_out + 2 * TC_BM - 1) / (2 * TC_BM);     // tiles of 256 features
+  const int n_tok_tiles = (M + BT - 1) / BT;
+  const int n_tiles = n_feat_tiles * n_tok_tiles;
+  const int nkb = (K + TC_BK - 1) / TC_BK;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&acc_full[b]), 1);
+      mbar_init(smem_u32(&acc_empty[b]), 2 * (SK_EPI_THREADS / 32));
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();                                        // both blocks' barriers exist
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abort_p = &abort_flag;
+  pdl_launch_dependents();
+
+  // tile -> (first feature of the pair's 256, first token); bands of 8 feature tiles
+  auto tile_of = [&](int t, int& feat0, int& tok0) {
+    const int band_tiles = SK_BAND * n_tok_tiles;
+    const int band = t / band_tiles;
+    const int in_band = t - band * band_tiles;
+    const int band_w = min(SK_BAND, n_feat_tiles - band * SK_BAND);
+    feat0 = (band * SK_BAND + in_band % band_w) * 2 * TC_BM;
+    tok0 = (in_band / band_w) * BT;
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer (one thread in each block)
+    if (lane == 0 && pair < n_tiles) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+      pdl_wait();
+      int it = 0;
+      bool ok = true;
+      for (int t = pair; t < n_tiles && ok; t += n_pairs) {
+        int feat0, tok0;
+        tile_of(t, feat0, tok0);
+        const int my_feat = feat0 + (int)rank * TC_BM;
+        const int my_tok = tok0 + (int)rank * (BT / 2);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t phase = (it / Cfg::STAGES) & 1;
+          ok = mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u, abort_p);
+          if (!ok) break;
+          const uint32_t stage = tiles_smem + s * Cfg::STAGE_BYTES;
+          const uint32_t bar0 = map_to_rank(smem_u32(&full_bar[s]), 0);   // the first block's
+          if (leader) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * Cfg::STAGE_BYTES);
+          const int kx = kb * TC_BK;
+          tma_load_2d_pair(stage, &map_w, kx, my_feat, bar0);
+          if (NACC == 2) tma_load_2d_pair(stage + Cfg::W_BYTES, &map_w, kx, n_out + my_feat, bar0);
+          tma_load_2d_pair(stage + NACC * Cfg::W_BYTES, &map_a, kx, my_tok, bar0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer: one thread of the first block, for the pair
+    if (lane == 0 && leader && pair < n_tiles) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BT >> 3) << 17) |
+                             ((uint32_t)((2 * TC_BM) >> 4) << 24);
+      bool ok = true;
+      int it = 0, part = 0;
+      for (int t = pair; t < n_tiles && ok; t += n_pairs, ++part) {
+        const int buf = part & 1;
+        ok = mbar_wait(smem_u32(&acc_empty[buf]), (((uint32_t)part >> 1) & 1u) ^ 1u, abort_p);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc_addr = tmem_base + (uint32_t)(buf * Cfg::ACC_COLS);
+        for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t phase = (it / Cfg::STAGES) & 1;
+          ok = mbar_wait(smem_u32(&full_bar[s]), phase, abort_p);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t stage = tiles_smem + s * Cfg::STAGE_BYTES;
+          const uint64_t wdesc = umma_desc_k_sw128(stage);
+          const uint64_t adesc = umma_desc_k_sw128(stage + NACC * Cfg::W_BYTES);
+#pragma unroll
+          for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
+            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+            const uint64_t koff = (uint64_t)((k * TC_UMMA_K * 2) >> 4);
+            umma_bf16_pair(acc_addr, wdesc + koff, adesc + koff, idesc, acc);
+            if (NACC == 2) {
+              const uint64_t w2 = umma_desc_k_sw128(stage + Cfg::W_BYTES);
+              umma_bf16_pair(acc_addr + BT, w2 + koff, adesc + koff, idesc, acc);
+            }
+          }
+          umma_commit_pair(smem_u32(&empty_bar[s]));           // frees the stage in both blocks
+        }
+        if (ok) umma_commit_pair(smem_u32(&acc_full[buf]));    // both blocks' epilogues may read
+      }
+    }
+  } else {
+    // ---------------- epilogue warps of both blocks: this block's 128 features
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    bool ok = true;
+    int part = 0;
+    pdl_wait();
+    for (int t = pair; t < n_tiles && ok; t += n_pairs, ++part) {
+      const int buf = part & 1;
+      int feat0, tok0;
+      tile_of(t, feat0, tok0);
+      const int f = feat0 + (int)rank * TC_BM + row;
+      mbar_wait(smem_u32(&acc_full[buf]), ((uint32_t)part >> 1) & 1u, abort_p);
+      asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
+      if (*abort_p) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                             (uint32_t)(buf * Cfg::ACC_COLS);
+      const int ncols = min(BT, M - tok0);
+#pragma unroll 1
+      for (int c0 = 0; c0 < ncols; c0 += 16) {
+        float v[16];
+        tmem_ld16(taddr + c0, v);
+        if (NACC == 2) {
+          float g2[16];
+          tmem_ld16(taddr + BT + c0, g2);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + expf(-v[j])) * g2[j];
+        }
+        sk_store_chunk(mode, out_dtype, out, v, f, tok0 + c0, M, n_out);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty[buf]), 0));
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (abort_flag) {
+    if (threadIdx.x == 0) atomicOr(status, ERR_WAIT_TIMEOUT);
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_sync_all();                  // nobody touches the peer's barriers or TMEM after this
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;"
+                 ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+  }
+}
+
+template <int BT, int NACC>
+static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
+                      int mode, int* status, cudaStream_t stream) {
+  using Cfg = G2Cfg<BT, NACC>;
+  static_assert(Cfg::STAGES >= 3, "pipeline depth");
+  CUtensorMap mw, ma;
+  int rc = make_map(&mw, W, N, K, TC_BM);
+  if (rc) return rc;
+  rc = make_map(&ma, A, M, K, BT / 2);
+  if (rc) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_2sm_kernel<BT, NACC>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int n_out = mode == 2 ? N / 2 : N;
+  const long long tiles = (long long)((n_out + 2 * TC_BM - 1) / (2 * TC_BM)) * ((M + BT - 1) / BT);
+  long long pairs = sm_count() / 2;
+  if (pairs > tiles) pairs = tiles;
+  if (pairs < 1) return -4;
+  launch_pdl(gemm_2sm_kernel<BT, NACC>, dim3((unsigned)(2 * pairs)), dim3(TC_THREADS), Cfg::SMEM,
+             stream, mw, ma, out, out_dtype, M, N, K, mode, status);
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
 }  // namespace yalm
 
 using namespace yalm;
@@ -804,4 +1087,18 @@ extern "C" int yalm_gemm_sk(const void* A, const void* W, void* out, int out_dty
   if (M <= 128) YALM_SK(128, 1);
   YALM_SK(256, 1);
 #undef YALM_SK
+}
+
+// Two-SM variant for many tokens (see gemm_2sm_kernel): mode 0 store, 1 add into
+// float32 out, 2 silu(gate)*up.
+extern "C" int yalm_gemm_2sm(const void* A, const void* W, void* out, int out_dtype, int M, int N,
+                             int K, int mode, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 != 0) return -2;
+  if (((uintptr_t)A | (uintptr_t)W) & 15) return -6;
+  if (mode < 0 || mode > 2) return -3;
+  if (mode == 2 && (N % 2 != 0)) return -3;
+  if (mode == 1 && out_dtype != DT_F32) return -3;
+  if (mode == 2) return launch_2sm<128, 2>(A, W, out, out_dtype, M, N, K, mode, status, stream);
+  return launch_2sm<256, 1>(A, W, out, out_dtype, M, N, K, mode, status, stream);
 }

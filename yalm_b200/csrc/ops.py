@@ -64,6 +64,7 @@ _SIGNATURES = {
     "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp],
     "yalm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_gemm_tc_available": [],
+    "yalm_gemm_2sm": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_gemm_sk": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _ll, _vp, _i, _vp, _vp],
 }
 
@@ -324,6 +325,18 @@ def gemm_sk(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, stat
                               1 if whole_tiles else 0, _p(scratch),
                               0 if scratch is None else scratch.numel(), _p(counters),
                               counters.numel(), _p(status), _stream()), "gemm_sk")
+
+
+def gemm_2sm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
+             status: torch.Tensor) -> None:
+    """Two-SM tcgen05 product (pairs of blocks on one 256-feature tile) with a fused epilogue."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+          and a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "gemm_2sm: operands")
+    _need(tuple(out.shape) == ((M, N // 2) if mode == GEMM_SILU_MUL else (M, N)), "gemm_2sm: out shape")
+    _check(lib().yalm_gemm_2sm(_p(a), _p(w), _p(out), dtype_code(out.dtype), M, N, K, mode,
+                               _p(status), _stream()), "gemm_2sm")
 
 
 def sample(logits: torch.Tensor, temperature: float, seed: int, row_key: torch.Tensor,
