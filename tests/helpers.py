@@ -54,7 +54,18 @@ TINY_D = {
     "tie_word_embeddings": True, "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
 }
 
-CONFIGS = {"tiny_a": (TINY_A, 0), "tiny_b": (TINY_B, 1), "tiny_c": (TINY_C, 2), "tiny_d": (TINY_D, 3)}
+# head size 64: the sizes at which the tcgen05 attention and the tensor-core decode run
+TINY_E = {
+    "architectures": ["MistralForCausalLM"],
+    "hidden_size": 128, "intermediate_size": 320, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "vocab_size": 512, "max_position_embeddings": 400, "rms_norm_eps": 1e-5,
+    "rope_theta": 10000.0, "rope_scaling": None, "sliding_window": 150,
+    "tie_word_embeddings": False, "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
+}
+
+CONFIGS = {"tiny_a": (TINY_A, 0), "tiny_b": (TINY_B, 1), "tiny_c": (TINY_C, 2), "tiny_d": (TINY_D, 3),
+           "tiny_e": (TINY_E, 4)}
 
 # Tolerances on logits, relative to the largest reference logit in magnitude.
 # float32: FMA chains in another order than the CPU's.  bfloat16: activations are

@@ -25,6 +25,9 @@ REQUESTS = {
     "tiny_c": {"lens": {"r0": 7, "r1": 45, "r2": 81, "r3": 160},
                "prompts": {"r0": 3, "r1": 41, "r2": 39, "r3": 100},
                "batches": [["r0", "r1", "r2"], ["r3", "r0"]]},
+    "tiny_e": {"lens": {"r0": 40, "r1": 400, "r2": 170, "r3": 129},
+               "prompts": {"r0": 8, "r1": 360, "r2": 160, "r3": 128},
+               "batches": [["r0", "r1", "r2"], ["r3", "r0"]]},
     "tiny_d": {"lens": {"r0": 9, "r1": 70, "r2": 38},
                "prompts": {"r0": 2, "r1": 50, "r2": 37},
                "batches": [["r0", "r1", "r2"], ["r2", "r0"]]},
@@ -63,7 +66,7 @@ def test_trace_run_matches_plain_model(name, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e"])
 def test_step_function_matches_plain_model(name, dtype):
     from yalm_b200 import LM
     from yalm_b200.config import config_from_dict
@@ -290,3 +293,18 @@ def test_a_prompt_cut_into_steps_on_a_full_ring(dtype):
            for a, b in ((0, 50), (50, 51), (51, 80), (80, 96))]
     err = float((torch.cat(got) - ref).abs().max() / ref.abs().max())
     assert err <= TOL[dtype], err
+
+
+def test_the_tcgen05_prefill_attention_inside_the_engine():
+    """attention="tcgen05" routes whole prompts through the TMEM attention kernel."""
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, seed = CONFIGS["tiny_e"]
+    w = make_weights(cfg, seed)
+    toks = [random_tokens(n, cfg["vocab_size"], 300 + n) for n in (390, 7, 129)]
+    lm = LM(config_from_dict(cfg), dict(w), dtype="bfloat16", max_batch=3, attention="tcgen05")
+    s = lm.acquire(3)
+    lg = lm.step(toks, s, [[len(t) - 1] for t in toks]).cpu()
+    for i, t in enumerate(toks):
+        ref = plain_forward(cfg, w, t)
+        assert float((lg[i] - ref[-1]).abs().max() / ref.abs().max()) <= TOL["bfloat16"]

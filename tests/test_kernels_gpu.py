@@ -496,3 +496,39 @@ def test_two_sm_matrix_product(ops, shape):
         assert (o2.double() - r2).abs().max() <= 4e-6 * math.sqrt(K) * max(1.0, r2.abs().max())
         torch.cuda.synchronize()
         assert status.item() == 0
+
+
+@pytest.mark.parametrize("H, G, hd, window", [(8, 2, 128, None), (4, 4, 64, None), (6, 3, 128, 100),
+                                              (3, 1, 64, 37)])
+def test_tcgen05_prefill_attention(ops, H, G, hd, window):
+    """attention_prefill_tc (S and P.V in tensor memory) against the plain attention:
+    ragged prompts from their first token, one of 300 tokens (three key blocks, the
+    diagonal block masked), one of a single token, one that ends inside a tile."""
+    dt = torch.bfloat16
+    inv = plain_inv_freq(hd, 10000.0, None).to(DEV)
+    lens, slots, cap = [300, 1, 130, 128], [2, 0, 3, 1], 512
+    slot_pos = torch.zeros(4, dtype=torch.int32, device=DEV)
+    kc = torch.zeros(4, G, cap, hd, device=DEV, dtype=dt)
+    vc = torch.zeros_like(kc)
+    b = B(lens, slots)
+    N = b.n_tokens
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for rep in range(2):
+        qkv = torch.randn(N, (H + 2 * G) * hd, device=DEV)
+        q_out = torch.empty(N, H * hd, device=DEV, dtype=dt)
+        kv_step = torch.empty(N, 2, G, hd, device=DEV, dtype=dt)
+        ops.rope_store(qkv, 1, inv, b, q_out, kv_step, kc, vc, slot_pos, H, G, hd, cap)
+        out = torch.full((N, H * hd), 9.0, device=DEV, dtype=dt)
+        ops.attention_prefill_tc(q_out, kv_step, b, out, H, G, hd, window, status)
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        qs = b.q_start.tolist()
+        for i in range(len(lens)):
+            t = qkv[qs[i]:qs[i + 1]].cpu().view(-1, H + 2 * G, hd)
+            pos = torch.arange(lens[i])
+            qq = plain_rope(t[:, :H], pos, inv.cpu()).to(dt).float()
+            kk = plain_rope(t[:, H:H + G], pos, inv.cpu()).to(dt).float()
+            vv = t[:, H + G:].to(dt).float()
+            ref = plain_attention(qq, kk, vv, window)
+            got = out[qs[i]:qs[i + 1]].float().cpu().view(-1, H, hd)
+            assert (got - ref).abs().max().item() <= 2.5e-2, (rep, i)

@@ -51,6 +51,12 @@ int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_
                               int hd, int capacity, int window, int max_context,
                               int chunks_per_block, cudaStream_t stream);
 
+// bfloat16 prefill attention on tcgen05 (attention_tc.cu): sequences that start at their
+// first token, head size 64 or 128
+int yalm_attention_prefill_tc(const void* q, const void* kv_step, const int* q_start, void* out,
+                              int n_tokens, int n_seqs, int max_q_len, int H, int G, int hd,
+                              int window, int* status, cudaStream_t stream);
+
 int yalm_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* out,
                    int out_dtype, int M, int N, int K, int accumulate, cudaStream_t stream);
 

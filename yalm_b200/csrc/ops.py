@@ -58,6 +58,7 @@ _SIGNATURES = {
                               _i, _i, _i, _i, _vp],
     "yalm_attention_prefill_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                    _i, _vp],
+    "yalm_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_attention_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _vp],
     "yalm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
@@ -242,6 +243,23 @@ def attention_prefill_mma(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch
                                             _p(out), batch.n_seqs, max(batch.q_lens), H, G, hd,
                                             capacity, int(window or 0), _stream()),
            "attention_prefill_mma")
+
+
+def tc_attention_usable(dtype: torch.dtype, hd: int, past) -> bool:
+    """The tcgen05 prefill attention takes bfloat16, head size 64 or 128, and sequences
+    that start at their first token (every key is one of this step's)."""
+    return dtype == torch.bfloat16 and hd in (64, 128) and all(p == 0 for p in past)
+
+
+def attention_prefill_tc(q: torch.Tensor, kv_step: torch.Tensor, batch, out: torch.Tensor,
+                         H: int, G: int, hd: int, window: Optional[int],
+                         status: torch.Tensor) -> None:
+    _need(q.dtype == kv_step.dtype == out.dtype == torch.bfloat16 and q.is_contiguous()
+          and kv_step.is_contiguous() and out.is_contiguous(), "attention_prefill_tc: bfloat16")
+    _check(lib().yalm_attention_prefill_tc(_p(q), _p(kv_step), _p(batch.q_start), _p(out),
+                                           q.shape[0], batch.n_seqs, max(batch.q_lens), H, G, hd,
+                                           int(window or 0), _p(status), _stream()),
+           "attention_prefill_tc")
 
 
 def decode_mma_parts(max_context: int, window: Optional[int], chunks_per_block: int) -> int:

@@ -116,6 +116,11 @@ class GQAAttention:
                 ops.attention_decode(q, view.k, view.v, batch.seq_slot, view.slot_pos, o, part_o,
                                      part_ml, counters, rt.status, H, G, hd, view.capacity,
                                      self.window, chunk, bound)
+        elif rt.attention == "tcgen05" and ops.tc_attention_usable(rt.dtype, hd, batch.past):
+            # correct but, with one query tile per block, a serial chain of barrier
+            # hand-offs per key block (569 us against 360 us per layer at 2,048 tokens):
+            # kept selectable until it runs two query tiles in ping-pong
+            ops.attention_prefill_tc(q, kv_step, batch, o, H, G, hd, self.window, rt.status)
         elif tensor_cores:
             ops.attention_prefill_mma(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G,
                                       hd, view.capacity, self.window)
