@@ -430,45 +430,6 @@ def test_tensor_core_decode_attention(ops, H, G, hd, cap, window):
             assert (got - ref).abs().max().item() <= 2.5e-2, (rep, b, n)
 
 
-@pytest.mark.parametrize("shape", [(1, 128, 64), (5, 160, 96), (8, 4096, 1024), (37, 300, 88),
-                                   (64, 2048, 512), (200, 1024, 1024), (700, 640, 448),
-                                   (1500, 1152, 320)])
-@pytest.mark.parametrize("whole_tiles", [False, True])
-def test_persistent_matrix_product(ops, shape, whole_tiles):
-    """gemm_sk: blocks that share tiles (the last one to arrive adds the parked
-    partial tiles in block order) and blocks that take whole tiles; every epilogue;
-    twice in a row (the tile counters must come back to zero)."""
-    M, N, K = shape
-    status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    counters = torch.zeros(4096, dtype=torch.int32, device=DEV)
-    scratch = torch.empty(ops.gemm_sk_scratch_floats(M, True), device=DEV)
-    a = (torch.randn(M, K, device=DEV) * 0.5).to(torch.bfloat16)
-    w = (torch.randn(N, K, device=DEV) * 0.5).to(torch.bfloat16)
-    ref = a.double() @ w.double().T
-    tol = 2e-6 * math.sqrt(K) * ref.abs().max()
-    for rep in range(2):
-        out = torch.full((M, N), 7.0, device=DEV)
-        ops.gemm_sk(a, w, out, ops.GEMM_STORE, status, scratch, counters, whole_tiles)
-        assert (out.double() - ref).abs().max() <= tol
-        first = out.clone()
-        ops.gemm_sk(a, w, out, ops.GEMM_ADD, status, scratch, counters, whole_tiles)
-        assert (out.double() - 2 * ref).abs().max() <= 2 * tol
-        outh = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
-        ops.gemm_sk(a, w, outh, ops.GEMM_STORE, status, scratch, counters, whole_tiles)
-        assert (outh.double() - ref).abs().max() <= 2 ** -8 * ref.abs().max()
-        g, u = ref[:, :N // 2], ref[:, N // 2:]
-        r2 = g / (1 + torch.exp(-g)) * u
-        o2 = torch.zeros(M, N // 2, device=DEV)
-        ops.gemm_sk(a, w, o2, ops.GEMM_SILU_MUL, status, scratch, counters, whole_tiles)
-        assert (o2.double() - r2).abs().max() <= 4e-6 * math.sqrt(K) * max(1.0, r2.abs().max())
-        # the sum over shared tiles is taken in block order: the same bits every time
-        again = torch.empty_like(first)
-        ops.gemm_sk(a, w, again, ops.GEMM_STORE, status, scratch, counters, whole_tiles)
-        assert torch.equal(again, first)
-        torch.cuda.synchronize()
-        assert status.item() == 0 and int(counters.abs().sum()) == 0
-
-
 @pytest.mark.parametrize("shape", [(1, 128, 64), (130, 300, 88), (256, 256, 64), (300, 512, 128),
                                    (700, 640, 448), (1500, 1152, 320), (2048, 1024, 1024)])
 def test_two_sm_matrix_product(ops, shape):

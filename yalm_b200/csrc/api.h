@@ -77,17 +77,6 @@ int yalm_gemm_tc(const void* A, const void* W, void* out, int out_dtype, int M, 
 // 0 if the driver's tensor-map encoder was found (host-side set-up of yalm_gemm_tc).
 int yalm_gemm_tc_available(void);
 
-// Persistent stream-K variant of the tcgen05 product with the epilogue fused for
-// every token count (mode 0 store, 1 add into float32 out, 2 silu(gate)*up).
-// whole_tiles: 1 = every block takes whole tiles (many tokens), 0 = blocks share tiles.
-// scratch: float32 workspace of at least yalm_gemm_sk_scratch_floats(M, mode == 2)
-// floats (unused with whole_tiles); counters: one int per output tile, zero before the first launch (the
-// kernel leaves them zero).
-long long yalm_gemm_sk_scratch_floats(int M, int dual);
-int yalm_gemm_sk(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
-                 int mode, int whole_tiles, float* scratch, long long scratch_floats,
-                 int* counters, int n_counters, int* status, cudaStream_t stream);
-
 // Two-SM (cta_group::2) variant for many tokens: mode 0 store, 1 add, 2 silu(gate)*up.
 int yalm_gemm_2sm(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
                   int mode, int* status, cudaStream_t stream);

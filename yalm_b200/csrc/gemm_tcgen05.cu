@@ -331,52 +331,11 @@ static int launch_tc(const CUtensorMap& mw, const void* A, void* out, int out_dt
 }
 
 
-// ===========================================================================
-// The persistent stream-K kernel.
-//
-// One block per SM.  The work is the list of (tile, k-block) units in tile
-// order; block c takes units [c*q, (c+1)*q).  Its range may begin in the middle
-// of one tile and end in the middle of another, so every SM streams the same
-// number of bytes whatever the shape is (a plain grid of 128-row tiles leaves
-// SMs idle whenever the tile count is not a multiple of the SM count).  A tile
-// that several blocks share is finished by the block that arrives last: each
-// writes its partial accumulator to scratch and bumps the tile's counter; the
-// last one adds the partials in block order (so the sum does not depend on
-// who was last) and runs the epilogue.  TMEM holds two accumulator buffers, so
-// the tensor cores start the next tile while the epilogue warps drain this one.
-//
-// Tiles are ordered in bands of 8 weight tiles with the token tile running
-// fastest inside a band, so blocks that run together share operands in L2.
+// Shared by the kernels below: tiles are ordered in bands of 8 weight tiles with the
+// token tile running fastest inside a band, so blocks that run together share
+// operands in L2.
 constexpr int SK_BAND = 8;
 constexpr int SK_EPI_THREADS = 128;
-
-template <int BT, int NACC> struct SkCfg {
-  static constexpr int W_BYTES = TC_BM * TC_BK * 2;
-  static constexpr int A_BYTES = BT * TC_BK * 2;
-  static constexpr int STAGE_BYTES = NACC * W_BYTES + A_BYTES;
-  static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
-  static constexpr int ACC_COLS = NACC * BT;                 // columns of one accumulator buffer
-  static constexpr int TMEM_RAW = 2 * ACC_COLS;
-  static constexpr int TMEM_COLS = TMEM_RAW <= 32 ? 32 : (TMEM_RAW <= 64 ? 64 :
-                                   (TMEM_RAW <= 128 ? 128 : (TMEM_RAW <= 256 ? 256 : 512)));
-  static constexpr int SLOT_FLOATS = NACC * BT * TC_BM;      // one partial tile in scratch
-  static_assert(TMEM_RAW <= 512, "two accumulator buffers must fit into TMEM");
-};
-
-struct SkTile { int feat0, tok0; };
-
-__device__ __forceinline__ SkTile sk_tile(int t, int n_feat_tiles, int n_tok_tiles, int BT) {
-  const int band_tiles = SK_BAND * n_tok_tiles;
-  const int band = t / band_tiles;
-  const int in_band = t - band * band_tiles;
-  const int band_w = min(SK_BAND, n_feat_tiles - band * SK_BAND);    // the last band may be narrow
-  SkTile r;
-  r.feat0 = (band * SK_BAND + in_band % band_w) * TC_BM;
-  r.tok0 = (in_band / band_w) * BT;
-  return r;
-}
 
 // One 16-column chunk of the epilogue for the thread that owns feature f.
 __device__ __forceinline__ void sk_store_chunk(int mode, int out_dtype, void* __restrict__ out,
@@ -412,266 +371,6 @@ __device__ __forceinline__ void sk_store_chunk(int mode, int out_dtype, void* __
   }
 }
 
-// mode 0: store, 1: add into float32 out, 2: silu(gate)*up (NACC == 2)
-template <int BT, int NACC>
-__global__ void __launch_bounds__(TC_THREADS)
-gemm_sk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-               void* __restrict__ out, int out_dtype, int M, int N, int K, int mode,
-               long long units_per_block, float* __restrict__ scratch, int* __restrict__ counters,
-               int* __restrict__ status) {
-  using Cfg = SkCfg<BT, NACC>;
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[Cfg::STAGES];
-  __shared__ __align__(8) uint64_t empty_bar[Cfg::STAGES];
-  __shared__ __align__(8) uint64_t acc_full[2];
-  __shared__ __align__(8) uint64_t acc_empty[2];
-  __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
-  __shared__ int last_flag;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t tiles_smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const int n_out = mode == 2 ? N / 2 : N;
-  const int n_feat_tiles = (n_out + TC_BM - 1) / TC_BM;
-  const int n_tok_tiles = (M + BT - 1) / BT;
-  const int nkb = (K + TC_BK - 1) / TC_BK;
-  const long long U = (long long)n_feat_tiles * n_tok_tiles * nkb;
-  const long long q = units_per_block;
-  const long long u_lo = min(U, (long long)blockIdx.x * q);
-  const long long u_hi = min(U, u_lo + q);
-
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-    for (int s = 0; s < Cfg::STAGES; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&acc_full[b]), 1);
-      mbar_init(smem_u32(&acc_empty[b]), SK_EPI_THREADS / 32);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = tmem_slot;
-  volatile int* abort_p = &abort_flag;
-  pdl_launch_dependents();
-
-  if (warp == 0) {
-    // ---------------- TMA producer: every unit of this block, in order
-    if (lane == 0 && u_hi > u_lo) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
-      // the first stages' weight tiles are requested before the wait on the
-      // previous kernel (weights do not depend on it), the activations after it
-      const int n_units = (int)(u_hi - u_lo);
-      const int pre = n_units < Cfg::STAGES ? n_units : Cfg::STAGES;
-      for (int it = 0; it < pre; ++it) {
-        const long long u = u_lo + it;
-        const int t = (int)(u / nkb);
-        const int kb = (int)(u - (long long)t * nkb);
-        const SkTile tl = sk_tile(t, n_feat_tiles, n_tok_tiles, BT);
-        const uint32_t stage = tiles_smem + it * Cfg::STAGE_BYTES;
-        const uint32_t bar = smem_u32(&full_bar[it]);
-        mbar_expect_tx(bar, Cfg::STAGE_BYTES);
-        tma_load_2d(stage, &map_w, kb * TC_BK, tl.feat0, bar);
-        if (NACC == 2) tma_load_2d(stage + Cfg::W_BYTES, &map_w, kb * TC_BK, n_out + tl.feat0, bar);
-      }
-      pdl_wait();
-      for (int it = 0; it < pre; ++it) {
-        const long long u = u_lo + it;
-        const int t = (int)(u / nkb);
-        const int kb = (int)(u - (long long)t * nkb);
-        const SkTile tl = sk_tile(t, n_feat_tiles, n_tok_tiles, BT);
-        tma_load_2d(tiles_smem + it * Cfg::STAGE_BYTES + NACC * Cfg::W_BYTES, &map_a, kb * TC_BK,
-                    tl.tok0, smem_u32(&full_bar[it]));
-      }
-      for (int it = pre; it < n_units; ++it) {
-        const long long u = u_lo + it;
-        const int t = (int)(u / nkb);
-        const int kb = (int)(u - (long long)t * nkb);
-        const SkTile tl = sk_tile(t, n_feat_tiles, n_tok_tiles, BT);
-        const int s = it % Cfg::STAGES;
-        const uint32_t phase = (it / Cfg::STAGES) & 1;
-        if (!mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u, abort_p)) break;
-        const uint32_t stage = tiles_smem + s * Cfg::STAGE_BYTES;
-        const uint32_t bar = smem_u32(&full_bar[s]);
-        mbar_expect_tx(bar, Cfg::STAGE_BYTES);
-        const int kx = kb * TC_BK;
-        tma_load_2d(stage, &map_w, kx, tl.feat0, bar);
-        if (NACC == 2) tma_load_2d(stage + Cfg::W_BYTES, &map_w, kx, n_out + tl.feat0, bar);
-        tma_load_2d(stage + NACC * Cfg::W_BYTES, &map_a, kx, tl.tok0, bar);
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer: one accumulator buffer per part, alternating
-    if (lane == 0 && u_hi > u_lo) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BT >> 3) << 17) |
-                             ((uint32_t)(TC_BM >> 4) << 24);
-      bool ok = true;
-      int it = 0, part = 0;
-      long long u = u_lo;
-      while (u < u_hi && ok) {
-        const int t = (int)(u / nkb);
-        const long long seg_end = min(u_hi, (long long)(t + 1) * nkb);
-        const int buf = part & 1;
-        ok = mbar_wait(smem_u32(&acc_empty[buf]), (((uint32_t)part >> 1) & 1u) ^ 1u, abort_p);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t acc_addr = tmem_base + (uint32_t)(buf * Cfg::ACC_COLS);
-        bool first = true;
-        for (; u < seg_end && ok; ++u, ++it) {
-          const int s = it % Cfg::STAGES;
-          const uint32_t phase = (it / Cfg::STAGES) & 1;
-          ok = mbar_wait(smem_u32(&full_bar[s]), phase, abort_p);
-          if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t stage = tiles_smem + s * Cfg::STAGE_BYTES;
-          const uint64_t wdesc = umma_desc_k_sw128(stage);
-          const uint64_t adesc = umma_desc_k_sw128(stage + NACC * Cfg::W_BYTES);
-#pragma unroll
-          for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
-            const uint32_t acc = (!first || k > 0) ? 1u : 0u;
-            const uint64_t koff = (uint64_t)((k * TC_UMMA_K * 2) >> 4);
-            umma_bf16(acc_addr, wdesc + koff, adesc + koff, idesc, acc);
-            if (NACC == 2) {
-              const uint64_t w2 = umma_desc_k_sw128(stage + Cfg::W_BYTES);
-              umma_bf16(acc_addr + BT, w2 + koff, adesc + koff, idesc, acc);
-            }
-          }
-          first = false;
-          umma_commit(smem_u32(&empty_bar[s]));
-        }
-        if (ok) umma_commit(smem_u32(&acc_full[buf]));
-        ++part;
-      }
-    }
-  } else {
-    // ---------------- epilogue warps
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;                      // TMEM lane = feature inside the tile
-    const int etid = threadIdx.x - 64;
-    bool ok = true;
-    int part = 0;
-    pdl_wait();                                   // out, scratch and counters belong to earlier kernels until now
-    long long u = u_lo;
-    while (u < u_hi && ok) {
-      const int t = (int)(u / nkb);
-      const long long tile_lo = (long long)t * nkb, tile_hi = tile_lo + nkb;
-      const long long seg_end = min(u_hi, tile_hi);
-      const bool whole = (u == tile_lo) && (seg_end == tile_hi);
-      const int buf = part & 1;
-      const SkTile tl = sk_tile(t, n_feat_tiles, n_tok_tiles, BT);
-      const int f = tl.feat0 + row;
-      mbar_wait(smem_u32(&acc_full[buf]), ((uint32_t)part >> 1) & 1u, abort_p);
-      // all epilogue threads take the same way out if a wait ran out anywhere
-      asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
-      if (*abort_p) { ok = false; break; }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
-                             (uint32_t)(buf * Cfg::ACC_COLS);
-      const int ncols = min(BT, M - tl.tok0);                 // columns that hold real tokens
-      if (whole) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < ncols; c0 += 16) {
-          float v[16];
-          tmem_ld16(taddr + c0, v);
-          if (NACC == 2) {
-            float g2[16];
-            tmem_ld16(taddr + BT + c0, g2);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + expf(-v[j])) * g2[j];
-          }
-          sk_store_chunk(mode, out_dtype, out, v, f, tl.tok0 + c0, M, n_out);
-        }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
-                                    ::"r"(smem_u32(&acc_empty[buf])) : "memory");
-      } else {
-        // a shared tile: park the partial, count, and let the last block finish it
-        const int which = (u == u_lo) ? 0 : 1;
-        float* slot = scratch + ((size_t)blockIdx.x * 2 + which) * Cfg::SLOT_FLOATS;
-#pragma unroll 1
-        for (int c0 = 0; c0 < ncols; c0 += 16) {
-#pragma unroll
-          for (int a = 0; a < NACC; ++a) {
-            float v[16];
-            tmem_ld16(taddr + a * BT + c0, v);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) slot[(size_t)(a * BT + c0 + j) * TC_BM + row] = v[j];
-          }
-        }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
-                                    ::"r"(smem_u32(&acc_empty[buf])) : "memory");
-        __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
-        const int c_first = (int)(tile_lo / q), c_last = (int)((tile_hi - 1) / q);
-        if (etid == 0) {
-          const int seen = atomicAdd(&counters[t], 1);
-          last_flag = (seen == c_last - c_first) ? 1 : 0;
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
-        if (last_flag) {
-          __threadfence();
-          if (etid == 0) counters[t] = 0;                     // ready for the next launch
-#pragma unroll 1
-          for (int c0 = 0; c0 < ncols; c0 += 16) {
-            float v[16], g2[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) { v[j] = 0.f; g2[j] = 0.f; }
-            for (int c = c_first; c <= c_last; ++c) {
-              const long long start = max((long long)c * q, tile_lo);
-              const int w = (start == (long long)c * q) ? 0 : 1;
-              const float* src = scratch + ((size_t)c * 2 + w) * Cfg::SLOT_FLOATS;
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + (size_t)(c0 + j) * TC_BM + row);
-              if (NACC == 2) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                  g2[j] += __ldcg(src + (size_t)(BT + c0 + j) * TC_BM + row);
-              }
-            }
-            if (NACC == 2) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + expf(-v[j])) * g2[j];
-            }
-            sk_store_chunk(mode, out_dtype, out, v, f, tl.tok0 + c0, M, n_out);
-          }
-        }
-        // the flag is reused by the next shared tile: keep the readers ahead of the next writer
-        asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
-      }
-      u = seg_end;
-      ++part;
-    }
-  }
-
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (abort_flag) {
-    if (threadIdx.x == 0) atomicOr(status, ERR_WAIT_TIMEOUT);
-    const unsigned long long t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
-    __syncthreads();
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
-                 ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
-  }
-}
-
 static int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -682,47 +381,6 @@ static int sm_count() {
   }
   return n;
 }
-
-template <int BT, int NACC>
-static int launch_sk(const CUtensorMap& mw, const void* A, void* out, int out_dtype, int M, int N,
-                     int K, int mode, int whole_tiles, float* scratch, long long scratch_floats,
-                     int* counters, int n_counters, int* status, cudaStream_t stream) {
-  using Cfg = SkCfg<BT, NACC>;
-  static_assert(Cfg::STAGES >= 2, "pipeline needs two stages");
-  CUtensorMap ma;
-  int rc = make_map(&ma, A, M, K, BT);
-  if (rc) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_sk_kernel<BT, NACC>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
-  const int n_out = mode == 2 ? N / 2 : N;
-  const long long nkb = (K + TC_BK - 1) / TC_BK;
-  const long long tiles = (long long)((n_out + TC_BM - 1) / TC_BM) * ((M + BT - 1) / BT);
-  const long long units = tiles * nkb;
-  long long blocks = sm_count();
-  long long q;
-  if (whole_tiles) {
-    // every block takes whole tiles: no tile is shared, nothing is parked in scratch
-    if (blocks > tiles) blocks = tiles;
-    q = ((tiles + blocks - 1) / blocks) * nkb;
-    blocks = (units + q - 1) / q;
-  } else {
-    if (blocks > units) blocks = units;
-    q = (units + blocks - 1) / blocks;
-    blocks = (units + q - 1) / q;
-    if (blocks * 2 * Cfg::SLOT_FLOATS > scratch_floats) return -13;
-  }
-  if (tiles > n_counters) return -12;
-  launch_pdl(gemm_sk_kernel<BT, NACC>, dim3((int)blocks), dim3(TC_THREADS), Cfg::SMEM, stream, 
-      mw, ma, out, out_dtype, M, N, K, mode, q, scratch, counters, status);
-  YALM_LAUNCH_CHECK();
-  return 0;
-}
-
 
 // ===========================================================================
 // The two-SM kernel for many tokens.
@@ -1045,48 +703,6 @@ extern "C" int yalm_gemm_tc(const void* A, const void* W, void* out, int out_dty
   if (M <= 128) YALM_TC(128, 1);
   YALM_TC(256, 1);
 #undef YALM_TC
-}
-
-// Scratch floats the stream-K kernel needs for M tokens (any N, K) on this device.
-extern "C" long long yalm_gemm_sk_scratch_floats(int M, int dual) {
-  const int bt = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 || dual ? 128 : 256)));
-  return (long long)sm_count() * 2 * (dual ? 2 : 1) * bt * TC_BM;
-}
-
-// out = A W^T with a fused epilogue (mode 0 store, 1 add to float32 out, 2 silu(gate)*up).
-// whole_tiles 0: blocks share tiles (every SM streams the same number of bytes: for a
-// few tokens); 1: every block takes whole tiles (no partial tiles: for many tokens).
-// scratch: float32 workspace of at least yalm_gemm_sk_scratch_floats(M, mode == 2)
-// (unused with whole_tiles); counters: one int per output tile, zero before the
-// first launch (the kernel leaves them zero).
-extern "C" int yalm_gemm_sk(const void* A, const void* W, void* out, int out_dtype, int M, int N,
-                            int K, int mode, int whole_tiles, float* scratch,
-                            long long scratch_floats, int* counters, int n_counters, int* status,
-                            cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 != 0) return -2;
-  if (((uintptr_t)A | (uintptr_t)W) & 15) return -6;
-  if (mode < 0 || mode > 2) return -3;
-  if (mode == 2 && (N % 2 != 0)) return -3;
-  if (mode == 1 && out_dtype != DT_F32) return -3;
-  CUtensorMap mw;
-  int rc = make_map(&mw, W, N, K, TC_BM);
-  if (rc) return rc;
-#define YALM_SK(BT, NACC)                                                                      \
-  return launch_sk<BT, NACC>(mw, A, out, out_dtype, M, N, K, mode, whole_tiles, scratch,        \
-                             scratch_floats, counters, n_counters, status, stream)
-  if (mode == 2) {
-    if (M <= 16) YALM_SK(16, 2);
-    if (M <= 32) YALM_SK(32, 2);
-    if (M <= 64) YALM_SK(64, 2);
-    YALM_SK(128, 2);
-  }
-  if (M <= 16) YALM_SK(16, 1);
-  if (M <= 32) YALM_SK(32, 1);
-  if (M <= 64) YALM_SK(64, 1);
-  if (M <= 128) YALM_SK(128, 1);
-  YALM_SK(256, 1);
-#undef YALM_SK
 }
 
 // Two-SM variant for many tokens (see gemm_2sm_kernel): mode 0 store, 1 add into

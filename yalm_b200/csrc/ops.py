@@ -26,8 +26,6 @@ _REFUSALS = {
     -6: "a pointer that is not 16-byte aligned",
     -10: "cuTensorMapEncodeTiled was not found in the driver",
     -11: "cuTensorMapEncodeTiled refused the tensor",
-    -12: "more output tiles than tile counters",
-    -13: "a scratch buffer that is too small",
 }
 
 
@@ -66,7 +64,6 @@ _SIGNATURES = {
     "yalm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_gemm_tc_available": [],
     "yalm_gemm_2sm": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
-    "yalm_gemm_sk": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _ll, _vp, _i, _vp, _vp],
 }
 
 _lib = None
@@ -80,8 +77,6 @@ def lib():
             fn = getattr(l, name)
             fn.argtypes = args
             fn.restype = _c.c_int
-        l.yalm_gemm_sk_scratch_floats.argtypes = [_i, _i]
-        l.yalm_gemm_sk_scratch_floats.restype = _c.c_longlong
         l.yalm_uniform01.argtypes = [_ull, _c.c_uint, _c.c_uint]
         l.yalm_uniform01.restype = _c.c_float
         _lib = l
@@ -322,27 +317,6 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, stat
         _need(tuple(out.shape) == (M, N), "gemm_tc: out is [M, N]")
     _check(lib().yalm_gemm_tc(_p(a), _p(w), _p(out), dtype_code(out.dtype), M, N, K, mode, splits,
                               _p(status), _stream()), "gemm_tc")
-
-
-def gemm_sk_scratch_floats(M: int, dual: bool) -> int:
-    return int(lib().yalm_gemm_sk_scratch_floats(int(M), 1 if dual else 0))
-
-
-def gemm_sk(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, status: torch.Tensor,
-            scratch: Optional[torch.Tensor], counters: torch.Tensor, whole_tiles: bool = False) -> None:
-    """Persistent stream-K tcgen05 product with a fused epilogue (GEMM_STORE,
-    GEMM_ADD or GEMM_SILU_MUL)."""
-    M, K = a.shape
-    N = w.shape[0]
-    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
-          and a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "gemm_sk: operands")
-    _need(tuple(out.shape) == ((M, N // 2) if mode == GEMM_SILU_MUL else (M, N)), "gemm_sk: out shape")
-    _need(counters.dtype == torch.int32 and (whole_tiles or scratch is not None),
-          "gemm_sk: workspace")
-    _check(lib().yalm_gemm_sk(_p(a), _p(w), _p(out), dtype_code(out.dtype), M, N, K, mode,
-                              1 if whole_tiles else 0, _p(scratch),
-                              0 if scratch is None else scratch.numel(), _p(counters),
-                              counters.numel(), _p(status), _stream()), "gemm_sk")
 
 
 def gemm_2sm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
