@@ -280,3 +280,125 @@ def test_a_layer_named_twice_and_a_layer_reading_anothers_cache():
         lg = eng2.step([[toks[p]]], s, [[0]]).cpu()
         assert (lg[0] - whole[p]).abs().max() <= 1e-5 * whole.abs().max(), p
     assert (whole - plain_forward(cfg, w, toks, run_order=[0, 1, 1])).abs().max() > 1e-3
+
+
+# ---------------------------------------------------------------------------
+# Two more toy parts, again defined here only: a position encoding that does not
+# rotate at all, and a feed-forward that routes each token to one of two experts
+# (router logits in 32 bits).  They sit in layer 0 of a model whose layer 1 is the
+# stock attention + SwiGLU.
+
+def _register_toy_position_and_routing():
+    from yalm_b200.config import LlamaConfig, PartSpec, register_architecture
+    from yalm_b200.csrc import ops
+    from yalm_b200.parts import FEED_FORWARDS, register_feed_forward, register_position
+    from yalm_b200.weights import TensorNeed
+    if "toy_top1" in FEED_FORWARDS:
+        return
+
+    @register_position("no_position")
+    class NoPosition:
+        """Keys and queries as they are: the rotary kernel with every frequency zero
+        (it still converts, and writes the cache)."""
+
+        def __init__(self, params, rt):
+            self.hd = int(params["head_dim"])
+            self.zero = torch.zeros(self.hd // 2, device=rt.device)
+
+        def rotate_and_store(self, qkv, n_partials, batch, view, q_out, kv_step, H, G,
+                             write_cache=True):
+            ops.rope_store(qkv, n_partials, self.zero, batch, q_out, kv_step, view.k, view.v,
+                           view.slot_pos, H, G, self.hd, view.capacity, write_cache)
+
+    @register_feed_forward("toy_top1")
+    class ToyTop1:
+        def __init__(self, params, rt):
+            self.rt, self.D, self.F, self.E = rt, params["size"], params["ffn"], params["experts"]
+
+        def tensor_needs(self):
+            n = {"router": TensorNeed((self.E, self.D))}
+            for e in range(self.E):
+                n[f"gate{e}"] = TensorNeed((self.F, self.D))
+                n[f"up{e}"] = TensorNeed((self.F, self.D))
+                n[f"down{e}"] = TensorNeed((self.D, self.F))
+            return n
+
+        def bind(self, tensors):
+            self.w = {k: v.to(self.rt.device, torch.float32) for k, v in tensors.items()}
+
+        def forward(self, h, batch, stream):
+            hf = h.float()
+            choice = (hf @ self.w["router"].T).argmax(-1)          # router logits in 32 bits
+            out = torch.zeros_like(hf)
+            for e in range(self.E):
+                rows = (choice == e).nonzero()[:, 0]
+                if rows.numel():
+                    x = hf[rows]
+                    g, u = x @ self.w[f"gate{e}"].T, x @ self.w[f"up{e}"].T
+                    out[rows] = (torch.nn.functional.silu(g) * u) @ self.w[f"down{e}"].T
+            stream.add_tensor(out)
+
+    class ToyRoutedConfig(LlamaConfig):
+        def to_spec(self):
+            spec = super().to_spec()
+            l0 = spec.layers[0]
+            mixer = dataclasses.replace(l0.mixer, params=dict(
+                l0.mixer.params, position=PartSpec("no_position", {"head_dim": self.head_dim})))
+            names = {"router": "model.layers.0.moe.router.weight"}
+            for e in range(2):
+                for k in ("gate", "up", "down"):
+                    names[f"{k}{e}"] = f"model.layers.0.moe.experts.{e}.{k}.weight"
+            ffn = PartSpec("toy_top1", {"size": self.hidden_size, "ffn": 40, "experts": 2}, names)
+            return dataclasses.replace(spec, layers=[dataclasses.replace(l0, mixer=mixer, feed_forward=ffn)]
+                                       + spec.layers[1:])
+
+    register_architecture("ToyRoutedForCausalLM", ToyRoutedConfig)
+
+
+def test_toy_position_encoding_and_routed_feed_forward():
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    _register_toy_position_and_routing()
+    cfg = dict(TINY_A, architectures=["ToyRoutedForCausalLM"])
+    w = make_weights(cfg, 6)
+    for k in ("gate_proj", "up_proj", "down_proj"):
+        del w[f"model.layers.0.mlp.{k}.weight"]
+    g = torch.Generator().manual_seed(9)
+    w["model.layers.0.moe.router.weight"] = torch.randn(2, 64, generator=g).to(torch.bfloat16)
+    for e in range(2):
+        w[f"model.layers.0.moe.experts.{e}.gate.weight"] = (0.1 * torch.randn(40, 64, generator=g)).to(torch.bfloat16)
+        w[f"model.layers.0.moe.experts.{e}.up.weight"] = (0.1 * torch.randn(40, 64, generator=g)).to(torch.bfloat16)
+        w[f"model.layers.0.moe.experts.{e}.down.weight"] = (0.1 * torch.randn(64, 40, generator=g)).to(torch.bfloat16)
+
+    def plain(toks):
+        T = len(toks)
+        H, G, hd, eps = 4, 2, 16, cfg["rms_norm_eps"]
+        x = plain_embedding(w["model.embed_tokens.weight"], toks)
+        h = plain_rmsnorm(x, w["model.layers.0.input_layernorm.weight"], eps)
+        q = (h @ w["model.layers.0.self_attn.q_proj.weight"].float().T).view(T, H, hd)
+        k = (h @ w["model.layers.0.self_attn.k_proj.weight"].float().T).view(T, G, hd)
+        v = (h @ w["model.layers.0.self_attn.v_proj.weight"].float().T).view(T, G, hd)
+        a = plain_attention(q, k, v, None).reshape(T, H * hd)          # no rotation
+        x = x + a @ w["model.layers.0.self_attn.o_proj.weight"].float().T
+        h = plain_rmsnorm(x, w["model.layers.0.post_attention_layernorm.weight"], eps)
+        choice = (h @ w["model.layers.0.moe.router.weight"].float().T).argmax(-1)
+        y = torch.zeros_like(x)
+        for t in range(T):
+            e = int(choice[t])
+            y[t] = plain_swiglu(h[t:t + 1], w[f"model.layers.0.moe.experts.{e}.gate.weight"],
+                                w[f"model.layers.0.moe.experts.{e}.up.weight"],
+                                w[f"model.layers.0.moe.experts.{e}.down.weight"])[0]
+        x = plain_block(x + y, cfg, w, 1, torch.arange(T))
+        x = plain_rmsnorm(x, w["model.norm.weight"], eps)
+        return x @ w["lm_head.weight"].float().T, choice
+
+    toks = random_tokens(50, 256, 12)
+    ref, choice = plain(toks)
+    assert 5 < int(choice.sum()) < 45                               # both experts are used
+    lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=1)
+    s = lm.acquire(1)
+    lg = lm.step([toks[:35]], s, [list(range(35))]).cpu()
+    assert (lg - ref[:35]).abs().max() <= 1e-5 * ref.abs().max()
+    for p in range(35, 50):
+        lg = lm.step([[toks[p]]], s, [[0]]).cpu()
+        assert (lg[0] - ref[p]).abs().max() <= 1e-5 * ref.abs().max(), p

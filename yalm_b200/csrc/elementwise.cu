@@ -155,14 +155,30 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, int n_partials,
 }
 
 // ------------------------------------------------- rotary + cache write
-// One block per (token, group of heads); one thread per (head, rotary pair).
+// One block per (token, group of heads); one thread per (head, VEC rotary pairs).
 // qkv: [N, (H+2G)*hd] in 32-bit (n_partials slices are summed).  Pair
 // (i, i+hd/2) of every q and k head is rotated by the angle pos * inv_freq[i],
 // all in 32-bit.  Rotated q goes to q_out [N, H*hd]; rotated k and plain v go
 // to kv_step [N, 2, G, hd] (this step's keys and values in token order) and,
 // for the positions that the ring keeps, to the cache [slots, G, capacity, hd]
-// at row pos % capacity.
-template <typename T>
+// at row pos % capacity.  VEC = 4 when hd/2 is a multiple of 4 (16-byte loads,
+// 8- or 16-byte stores), else 1.
+template <typename T, int VEC> struct RopeIO;
+template <> struct RopeIO<float, 4> {
+  static __device__ __forceinline__ void store(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct RopeIO<__nv_bfloat16, 4> {
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    store4(p, make_float4(v[0], v[1], v[2], v[3]));
+  }
+};
+template <typename T> struct RopeIO<T, 1> {
+  static __device__ __forceinline__ void store(T* p, const float* v) { p[0] = from_float<T>(v[0]); }
+};
+
+template <typename T, int VEC>
 __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
                                   long long partial_stride, const float* __restrict__ inv_freq,
                                   const int* __restrict__ token_seq, const int* __restrict__ q_start,
@@ -174,8 +190,9 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
   pdl_wait();
   const int t = blockIdx.x;
   const int half = hd >> 1;
-  const int i = threadIdx.x % half;
-  const int head = blockIdx.y * heads_per_block + threadIdx.x / half;
+  const int lanes = half / VEC;                             // threads per head
+  const int i = (threadIdx.x % lanes) * VEC;
+  const int head = blockIdx.y * heads_per_block + threadIdx.x / lanes;
   if (head >= H + 2 * G) return;
   const int b = token_seq[t];
   const int slot = seq_slot[b];
@@ -186,34 +203,46 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
   const bool keep = write_cache && pos >= end - capacity;
   const int row_elems = (H + 2 * G) * hd;
   const float* sp = qkv + (size_t)t * row_elems + head * hd + i;
-  float a = 0.f, bb = 0.f;
+  float a[VEC], bb[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) { a[v] = 0.f; bb[v] = 0.f; }
   for (int p = 0; p < n_partials; ++p) {
-    a += sp[(size_t)p * partial_stride];
-    bb += sp[(size_t)p * partial_stride + half];
+    const float* pp = sp + (size_t)p * partial_stride;
+    if (VEC == 4) {
+      const float4 x = *reinterpret_cast<const float4*>(pp);
+      const float4 y = *reinterpret_cast<const float4*>(pp + half);
+      a[0] += x.x; a[VEC > 1 ? 1 : 0] += x.y; a[VEC > 2 ? 2 : 0] += x.z; a[VEC > 3 ? 3 : 0] += x.w;
+      bb[0] += y.x; bb[VEC > 1 ? 1 : 0] += y.y; bb[VEC > 2 ? 2 : 0] += y.z; bb[VEC > 3 ? 3 : 0] += y.w;
+    } else {
+      a[0] += pp[0];
+      bb[0] += pp[half];
+    }
   }
   if (head < H + G) {
-    const float ang = (float)pos * inv_freq[i];
-    const float c = cosf(ang), s = sinf(ang);
-    const float r0 = a * c - bb * s, r1 = a * s + bb * c;
-    a = r0;
-    bb = r1;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const float ang = (float)pos * inv_freq[i + v];
+      const float c = cosf(ang), s = sinf(ang);
+      const float r0 = a[v] * c - bb[v] * s, r1 = a[v] * s + bb[v] * c;
+      a[v] = r0;
+      bb[v] = r1;
+    }
   }
-  const T o0 = from_float<T>(a), o1 = from_float<T>(bb);
   if (head < H) {
-    T* o = q_out + ((size_t)t * H + head) * hd;
-    o[i] = o0;
-    o[i + half] = o1;
+    T* o = q_out + ((size_t)t * H + head) * hd + i;
+    RopeIO<T, VEC>::store(o, a);
+    RopeIO<T, VEC>::store(o + half, bb);
     return;
   }
   const bool is_v = head >= H + G;
   const int g = head - H - (is_v ? G : 0);
-  T* o = kv_step + ((size_t)t * 2 * G + (is_v ? G : 0) + g) * hd;
-  o[i] = o0;
-  o[i + half] = o1;
+  T* o = kv_step + ((size_t)t * 2 * G + (is_v ? G : 0) + g) * hd + i;
+  RopeIO<T, VEC>::store(o, a);
+  RopeIO<T, VEC>::store(o + half, bb);
   if (keep) {
-    T* c = (is_v ? v_cache : k_cache) + (((size_t)slot * G + g) * capacity + pos % capacity) * hd;
-    c[i] = o0;
-    c[i + half] = o1;
+    T* c = (is_v ? v_cache : k_cache) + (((size_t)slot * G + g) * capacity + pos % capacity) * hd + i;
+    RopeIO<T, VEC>::store(c, a);
+    RopeIO<T, VEC>::store(c + half, bb);
   }
 }
 
@@ -318,22 +347,27 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
   if (n_tokens <= 0) return 0;
   if (hd % 2 != 0 || hd / 2 > 512 || hd <= 0) return -2;
   const int half = hd / 2;
-  int hpb = 1024 / half;                       // heads per block
-  if (hpb > 8) hpb = 8;
+  const bool vec = half % 4 == 0 && partial_stride % 4 == 0 &&
+                   ((((uintptr_t)qkv) | ((uintptr_t)q_out) | ((uintptr_t)kv_step) |
+                     ((uintptr_t)k_cache) | ((uintptr_t)v_cache)) & 15) == 0;
+  const int lanes = vec ? half / 4 : half;                  // threads per head
+  int hpb = 512 / lanes;                                    // heads per block
+  if (hpb > 16) hpb = 16;
+  if (hpb < 1) hpb = 1;
   if (hpb > H + 2 * G) hpb = H + 2 * G;
   const dim3 grid(n_tokens, (H + 2 * G + hpb - 1) / hpb);
-  const int threads = half * hpb;
-  if (grid.y > 65535) return -4;
-  if (dtype == DT_F32)
-    launch_pdl(rope_store_kernel<float>, dim3(grid), dim3(threads), 0, stream, 
-        qkv, n_partials, partial_stride, inv_freq, token_seq, q_start, seq_slot, slot_pos,
-        (float*)q_out, (float*)kv_step, (float*)k_cache, (float*)v_cache, H, G, hd, capacity,
-        write_cache, hpb);
-  else
-    launch_pdl(rope_store_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, 
-        qkv, n_partials, partial_stride, inv_freq, token_seq, q_start, seq_slot, slot_pos,
-        (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_step, (__nv_bfloat16*)k_cache,
-        (__nv_bfloat16*)v_cache, H, G, hd, capacity, write_cache, hpb);
+  const int threads = lanes * hpb;
+  if (grid.y > 65535 || threads > 1024) return -4;
+#define YALM_ROPE(T, V)                                                                        \
+  launch_pdl(rope_store_kernel<T, V>, grid, dim3(threads), 0, stream, qkv, n_partials,         \
+             partial_stride, inv_freq, token_seq, q_start, seq_slot, slot_pos, (T*)q_out,      \
+             (T*)kv_step, (T*)k_cache, (T*)v_cache, H, G, hd, capacity, write_cache, hpb)
+  if (dtype == DT_F32) {
+    if (vec) YALM_ROPE(float, 4); else YALM_ROPE(float, 1);
+  } else {
+    if (vec) YALM_ROPE(__nv_bfloat16, 4); else YALM_ROPE(__nv_bfloat16, 1);
+  }
+#undef YALM_ROPE
   YALM_LAUNCH_CHECK();
   return 0;
 }
