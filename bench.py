@@ -250,6 +250,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1/64 and prefill")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (profiling)")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="only the 2,048-token prefill, once (profiling); prints its record alone")
     ap.add_argument("--no-graphs", action="store_true",
                     help="launch decode kernels one by one instead of replaying a CUDA graph")
     args = ap.parse_args()
@@ -274,7 +276,8 @@ def main():
     t0 = time.time()
     lm = LM.from_random(cfg, seed=0, dtype="bfloat16", std=0.02, norm_jitter=0.0,
                         max_context=context,
-                        max_batch=max(64, args.batch) if headline and not args.no_points else args.batch)
+                        max_batch=max(64, args.batch) if headline and not (args.no_points or args.prefill_only)
+                        else args.batch)
     torch.cuda.synchronize()
     print(f"[bench] model ready in {time.time() - t0:.0f} s "
           f"({lm.model.weight_bytes() / 1e9:.1f} GB weights, {lm.engine.cache.bytes() / 1e9:.1f} GB cache)",
@@ -282,6 +285,9 @@ def main():
 
     if args.no_graphs:
         lm.engine.use_graphs = False
+    if args.prefill_only:
+        print(json.dumps({"prefill": time_prefill(lm, 2048, 1, pk), "layers": args.layers}))
+        return 0
     W = max(3, args.warmup)
     main_run = time_decode(lm, args.batch, args.steps, W, seed=1, sampler=ClockSampler(), lo=lo, hi=hi)
     by = decode_bytes(lm, main_run["contexts"])

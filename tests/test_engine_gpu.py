@@ -247,6 +247,15 @@ def test_step_refuses_bad_requests():
     lm.step([[1, 2]], [s], [[1]])                               # still usable afterwards
 
 
+def test_a_cache_beyond_the_device_memory_is_refused_before_it_is_allocated():
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    from yalm_b200.engine.step import CacheMemoryError
+    cfg, seed = CONFIGS["tiny_a"]
+    with pytest.raises(CacheMemoryError, match="GiB are free"):
+        LM(config_from_dict(cfg), make_weights(cfg, seed), dtype="float32", max_batch=10 ** 8)
+
+
 def test_command_line_completion_and_perplexity(tmp_path):
     """python -m yalm_b200 with token-id prompts on a random model folder that
     the random-weights mode wrote."""

@@ -28,6 +28,10 @@ class StepError(RuntimeError):
     pass
 
 
+class CacheMemoryError(StepError):
+    """The cache that was asked for does not fit the device's free memory."""
+
+
 class Engine:
     def __init__(self, model: Model, n_slots: int, context: int):
         self.model = model
@@ -35,7 +39,16 @@ class Engine:
         self.context = int(context)
         if self.context > model.spec.max_positions:
             raise StepError(f"context {context} exceeds the model's {model.spec.max_positions} positions")
-        self.cache = Cache(model.cache_needs(), n_slots, self.context, self.rt.dtype, self.rt.device)
+        needs = model.cache_needs()
+        want = Cache.bytes_needed(needs, n_slots, self.context, self.rt.dtype)
+        if torch.device(self.rt.device).type == "cuda":
+            free, _ = torch.cuda.mem_get_info(self.rt.device)
+            if want > free:
+                raise CacheMemoryError(
+                    f"the cache for {n_slots} sequences of {self.context} positions needs "
+                    f"{want / 2**30:.1f} GiB; {free / 2**30:.1f} GiB are free on {self.rt.device}: "
+                    f"ask for fewer sequences (max_batch) or a shorter context (max_context)")
+        self.cache = Cache(needs, n_slots, self.context, self.rt.dtype, self.rt.device)
         self.vocab = model.spec.vocab_size
         self._graphs: Dict[tuple, dict] = {}
         self._dec: Optional[dict] = None
