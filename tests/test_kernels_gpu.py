@@ -392,6 +392,7 @@ def test_tensor_core_prefill_attention(ops, H, G, hd, cap, window):
     (6, 3, 48, 40, 40),
     (40, 2, 64, 300, 100),      # 20 query heads per kv head: two head groups of the tile
     (3, 1, 32, 1000, None),
+    (24, 2, 80, 200, None),     # 12 query heads per kv head: both 8-head tiles, one partly empty
 ])
 def test_tensor_core_decode_attention(ops, H, G, hd, cap, window):
     dt = torch.bfloat16

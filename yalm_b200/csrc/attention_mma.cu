@@ -328,20 +328,53 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 }
 
 // ------------------------------------------------------------------ decode
-// One query token per sequence; every key in the cache.  The rows of the MMA
-// tile are the (up to 16) query heads that share a kv head.  A block takes a run
-// of `cpc` consecutive chunks of 64 positions of one (sequence, kv head, head
-// group) and walks through them with double-buffered cp.async staging and an
-// online softmax; each warp takes 16 of a chunk's keys.  With few sequences cpc
-// is small, so that many blocks work on one sequence at once and the block that
-// finishes last merges their partial results (as in attn_decode_kernel); with many
-// sequences cpc covers the whole sequence and nothing is merged.  Maxima are
-// kept in the log2 domain (scores times log2(e)/sqrt(hd)).
-constexpr int FD_CHUNK = 64;
-constexpr int FD_ROWS = 16;
-constexpr int FD_STAGES = 3;       // chunks in flight or in use per block
+// One query token per sequence; every key in the cache.  The product is taken
+// transposed: S^T = K.Q^T and O^T = V^T.P^T, so the 16 rows of an MMA tile are keys
+// (or features of the head) and the 8 columns are the query heads that share the kv
+// head -- with grouped queries nothing of a tile is padding, and the running
+// output is 32 registers instead of 64.  A block takes a run of `cpc` consecutive
+// chunks of 64 positions of one (sequence, kv head, group of up to 16 heads).
+// Inside the block each warp walks through its own units of 32 keys (unit u of the
+// run goes to warp u % 4) with a ring of cp.async stages of its own: no barrier
+// of the block inside the loop.  The warps' partial results are merged through
+// shared memory at the end; with few sequences cpc is small, many blocks work on
+// one sequence and the block that finishes last merges their parts (as in
+// attn_decode_kernel); with many sequences a block takes a whole sequence.
+// Maxima are kept in the log2 domain (scores times log2(e)/sqrt(hd)).
+constexpr int FD_CHUNK = 64;       // the unit of the host's plan
+constexpr int FD_UNIT = 32;        // keys a warp takes at a time
+constexpr int FD_ROWS = 16;        // query heads per block
+constexpr int FD_STAGES = 3;       // units in flight or in use per warp
+constexpr int FD_OPAD = 20;        // row length of the merge buffer [warp][feature][head]
 
+__device__ __forceinline__ uint32_t movmatrix_t(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+
+// One warp loads `n` consecutive positions of a cache ring (rows first_row,
+// first_row + 1, ... modulo capacity) into a swizzled tile and zero-fills rows
+// n..rows-1.  Each lane keeps one 16-byte column and steps through the rows.
 template <int HDP>
+__device__ __forceinline__ void warp_load_ring_tile(uint32_t base, int rows, int n, int hd,
+                                                    const __nv_bfloat16* ring, int first_row,
+                                                    int capacity, int lane) {
+  const int cpr = hd >> 3;
+  const int rstep = 32 / cpr;                                 // rows covered per pass (hd <= 128)
+  if (lane >= rstep * cpr) return;
+  const int ch = lane % cpr;
+  int r = lane / cpr;
+  int row = (first_row + r) % capacity;
+  const int wrap = rstep % capacity;
+  for (; r < rows; r += rstep) {
+    cp_async16(tile_addr<HDP>(base, r, ch), ring + (size_t)row * hd + ch * 8, r < n);
+    row += wrap;
+    if (row >= capacity) row -= capacity;
+  }
+}
+
+template <int HDP, int NT>
 __global__ void __launch_bounds__(FA_THREADS)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                        const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ seq_slot,
@@ -349,8 +382,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                        float* __restrict__ part_o, float* __restrict__ part_ml,
                        int* __restrict__ counters, int* __restrict__ status, int H, int G, int hd,
                        int capacity, int window, int cpc, int max_parts, float scale_log2) {
-  constexpr int NKS = HDP / 16, NOT = HDP / 8;
-  constexpr int STAGE = 2 * FD_CHUNK * HDP * 2;              // K and V of one chunk, bytes
+  constexpr int NKS = HDP / 16;                              // 16-wide steps over the head size
+  constexpr int TILE = FD_UNIT * HDP * 2;                    // K (or V) of one unit, bytes
+  constexpr int WARP_RING = FD_STAGES * 2 * TILE;
+  constexpr uint32_t FULL = 0xffffffffu;
   extern __shared__ __align__(128) uint8_t fa_smem[];
   __shared__ float wm_s[FA_WARPS][FD_ROWS];                  // per warp: row max, row sum
   __shared__ float wl_s[FA_WARPS][FD_ROWS];
@@ -373,136 +408,188 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   const int n_parts = (n_chunks + cpc - 1) / cpc;
   if (n_parts > max_parts && part == 0 && threadIdx.x == 0) atomicOr(status, ERR_CONTEXT_RANGE);
   if (part >= n_parts) return;
-  const int c0 = part * cpc, c1 = min(n_chunks, c0 + cpc);
-  const int nks = hd >> 4, n_ot = hd >> 3;
+  constexpr int UPC = FD_CHUNK / FD_UNIT;
+  const int u0 = part * cpc * UPC;
+  const int u1 = min((nkeys + FD_UNIT - 1) / FD_UNIT, u0 + cpc * UPC);
+  const int nks = hd >> 4;
 
-  const uint32_t kv_s = smem_u32(fa_smem);                   // FD_STAGES stages of (K, V)
-  const uint32_t q_s = kv_s + FD_STAGES * STAGE;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
+  const uint32_t q_s = smem_u32(fa_smem);                    // [16 heads][HDP]
+  const uint32_t ring_s = q_s + FD_ROWS * HDP * 2 + warp * WARP_RING;
   const __nv_bfloat16* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
   const __nv_bfloat16* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
-  auto load_chunk = [&](int c, int stage) {
-    const int k_lo = lo + c * FD_CHUNK;
-    const int n = min(FD_CHUNK, pos + 1 - k_lo);
-    load_ring_tile<HDP>(kv_s + stage * STAGE, FD_CHUNK, n, hd, kc, k_lo % capacity, capacity);
-    load_ring_tile<HDP>(kv_s + stage * STAGE + FD_CHUNK * HDP * 2, FD_CHUNK, n, hd, vc,
-                        k_lo % capacity, capacity);
+  auto load_unit = [&](int u, int stage) {
+    const int k_lo = lo + u * FD_UNIT;
+    const int n = min(FD_UNIT, pos + 1 - k_lo);
+    const uint32_t dst = ring_s + stage * 2 * TILE;
+    warp_load_ring_tile<HDP>(dst, FD_UNIT, n, hd, kc, k_lo % capacity, capacity, lane);
+    warp_load_ring_tile<HDP>(dst + TILE, FD_UNIT, n, hd, vc, k_lo % capacity, capacity, lane);
   };
   load_tile<HDP>(q_s, FD_ROWS, hd, q, [&](int r) -> const __nv_bfloat16* {
     return r < nh ? q + ((size_t)t * H + h0 + r) * hd : nullptr;
   });
-  // FD_STAGES - 1 chunks are requested before the first is used
+  cp_async_commit();
+  // FD_STAGES - 1 units are requested before the first is used
+  int u_next = u0 + warp;
 #pragma unroll
   for (int i = 0; i < FD_STAGES - 1; ++i) {
-    if (c0 + i < c1) load_chunk(c0 + i, i);
+    if (u_next < u1) load_unit(u_next, i);
+    u_next += FA_WARPS;
     cp_async_commit();
   }
-
-  float o[NOT][4];
+  cp_async_wait<FD_STAGES - 1>();                            // this thread's share of Q
+  __syncthreads();                                           // everybody's
+  // Q^T as the B operand: per 16-wide step two registers for heads 0-7, two for 8-15
+  uint32_t qf[NKS][4];
 #pragma unroll
-  for (int i = 0; i < NOT; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
-  float m_w[2] = {-INFINITY, -INFINITY}, l_w[2] = {0.f, 0.f};
-  const int key0 = warp * 16;                                // this warp's keys inside a chunk
+  for (int ks = 0; ks < NKS; ++ks)
+    if (ks < nks)
+      ldsm_x4(qf[ks], tile_addr<HDP>(q_s, (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
 
-  for (int c = c0; c < c1; ++c) {
-    const int stage = (c - c0) % FD_STAGES;
-    cp_async_wait<FD_STAGES - 2>();                          // chunk c (and Q) have landed
-    __syncthreads();                                         // ... and chunk c-1 is no longer read
-    if (c + FD_STAGES - 1 < c1) load_chunk(c + FD_STAGES - 1, (c - c0 + FD_STAGES - 1) % FD_STAGES);
+  float o[NKS][NT][4];                                       // O^T: 16 features x 8 heads per tile
+#pragma unroll
+  for (int i = 0; i < NKS; ++i)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[i][nt][j] = 0.f;
+  float m_w[NT][2], l_w[NT][2];                              // per head (column): tig*2, tig*2+1
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    m_w[nt][0] = m_w[nt][1] = -INFINITY;
+    l_w[nt][0] = l_w[nt][1] = 0.f;
+  }
+
+  int it = 0;
+  for (int u = u0 + warp; u < u1; u += FA_WARPS, ++it) {
+    const int stage = it % FD_STAGES;
+    cp_async_wait<FD_STAGES - 2>();                          // unit u has landed (this lane's share)
+    __syncwarp();                                            // ... every lane's; unit u-1 is read out
+    if (u_next < u1) load_unit(u_next, (it + FD_STAGES - 1) % FD_STAGES);
+    u_next += FA_WARPS;
     cp_async_commit();
-    const uint32_t k_s = kv_s + stage * STAGE, v_s = k_s + FD_CHUNK * HDP * 2;
-    const int n = min(FD_CHUNK, pos + 1 - (lo + c * FD_CHUNK));
+    const uint32_t k_s = ring_s + stage * 2 * TILE, v_s = k_s + TILE;
+    const int n = min(FD_UNIT, pos + 1 - (lo + u * FD_UNIT));
 
-    float s[2][4];
+    float s[2][NT][4];                                       // S^T: two tiles of 16 keys x 8 heads
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[mt][nt][j] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < NKS; ++ks) {
       if (ks < nks) {
-        uint32_t qf[4], kf[4];
-        ldsm_x4(qf, tile_addr<HDP>(q_s, lane & 15, ks * 2 + (lane >> 4)));
-        const int row = key0 + (lane & 7) + ((lane >> 4) << 3);
-        ldsm_x4(kf, tile_addr<HDP>(k_s, row, ks * 2 + ((lane >> 3) & 1)));
-        mma_bf16(s[0], qf, kf);
-        mma_bf16(s[1], qf, kf + 2);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          uint32_t kf[4];
+          ldsm_x4(kf, tile_addr<HDP>(k_s, mt * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) mma_bf16(s[mt][nt], kf, &qf[ks][2 * nt]);
+        }
       }
     }
-    float m_new[2] = {m_w[0], m_w[1]};
+    float m_new[NT][2];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int nt = 0; nt < NT; ++nt) { m_new[nt][0] = m_w[nt][0]; m_new[nt][1] = m_w[nt][1]; }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int key = key0 + i * 8 + tig * 2 + (j & 1);
-        s[i][j] = key < n ? s[i][j] * scale_log2 : -INFINITY;
-        m_new[j >> 1] = fmaxf(m_new[j >> 1], s[i][j]);
+        const bool live = mt * 16 + gid + ((j >> 1) << 3) < n;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          s[mt][nt][j] = live ? s[mt][nt][j] * scale_log2 : -INFINITY;
+          m_new[nt][j & 1] = fmaxf(m_new[nt][j & 1], s[mt][nt][j]);
+        }
+      }
+    bool changed = false;
+    float corr[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float m = m_new[nt][c];
+        m = fmaxf(m, __shfl_xor_sync(FULL, m, 4));
+        m = fmaxf(m, __shfl_xor_sync(FULL, m, 8));
+        m = fmaxf(m, __shfl_xor_sync(FULL, m, 16));
+        m_new[nt][c] = m;
+        corr[nt][c] = m > -INFINITY ? exp2f(m_w[nt][c] - m) : 1.f;
+        changed |= m != m_w[nt][c];
+        l_w[nt][c] *= corr[nt][c];
+        m_w[nt][c] = m;
+      }
+    if (__any_sync(FULL, changed)) {                         // rare after the first units
+#pragma unroll
+      for (int i = 0; i < NKS; ++i)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          o[i][nt][0] *= corr[nt][0]; o[i][nt][1] *= corr[nt][1];
+          o[i][nt][2] *= corr[nt][0]; o[i][nt][3] *= corr[nt][1];
+        }
+    }
+    // P^T as the B operand of the second product: each 8x8 block of S^T, transposed
+    uint32_t pb[2][NT][2];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float p[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float mr = m_new[nt][j & 1];
+          p[j] = mr > -INFINITY ? exp2f(s[mt][nt][j] - mr) : 0.f;
+          l_w[nt][j & 1] += p[j];                            // this lane's keys only
+        }
+        pb[mt][nt][0] = movmatrix_t(pack_bf16(p[0], p[1]));
+        pb[mt][nt][1] = movmatrix_t(pack_bf16(p[2], p[3]));
       }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
-      m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
-    }
-    float corr[2], l_add[2] = {0.f, 0.f};
+    for (int i = 0; i < NKS; ++i) {
+      if (i < nks) {
 #pragma unroll
-    for (int r = 0; r < 2; ++r) corr[r] = m_new[r] > -INFINITY ? exp2f(m_w[r] - m_new[r]) : 1.f;
-    uint32_t pf[4];
+        for (int mt = 0; mt < 2; ++mt) {
+          uint32_t vf[4];
+          ldsm_x4_t(vf, tile_addr<HDP>(v_s, mt * 16 + (lane & 7) + ((lane >> 4) << 3),
+                                       i * 2 + ((lane >> 3) & 1)));
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      float p[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float mr = m_new[j >> 1];
-        p[j] = mr > -INFINITY ? exp2f(s[i][j] - mr) : 0.f;
-        l_add[j >> 1] += p[j];
-      }
-      pf[i * 2 + 0] = pack_bf16(p[0], p[1]);
-      pf[i * 2 + 1] = pack_bf16(p[2], p[3]);
-    }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      l_w[r] = l_w[r] * corr[r] + l_add[r];                  // each lane: its own columns' share
-      m_w[r] = m_new[r];
-    }
-#pragma unroll
-    for (int i = 0; i < NOT; ++i) {
-      o[i][0] *= corr[0]; o[i][1] *= corr[0];
-      o[i][2] *= corr[1]; o[i][3] *= corr[1];
-    }
-#pragma unroll
-    for (int np = 0; np < NOT / 2; ++np) {
-      if (np * 2 < n_ot) {
-        uint32_t vf[4];
-        const int row = key0 + (lane & 7) + (((lane >> 3) & 1) << 3);
-        ldsm_x4_t(vf, tile_addr<HDP>(v_s, row, np * 2 + (lane >> 4)));
-        mma_bf16(o[2 * np], pf, vf);
-        mma_bf16(o[2 * np + 1], pf, vf + 2);
+          for (int nt = 0; nt < NT; ++nt) mma_bf16(o[i][nt], vf, pb[mt][nt]);
+        }
       }
     }
   }
   cp_async_wait<0>();
-  __syncthreads();                                           // the staging area is free
+  __syncthreads();                                           // Q and every ring are free
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 1);
-    l_w[r] += __shfl_xor_sync(0xffffffffu, l_w[r], 2);
-  }
-  if (tig == 0) {
-    wm_s[warp][gid] = m_w[0]; wm_s[warp][gid + 8] = m_w[1];
-    wl_s[warp][gid] = l_w[0]; wl_s[warp][gid + 8] = l_w[1];
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      float l = l_w[nt][c];
+      l += __shfl_xor_sync(FULL, l, 4);
+      l += __shfl_xor_sync(FULL, l, 8);
+      l += __shfl_xor_sync(FULL, l, 16);
+      if (gid == 0) {
+        wm_s[warp][nt * 8 + tig * 2 + c] = m_w[nt][c];
+        wl_s[warp][nt * 8 + tig * 2 + c] = l;
+      }
+    }
+  if (NT == 1 && gid == 1) {                                 // heads 8-15 do not exist
+    wm_s[warp][8 + tig * 2] = wm_s[warp][9 + tig * 2] = -INFINITY;
+    wl_s[warp][8 + tig * 2] = wl_s[warp][9 + tig * 2] = 0.f;
   }
   // merge the four warps (they saw different keys): partial outputs over the staging area
-  float* o_s = reinterpret_cast<float*>(fa_smem);            // [warps][16 rows][hd]
+  float* o_s = reinterpret_cast<float*>(fa_smem);            // [warps][hd][FD_OPAD >= 16 heads]
 #pragma unroll
-  for (int i = 0; i < NOT; ++i) {
-    if (i < n_ot) {
-      float* p0 = o_s + ((size_t)warp * FD_ROWS + gid) * hd + i * 8 + tig * 2;
-      float* p1 = o_s + ((size_t)warp * FD_ROWS + gid + 8) * hd + i * 8 + tig * 2;
-      p0[0] = o[i][0]; p0[1] = o[i][1];
-      p1[0] = o[i][2]; p1[1] = o[i][3];
+  for (int i = 0; i < NKS; ++i) {
+    if (i < nks) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float* p0 = o_s + ((size_t)warp * hd + i * 16 + gid) * FD_OPAD + nt * 8 + tig * 2;
+        *reinterpret_cast<float2*>(p0) = make_float2(o[i][nt][0], o[i][nt][1]);
+        *reinterpret_cast<float2*>(p0 + 8 * FD_OPAD) = make_float2(o[i][nt][2], o[i][nt][3]);
+      }
     }
   }
   __syncthreads();
@@ -524,10 +611,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   __syncthreads();
   const size_t qh = (size_t)t * H + h0;
   for (int idx = threadIdx.x; idx < nh * hd; idx += FA_THREADS) {
-    const int r = idx / hd, d = idx - r * hd;
+    const int d = idx / nh, r = idx - d * nh;
     float O = 0.f;
 #pragma unroll
-    for (int w = 0; w < FA_WARPS; ++w) O += o_s[((size_t)w * FD_ROWS + r) * hd + d] * wm_s[w][r];
+    for (int w = 0; w < FA_WARPS; ++w) O += o_s[((size_t)w * hd + d) * FD_OPAD + r] * wm_s[w][r];
     if (n_parts == 1) {
       out[(qh + r) * hd + d] = __float2bfloat16_rn(O / row_l[r]);
     } else {
@@ -587,18 +674,19 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   }
 }
 
-template <int HDP>
+template <int HDP, int NT>
 static int launch_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                              const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                              float* part_ml, int* counters, int* status, int n_seqs, int H, int G,
                              int hd, int capacity, int window, int cpc, int max_parts,
                              cudaStream_t stream) {
-  size_t smem = (size_t)(2 * FD_STAGES * FD_CHUNK + FD_ROWS) * HDP * 2;   // (K, V) stages and Q
-  const size_t merge = (size_t)FA_WARPS * FD_ROWS * hd * 4;  // the warps' partial outputs
+  // Q, then every warp's ring of (K, V) stages; the merge buffer lies over them
+  size_t smem = (size_t)(FD_ROWS + FA_WARPS * FD_STAGES * 2 * FD_UNIT) * HDP * 2;
+  const size_t merge = (size_t)FA_WARPS * hd * FD_OPAD * 4;
   if (smem < merge) smem = merge;
   static size_t attr_smem = 0;
   if (smem > attr_smem) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HDP>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HDP, NT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_smem = smem;
@@ -606,7 +694,7 @@ static int launch_decode_mma(const void* q, const void* k_cache, const void* v_c
   const int nhc = (H / G + FD_ROWS - 1) / FD_ROWS;
   const dim3 grid(max_parts, G * nhc, n_seqs);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
-  launch_pdl(attn_decode_mma_kernel<HDP>, grid, dim3(FA_THREADS), smem, stream,
+  launch_pdl(attn_decode_mma_kernel<HDP, NT>, grid, dim3(FA_THREADS), smem, stream,
              (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
              seq_slot, slot_pos, (__nv_bfloat16*)out, part_o, part_ml, counters, status, H, G, hd,
              capacity, window, cpc, max_parts, scale_log2);
@@ -684,11 +772,12 @@ extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, con
   const int max_chunks = (visible + FD_CHUNK - 1) / FD_CHUNK;
   const int max_parts = (max_chunks + chunks_per_block - 1) / chunks_per_block;
   if ((size_t)G * ((H / G + FD_ROWS - 1) / FD_ROWS) > 65535) return -4;
-  if (hd <= 64)
-    return launch_decode_mma<64>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,
-                                 counters, status, n_seqs, H, G, hd, capacity, window,
-                                 chunks_per_block, max_parts, stream);
-  return launch_decode_mma<128>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,
-                                counters, status, n_seqs, H, G, hd, capacity, window,
-                                chunks_per_block, max_parts, stream);
+  const bool two = H / G > 8;                                 // a second tile of 8 heads
+#define YALM_FD(HDP, NT)                                                                         \
+  launch_decode_mma<HDP, NT>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,      \
+                             counters, status, n_seqs, H, G, hd, capacity, window,               \
+                             chunks_per_block, max_parts, stream)
+  if (hd <= 64) return two ? YALM_FD(64, 2) : YALM_FD(64, 1);
+  return two ? YALM_FD(128, 2) : YALM_FD(128, 1);
+#undef YALM_FD
 }

@@ -63,14 +63,19 @@ class GQAAttention:
 
     def decode_chunks_per_block(self, batch, visible: int) -> int:
         """How many 64-key chunks one block of the tensor-core decode kernel walks
-        through: as few as keeps every block resident at once (two per SM).  A few
-        sequences then get many blocks each and a merge; with many sequences a
-        block takes its whole sequence and nothing is merged."""
+        through: the fewest with which all blocks are resident at once (one per
+        SM; its four warps take the chunks' halves in turn).  A few sequences then
+        get many blocks each and a merge; with many sequences a block takes its
+        whole sequence and nothing is merged."""
         groups = self.G * -(-(self.H // self.G) // 16)
-        lengths = [min(p + 1, self.window) if self.window else p + 1 for p in batch.past]
-        total = groups * sum(-(-n // 64) for n in lengths)
-        resident = 2 * self.rt.sm_count
-        return max(1, min(-(-visible // 64), -(-total // resident)))
+        chunks = [-(-(min(p + 1, self.window) if self.window else p + 1) // 64)
+                  for p in batch.past]
+        resident = self.rt.sm_count
+        most = max(1, -(-visible // 64))
+        cpc = max(1, min(most, -(-groups * sum(chunks) // resident)))
+        while cpc < most and groups * sum(-(-c // cpc) for c in chunks) > resident:
+            cpc += 1
+        return cpc
 
     def forward(self, h, batch, stream, view, shared: bool = False) -> None:
         rt, H, G, hd = self.rt, self.H, self.G, self.hd
