@@ -353,24 +353,45 @@ __device__ __forceinline__ uint32_t movmatrix_t(uint32_t a) {
   return d;
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {       // 2^x; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // One warp loads `n` consecutive positions of a cache ring (rows first_row,
-// first_row + 1, ... modulo capacity) into a swizzled tile and zero-fills rows
-// n..rows-1.  Each lane keeps one 16-byte column and steps through the rows.
+// first_row + 1, ... modulo capacity) into a swizzled tile of FD_UNIT rows and
+// zero-fills rows n and up.  Lane l takes rows (l & 7) + 8 rb and the 16-byte
+// columns (l >> 3) + 4 j: its row's swizzle is then one constant, and a full unit
+// that does not wrap needs an add and an exclusive-or per copy.
 template <int HDP>
-__device__ __forceinline__ void warp_load_ring_tile(uint32_t base, int rows, int n, int hd,
+__device__ __forceinline__ void warp_load_ring_tile(uint32_t base, int n, int hd,
                                                     const __nv_bfloat16* ring, int first_row,
                                                     int capacity, int lane) {
+  const int r7 = lane & 7, cg = lane >> 3;
   const int cpr = hd >> 3;
-  const int rstep = 32 / cpr;                                 // rows covered per pass (hd <= 128)
-  if (lane >= rstep * cpr) return;
-  const int ch = lane % cpr;
-  int r = lane / cpr;
-  int row = (first_row + r) % capacity;
-  const int wrap = rstep % capacity;
-  for (; r < rows; r += rstep) {
-    cp_async16(tile_addr<HDP>(base, r, ch), ring + (size_t)row * hd + ch * 8, r < n);
-    row += wrap;
-    if (row >= capacity) row -= capacity;
+  const uint32_t s_lane = base + r7 * (HDP * 2) + ((cg ^ (r7 & 3)) << 4);
+  const uint32_t x_lane = (uint32_t)(r7 >> 2) << 6;
+  if (n == FD_UNIT && first_row + FD_UNIT <= capacity) {
+    const __nv_bfloat16* g = ring + (size_t)(first_row + r7) * hd + cg * 8;
+#pragma unroll
+    for (int rb = 0; rb < FD_UNIT / 8; ++rb) {
+#pragma unroll
+      for (int j = 0; j < HDP / 32; ++j)
+        if (cg + 4 * j < cpr)
+          cp_async16(s_lane + rb * 8 * HDP * 2 + ((uint32_t)(j << 6) ^ x_lane), g + j * 32, true);
+      g += (size_t)8 * hd;
+    }
+    return;
+  }
+#pragma unroll 1
+  for (int rb = 0; rb < FD_UNIT / 8; ++rb) {
+    const int r = rb * 8 + r7;
+    const __nv_bfloat16* g = ring + (size_t)((first_row + r) % capacity) * hd + cg * 8;
+#pragma unroll
+    for (int j = 0; j < HDP / 32; ++j)
+      if (cg + 4 * j < cpr)
+        cp_async16(s_lane + rb * 8 * HDP * 2 + ((uint32_t)(j << 6) ^ x_lane), g + j * 32, r < n);
   }
 }
 
@@ -423,8 +444,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const int k_lo = lo + u * FD_UNIT;
     const int n = min(FD_UNIT, pos + 1 - k_lo);
     const uint32_t dst = ring_s + stage * 2 * TILE;
-    warp_load_ring_tile<HDP>(dst, FD_UNIT, n, hd, kc, k_lo % capacity, capacity, lane);
-    warp_load_ring_tile<HDP>(dst + TILE, FD_UNIT, n, hd, vc, k_lo % capacity, capacity, lane);
+    const int first = k_lo % capacity;
+    warp_load_ring_tile<HDP>(dst, n, hd, kc, first, capacity, lane);
+    warp_load_ring_tile<HDP>(dst + TILE, n, hd, vc, first, capacity, lane);
   };
   load_tile<HDP>(q_s, FD_ROWS, hd, q, [&](int r) -> const __nv_bfloat16* {
     return r < nh ? q + ((size_t)t * H + h0 + r) * hd : nullptr;
@@ -461,6 +483,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     l_w[nt][0] = l_w[nt][1] = 0.f;
   }
 
+  // ldmatrix addresses: a lane's row, and its column's swizzle as an exclusive-or
+  const uint32_t k_lane = (lane & 15) * (HDP * 2), k_x = (uint32_t)((lane >> 4) ^ (lane & 7)) << 4;
+  const uint32_t v_lane = ((lane & 7) + ((lane >> 4) << 3)) * (HDP * 2),
+                 v_x = (uint32_t)(((lane >> 3) & 1) ^ (lane & 7)) << 4;
   int it = 0;
   for (int u = u0 + warp; u < u1; u += FA_WARPS, ++it) {
     const int stage = it % FD_STAGES;
@@ -469,7 +495,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     if (u_next < u1) load_unit(u_next, (it + FD_STAGES - 1) % FD_STAGES);
     u_next += FA_WARPS;
     cp_async_commit();
-    const uint32_t k_s = ring_s + stage * 2 * TILE, v_s = k_s + TILE;
+    const uint32_t k_s = ring_s + stage * 2 * TILE + k_lane, v_s = ring_s + stage * 2 * TILE + TILE + v_lane;
     const int n = min(FD_UNIT, pos + 1 - (lo + u * FD_UNIT));
 
     float s[2][NT][4];                                       // S^T: two tiles of 16 keys x 8 heads
@@ -482,44 +508,42 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 #pragma unroll
     for (int ks = 0; ks < NKS; ++ks) {
       if (ks < nks) {
+        const uint32_t a = k_s + ((uint32_t)(ks << 5) ^ k_x);
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt) {
           uint32_t kf[4];
-          ldsm_x4(kf, tile_addr<HDP>(k_s, mt * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+          ldsm_x4(kf, a + mt * 16 * HDP * 2);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) mma_bf16(s[mt][nt], kf, &qf[ks][2 * nt]);
         }
       }
     }
-    float m_new[NT][2];
+    if (n < FD_UNIT) {                                       // the sequence's last unit
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) { m_new[nt][0] = m_w[nt][0]; m_new[nt][1] = m_w[nt][1]; }
+      for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+        for (int j = 0; j < 4; ++j)
+          if (mt * 16 + gid + ((j >> 1) << 3) >= n)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const bool live = mt * 16 + gid + ((j >> 1) << 3) < n;
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          s[mt][nt][j] = live ? s[mt][nt][j] * scale_log2 : -INFINITY;
-          m_new[nt][j & 1] = fmaxf(m_new[nt][j & 1], s[mt][nt][j]);
-        }
-      }
+            for (int nt = 0; nt < NT; ++nt) s[mt][nt][j] = -INFINITY;
+    }
+    // maxima of the raw scores (the scale is positive); every unit has a live key
     bool changed = false;
-    float corr[NT][2];
+    float corr[NT][2], m_neg[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        float m = m_new[nt][c];
+        float m = fmaxf(fmaxf(s[0][nt][c], s[0][nt][c + 2]), fmaxf(s[1][nt][c], s[1][nt][c + 2]));
         m = fmaxf(m, __shfl_xor_sync(FULL, m, 4));
         m = fmaxf(m, __shfl_xor_sync(FULL, m, 8));
         m = fmaxf(m, __shfl_xor_sync(FULL, m, 16));
-        m_new[nt][c] = m;
-        corr[nt][c] = m > -INFINITY ? exp2f(m_w[nt][c] - m) : 1.f;
+        m = fmaxf(m * scale_log2, m_w[nt][c]);
+        corr[nt][c] = ex2_approx(m_w[nt][c] - m);
         changed |= m != m_w[nt][c];
         l_w[nt][c] *= corr[nt][c];
         m_w[nt][c] = m;
+        m_neg[nt][c] = -m;
       }
     if (__any_sync(FULL, changed)) {                         // rare after the first units
 #pragma unroll
@@ -539,8 +563,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         float p[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float mr = m_new[nt][j & 1];
-          p[j] = mr > -INFINITY ? exp2f(s[mt][nt][j] - mr) : 0.f;
+          p[j] = ex2_approx(fmaf(s[mt][nt][j], scale_log2, m_neg[nt][j & 1]));
           l_w[nt][j & 1] += p[j];                            // this lane's keys only
         }
         pb[mt][nt][0] = movmatrix_t(pack_bf16(p[0], p[1]));
@@ -549,11 +572,11 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 #pragma unroll
     for (int i = 0; i < NKS; ++i) {
       if (i < nks) {
+        const uint32_t a = v_s + ((uint32_t)(i << 5) ^ v_x);
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt) {
           uint32_t vf[4];
-          ldsm_x4_t(vf, tile_addr<HDP>(v_s, mt * 16 + (lane & 7) + ((lane >> 4) << 3),
-                                       i * 2 + ((lane >> 3) & 1)));
+          ldsm_x4_t(vf, a + mt * 16 * HDP * 2);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) mma_bf16(o[i][nt], vf, pb[mt][nt]);
         }
