@@ -78,7 +78,9 @@ template <int BT, int NACC> struct TcCfg {
   static constexpr int W_BYTES = TC_BM * TC_BK * 2;              // 16 KiB per weight tile
   static constexpr int A_BYTES = BT * TC_BK * 2;
   static constexpr int STAGE_BYTES = NACC * W_BYTES + A_BYTES;
-  static constexpr int BUDGET = BT <= 32 ? 110 * 1024 : 200 * 1024;   // small tiles: 2 blocks/SM
+  // two blocks per SM wherever the stages stay deep enough: a grid of up to 2 x SMs
+  // tiles (or K slices) is then resident at once instead of running as two waves
+  static constexpr int BUDGET = (BT <= 32 || (NACC == 1 && BT <= 128)) ? 110 * 1024 : 200 * 1024;
   static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;       // + slack to align to 1024
