@@ -80,36 +80,55 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 }
 
 template <typename TO, int VPT>
-__global__ void rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partials,
-                                   int n_partials, long long partial_stride,
-                                   const int* __restrict__ rows, const float* __restrict__ weight,
-                                   TO* __restrict__ out, int dim, float eps) {
+__global__ void __launch_bounds__(VPT <= 2 ? 1024 : 512)
+rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partials,
+                   int n_partials, long long partial_stride,
+                   const int* __restrict__ rows, const float* __restrict__ weight,
+                   TO* __restrict__ out, int dim, float eps) {
   pdl_launch_dependents();
+  const int nvec = dim >> 2;
+  // the norm's weights do not depend on the previous kernel
+  float4 w[VPT];
+  {
+    const float4* wr = reinterpret_cast<const float4*>(weight);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int c = threadIdx.x + k * blockDim.x;
+      w[k] = c < nvec ? wr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   pdl_wait();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
-  const int nvec = dim >> 2;
   float4* xr = reinterpret_cast<float4*>(x + (size_t)src * dim);
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
   float4 v[VPT];
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int c = threadIdx.x + k * blockDim.x;
-    v[k] = c < nvec ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    v[k] = c < nvec ? xr[c] : zero;
   }
-  for (int s = 0; s < n_partials; ++s) {
-    const float4* pr = reinterpret_cast<const float4*>(partials + (size_t)s * partial_stride +
-                                                       (size_t)src * dim);
-    float4 p[VPT];
+  // four slices at a time, so that their loads are in flight together
+  constexpr int SB = 4;
+  for (int s0 = 0; s0 < n_partials; s0 += SB) {
+    float4 p[SB][VPT];
 #pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-      const int c = threadIdx.x + k * blockDim.x;
-      p[k] = c < nvec ? pr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < SB; ++j) {
+      const float4* pr = reinterpret_cast<const float4*>(
+          partials + (size_t)(s0 + j) * partial_stride + (size_t)src * dim);
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        p[j][k] = (s0 + j < n_partials && c < nvec) ? pr[c] : zero;
+      }
     }
 #pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-      v[k].x += p[k].x; v[k].y += p[k].y; v[k].z += p[k].z; v[k].w += p[k].w;
-    }
+    for (int j = 0; j < SB; ++j)
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        v[k].x += p[j][k].x; v[k].y += p[j][k].y; v[k].z += p[j][k].z; v[k].w += p[j][k].w;
+      }
   }
   float ss = 0.f;
 #pragma unroll
@@ -120,16 +139,13 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ x, const float* __restric
   }
   ss = block_sum(ss, scratch);
   const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
-  const float4* wr = reinterpret_cast<const float4*>(weight);
   TO* o = out + (size_t)r * dim;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int c = threadIdx.x + k * blockDim.x;
-    if (c < nvec) {
-      const float4 w = wr[c];
-      store4(o + 4 * c, make_float4(v[k].x * scale * w.x, v[k].y * scale * w.y,
-                                    v[k].z * scale * w.z, v[k].w * scale * w.w));
-    }
+    if (c < nvec)
+      store4(o + 4 * c, make_float4(v[k].x * scale * w[k].x, v[k].y * scale * w[k].y,
+                                    v[k].z * scale * w[k].z, v[k].w * scale * w[k].w));
   }
 }
 
@@ -206,14 +222,26 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
   float a[VEC], bb[VEC];
 #pragma unroll
   for (int v = 0; v < VEC; ++v) { a[v] = 0.f; bb[v] = 0.f; }
-  for (int p = 0; p < n_partials; ++p) {
-    const float* pp = sp + (size_t)p * partial_stride;
-    if (VEC == 4) {
-      const float4 x = *reinterpret_cast<const float4*>(pp);
-      const float4 y = *reinterpret_cast<const float4*>(pp + half);
-      a[0] += x.x; a[VEC > 1 ? 1 : 0] += x.y; a[VEC > 2 ? 2 : 0] += x.z; a[VEC > 3 ? 3 : 0] += x.w;
-      bb[0] += y.x; bb[VEC > 1 ? 1 : 0] += y.y; bb[VEC > 2 ? 2 : 0] += y.z; bb[VEC > 3 ? 3 : 0] += y.w;
-    } else {
+  if (VEC == 4) {
+    // four slices at a time, so that their loads are in flight together
+    for (int p0 = 0; p0 < n_partials; p0 += 4) {
+      float4 x[4], y[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float* pp = sp + (size_t)(p0 + j) * partial_stride;
+        const bool live = p0 + j < n_partials;
+        x[j] = live ? *reinterpret_cast<const float4*>(pp) : make_float4(0.f, 0.f, 0.f, 0.f);
+        y[j] = live ? *reinterpret_cast<const float4*>(pp + half) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        a[0] += x[j].x; a[VEC > 1 ? 1 : 0] += x[j].y; a[VEC > 2 ? 2 : 0] += x[j].z; a[VEC > 3 ? 3 : 0] += x[j].w;
+        bb[0] += y[j].x; bb[VEC > 1 ? 1 : 0] += y[j].y; bb[VEC > 2 ? 2 : 0] += y[j].z; bb[VEC > 3 ? 3 : 0] += y[j].w;
+      }
+    }
+  } else {
+    for (int p = 0; p < n_partials; ++p) {
+      const float* pp = sp + (size_t)p * partial_stride;
       a[0] += pp[0];
       bb[0] += pp[half];
     }
@@ -288,7 +316,8 @@ static void launch_rmsnorm(float* x, const float* partials, int n_partials,
                      ((uintptr_t)out)) & 15) == 0;
   const int nvec = dim / 4;
   if (vec && nvec <= 8 * 512) {
-    const int threads = nvec <= 128 ? 128 : (nvec <= 1024 ? 256 : 512);
+    // few vectors per thread: the kernel is a chain of memory round trips, not arithmetic
+    const int threads = nvec <= 1024 ? (nvec + 31) / 32 * 32 : (nvec <= 2048 ? 1024 : 512);
     const int vpt = (nvec + threads - 1) / threads;
 #define YALM_RMS(V)                                                                          \
   launch_pdl(rmsnorm_vec_kernel<TO, V>, dim3(n_rows), dim3(threads), 0, stream, x, partials, n_partials,          \
