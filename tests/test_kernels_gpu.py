@@ -70,6 +70,15 @@ def test_rmsnorm_with_partials_and_gather(ops, dim):
     assert (outg.float().cpu() - ref[rows.long().cpu()]).abs().max() <= 1e-2 * ref.abs().max()
 
 
+def _paired_silu(ref):
+    """silu(gate)*up when the columns of ref come as 16 gate columns followed by the 16
+    up columns of the same features (the last group may be cut short by the caller)."""
+    M, N = ref.shape
+    r = ref.reshape(M, N // 32, 2, 16)
+    g, u = r[:, :, 0], r[:, :, 1]
+    return (g / (1 + torch.exp(-g)) * u).reshape(M, N // 2)
+
+
 def test_silu_mul_sums_partials(ops):
     gu = torch.randn(3, 11, 2 * 333, device=DEV) * 2
     out = torch.empty(11, 333, device=DEV)
@@ -78,6 +87,11 @@ def test_silu_mul_sums_partials(ops):
     g, u = s[:, :333], s[:, 333:]
     ref = g / (1 + torch.exp(-g)) * u
     assert (out.cpu() - ref).abs().max() <= 1e-5 * ref.abs().max()
+    gu = torch.randn(2, 7, 2 * 336, device=DEV) * 2            # paired columns
+    out = torch.empty(7, 336, device=DEV, dtype=torch.bfloat16)
+    ops.silu_mul(gu, out, n_partials=2, paired=True)
+    ref = _paired_silu(gu.sum(0).cpu())
+    assert (out.float().cpu() - ref).abs().max() <= 2 ** -8 * ref.abs().max()
 
 
 @pytest.mark.parametrize("shape", [(1, 70, 50), (65, 129, 17), (300, 520, 260)])
@@ -132,6 +146,11 @@ def test_tcgen05_matrix_product_all_epilogues(ops, shape):
     o2 = torch.zeros(M, N // 2, device=DEV)
     ops.gemm_tc(a, w, o2, ops.GEMM_SILU_MUL, status)
     assert (o2.double() - r2).abs().max() <= 4e-6 * math.sqrt(K) * max(1.0, r2.abs().max())
+    if N % 32 == 0:
+        r4 = _paired_silu(ref)
+        o4 = torch.full((M, N // 2), 9.0, device=DEV)
+        ops.gemm_tc(a, w, o4, ops.GEMM_SILU_PAIRED, status)
+        assert (o4.double() - r4).abs().max() <= 4e-6 * math.sqrt(K) * max(1.0, r4.abs().max())
     assert status.item() == 0
 
 
@@ -456,6 +475,11 @@ def test_two_sm_matrix_product(ops, shape):
         o2 = torch.zeros(M, N // 2, device=DEV)
         ops.gemm_2sm(a, w, o2, ops.GEMM_SILU_MUL, status)
         assert (o2.double() - r2).abs().max() <= 4e-6 * math.sqrt(K) * max(1.0, r2.abs().max())
+        if N % 32 == 0:
+            r4 = _paired_silu(ref)
+            o4 = torch.full((M, N // 2), 9.0, device=DEV, dtype=torch.bfloat16)
+            ops.gemm_2sm(a, w, o4, ops.GEMM_SILU_PAIRED, status)
+            assert (o4.double() - r4).abs().max() <= 2 ** -8 * max(1.0, r4.abs().max())
         torch.cuda.synchronize()
         assert status.item() == 0
 

@@ -17,7 +17,7 @@ int yalm_rmsnorm(float* x, const float* partials, int n_partials, long long part
                  int dim, float eps, cudaStream_t stream);
 
 int yalm_silu_mul(const float* gu, int n_partials, long long partial_stride, void* out,
-                  int out_dtype, int rows, int F, cudaStream_t stream);
+                  int out_dtype, int rows, int F, int paired, cudaStream_t stream);
 
 int yalm_rope_store(const float* qkv, int n_partials, long long partial_stride,
                     const float* inv_freq, const int* token_seq, const int* q_start,

@@ -150,21 +150,26 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partials,
 }
 
 // ---------------------------------------------------------------- silu * up
-// gu: [rows, 2F] (gate | up) in 32-bit, possibly as n_partials split-K slices.
+// gu: [rows, 2F] in 32-bit, possibly as n_partials split-K slices.  Columns are
+// (gate | up), or with `paired` groups of 16 gate columns each followed by the 16
+// up columns of the same features.
 template <typename TO>
 __global__ void silu_mul_kernel(const float* __restrict__ gu, int n_partials,
-                                long long partial_stride, TO* __restrict__ out, int rows, int F) {
+                                long long partial_stride, TO* __restrict__ out, int rows, int F,
+                                int paired) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t total = (size_t)rows * F;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t r = idx / F, f = idx % F;
+    const size_t gc = paired ? (f >> 4) * 32 + (f & 15) : f;
+    const size_t uc = paired ? gc + 16 : F + f;
     float g = 0.f, u = 0.f;
     for (int s = 0; s < n_partials; ++s) {
       const float* p = gu + (size_t)s * partial_stride + r * 2 * F;
-      g += p[f];
-      u += p[F + f];
+      g += p[gc];
+      u += p[uc];
     }
     out[idx] = from_float<TO>(g / (1.0f + expf(-g)) * u);
   }
@@ -351,18 +356,19 @@ extern "C" int yalm_rmsnorm(float* x, const float* partials, int n_partials,
 }
 
 extern "C" int yalm_silu_mul(const float* gu, int n_partials, long long partial_stride, void* out,
-                             int out_dtype, int rows, int F, cudaStream_t stream) {
+                             int out_dtype, int rows, int F, int paired, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (paired && F % 16 != 0) return -2;
   const size_t total = (size_t)rows * F;
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (out_dtype == DT_F32)
     launch_pdl(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, gu, n_partials, partial_stride,
-                                                               (float*)out, rows, F);
+                                                               (float*)out, rows, F, paired);
   else
     launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, 
-        gu, n_partials, partial_stride, (__nv_bfloat16*)out, rows, F);
+        gu, n_partials, partial_stride, (__nv_bfloat16*)out, rows, F, paired);
   YALM_LAUNCH_CHECK();
   return 0;
 }

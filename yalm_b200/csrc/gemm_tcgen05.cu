@@ -89,7 +89,8 @@ template <int BT, int NACC> struct TcCfg {
                                    (TMEM_COLS_RAW <= 128 ? 128 : (TMEM_COLS_RAW <= 256 ? 256 : 512)));
 };
 
-// mode 0: store, 1: add into float32 out, 2: silu(gate)*up (NACC == 2), 3: split-K partials
+// mode 0: store, 1: add into float32 out, 2: silu(gate)*up (NACC == 2), 3: split-K partials,
+// 4: silu(gate)*up with gate and up rows interleaved in groups of 16 (out is [M, N/2])
 template <int BT, int NACC>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
@@ -225,6 +226,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           tmem_ld16(taddr + BT + c0, u);
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + expf(-v[j])) * u[j];
+        }
+        if (mode == 4) {
+          // weight rows come as 16 gate rows followed by the 16 up rows of the same
+          // features: lane l < 16 holds the gate, lane l + 16 the up value
+          const int fo = (feat0 >> 1) + quarter * 16 + lane;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float u = __shfl_down_sync(0xffffffffu, v[j], 16);
+            v[j] = v[j] / (1.0f + expf(-v[j])) * u;
+          }
+          if (lane < 16 && fo < (N >> 1)) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int tok = tok0 + c0 + j;
+              if (tok < M) {
+                if (out_dtype == DT_F32) outf[(size_t)tok * (N >> 1) + fo] = v[j];
+                else outh[(size_t)tok * (N >> 1) + fo] = __float2bfloat16_rn(v[j]);
+              }
+            }
+          }
+          continue;
         }
         if (f < n_out && mode == 1) {
           // residual add: all 16 loads are issued before the first store
@@ -458,7 +480,8 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
                ::"r"(bar_cluster_addr) : "memory");
 }
 
-// mode 0: store, 1: add into float32 out, 2: silu(gate)*up (NACC == 2)
+// mode 0: store, 1: add into float32 out, 2: silu(gate)*up (NACC == 2), 4: silu(gate)*up
+// with gate and up rows interleaved in groups of 16
 template <int BT, int NACC>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS)
 gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
@@ -614,7 +637,18 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + expf(-v[j])) * g2[j];
         }
-        sk_store_chunk(mode, out_dtype, out, v, f, tok0 + c0, M, n_out);
+        if (mode == 4) {
+          // rows interleaved in groups of 16: lane l < 16 the gate, lane l + 16 the up value
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float u = __shfl_down_sync(0xffffffffu, v[j], 16);
+            v[j] = v[j] / (1.0f + expf(-v[j])) * u;
+          }
+          const int fo = ((feat0 + (int)rank * TC_BM) >> 1) + quarter * 16 + lane;
+          sk_store_chunk(0, out_dtype, out, v, lane < 16 ? fo : (N >> 1), tok0 + c0, M, N >> 1);
+        } else {
+          sk_store_chunk(mode, out_dtype, out, v, f, tok0 + c0, M, n_out);
+        }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -677,8 +711,9 @@ extern "C" int yalm_gemm_tc(const void* A, const void* W, void* out, int out_dty
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0) return -2;               // TMA: rows must be 16-byte multiples
   if (((uintptr_t)A | (uintptr_t)W) & 15) return -6; // TMA: 16-byte aligned bases
-  if (mode < 0 || mode > 3) return -3;
+  if (mode < 0 || mode > 4) return -3;
   if (mode == 2 && (N % 2 != 0)) return -3;
+  if (mode == 4 && (N % 32 != 0)) return -3;
   if ((mode == 1 || mode == 3) && out_dtype != DT_F32) return -3;
   const int nkb = (K + TC_BK - 1) / TC_BK;
   if (mode != 3) splits = 1;
@@ -708,14 +743,15 @@ extern "C" int yalm_gemm_tc(const void* A, const void* W, void* out, int out_dty
 }
 
 // Two-SM variant for many tokens (see gemm_2sm_kernel): mode 0 store, 1 add into
-// float32 out, 2 silu(gate)*up.
+// float32 out, 2 silu(gate)*up, 4 the same with interleaved rows.
 extern "C" int yalm_gemm_2sm(const void* A, const void* W, void* out, int out_dtype, int M, int N,
                              int K, int mode, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0) return -2;
   if (((uintptr_t)A | (uintptr_t)W) & 15) return -6;
-  if (mode < 0 || mode > 2) return -3;
+  if (mode < 0 || mode == 3 || mode > 4) return -3;
   if (mode == 2 && (N % 2 != 0)) return -3;
+  if (mode == 4 && (N % 32 != 0)) return -3;
   if (mode == 1 && out_dtype != DT_F32) return -3;
   if (mode == 2) return launch_2sm<128, 2>(A, W, out, out_dtype, M, N, K, mode, status, stream);
   return launch_2sm<256, 1>(A, W, out, out_dtype, M, N, K, mode, status, stream);

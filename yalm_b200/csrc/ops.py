@@ -46,7 +46,7 @@ _vp, _i, _ll, _f, _ull = _c.c_void_p, _c.c_int, _c.c_longlong, _c.c_float, _c.c_
 _SIGNATURES = {
     "yalm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp],
     "yalm_rmsnorm": [_vp, _vp, _i, _ll, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
-    "yalm_silu_mul": [_vp, _i, _ll, _vp, _i, _i, _i, _vp],
+    "yalm_silu_mul": [_vp, _i, _ll, _vp, _i, _i, _i, _i, _vp],
     "yalm_rope_store": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                         _i, _i, _i, _vp],
     "yalm_advance": [_vp, _vp, _vp, _i, _vp],
@@ -149,13 +149,15 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
                               float(eps), _stream()), "rmsnorm")
 
 
-def silu_mul(gu: torch.Tensor, out: torch.Tensor, n_partials: int = 1) -> None:
-    """gu: float32 [(n_partials,) rows, 2F] (gate | up); out: [rows, F]."""
+def silu_mul(gu: torch.Tensor, out: torch.Tensor, n_partials: int = 1, paired: bool = False) -> None:
+    """gu: float32 [(n_partials,) rows, 2F]; out: [rows, F].  Columns of gu are
+    (gate | up) or, with ``paired``, 16 gate columns then the 16 up columns of the
+    same features, and so on."""
     rows, F = out.shape
     _need(gu.dtype == torch.float32 and gu.shape[-1] == 2 * F and gu.shape[-2] == rows
           and gu.is_contiguous() and out.is_contiguous(), "silu_mul: shapes")
     _check(lib().yalm_silu_mul(_p(gu), n_partials, rows * 2 * F, _p(out), dtype_code(out.dtype),
-                               rows, F, _stream()), "silu_mul")
+                               rows, F, 1 if paired else 0, _stream()), "silu_mul")
 
 
 def rope_store(qkv: torch.Tensor, n_partials: int, inv_freq: torch.Tensor, batch,
@@ -295,7 +297,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: b
            "gemm_simt")
 
 
-GEMM_STORE, GEMM_ADD, GEMM_SILU_MUL, GEMM_SPLIT = 0, 1, 2, 3
+GEMM_STORE, GEMM_ADD, GEMM_SILU_MUL, GEMM_SPLIT, GEMM_SILU_PAIRED = 0, 1, 2, 3, 4
 
 
 def gemm_tc_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -309,7 +311,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, stat
     N = w.shape[0]
     _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
           and a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "gemm_tc: operands")
-    if mode == GEMM_SILU_MUL:
+    if mode in (GEMM_SILU_MUL, GEMM_SILU_PAIRED):
         _need(tuple(out.shape) == (M, N // 2), "gemm_tc: silu-mul out is [M, N/2]")
     elif mode == GEMM_SPLIT:
         _need(out.dtype == torch.float32 and out.numel() >= splits * M * N, "gemm_tc: split scratch")
@@ -326,7 +328,8 @@ def gemm_2sm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
     N = w.shape[0]
     _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
           and a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "gemm_2sm: operands")
-    _need(tuple(out.shape) == ((M, N // 2) if mode == GEMM_SILU_MUL else (M, N)), "gemm_2sm: out shape")
+    _need(tuple(out.shape) == ((M, N // 2) if mode in (GEMM_SILU_MUL, GEMM_SILU_PAIRED) else (M, N)),
+          "gemm_2sm: out shape")
     _check(lib().yalm_gemm_2sm(_p(a), _p(w), _p(out), dtype_code(out.dtype), M, N, K, mode,
                                _p(status), _stream()), "gemm_2sm")
 

@@ -109,15 +109,27 @@ def matmul_into_stream(rt, a: torch.Tensor, w: torch.Tensor, stream) -> None:
         ops.gemm_simt(a, w, stream.x, accumulate=True)
 
 
-def matmul_silu_mul(rt, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(a @ Wg.T) * (a @ Wu.T), w_gate_up = [Wg; Wu]."""
+def matmul_silu_mul(rt, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
+                    paired: bool = False) -> None:
+    """out = silu(a @ Wg.T) * (a @ Wu.T).  w_gate_up is [Wg; Wu], or with ``paired``
+    16 rows of Wg, the 16 rows of Wu for the same features, and so on: a 128-row
+    tile of the product then holds gate and up of 64 features, and the epilogue
+    pairs them inside a warp."""
     M, K = a.shape
     N2 = w_gate_up.shape[0]
-    if _use_tc(rt, a, w_gate_up) and not _small(rt, M, N2 // 2):
-        if M > 128:
-            _many_tokens(rt, a, w_gate_up, out, ops.GEMM_SILU_MUL)
-        else:
-            ops.gemm_tc(a, w_gate_up, out, ops.GEMM_SILU_MUL, rt.status)
-        return
+    if _use_tc(rt, a, w_gate_up):
+        if paired:
+            if M > 128:
+                ops.gemm_2sm(a, w_gate_up, out, ops.GEMM_SILU_PAIRED, rt.status)
+                return
+            if not _small(rt, M, N2):
+                ops.gemm_tc(a, w_gate_up, out, ops.GEMM_SILU_PAIRED, rt.status)
+                return
+        elif not _small(rt, M, N2 // 2):
+            if M > 128:
+                _many_tokens(rt, a, w_gate_up, out, ops.GEMM_SILU_MUL)
+            else:
+                ops.gemm_tc(a, w_gate_up, out, ops.GEMM_SILU_MUL, rt.status)
+            return
     buf, S = matmul_partials(rt, a, w_gate_up, "gate_up")
-    ops.silu_mul(buf, out, n_partials=S)
+    ops.silu_mul(buf, out, n_partials=S, paired=paired)
