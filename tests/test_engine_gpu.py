@@ -304,14 +304,16 @@ def test_a_prompt_cut_into_steps_on_a_full_ring(dtype):
     assert err <= TOL[dtype], err
 
 
-def test_the_tcgen05_prefill_attention_inside_the_engine():
-    """attention="tcgen05" routes whole prompts through the TMEM attention kernel."""
+@pytest.mark.parametrize("attention", ["auto", "mma"])
+def test_both_tensor_core_prefill_attentions_inside_the_engine(attention):
+    """Whole prompts go through the TMEM attention kernel by default; attention="mma" keeps
+    them on the mma.sync kernel, which otherwise only sees prompts cut into steps."""
     from yalm_b200 import LM
     from yalm_b200.config import config_from_dict
     cfg, seed = CONFIGS["tiny_e"]
     w = make_weights(cfg, seed)
     toks = [random_tokens(n, cfg["vocab_size"], 300 + n) for n in (390, 7, 129)]
-    lm = LM(config_from_dict(cfg), dict(w), dtype="bfloat16", max_batch=3, attention="tcgen05")
+    lm = LM(config_from_dict(cfg), dict(w), dtype="bfloat16", max_batch=3, attention=attention)
     s = lm.acquire(3)
     lg = lm.step(toks, s, [[len(t) - 1] for t in toks]).cpu()
     for i, t in enumerate(toks):

@@ -488,19 +488,28 @@ def test_two_sm_matrix_product(ops, shape):
                                               (3, 1, 64, 37)])
 def test_tcgen05_prefill_attention(ops, H, G, hd, window):
     """attention_prefill_tc (S and P.V in tensor memory) against the plain attention:
-    ragged prompts from their first token, one of 300 tokens (three key blocks, the
-    diagonal block masked), one of a single token, one that ends inside a tile."""
+    ragged prompts from their first token: 300 tokens (a second block with one tile only),
+    a single token, ends just past and at a tile, 700 tokens (three blocks of two tiles).
+    On the second pass one early key of each prompt is made to dominate, and late ones
+    grow, so the reference maximum of the rows is raised along the way."""
     dt = torch.bfloat16
     inv = plain_inv_freq(hd, 10000.0, None).to(DEV)
-    lens, slots, cap = [300, 1, 130, 128], [2, 0, 3, 1], 512
-    slot_pos = torch.zeros(4, dtype=torch.int32, device=DEV)
-    kc = torch.zeros(4, G, cap, hd, device=DEV, dtype=dt)
+    lens, slots, cap = [300, 1, 130, 128, 700], [2, 0, 3, 1, 4], 1024
+    slot_pos = torch.zeros(5, dtype=torch.int32, device=DEV)
+    kc = torch.zeros(5, G, cap, hd, device=DEV, dtype=dt)
     vc = torch.zeros_like(kc)
     b = B(lens, slots)
     N = b.n_tokens
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     for rep in range(2):
         qkv = torch.randn(N, (H + 2 * G) * hd, device=DEV)
+        if rep == 1:
+            # keys grow with the position: later blocks keep raising the rows' maxima
+            # (values halved: the output is then nearly one value row, and its own
+            # rounding to bfloat16 must stay well inside the tolerance)
+            ramp = 1.0 + torch.arange(N, device=DEV).float().remainder(701.0) / 100.0
+            qkv.view(N, H + 2 * G, hd)[:, H:H + G] *= ramp[:, None, None]
+            qkv.view(N, H + 2 * G, hd)[:, H + G:] *= 0.5
         q_out = torch.empty(N, H * hd, device=DEV, dtype=dt)
         kv_step = torch.empty(N, 2, G, hd, device=DEV, dtype=dt)
         ops.rope_store(qkv, 1, inv, b, q_out, kv_step, kc, vc, slot_pos, H, G, hd, cap)

@@ -342,7 +342,11 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 // attn_decode_kernel); with many sequences a block takes a whole sequence.
 // Maxima are kept in the log2 domain (scores times log2(e)/sqrt(hd)).
 constexpr int FD_CHUNK = 64;       // the unit of the host's plan
-constexpr int FD_UNIT = 32;        // keys a warp takes at a time
+#ifndef YALM_FD_UNIT
+#define YALM_FD_UNIT 32
+#endif
+constexpr int FD_UNIT = YALM_FD_UNIT;   // keys a warp takes at a time (16 or 32)
+constexpr int FD_MT = FD_UNIT / 16;
 constexpr int FD_ROWS = 16;        // query heads per block
 constexpr int FD_STAGES = 3;       // units in flight or in use per warp
 constexpr int FD_OPAD = 20;        // row length of the merge buffer [warp][feature][head]
@@ -498,9 +502,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const uint32_t k_s = ring_s + stage * 2 * TILE + k_lane, v_s = ring_s + stage * 2 * TILE + TILE + v_lane;
     const int n = min(FD_UNIT, pos + 1 - (lo + u * FD_UNIT));
 
-    float s[2][NT][4];                                       // S^T: two tiles of 16 keys x 8 heads
+    float s[FD_MT][NT][4];                                       // S^T: two tiles of 16 keys x 8 heads
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < FD_MT; ++mt)
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -510,7 +514,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
       if (ks < nks) {
         const uint32_t a = k_s + ((uint32_t)(ks << 5) ^ k_x);
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
+        for (int mt = 0; mt < FD_MT; ++mt) {
           uint32_t kf[4];
           ldsm_x4(kf, a + mt * 16 * HDP * 2);
 #pragma unroll
@@ -520,7 +524,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     }
     if (n < FD_UNIT) {                                       // the sequence's last unit
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < FD_MT; ++mt)
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           if (mt * 16 + gid + ((j >> 1) << 3) >= n)
@@ -534,7 +538,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        float m = fmaxf(fmaxf(s[0][nt][c], s[0][nt][c + 2]), fmaxf(s[1][nt][c], s[1][nt][c + 2]));
+        float m = fmaxf(s[0][nt][c], s[0][nt][c + 2]);
+#pragma unroll
+        for (int mt = 1; mt < FD_MT; ++mt) m = fmaxf(m, fmaxf(s[mt][nt][c], s[mt][nt][c + 2]));
         m = fmaxf(m, __shfl_xor_sync(FULL, m, 4));
         m = fmaxf(m, __shfl_xor_sync(FULL, m, 8));
         m = fmaxf(m, __shfl_xor_sync(FULL, m, 16));
@@ -555,9 +561,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         }
     }
     // P^T as the B operand of the second product: each 8x8 block of S^T, transposed
-    uint32_t pb[2][NT][2];
+    uint32_t pb[FD_MT][NT][2];
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < FD_MT; ++mt)
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         float p[4];
@@ -574,7 +580,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
       if (i < nks) {
         const uint32_t a = v_s + ((uint32_t)(i << 5) ^ v_x);
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
+        for (int mt = 0; mt < FD_MT; ++mt) {
           uint32_t vf[4];
           ldsm_x4_t(vf, a + mt * 16 * HDP * 2);
 #pragma unroll

@@ -1,14 +1,24 @@
-// Prefill attention on tcgen05: S = Q.K^T and P.V as UMMA instructions with the
+// Prefill attention on tcgen05: S = Q.K^T and O += P.V as UMMA instructions with the
 // accumulators in tensor memory, operands brought by TMA.
 //
-// A block takes 128 query tokens of one head of one sequence; 128 threads own one
-// query row each.  Per block of 128 keys: the MMA thread issues S = Q.K^T into TMEM;
-// every softmax thread reads its row of S (tcgen05.ld), applies scale and mask,
-// keeps the running max and sum in 32-bit, writes exp2(s - max) as bfloat16 into a
-// swizzled shared-memory tile P; the MMA thread issues P.V (V is the MN-major B
-// operand, exactly as TMA lays its rows down); the threads read the product and
-// add it to their output row in registers, rescaled when the max moved.  While the
-// threads do that, the next block's S is already being computed.
+// A block takes 256 query tokens of one head of one sequence as two tiles of 128
+// rows, A and B.  Warp 0 is the TMA producer, warp 1 issues the MMAs, warps 2-5 are
+// the softmax group of tile A and warps 6-9 that of tile B: one query row per
+// thread.  Keys and values come in blocks of 64 through rings of three stages each
+// and serve both tiles.  Per block of keys and per tile: the MMA thread issues
+// S = Q.K^T into the tile's 64 columns of TMEM; each softmax thread reads its row of
+// S (tcgen05.ld), applies scale and mask, keeps a reference maximum and the sum in
+// 32-bit, and writes exp2(s - reference) as bfloat16 into the tile's swizzled P
+// buffer in shared memory; the MMA thread then issues O += P.V (V is the MN-major B
+// operand, exactly as TMA lays its rows down) into the tile's O columns of TMEM.  The
+// two tiles alternate on the tensor core, so that while one group computes its
+// softmax the other tile's products run.
+//
+// O stays in TMEM for the whole row of blocks.  Its reference maximum is raised
+// only when a block's maximum exceeds it by more than 8 (in log2 units, so
+// probabilities stay below 256): then the warp reads its O rows, scales them and
+// writes them back (tcgen05.st) before the next product is issued.  The final
+// division by the sum uses the same reference, so the result is the plain softmax.
 //
 // Same mathematics as the reference's attn_dot / attn_softmax / att_mix
 // (infer.cu:339-523) and as attention.cu.  Takes the case "all keys are this step's
@@ -22,10 +32,12 @@
 
 namespace yalm {
 
-constexpr int TA_BM = 128;     // query rows per block
-constexpr int TA_BN = 128;     // keys per iteration
-constexpr int TA_THREADS = 192;
-constexpr int TA_STAGES = 2;
+constexpr int TA_BM = 128;     // query rows per tile; a block takes two tiles
+constexpr int TA_BN = 64;      // keys per iteration
+constexpr int TA_THREADS = 320;
+constexpr int TA_KSTAGES = 3;
+constexpr int TA_VSTAGES = 3;
+constexpr float TA_RAISE = 8.f;   // a block's maximum may exceed the reference by this much (log2)
 
 __device__ __forceinline__ void ta_tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
                                                uint32_t bar) {
@@ -84,6 +96,30 @@ __device__ __forceinline__ void ta_ld32(uint32_t taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void ta_st32(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])),
+        "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])),
+        "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
+        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ta_ex2(float x) {            // 2^x; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -94,12 +130,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ q_start, __nv_bfloat16* __restrict__ out, int H, int G,
                        int window, float scale_log2, int* __restrict__ status) {
   constexpr int SUB = HD / 64;                     // 64-column sub-tiles of a head
-  constexpr int Q_BYTES = TA_BM * HD * 2;
-  constexpr int KV_BYTES = TA_BN * HD * 2;         // one of K or V
-  constexpr int TMEM_COLS = 256;                   // S: 128 columns, P.V: HD columns
+  constexpr int Q_BYTES = TA_BM * HD * 2;          // one query tile
+  constexpr int KV_BYTES = TA_BN * HD * 2;         // one block of K or of V
+  constexpr int P_BYTES = TA_BM * TA_BN * 2;
+  constexpr int TMEM_COLS = 2 * TA_BN + 2 * HD <= 256 ? 256 : 512;
   extern __shared__ uint8_t ta_smem[];
-  __shared__ __align__(8) uint64_t q_full, s_full, pv_full, p_ready;
-  __shared__ __align__(8) uint64_t kv_full[TA_STAGES], kv_empty[TA_STAGES];
+  __shared__ __align__(8) uint64_t q_full, s_full[2], p_ready[2], pv_done[2];
+  __shared__ __align__(8) uint64_t k_full[TA_KSTAGES], k_empty[TA_KSTAGES];
+  __shared__ __align__(8) uint64_t v_full[TA_VSTAGES], v_empty[TA_VSTAGES];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -107,29 +145,45 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int b = blockIdx.z, h = blockIdx.y;
   const int g = h / (H / G);
   const int qs = q_start[b], q_len = q_start[b + 1] - qs;       // written by a host copy: safe early
-  const int m0 = (gridDim.x - 1 - blockIdx.x) * TA_BM;          // heaviest tiles first
+  const int m0 = (gridDim.x - 1 - blockIdx.x) * 2 * TA_BM;      // heaviest blocks first
   if (m0 >= q_len) return;
-  const int rows = min(TA_BM, q_len - m0);
-  const int p_last = m0 + rows - 1;
-  const int k_end = p_last + 1;
-  const int k_begin = window > 0 ? max(0, m0 - window + 1) : 0;
-  const int kb0 = k_begin / TA_BN, kb1 = (k_end + TA_BN - 1) / TA_BN;
-  const int nkb = kb1 - kb0;
+  // per tile: first row, rows, and the blocks of keys [kb0, kb1) its rows can see
+  int t_m0[2], t_rows[2], t_kb0[2], t_kb1[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    t_m0[x] = m0 + x * TA_BM;
+    t_rows[x] = max(0, min(TA_BM, q_len - t_m0[x]));
+    const int k_end = t_m0[x] + t_rows[x];
+    const int k_begin = window > 0 ? max(0, t_m0[x] - window + 1) : 0;
+    t_kb0[x] = k_begin / TA_BN;
+    t_kb1[x] = t_rows[x] > 0 ? (k_end + TA_BN - 1) / TA_BN : t_kb0[x];
+  }
+  const int kb_lo = t_kb0[0];
+  const int kb_hi = t_rows[1] > 0 ? t_kb1[1] : t_kb1[0];
+  const int n_it = kb_hi - kb_lo;
+  auto active = [&](int x, int kb) { return kb >= t_kb0[x] && kb < t_kb1[x]; };
 
   const uint32_t base = (smem_u32(ta_smem) + 1023u) & ~1023u;
-  const uint32_t q_s = base;
-  const uint32_t kv_s = q_s + Q_BYTES;                          // stages of (K, V)
-  const uint32_t p_s = kv_s + TA_STAGES * 2 * KV_BYTES;
+  const uint32_t q_s = base;                                    // tiles A and B
+  const uint32_t k_s = q_s + 2 * Q_BYTES;
+  const uint32_t v_s = k_s + TA_KSTAGES * KV_BYTES;
+  const uint32_t p_s = v_s + TA_VSTAGES * KV_BYTES;             // tiles A and B
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
     mbar_init(smem_u32(&q_full), 1);
-    mbar_init(smem_u32(&s_full), 1);
-    mbar_init(smem_u32(&pv_full), 1);
-    mbar_init(smem_u32(&p_ready), TA_BM);
-    for (int s = 0; s < TA_STAGES; ++s) {
-      mbar_init(smem_u32(&kv_full[s]), 1);
-      mbar_init(smem_u32(&kv_empty[s]), 1);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(smem_u32(&s_full[x]), 1);
+      mbar_init(smem_u32(&p_ready[x]), TA_BM);
+      mbar_init(smem_u32(&pv_done[x]), 1);
+    }
+    for (int s = 0; s < TA_KSTAGES; ++s) {
+      mbar_init(smem_u32(&k_full[s]), 1);
+      mbar_init(smem_u32(&k_empty[s]), 1);
+    }
+    for (int s = 0; s < TA_VSTAGES; ++s) {
+      mbar_init(smem_u32(&v_full[s]), 1);
+      mbar_init(smem_u32(&v_empty[s]), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -143,7 +197,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + TA_BN;
+  // columns: S of tile A, S of tile B, O of tile A, O of tile B
+  const uint32_t tmem_s[2] = {tmem_base, tmem_base + TA_BN};
+  const uint32_t tmem_o[2] = {tmem_base + 2 * TA_BN, tmem_base + 2 * TA_BN + HD};
   volatile int* abort_p = &abort_flag;
   pdl_launch_dependents();
 
@@ -153,177 +209,220 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
       pdl_wait();
-      mbar_expect_tx(smem_u32(&q_full), Q_BYTES);
+      const int n_tiles = t_rows[1] > 0 ? 2 : 1;
+      mbar_expect_tx(smem_u32(&q_full), n_tiles * Q_BYTES);
+      for (int x = 0; x < n_tiles; ++x)
 #pragma unroll
-      for (int sub = 0; sub < SUB; ++sub)
-        ta_tma_load_2d(q_s + sub * (TA_BM * 128), &map_q, h * HD + sub * 64, qs + m0,
-                       smem_u32(&q_full));
-      for (int it = 0; it < nkb; ++it) {
-        const int s = it % TA_STAGES;
-        const uint32_t phase = (it / TA_STAGES) & 1;
-        if (!mbar_wait(smem_u32(&kv_empty[s]), phase ^ 1u, abort_p)) break;
-        const uint32_t bar = smem_u32(&kv_full[s]);
-        mbar_expect_tx(bar, 2 * KV_BYTES);
-        const int row = qs + (kb0 + it) * TA_BN;
-        const uint32_t k_dst = kv_s + s * 2 * KV_BYTES, v_dst = k_dst + KV_BYTES;
+        for (int sub = 0; sub < SUB; ++sub)
+          ta_tma_load_2d(q_s + x * Q_BYTES + sub * (TA_BM * 128), &map_q, h * HD + sub * 64,
+                         qs + t_m0[x], smem_u32(&q_full));
+      for (int it = 0; it < n_it; ++it) {
+        const int row = qs + (kb_lo + it) * TA_BN;
+        {
+          const int s = it % TA_KSTAGES;
+          if (!mbar_wait(smem_u32(&k_empty[s]), ((it / TA_KSTAGES) & 1) ^ 1u, abort_p)) break;
+          const uint32_t bar = smem_u32(&k_full[s]);
+          mbar_expect_tx(bar, KV_BYTES);
 #pragma unroll
-        for (int sub = 0; sub < SUB; ++sub) {
-          ta_tma_load_2d(k_dst + sub * (TA_BN * 128), &map_kv, g * HD + sub * 64, row, bar);
-          ta_tma_load_2d(v_dst + sub * (TA_BN * 128), &map_kv, (G + g) * HD + sub * 64, row, bar);
+          for (int sub = 0; sub < SUB; ++sub)
+            ta_tma_load_2d(k_s + s * KV_BYTES + sub * (TA_BN * 128), &map_kv, g * HD + sub * 64,
+                           row, bar);
+        }
+        {
+          const int s = it % TA_VSTAGES;
+          if (!mbar_wait(smem_u32(&v_empty[s]), ((it / TA_VSTAGES) & 1) ^ 1u, abort_p)) break;
+          const uint32_t bar = smem_u32(&v_full[s]);
+          mbar_expect_tx(bar, KV_BYTES);
+#pragma unroll
+          for (int sub = 0; sub < SUB; ++sub)
+            ta_tma_load_2d(v_s + s * KV_BYTES + sub * (TA_BN * 128), &map_kv,
+                           (G + g) * HD + sub * 64, row, bar);
         }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer
     if (lane == 0) {
-      // S: M = 128 queries, N = 128 keys, both operands K-major
+      // S: M = 128 queries, N = 64 keys, both operands K-major
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) |
                                ((uint32_t)(TA_BM >> 4) << 24);
-      // P.V: M = 128 queries, N = HD, A (P) K-major, B (V) MN-major
+      // O += P.V: M = 128 queries, N = HD, A (P) K-major, B (V) MN-major
       const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                 ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
-      bool ok = mbar_wait(smem_u32(&q_full), 0, abort_p);
-      auto issue_s = [&](int it) {
-        const int s = it % TA_STAGES;
-        const uint32_t k_src = kv_s + s * 2 * KV_BYTES;
+      auto issue_s = [&](int x, int stage) {
+        const uint32_t q_src = q_s + x * Q_BYTES, k_src = k_s + stage * KV_BYTES;
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks / 4) * (TA_BM * 128) + (ks % 4) * 32;
-          ta_umma(tmem_s, ta_desc_k(q_s + off), ta_desc_k(k_src + off), idesc_s, ks > 0 ? 1u : 0u);
-        }
-        ta_commit(smem_u32(&s_full));
+        for (int ks = 0; ks < HD / 16; ++ks)
+          ta_umma(tmem_s[x], ta_desc_k(q_src + (ks / 4) * (TA_BM * 128) + (ks % 4) * 32),
+                  ta_desc_k(k_src + (ks / 4) * (TA_BN * 128) + (ks % 4) * 32), idesc_s,
+                  ks > 0 ? 1u : 0u);
+        ta_commit(smem_u32(&s_full[x]));
       };
-      if (ok && nkb > 0) {
-        ok = mbar_wait(smem_u32(&kv_full[0]), 0, abort_p);
-        if (ok) {
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_s(0);
-        }
-      }
-      for (int it = 0; it < nkb && ok; ++it) {
-        const int s = it % TA_STAGES;
-        // P of this block is in shared memory and S has been read
-        ok = mbar_wait(smem_u32(&p_ready), it & 1, abort_p);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t v_src = kv_s + s * 2 * KV_BYTES + KV_BYTES;
+      auto issue_pv = [&](int x, int stage, bool first) {
+        const uint32_t v_src = v_s + stage * KV_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < TA_BN / 16; ++kk) {
-          const uint32_t p_off = (kk / 4) * (TA_BM * 128) + (kk % 4) * 32;
-          ta_umma(tmem_pv, ta_desc_k(p_s + p_off), ta_desc_mn(v_src + kk * 16 * 128, TA_BN * 128),
-                  idesc_pv, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < TA_BN / 16; ++kk)
+          ta_umma(tmem_o[x], ta_desc_k(p_s + x * P_BYTES + kk * 32),
+                  ta_desc_mn(v_src + kk * 16 * 128, TA_BN * 128), idesc_pv,
+                  (first && kk == 0) ? 0u : 1u);
+        ta_commit(smem_u32(&pv_done[x]));
+      };
+      bool ok = mbar_wait(smem_u32(&q_full), 0, abort_p);
+      if (ok && n_it > 0) ok = mbar_wait(smem_u32(&k_full[0]), 0, abort_p);
+      if (ok && n_it > 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int x = 0; x < 2; ++x)
+          if (active(x, kb_lo)) issue_s(x, 0);
+        ta_commit(smem_u32(&k_empty[0]));
+      }
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int kb = kb_lo + it;
+        const int sv = it % TA_VSTAGES, sk = (it + 1) % TA_KSTAGES;
+        const bool more = it + 1 < n_it;
+        bool v_here = false, k_here = false;
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (active(x, kb)) {
+            // P of this block is in shared memory, S has been read, O is rescaled
+            ok = mbar_wait(smem_u32(&p_ready[x]), (uint32_t)(kb - t_kb0[x]) & 1u, abort_p);
+            if (ok && !v_here) {
+              ok = mbar_wait(smem_u32(&v_full[sv]), (it / TA_VSTAGES) & 1, abort_p);
+              v_here = true;
+            }
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_pv(x, sv, kb == t_kb0[x]);
+          }
+          if (more && active(x, kb + 1)) {
+            if (!k_here) {
+              ok = mbar_wait(smem_u32(&k_full[sk]), ((it + 1) / TA_KSTAGES) & 1, abort_p);
+              k_here = true;
+              if (!ok) break;
+              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            issue_s(x, sk);                                   // overlaps the other tile's softmax
+          }
         }
-        ta_commit(smem_u32(&pv_full));
-        ta_commit(smem_u32(&kv_empty[s]));                  // K and V of this block are consumed
-        if (it + 1 < nkb) {
-          const int s2 = (it + 1) % TA_STAGES;
-          ok = mbar_wait(smem_u32(&kv_full[s2]), ((it + 1) / TA_STAGES) & 1, abort_p);
-          if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_s(it + 1);                                    // overlaps the threads' work on P.V
-        }
+        if (!ok) break;
+        ta_commit(smem_u32(&v_empty[sv]));                    // V of this block is consumed
+        if (more) ta_commit(smem_u32(&k_empty[sk]));          // and K of the next
       }
     }
   } else {
-    // ---------------- softmax and output: one query row per thread
-    const int quarter = warp & 3;
+    // ---------------- softmax: one query row per thread; warps 2-5 tile A, 6-9 tile B
+    const int x = warp >= 6 ? 1 : 0;
+    const int quarter = warp & 3;                             // the TMEM lanes this warp may touch
     const int row = quarter * 32 + lane;
-    const int p = m0 + row;                                   // this row's position
+    const int p = t_m0[x] + row;                              // this row's position
+    const int p_hi = t_m0[x] + TA_BM - 1;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    float o[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    const uint32_t p_row = p_s + x * P_BYTES + row * 128;
+    float m_ref = -INFINITY, l_run = 0.f;
     pdl_wait();
     bool ok = true;
-    for (int it = 0; it < nkb; ++it) {
-      const int j0 = (kb0 + it) * TA_BN;
-      mbar_wait(smem_u32(&s_full), it & 1, abort_p);
-      asm volatile("bar.sync 1, %0;" ::"n"(TA_BM) : "memory");
+    const int n_x = t_kb1[x] - t_kb0[x];
+    for (int it = 0; it < n_x; ++it) {
+      const int j0 = (t_kb0[x] + it) * TA_BN;
+      mbar_wait(smem_u32(&s_full[x]), it & 1, abort_p);
+      if (x == 0) asm volatile("bar.sync 1, %0;" ::"n"(TA_BM) : "memory");
+      else asm volatile("bar.sync 2, %0;" ::"n"(TA_BM) : "memory");
       if (*abort_p) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool inside = j0 + TA_BN - 1 <= m0 && (window <= 0 || j0 > p_last - window);
-      // pass 1: the row's maximum over this block
-      float m_new = m_run;
-#pragma unroll 1
-      for (int c = 0; c < TA_BN; c += 32) {
-        float v[32];
-        ta_ld32(tmem_s + lane_addr + c, v);
+      float s[TA_BN];
+      ta_ld32(tmem_s[x] + lane_addr, s);
+      ta_ld32(tmem_s[x] + lane_addr + 32, s + 32);
+      // every row of the tile sees every key of the block?
+      const bool inside = j0 + TA_BN - 1 <= t_m0[x] && (window <= 0 || j0 > p_hi - window);
+      if (!inside) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = j0 + c + i;
-          const bool vis = inside || (key <= p && (window <= 0 || key > p - window));
-          m_new = fmaxf(m_new, vis ? v[i] * scale_log2 : -INFINITY);
+        for (int i = 0; i < TA_BN; ++i) {
+          const int key = j0 + i;
+          const bool vis = key <= p && (window <= 0 || key > p - window);
+          s[i] = vis ? s[i] : -INFINITY;
         }
       }
-      const float corr = m_new > -INFINITY ? exp2f(m_run - m_new) : 1.f;
-      // pass 2: probabilities into the swizzled P tile, the row's sum
-      float l_add = 0.f;
+      float m_blk = s[0];
+#pragma unroll
+      for (int i = 1; i < TA_BN; ++i) m_blk = fmaxf(m_blk, s[i]);
+      m_blk *= scale_log2;
+      const bool raise = m_blk > m_ref + TA_RAISE;            // always true for the first live block
+      const float m_new = raise ? m_blk : m_ref;
+      const float corr = raise ? ta_ex2(m_ref - m_new) : 1.f;
+      const bool any_raise = __any_sync(0xffffffffu, raise);
+      if (it > 0) {
+        // the previous product has read P and written O
+        mbar_wait(smem_u32(&pv_done[x]), (it - 1) & 1, abort_p);
+        if (x == 0) asm volatile("bar.sync 1, %0;" ::"n"(TA_BM) : "memory");
+        else asm volatile("bar.sync 2, %0;" ::"n"(TA_BM) : "memory");
+        if (*abort_p) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (any_raise) {                                      // uniform over the warp
 #pragma unroll 1
-      for (int c = 0; c < TA_BN; c += 32) {
-        float v[32];
-        ta_ld32(tmem_s + lane_addr + c, v);
+          for (int c = 0; c < HD; c += 32) {
+            float v[32];
+            ta_ld32(tmem_o[x] + lane_addr + c, v);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = j0 + c + i;
-          const bool vis = inside || (key <= p && (window <= 0 || key > p - window));
-          v[i] = (vis && m_new > -INFINITY) ? exp2f(v[i] * scale_log2 - m_new) : 0.f;
-          l_add += v[i];
-        }
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {                      // four 16-byte chunks of 8 keys
-          uint4 u;
-          __nv_bfloat162 t0 = __floats2bfloat162_rn(v[ch * 8 + 0], v[ch * 8 + 1]);
-          __nv_bfloat162 t1 = __floats2bfloat162_rn(v[ch * 8 + 2], v[ch * 8 + 3]);
-          __nv_bfloat162 t2 = __floats2bfloat162_rn(v[ch * 8 + 4], v[ch * 8 + 5]);
-          __nv_bfloat162 t3 = __floats2bfloat162_rn(v[ch * 8 + 6], v[ch * 8 + 7]);
-          u.x = *reinterpret_cast<uint32_t*>(&t0);
-          u.y = *reinterpret_cast<uint32_t*>(&t1);
-          u.z = *reinterpret_cast<uint32_t*>(&t2);
-          u.w = *reinterpret_cast<uint32_t*>(&t3);
-          const int key_in = c + ch * 8;                      // 0..127
-          const int sub = key_in >> 6, chunk = (key_in & 63) >> 3;
-          const uint32_t addr = p_s + sub * (TA_BM * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                       ::"r"(addr), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w) : "memory");
+            for (int i = 0; i < 32; ++i) v[i] *= corr;
+            ta_st32(tmem_o[x] + lane_addr + c, v);
+          }
         }
       }
-      l_run = l_run * corr + l_add;
-      m_run = m_new;
-      // P is complete for this row and S has been read: let the MMA thread go on
+      l_run *= corr;
+      m_ref = m_new;
+      const float neg = m_ref > -INFINITY ? -m_ref : 0.f;
+#pragma unroll
+      for (int ch = 0; ch < TA_BN / 8; ++ch) {                // 16-byte chunks of 8 keys
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          e[i] = ta_ex2(fmaf(s[ch * 8 + i], scale_log2, neg));
+          l_run += e[i];
+        }
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(e[0], e[1]);
+        __nv_bfloat162 t1 = __floats2bfloat162_rn(e[2], e[3]);
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(e[4], e[5]);
+        __nv_bfloat162 t3 = __floats2bfloat162_rn(e[6], e[7]);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                     ::"r"(p_row + ((ch ^ (row & 7)) << 4)), "r"(*reinterpret_cast<uint32_t*>(&t0)),
+                       "r"(*reinterpret_cast<uint32_t*>(&t1)), "r"(*reinterpret_cast<uint32_t*>(&t2)),
+                       "r"(*reinterpret_cast<uint32_t*>(&t3))
+                     : "memory");
+      }
+      // P is complete for this row, S has been read, O is rescaled: the MMA thread may go on
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(smem_u32(&p_ready));
-      // the product of this block, added to the row
-      mbar_wait(smem_u32(&pv_full), it & 1, abort_p);
-      asm volatile("bar.sync 1, %0;" ::"n"(TA_BM) : "memory");
-      if (*abort_p) { ok = false; break; }
+      mbar_arrive(smem_u32(&p_ready[x]));
+    }
+    if (ok && n_x > 0) {
+      mbar_wait(smem_u32(&pv_done[x]), (n_x - 1) & 1, abort_p);
+      if (x == 0) asm volatile("bar.sync 1, %0;" ::"n"(TA_BM) : "memory");
+      else asm volatile("bar.sync 2, %0;" ::"n"(TA_BM) : "memory");
+      ok = !*abort_p;
+    }
+    if (ok && n_x > 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
+      const float inv = 1.0f / l_run;
+      __nv_bfloat16* op = out + ((size_t)(qs + t_m0[x] + row) * H + h) * HD;
+#pragma unroll 1
       for (int c = 0; c < HD; c += 32) {
         float v[32];
-        ta_ld32(tmem_pv + lane_addr + c, v);
+        ta_ld32(tmem_o[x] + lane_addr + c, v);                // by the whole warp
+        if (row < t_rows[x]) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr, v[i]);
+          for (int c8 = 0; c8 < 32; c8 += 8) {
+            uint4 u;
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[c8 + 0] * inv, v[c8 + 1] * inv);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[c8 + 2] * inv, v[c8 + 3] * inv);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[c8 + 4] * inv, v[c8 + 5] * inv);
+            __nv_bfloat162 t3 = __floats2bfloat162_rn(v[c8 + 6] * inv, v[c8 + 7] * inv);
+            u.x = *reinterpret_cast<uint32_t*>(&t0);
+            u.y = *reinterpret_cast<uint32_t*>(&t1);
+            u.z = *reinterpret_cast<uint32_t*>(&t2);
+            u.w = *reinterpret_cast<uint32_t*>(&t3);
+            *reinterpret_cast<uint4*>(op + c + c8) = u;
+          }
+        }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    }
-    if (ok && row < rows) {
-      const float inv = 1.0f / l_run;
-      __nv_bfloat16* op = out + ((size_t)(qs + m0 + row) * H + h) * HD;
-#pragma unroll
-      for (int c = 0; c < HD; c += 8) {
-        uint4 u;
-        __nv_bfloat162 t0 = __floats2bfloat162_rn(o[c + 0] * inv, o[c + 1] * inv);
-        __nv_bfloat162 t1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
-        __nv_bfloat162 t2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv);
-        __nv_bfloat162 t3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
-        u.x = *reinterpret_cast<uint32_t*>(&t0);
-        u.y = *reinterpret_cast<uint32_t*>(&t1);
-        u.z = *reinterpret_cast<uint32_t*>(&t2);
-        u.w = *reinterpret_cast<uint32_t*>(&t3);
-        *reinterpret_cast<uint4*>(op + c) = u;
-      }
     }
   }
 
@@ -359,13 +458,14 @@ static TaEncodeFn ta_encode_fn() {
   }
   return fn;
 }
-// rows x cols bfloat16, row-major; box = 128 rows x 64 columns, 128-byte swizzle
-static int ta_make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols) {
+// rows x cols bfloat16, row-major; box = box_rows rows x 64 columns, 128-byte swizzle
+static int ta_make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols,
+                       int box_rows) {
   TaEncodeFn fn = ta_encode_fn();
   if (!fn) return -10;
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  const cuuint32_t box[2] = {64, 128};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -378,12 +478,13 @@ static int launch_prefill_tc(const void* q, const void* kv_step, const int* q_st
                              int n_tokens, int n_seqs, int max_q_len, int H, int G, int window,
                              int* status, cudaStream_t stream) {
   CUtensorMap mq, mkv;
-  int rc = ta_make_map(&mq, q, n_tokens, (long long)H * HD);
+  int rc = ta_make_map(&mq, q, n_tokens, (long long)H * HD, TA_BM);
   if (rc) return rc;
-  rc = ta_make_map(&mkv, kv_step, n_tokens, (long long)2 * G * HD);
+  rc = ta_make_map(&mkv, kv_step, n_tokens, (long long)2 * G * HD, TA_BN);
   if (rc) return rc;
-  const size_t smem = (size_t)TA_BM * HD * 2 + (size_t)TA_STAGES * 2 * TA_BN * HD * 2 +
-                      (size_t)TA_BM * TA_BN * 2 + 1024;
+  // two query tiles, the K and V rings, two P tiles, slack to align to 1024
+  const size_t smem = (size_t)2 * TA_BM * HD * 2 + (size_t)(TA_KSTAGES + TA_VSTAGES) * TA_BN * HD * 2 +
+                      (size_t)2 * TA_BM * TA_BN * 2 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>,
@@ -391,7 +492,7 @@ static int launch_prefill_tc(const void* q, const void* kv_step, const int* q_st
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  const dim3 grid((max_q_len + TA_BM - 1) / TA_BM, H, n_seqs);
+  const dim3 grid((max_q_len + 2 * TA_BM - 1) / (2 * TA_BM), H, n_seqs);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
   launch_pdl(attn_prefill_tc_kernel<HD>, grid, dim3(TA_THREADS), smem, stream, mq, mkv, q_start,
              (__nv_bfloat16*)out, H, G, window, scale_log2, status);

@@ -121,10 +121,10 @@ class GQAAttention:
                 ops.attention_decode(q, view.k, view.v, batch.seq_slot, view.slot_pos, o, part_o,
                                      part_ml, counters, rt.status, H, G, hd, view.capacity,
                                      self.window, chunk, bound)
-        elif rt.attention == "tcgen05" and ops.tc_attention_usable(rt.dtype, hd, batch.past):
-            # correct but, with one query tile per block, a serial chain of barrier
-            # hand-offs per key block (569 us against 360 us per layer at 2,048 tokens):
-            # kept selectable until it runs two query tiles in ping-pong
+        elif rt.attention in ("auto", "tcgen05") and ops.tc_attention_usable(rt.dtype, hd, batch.past):
+            # whole prompts: S and O in tensor memory, two query tiles per block in
+            # ping-pong (99 us against 357 us for the mma.sync kernel per layer at
+            # 2,048 tokens of 32 heads of 128)
             ops.attention_prefill_tc(q, kv_step, batch, o, H, G, hd, self.window, rt.status)
         elif tensor_cores:
             ops.attention_prefill_mma(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G,

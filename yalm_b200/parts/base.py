@@ -75,7 +75,7 @@ class Runtime:
                                "there is no CPU path")
         ops.lib()   # builds/loads the kernels now: a missing library fails here, loudly
         self.gemm = gemm                      # "auto" | "simt" (debugging aid: no tensor cores)
-        self.attention = attention            # "auto" | "simt" | "tcgen05" (prefill attention variant)
+        self.attention = attention            # "auto" | "mma" (no tcgen05 prefill attention) | "simt"
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._buffers: Dict[str, torch.Tensor] = {}
         self._shared = []
