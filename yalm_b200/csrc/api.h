@@ -9,6 +9,8 @@
 extern "C" {
 #endif
 
+int yalm_copy_async(void* dst, const void* src, long long bytes, int to_device, cudaStream_t stream);
+int yalm_stream_wait(cudaStream_t stream);
 int yalm_embed(const int* tokens, const void* table, int table_dtype, float* x, int n_tokens,
                int dim, int vocab, int* status, cudaStream_t stream);
 

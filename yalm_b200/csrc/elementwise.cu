@@ -298,6 +298,17 @@ extern "C" int yalm_set_pdl(int on) {
   return 0;
 }
 
+// Host <-> device copies of a decode step's few tokens without a tensor library in
+// between: `to_device` 1 copies host (pinned) to device, 0 device to host; both are
+// asynchronous on the stream.  yalm_stream_wait blocks the host until the stream is idle.
+extern "C" int yalm_copy_async(void* dst, const void* src, long long bytes, int to_device,
+                               cudaStream_t stream) {
+  if (bytes <= 0) return 0;
+  return (int)cudaMemcpyAsync(dst, src, (size_t)bytes,
+                              to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, stream);
+}
+extern "C" int yalm_stream_wait(cudaStream_t stream) { return (int)cudaStreamSynchronize(stream); }
+
 extern "C" int yalm_embed(const int* tokens, const void* table, int table_dtype, float* x,
                           int n_tokens, int dim, int vocab, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;

@@ -46,6 +46,8 @@ _vp, _i, _ll, _f, _ull = _c.c_void_p, _c.c_int, _c.c_longlong, _c.c_float, _c.c_
 _SIGNATURES = {
     "yalm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp],
     "yalm_rmsnorm": [_vp, _vp, _i, _ll, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+    "yalm_copy_async": [_vp, _vp, _ll, _i, _vp],
+    "yalm_stream_wait": [_vp],
     "yalm_silu_mul": [_vp, _i, _ll, _vp, _i, _i, _i, _i, _vp],
     "yalm_rope_store": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                         _i, _i, _i, _vp],
@@ -147,6 +149,16 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
     _check(lib().yalm_rmsnorm(_p(x), _p(partials) if n_partials else None, n_partials, stride,
                               _p(rows), _p(weight), _p(out), dtype_code(out.dtype), n_rows, dim,
                               float(eps), _stream()), "rmsnorm")
+
+
+def copy_async(dst_ptr: int, src_ptr: int, n_bytes: int, to_device: bool) -> None:
+    """A small copy between pinned host memory and the device on the current stream."""
+    _check(lib().yalm_copy_async(dst_ptr, src_ptr, n_bytes, 1 if to_device else 0, _stream()),
+           "copy_async", kernels=0)
+
+
+def stream_wait() -> None:
+    _check(lib().yalm_stream_wait(_stream()), "stream_wait", kernels=0)
 
 
 def silu_mul(gu: torch.Tensor, out: torch.Tensor, n_partials: int = 1, paired: bool = False) -> None:

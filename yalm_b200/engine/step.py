@@ -109,6 +109,11 @@ class Engine:
                 "host": torch.zeros(3 * n, dtype=torch.int32).pin_memory(),
                 "host_out": torch.zeros(n, dtype=torch.int32).pin_memory(),
             }
+            # views and addresses for the per-step copies (no tensor operations on that path)
+            self._dec["host_np"] = self._dec["host"].numpy()
+            self._dec["host_out_np"] = self._dec["host_out"].numpy()
+            self._dec["ptr"] = {k: self._dec[k].data_ptr()
+                                for k in ("tokens", "seq_slot", "row_key", "host", "host_out")}
         return self._dec
 
     def set_decode_batch(self, tokens: Sequence[int], slots: Sequence[int],
@@ -118,22 +123,21 @@ class Engine:
         d = self._decode_buffers()
         B = len(tokens)
         n = self.cache.n_slots
-        h = d["host"]
-        h[0:B] = torch.tensor(list(tokens), dtype=torch.int32)
-        h[n:n + B] = torch.tensor(list(slots), dtype=torch.int32)
-        h[2 * n:2 * n + B] = torch.tensor(list(keys), dtype=torch.int32)
-        d["tokens"][:B].copy_(h[0:B], non_blocking=True)
-        d["seq_slot"][:B].copy_(h[n:n + B], non_blocking=True)
-        d["row_key"][:B].copy_(h[2 * n:2 * n + B], non_blocking=True)
+        h, ptr = d["host_np"], d["ptr"]
+        h[0:B] = tokens
+        h[n:n + B] = slots
+        h[2 * n:2 * n + B] = keys
+        ops.copy_async(ptr["tokens"], ptr["host"], 4 * B, True)
+        ops.copy_async(ptr["seq_slot"], ptr["host"] + 4 * n, 4 * B, True)
+        ops.copy_async(ptr["row_key"], ptr["host"] + 8 * n, 4 * B, True)
         d["slots_host"] = list(slots)
 
     def set_decode_tokens(self, tokens: Sequence[int]) -> None:
         """Only the next tokens (the decoding sequences are unchanged)."""
         d = self._decode_buffers()
         B = len(tokens)
-        h = d["host"]
-        h[0:B] = torch.tensor(list(tokens), dtype=torch.int32)
-        d["tokens"][:B].copy_(h[0:B], non_blocking=True)
+        d["host_np"][0:B] = tokens
+        ops.copy_async(d["ptr"]["tokens"], d["ptr"]["host"], 4 * B, True)
 
     def _decode_batch(self, B: int) -> StepBatch:
         d = self._decode_buffers()
@@ -202,8 +206,9 @@ class Engine:
 
     def read_decode_tokens(self, B: int) -> List[int]:
         d = self._decode_buffers()
-        d["host_out"][:B].copy_(d["tokens"][:B], non_blocking=False)
-        return d["host_out"][:B].tolist()
+        ops.copy_async(d["ptr"]["host_out"], d["ptr"]["tokens"], 4 * B, False)
+        ops.stream_wait()
+        return d["host_out_np"][:B].tolist()
 
     def decode_logits(self, B: int) -> torch.Tensor:
         return self._decode_buffers()["logits"][:B]
