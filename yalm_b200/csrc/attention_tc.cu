@@ -96,6 +96,34 @@ __device__ __forceinline__ void ta_ld32(uint32_t taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// The same load without the wait: several can be in flight; ta_ld_wait32 then makes
+// the registers of one of them (and, by the instruction's meaning, of all earlier
+// ones) valid, and ta_ld_after32 ties the registers of another to that point.
+__device__ __forceinline__ void ta_ld32_issue(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+#define YALM_R32(r)                                                                              \
+  "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), \
+  "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),       \
+  "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),     \
+  "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),     \
+  "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+__device__ __forceinline__ void ta_ld_wait32(uint32_t* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : YALM_R32(r) : : "memory");
+}
+__device__ __forceinline__ void ta_ld_after32(uint32_t* r) {
+  asm volatile("" : YALM_R32(r) : : "memory");
+}
+#undef YALM_R32
 __device__ __forceinline__ void ta_st32(uint32_t taddr, const float* v) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -142,10 +170,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, h = blockIdx.y;
+  // heads run fastest in the grid and the blocks with the most keys come first, so that
+  // the long blocks of every head start before any short one
+  const int b = blockIdx.z, h = blockIdx.x;
   const int g = h / (H / G);
   const int qs = q_start[b], q_len = q_start[b + 1] - qs;       // written by a host copy: safe early
-  const int m0 = (gridDim.x - 1 - blockIdx.x) * 2 * TA_BM;      // heaviest blocks first
+  const int m0 = (gridDim.y - 1 - blockIdx.y) * 2 * TA_BM;
   if (m0 >= q_len) return;
   // per tile: first row, rows, and the blocks of keys [kb0, kb1) its rows can see
   int t_m0[2], t_rows[2], t_kb0[2], t_kb1[2];
@@ -249,21 +279,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // O += P.V: M = 128 queries, N = HD, A (P) K-major, B (V) MN-major
       const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                 ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
+      // descriptors: one per operand tile, advanced by constants inside the loops
+      const uint64_t q_desc[2] = {ta_desc_k(q_s), ta_desc_k(q_s + Q_BYTES)};
+      const uint64_t p_desc[2] = {ta_desc_k(p_s), ta_desc_k(p_s + P_BYTES)};
       auto issue_s = [&](int x, int stage) {
-        const uint32_t q_src = q_s + x * Q_BYTES, k_src = k_s + stage * KV_BYTES;
+        const uint64_t k_desc = ta_desc_k(k_s + stage * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          ta_umma(tmem_s[x], ta_desc_k(q_src + (ks / 4) * (TA_BM * 128) + (ks % 4) * 32),
-                  ta_desc_k(k_src + (ks / 4) * (TA_BN * 128) + (ks % 4) * 32), idesc_s,
+          ta_umma(tmem_s[x], q_desc[x] + (uint64_t)(((ks / 4) * (TA_BM * 128) + (ks % 4) * 32) >> 4),
+                  k_desc + (uint64_t)(((ks / 4) * (TA_BN * 128) + (ks % 4) * 32) >> 4), idesc_s,
                   ks > 0 ? 1u : 0u);
         ta_commit(smem_u32(&s_full[x]));
       };
       auto issue_pv = [&](int x, int stage, bool first) {
-        const uint32_t v_src = v_s + stage * KV_BYTES;
+        const uint64_t v_desc = ta_desc_mn(v_s + stage * KV_BYTES, TA_BN * 128);
 #pragma unroll
         for (int kk = 0; kk < TA_BN / 16; ++kk)
-          ta_umma(tmem_o[x], ta_desc_k(p_s + x * P_BYTES + kk * 32),
-                  ta_desc_mn(v_src + kk * 16 * 128, TA_BN * 128), idesc_pv,
+          ta_umma(tmem_o[x], p_desc[x] + (uint64_t)((kk * 32) >> 4),
+                  v_desc + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv,
                   (first && kk == 0) ? 0u : 1u);
         ta_commit(smem_u32(&pv_done[x]));
       };
@@ -271,6 +304,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (ok && n_it > 0) ok = mbar_wait(smem_u32(&k_full[0]), 0, abort_p);
       if (ok && n_it > 0) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
         for (int x = 0; x < 2; ++x)
           if (active(x, kb_lo)) issue_s(x, 0);
         ta_commit(smem_u32(&k_empty[0]));
@@ -280,7 +314,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int sv = it % TA_VSTAGES, sk = (it + 1) % TA_KSTAGES;
         const bool more = it + 1 < n_it;
         bool v_here = false, k_here = false;
-        for (int x = 0; x < 2 && ok; ++x) {
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (!ok) break;
           if (active(x, kb)) {
             // P of this block is in shared memory, S has been read, O is rescaled
             ok = mbar_wait(smem_u32(&p_ready[x]), (uint32_t)(kb - t_kb0[x]) & 1u, abort_p);
@@ -312,26 +348,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int x = warp >= 6 ? 1 : 0;
     const int quarter = warp & 3;                             // the TMEM lanes this warp may touch
     const int row = quarter * 32 + lane;
-    const int p = t_m0[x] + row;                              // this row's position
-    const int p_hi = t_m0[x] + TA_BM - 1;
+    const int my_m0 = x ? t_m0[1] : t_m0[0], my_rows = x ? t_rows[1] : t_rows[0];
+    const int my_kb0 = x ? t_kb0[1] : t_kb0[0], my_kb1 = x ? t_kb1[1] : t_kb1[0];
+    const int p = my_m0 + row;                                // this row's position
+    const int p_hi = my_m0 + TA_BM - 1;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t my_s = (x ? tmem_s[1] : tmem_s[0]) + lane_addr;
+    const uint32_t my_o = (x ? tmem_o[1] : tmem_o[0]) + lane_addr;
+    const uint32_t bar_s = smem_u32(x ? &s_full[1] : &s_full[0]);
+    const uint32_t bar_p = smem_u32(x ? &p_ready[1] : &p_ready[0]);
+    const uint32_t bar_pv = smem_u32(x ? &pv_done[1] : &pv_done[0]);
     const uint32_t p_row = p_s + x * P_BYTES + row * 128;
     float m_ref = -INFINITY, l_run = 0.f;
     pdl_wait();
     bool ok = true;
-    const int n_x = t_kb1[x] - t_kb0[x];
+    const int n_x = my_kb1 - my_kb0;
     for (int it = 0; it < n_x; ++it) {
-      const int j0 = (t_kb0[x] + it) * TA_BN;
-      mbar_wait(smem_u32(&s_full[x]), it & 1, abort_p);
+      const int j0 = (my_kb0 + it) * TA_BN;
+      mbar_wait(bar_s, it & 1, abort_p);
       if (x == 0) asm volatile("bar.sync 1, %0;" ::"n"(TA_BM) : "memory");
       else asm volatile("bar.sync 2, %0;" ::"n"(TA_BM) : "memory");
       if (*abort_p) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float s[TA_BN];
-      ta_ld32(tmem_s[x] + lane_addr, s);
-      ta_ld32(tmem_s[x] + lane_addr + 32, s + 32);
+      {
+        uint32_t raw[TA_BN];
+        ta_ld32_issue(my_s, raw);                             // both halves in flight, one wait
+        ta_ld32_issue(my_s + 32, raw + 32);
+        ta_ld_wait32(raw);
+        ta_ld_after32(raw + 32);
+#pragma unroll
+        for (int i = 0; i < TA_BN; ++i) s[i] = __uint_as_float(raw[i]);
+      }
       // every row of the tile sees every key of the block?
-      const bool inside = j0 + TA_BN - 1 <= t_m0[x] && (window <= 0 || j0 > p_hi - window);
+      const bool inside = j0 + TA_BN - 1 <= my_m0 && (window <= 0 || j0 > p_hi - window);
       if (!inside) {
 #pragma unroll
         for (int i = 0; i < TA_BN; ++i) {
@@ -340,17 +390,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           s[i] = vis ? s[i] : -INFINITY;
         }
       }
-      float m_blk = s[0];
+      float mx[4] = {s[0], s[1], s[2], s[3]};                 // four chains instead of one
 #pragma unroll
-      for (int i = 1; i < TA_BN; ++i) m_blk = fmaxf(m_blk, s[i]);
-      m_blk *= scale_log2;
+      for (int i = 4; i < TA_BN; ++i) mx[i & 3] = fmaxf(mx[i & 3], s[i]);
+      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
       const bool raise = m_blk > m_ref + TA_RAISE;            // always true for the first live block
       const float m_new = raise ? m_blk : m_ref;
       const float corr = raise ? ta_ex2(m_ref - m_new) : 1.f;
       const bool any_raise = __any_sync(0xffffffffu, raise);
       if (it > 0) {
         // the previous product has read P and written O
-        mbar_wait(smem_u32(&pv_done[x]), (it - 1) & 1, abort_p);
+        mbar_wait(bar_pv, (it - 1) & 1, abort_p);
         if (x == 0) asm volatile("bar.sync 1, %0;" ::"n"(TA_BM) : "memory");
         else asm volatile("bar.sync 2, %0;" ::"n"(TA_BM) : "memory");
         if (*abort_p) { ok = false; break; }
@@ -359,23 +409,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll 1
           for (int c = 0; c < HD; c += 32) {
             float v[32];
-            ta_ld32(tmem_o[x] + lane_addr + c, v);
+            ta_ld32(my_o + c, v);
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] *= corr;
-            ta_st32(tmem_o[x] + lane_addr + c, v);
+            ta_st32(my_o + c, v);
           }
         }
       }
-      l_run *= corr;
       m_ref = m_new;
       const float neg = m_ref > -INFINITY ? -m_ref : 0.f;
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ch = 0; ch < TA_BN / 8; ++ch) {                // 16-byte chunks of 8 keys
         float e[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           e[i] = ta_ex2(fmaf(s[ch * 8 + i], scale_log2, neg));
-          l_run += e[i];
+          ls[i & 3] += e[i];
         }
         __nv_bfloat162 t0 = __floats2bfloat162_rn(e[0], e[1]);
         __nv_bfloat162 t1 = __floats2bfloat162_rn(e[2], e[3]);
@@ -387,13 +437,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        "r"(*reinterpret_cast<uint32_t*>(&t3))
                      : "memory");
       }
+      l_run = l_run * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
       // P is complete for this row, S has been read, O is rescaled: the MMA thread may go on
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(smem_u32(&p_ready[x]));
+      mbar_arrive(bar_p);
     }
     if (ok && n_x > 0) {
-      mbar_wait(smem_u32(&pv_done[x]), (n_x - 1) & 1, abort_p);
+      mbar_wait(bar_pv, (n_x - 1) & 1, abort_p);
       if (x == 0) asm volatile("bar.sync 1, %0;" ::"n"(TA_BM) : "memory");
       else asm volatile("bar.sync 2, %0;" ::"n"(TA_BM) : "memory");
       ok = !*abort_p;
@@ -401,12 +452,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (ok && n_x > 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = 1.0f / l_run;
-      __nv_bfloat16* op = out + ((size_t)(qs + t_m0[x] + row) * H + h) * HD;
+      __nv_bfloat16* op = out + ((size_t)(qs + my_m0 + row) * H + h) * HD;
 #pragma unroll 1
       for (int c = 0; c < HD; c += 32) {
         float v[32];
-        ta_ld32(tmem_o[x] + lane_addr + c, v);                // by the whole warp
-        if (row < t_rows[x]) {
+        ta_ld32(my_o + c, v);                // by the whole warp
+        if (row < my_rows) {
 #pragma unroll
           for (int c8 = 0; c8 < 32; c8 += 8) {
             uint4 u;
@@ -492,7 +543,7 @@ static int launch_prefill_tc(const void* q, const void* kv_step, const int* q_st
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  const dim3 grid((max_q_len + 2 * TA_BM - 1) / (2 * TA_BM), H, n_seqs);
+  const dim3 grid(H, (max_q_len + 2 * TA_BM - 1) / (2 * TA_BM), n_seqs);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
   launch_pdl(attn_prefill_tc_kernel<HD>, grid, dim3(TA_THREADS), smem, stream, mq, mkv, q_start,
              (__nv_bfloat16*)out, H, G, window, scale_log2, status);
@@ -515,7 +566,7 @@ extern "C" int yalm_attention_prefill_tc(const void* q, const void* kv_step, con
   if (n_seqs <= 0 || max_q_len <= 0 || n_tokens <= 0) return 0;
   if (hd != 64 && hd != 128) return -2;
   if (G <= 0 || H % G != 0) return -3;
-  if (H > 65535 || n_seqs > 65535) return -4;
+  if (n_seqs > 65535 || (max_q_len + 2 * TA_BM - 1) / (2 * TA_BM) > 65535) return -4;
   if (((uintptr_t)q | (uintptr_t)kv_step | (uintptr_t)out) & 15) return -6;
   if (hd == 64)
     return launch_prefill_tc<64>(q, kv_step, q_start, out, n_tokens, n_seqs, max_q_len, H, G,
