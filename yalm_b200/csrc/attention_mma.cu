@@ -417,15 +417,14 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   __shared__ float row_m[FD_ROWS], row_l[FD_ROWS];
   __shared__ int last_flag;
   pdl_launch_dependents();
-  pdl_wait();
-
   const int R = H / G;
   const int nhc = (R + FD_ROWS - 1) / FD_ROWS;
   const int g = blockIdx.y / nhc, hchunk = blockIdx.y % nhc;
   const int h0 = g * R + hchunk * FD_ROWS;
   const int nh = min(FD_ROWS, R - hchunk * FD_ROWS);
   const int t = blockIdx.z, part = blockIdx.x;
-  const int slot = seq_slot[t];
+  const int slot = seq_slot[t];           // written by a host copy, never by a kernel: safe early
+  pdl_wait();
   const int pos = slot_pos[slot];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int nkeys = pos - lo + 1;

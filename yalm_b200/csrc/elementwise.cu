@@ -208,19 +208,25 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G,
                                   int hd, int capacity, int write_cache, int heads_per_block) {
   pdl_launch_dependents();
-  pdl_wait();
   const int t = blockIdx.x;
   const int half = hd >> 1;
   const int lanes = half / VEC;                             // threads per head
   const int i = (threadIdx.x % lanes) * VEC;
   const int head = blockIdx.y * heads_per_block + threadIdx.x / lanes;
-  if (head >= H + 2 * G) return;
+  // the batch's index arrays are written by host copies, never by a kernel: they may be
+  // read while the previous kernel still runs; positions and the product may not
   const int b = token_seq[t];
   const int slot = seq_slot[b];
-  const int past = slot_pos[slot];
   const int qs = q_start[b];
+  const int q_end = q_start[b + 1];
+  float fr[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) fr[v] = inv_freq[i + v];
+  pdl_wait();
+  if (head >= H + 2 * G) return;
+  const int past = slot_pos[slot];
   const int pos = past + (t - qs);
-  const int end = past + (q_start[b + 1] - qs);            // positions after this step
+  const int end = past + (q_end - qs);                     // positions after this step
   const bool keep = write_cache && pos >= end - capacity;
   const int row_elems = (H + 2 * G) * hd;
   const float* sp = qkv + (size_t)t * row_elems + head * hd + i;
@@ -254,7 +260,7 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
   if (head < H + G) {
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
-      const float ang = (float)pos * inv_freq[i + v];
+      const float ang = (float)pos * fr[v];
       const float c = cosf(ang), s = sinf(ang);
       const float r0 = a[v] * c - bb[v] * s, r1 = a[v] * s + bb[v] * c;
       a[v] = r0;
