@@ -24,7 +24,9 @@ __host__ __device__ inline float uniform01(unsigned long long seed, unsigned key
   return (float)(x >> 40) * (1.0f / 16777216.0f);   // 24 bits: [0, 1)
 }
 
-constexpr int SAMPLE_THREADS = 256;
+// a row is read once or twice: what matters is how many loads are in flight
+constexpr int SAMPLE_THREADS = 1024;
+static_assert(SAMPLE_THREADS == 1024, "the scan over the warps' sums assumes 32 warps");
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int vocab, float temperature,
@@ -35,7 +37,6 @@ sample_kernel(const float* __restrict__ logits, int vocab, float temperature,
   pdl_wait();
   __shared__ float red_v[SAMPLE_THREADS];
   __shared__ int red_i[SAMPLE_THREADS];
-  __shared__ float prefix[SAMPLE_THREADS + 1];
   __shared__ int result;
   const int row = blockIdx.x, tid = threadIdx.x;
   const float* l = logits + (size_t)row * vocab;
@@ -43,7 +44,16 @@ sample_kernel(const float* __restrict__ logits, int vocab, float temperature,
   // first maximal index
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+  int i = tid;
+  for (; i + 3 * SAMPLE_THREADS < vocab; i += 4 * SAMPLE_THREADS) {   // four loads in flight
+    const float v0 = l[i], v1 = l[i + SAMPLE_THREADS], v2 = l[i + 2 * SAMPLE_THREADS],
+                v3 = l[i + 3 * SAMPLE_THREADS];
+    if (v0 > bv) { bv = v0; bi = i; }
+    if (v1 > bv) { bv = v1; bi = i + SAMPLE_THREADS; }
+    if (v2 > bv) { bv = v2; bi = i + 2 * SAMPLE_THREADS; }
+    if (v3 > bv) { bv = v3; bi = i + 3 * SAMPLE_THREADS; }
+  }
+  for (; i < vocab; i += SAMPLE_THREADS) {
     const float v = l[i];
     if (v > bv) { bv = v; bi = i; }
   }
@@ -73,16 +83,37 @@ sample_kernel(const float* __restrict__ logits, int vocab, float temperature,
   const int c0 = min(tid * chunk, vocab), c1 = min(c0 + chunk, vocab);
   float mine = 0.f;
   for (int i = c0; i < c1; ++i) mine += expf((l[i] - maxv) / temperature);
-  prefix[tid + 1] = mine;
-  if (tid == 0) { prefix[0] = 0.f; result = vocab - 1; }
+  // running sums over the threads' chunks: a scan inside each warp, then over the warps
+  const int lane = tid & 31, warp = tid >> 5;
+  float incl = mine;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const float n = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += n;
+  }
+  float excl = __shfl_up_sync(0xffffffffu, incl, 1);
+  if (lane == 0) excl = 0.f;
+  __syncthreads();                                   // red_v is free again
+  if (lane == 31) red_v[warp] = incl;
+  if (tid == 0) result = vocab - 1;
   __syncthreads();
-  if (tid == 0)
-    for (int i = 1; i <= SAMPLE_THREADS; ++i) prefix[i] += prefix[i - 1];
+  if (warp == 0) {
+    float w = red_v[lane];                           // SAMPLE_THREADS / 32 == 32 warps
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const float n = __shfl_up_sync(0xffffffffu, w, off);
+      if (lane >= off) w += n;
+    }
+    red_v[lane] = w;
+  }
   __syncthreads();
-  const float total = prefix[SAMPLE_THREADS];
+  // a warp's last running sum is, to the bit, the next warp's first exclusive sum
+  const float base = warp > 0 ? red_v[warp - 1] : 0.f;
+  incl = lane == 31 ? red_v[warp] : incl + base;
+  excl += base;
+  const float total = red_v[SAMPLE_THREADS / 32 - 1];
   const unsigned counter = (unsigned)slot_pos[seq_slot[row]];
   const float target = uniform01(seed, (unsigned)row_key[row], counter) * total;
-  const float excl = prefix[tid], incl = prefix[tid + 1];
   if (c1 > c0 && incl >= target && (tid == 0 || excl < target)) {
     float cum = excl;
     int pick = c1 - 1;

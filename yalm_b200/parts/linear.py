@@ -122,7 +122,7 @@ def matmul_silu_mul(rt, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Ten
             if M > 128:
                 ops.gemm_2sm(a, w_gate_up, out, ops.GEMM_SILU_PAIRED, rt.status)
                 return
-            if not _small(rt, M, N2):
+            if not _small(rt, M, N2) or plan_splits(M, N2, K, rt.sm_count) == 1:
                 ops.gemm_tc(a, w_gate_up, out, ops.GEMM_SILU_PAIRED, rt.status)
                 return
         elif not _small(rt, M, N2 // 2):
