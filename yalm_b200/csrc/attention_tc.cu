@@ -170,13 +170,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // heads run fastest in the grid and the blocks with the most keys come first, so that
-  // the long blocks of every head start before any short one
-  const int b = blockIdx.z, h = blockIdx.x;
+  // heads run fastest in the grid, then sequences, and a sequence's blocks come from its
+  // end: the long blocks of every head and sequence start before any short one
+  const int b = blockIdx.y, h = blockIdx.x;
   const int g = h / (H / G);
   const int qs = q_start[b], q_len = q_start[b + 1] - qs;       // written by a host copy: safe early
-  const int m0 = (gridDim.y - 1 - blockIdx.y) * 2 * TA_BM;
-  if (m0 >= q_len) return;
+  const int n_blocks = (q_len + 2 * TA_BM - 1) / (2 * TA_BM);
+  if ((int)blockIdx.z >= n_blocks) return;
+  const int m0 = (n_blocks - 1 - (int)blockIdx.z) * 2 * TA_BM;
   // per tile: first row, rows, and the blocks of keys [kb0, kb1) its rows can see
   int t_m0[2], t_rows[2], t_kb0[2], t_kb1[2];
 #pragma unroll
@@ -543,7 +544,7 @@ static int launch_prefill_tc(const void* q, const void* kv_step, const int* q_st
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  const dim3 grid(H, (max_q_len + 2 * TA_BM - 1) / (2 * TA_BM), n_seqs);
+  const dim3 grid(H, n_seqs, (max_q_len + 2 * TA_BM - 1) / (2 * TA_BM));
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
   launch_pdl(attn_prefill_tc_kernel<HD>, grid, dim3(TA_THREADS), smem, stream, mq, mkv, q_start,
              (__nv_bfloat16*)out, H, G, window, scale_log2, status);

@@ -112,6 +112,7 @@ class LM:
                            "new_tokens": sum(len(c.tokens) for c in out),
                            "decode_steps": backend.decode_steps,
                            "decode_seconds": backend.decode_seconds,
+                           "step_seconds": backend.step_seconds,
                            "h2d_bytes": backend.h2d_bytes, "d2h_bytes": backend.d2h_bytes}
         return out
 
@@ -153,6 +154,7 @@ class _DeviceBackend:
         self.context = lm.context
         self.prefill_seconds = 0.0
         self.decode_seconds = 0.0
+        self.step_seconds = []                # wall time of each decode step, host to host
         self.decode_steps = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -195,7 +197,9 @@ class _DeviceBackend:
         out = eng.read_decode_tokens(B)
         self.d2h_bytes += 4 * B
         self.decode_steps += 1
-        self.decode_seconds += time.perf_counter() - t0
+        dt = time.perf_counter() - t0
+        self.decode_seconds += dt
+        self.step_seconds.append(dt)
         return out
 
     def end(self, handle):
