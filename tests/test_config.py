@@ -4,7 +4,7 @@ import json
 import pytest
 
 from helpers import TINY_A, TINY_B
-from yalm_b200.config import (ConfigError, LlamaConfig, ModelSpec, PartSpec, RunEntry,
+from yalm_b200.config import (ConfigError, LlamaConfig, RunEntry,
                               architectures, config_from_dict, load_config,
                               register_architecture)
 

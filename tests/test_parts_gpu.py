@@ -1,12 +1,11 @@
 """Each part alone against its plain function, and a toy mixer with state of
 its own that is registered, built and stepped without touching the library."""
 import dataclasses
-import math
 
 import pytest
 import torch
 
-from helpers import TINY_A, TINY_C, TOL, make_weights, random_tokens
+from helpers import TINY_A, TINY_C, make_weights, random_tokens
 from plain_model import (plain_attention, plain_block, plain_embedding, plain_forward,
                          plain_inv_freq, plain_rmsnorm, plain_rope, plain_swiglu)
 

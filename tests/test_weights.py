@@ -6,10 +6,10 @@ import struct
 import pytest
 import torch
 
-from helpers import TINY_A, TINY_B, make_weights, write_model
+from helpers import TINY_A, TINY_B, make_weights
 from yalm_b200.config import config_from_dict
 from yalm_b200.engine.lm import tensor_needs_of
-from yalm_b200.weights import (SafetensorsError, TensorNeed, WeightsError, check_tensors,
+from yalm_b200.weights import (SafetensorsError, WeightsError, check_tensors,
                                load_checkpoint, read_file, write_file, write_model_dir)
 
 

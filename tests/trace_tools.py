@@ -5,7 +5,6 @@ from __future__ import annotations
 import json
 import os
 import subprocess
-import sys
 from typing import Dict, List, Sequence, Tuple
 
 import numpy as np

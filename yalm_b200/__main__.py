@@ -75,7 +75,7 @@ def parse(argv):
 
 def main(argv=None) -> int:
     o = parse(list(sys.argv[1:] if argv is None else argv))
-    from .config import config_from_dict, load_config
+    from .config import load_config
     if o["random_weights"] and not os.path.isfile(os.path.join(o["model"], "config.json")):
         from .engine.lm import LM
         with open(o["random_weights"]) as f:

@@ -26,7 +26,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from .slots import SlotAllocator, SlotError
+from .slots import SlotAllocator
 
 
 @dataclass(frozen=True)

@@ -7,10 +7,9 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Any, Callable, Dict
+from typing import Any, Dict
 
 from .llama import ConfigError, LlamaConfig
-from .spec import ModelSpec
 
 _ARCHITECTURES: Dict[str, Any] = {}
 

@@ -9,7 +9,7 @@ decode steps of the same sequences except ``tokens``.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
 import torch

@@ -17,7 +17,7 @@ decisions can be tested without one:
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import List, Sequence
 
 
 @dataclass

@@ -10,9 +10,7 @@ The reference has no Python interface; its C++ ``main`` is the counterpart
 """
 from __future__ import annotations
 
-import json
 import math
-import os
 import time
 from typing import Any, Dict, List, Optional, Sequence, Union
 
@@ -23,7 +21,7 @@ from ..csrc import ops
 from ..parts import Model, Runtime
 from ..weights import load_checkpoint, random_tensors, write_model_dir
 from .generate import Completion, run_generation
-from .step import Engine, StepError
+from .step import Engine
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}

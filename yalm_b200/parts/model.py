@@ -10,13 +10,12 @@ classifier skipped when no logits are wanted (infer.cu:1172-1176).
 from __future__ import annotations
 
 import dataclasses
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import torch
 
 from ..cache import Cache, CacheNeed
 from ..config import ModelSpec
-from ..csrc import ops
 from ..weights import TensorNeed, check_tensors
 from .base import (BLOCKS, EMBEDDINGS, HEADS, NORMS, ResidualStream, Runtime, make_part)
 
