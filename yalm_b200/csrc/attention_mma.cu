@@ -93,28 +93,6 @@ __device__ __forceinline__ void load_strided_tile(uint32_t base, int rows, int n
                r < n);
 }
 
-// Loads `n` consecutive positions of a cache ring (rows first_row, first_row + 1, ...
-// modulo capacity) into a swizzled tile and zero-fills rows n..rows-1.  Each thread
-// keeps one 16-byte column and steps through the rows, so the row arithmetic is an
-// add and a compare per copy.
-template <int HDP>
-__device__ __forceinline__ void load_ring_tile(uint32_t base, int rows, int n, int hd,
-                                               const __nv_bfloat16* ring, int first_row,
-                                               int capacity) {
-  const int cpr = hd >> 3;
-  const int rstep = FA_THREADS / cpr;                         // rows covered per pass
-  if ((int)threadIdx.x >= rstep * cpr) return;
-  const int ch = threadIdx.x % cpr;
-  int r = threadIdx.x / cpr;
-  int row = (first_row + r) % capacity;
-  const int wrap = rstep % capacity;
-  for (; r < rows; r += rstep) {
-    cp_async16(tile_addr<HDP>(base, r, ch), ring + (size_t)row * hd + ch * 8, r < n);
-    row += wrap;
-    if (row >= capacity) row -= capacity;
-  }
-}
-
 // ----------------------------------------------------------------- prefill
 // grid (query tiles of a sequence, heads, sequences); a block takes 64 query
 // tokens of one head.  scale_log2 = log2(e) / sqrt(hd).
