@@ -161,9 +161,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   constexpr int Q_BYTES = TA_BM * HD * 2;          // one query tile
   constexpr int KV_BYTES = TA_BN * HD * 2;         // one block of K or of V
   constexpr int P_BYTES = TA_BM * TA_BN * 2;
-  constexpr int TMEM_COLS = 2 * TA_BN + 2 * HD <= 256 ? 256 : 512;
+  constexpr int TMEM_COLS = 512;                   // S: 2 tiles x 2 buffers x 64; O: 2 tiles x HD
   extern __shared__ uint8_t ta_smem[];
-  __shared__ __align__(8) uint64_t q_full, s_full[2], p_ready[2], pv_done[2];
+  __shared__ __align__(8) uint64_t q_full, s_full[2][2], p_ready[2], pv_done[2];
   __shared__ __align__(8) uint64_t k_full[TA_KSTAGES], k_empty[TA_KSTAGES];
   __shared__ __align__(8) uint64_t v_full[TA_VSTAGES], v_empty[TA_VSTAGES];
   __shared__ uint32_t tmem_slot;
@@ -204,7 +204,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     abort_flag = 0;
     mbar_init(smem_u32(&q_full), 1);
     for (int x = 0; x < 2; ++x) {
-      mbar_init(smem_u32(&s_full[x]), 1);
+      mbar_init(smem_u32(&s_full[x][0]), 1);
+      mbar_init(smem_u32(&s_full[x][1]), 1);
       mbar_init(smem_u32(&p_ready[x]), TA_BM);
       mbar_init(smem_u32(&pv_done[x]), 1);
     }
@@ -228,9 +229,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_slot;
-  // columns: S of tile A, S of tile B, O of tile A, O of tile B
-  const uint32_t tmem_s[2] = {tmem_base, tmem_base + TA_BN};
-  const uint32_t tmem_o[2] = {tmem_base + 2 * TA_BN, tmem_base + 2 * TA_BN + HD};
+  // columns: two S buffers of tile A, two of tile B, O of tile A, O of tile B
+  const uint32_t tmem_s[2] = {tmem_base, tmem_base + 2 * TA_BN};
+  const uint32_t tmem_o[2] = {tmem_base + 4 * TA_BN, tmem_base + 4 * TA_BN + HD};
   volatile int* abort_p = &abort_flag;
   pdl_launch_dependents();
 
@@ -283,14 +284,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // descriptors: one per operand tile, advanced by constants inside the loops
       const uint64_t q_desc[2] = {ta_desc_k(q_s), ta_desc_k(q_s + Q_BYTES)};
       const uint64_t p_desc[2] = {ta_desc_k(p_s), ta_desc_k(p_s + P_BYTES)};
-      auto issue_s = [&](int x, int stage) {
+      auto issue_s = [&](int x, int stage, int buf) {         // buf: the block's parity for this tile
         const uint64_t k_desc = ta_desc_k(k_s + stage * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          ta_umma(tmem_s[x], q_desc[x] + (uint64_t)(((ks / 4) * (TA_BM * 128) + (ks % 4) * 32) >> 4),
+          ta_umma(tmem_s[x] + buf * TA_BN,
+                  q_desc[x] + (uint64_t)(((ks / 4) * (TA_BM * 128) + (ks % 4) * 32) >> 4),
                   k_desc + (uint64_t)(((ks / 4) * (TA_BN * 128) + (ks % 4) * 32) >> 4), idesc_s,
                   ks > 0 ? 1u : 0u);
-        ta_commit(smem_u32(&s_full[x]));
+        ta_commit(smem_u32(&s_full[x][buf]));
       };
       auto issue_pv = [&](int x, int stage, bool first) {
         const uint64_t v_desc = ta_desc_mn(v_s + stage * KV_BYTES, TA_BN * 128);
@@ -301,19 +303,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                   (first && kk == 0) ? 0u : 1u);
         ta_commit(smem_u32(&pv_done[x]));
       };
+      // S runs two blocks of keys ahead of the softmax: each tile has two S buffers, and
+      // a buffer is free again once the row threads have signalled the block that used it.
       bool ok = mbar_wait(smem_u32(&q_full), 0, abort_p);
-      if (ok && n_it > 0) ok = mbar_wait(smem_u32(&k_full[0]), 0, abort_p);
-      if (ok && n_it > 0) {
+      for (int pre = 0; pre < 2 && pre < n_it && ok; ++pre) {
+        ok = mbar_wait(smem_u32(&k_full[pre]), 0, abort_p);
+        if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int x = 0; x < 2; ++x)
-          if (active(x, kb_lo)) issue_s(x, 0);
-        ta_commit(smem_u32(&k_empty[0]));
+          if (active(x, kb_lo + pre)) issue_s(x, pre, (kb_lo + pre - t_kb0[x]) & 1);
+        ta_commit(smem_u32(&k_empty[pre]));
       }
       for (int it = 0; it < n_it && ok; ++it) {
         const int kb = kb_lo + it;
-        const int sv = it % TA_VSTAGES, sk = (it + 1) % TA_KSTAGES;
-        const bool more = it + 1 < n_it;
+        const int sv = it % TA_VSTAGES, sk = (it + 2) % TA_KSTAGES;
+        const bool more = it + 2 < n_it;
         bool v_here = false, k_here = false;
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
@@ -329,19 +334,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_pv(x, sv, kb == t_kb0[x]);
           }
-          if (more && active(x, kb + 1)) {
+          if (more && active(x, kb + 2)) {
             if (!k_here) {
-              ok = mbar_wait(smem_u32(&k_full[sk]), ((it + 1) / TA_KSTAGES) & 1, abort_p);
+              ok = mbar_wait(smem_u32(&k_full[sk]), ((it + 2) / TA_KSTAGES) & 1, abort_p);
               k_here = true;
               if (!ok) break;
               asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
-            issue_s(x, sk);                                   // overlaps the other tile's softmax
+            issue_s(x, sk, (kb + 2 - t_kb0[x]) & 1);          // into the buffer just read out
           }
         }
         if (!ok) break;
         ta_commit(smem_u32(&v_empty[sv]));                    // V of this block is consumed
-        if (more) ta_commit(smem_u32(&k_empty[sk]));          // and K of the next
+        if (more) ta_commit(smem_u32(&k_empty[sk]));          // and K of the block after next
       }
     }
   } else {
@@ -356,7 +361,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t my_s = (x ? tmem_s[1] : tmem_s[0]) + lane_addr;
     const uint32_t my_o = (x ? tmem_o[1] : tmem_o[0]) + lane_addr;
-    const uint32_t bar_s = smem_u32(x ? &s_full[1] : &s_full[0]);
+    const uint32_t bar_s = smem_u32(x ? &s_full[1][0] : &s_full[0][0]);   // [1] is 8 bytes on
     const uint32_t bar_p = smem_u32(x ? &p_ready[1] : &p_ready[0]);
     const uint32_t bar_pv = smem_u32(x ? &pv_done[1] : &pv_done[0]);
     const uint32_t p_row = p_s + x * P_BYTES + row * 128;
@@ -366,7 +371,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int n_x = my_kb1 - my_kb0;
     for (int it = 0; it < n_x; ++it) {
       const int j0 = (my_kb0 + it) * TA_BN;
-      mbar_wait(bar_s, it & 1, abort_p);
+      mbar_wait(bar_s + 8 * (it & 1), (it >> 1) & 1, abort_p);
       if (x == 0) asm volatile("bar.sync 1, %0;" ::"n"(TA_BM) : "memory");
       else asm volatile("bar.sync 2, %0;" ::"n"(TA_BM) : "memory");
       if (*abort_p) { ok = false; break; }
@@ -374,8 +379,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       float s[TA_BN];
       {
         uint32_t raw[TA_BN];
-        ta_ld32_issue(my_s, raw);                             // both halves in flight, one wait
-        ta_ld32_issue(my_s + 32, raw + 32);
+        const uint32_t s_addr = my_s + (it & 1) * TA_BN;
+        ta_ld32_issue(s_addr, raw);                           // both halves in flight, one wait
+        ta_ld32_issue(s_addr + 32, raw + 32);
         ta_ld_wait32(raw);
         ta_ld_after32(raw + 32);
 #pragma unroll
