@@ -332,6 +332,9 @@ def main():
             pts[f"decode_b{b}_ms"] = r["ms_per_step"]
             bb = decode_bytes(lm, r["contexts"])
             pts[f"decode_b{b}_hbm_frac"] = bb / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"]
+        # the reference's one published figure: 63.8 tokens/s at batch 1 on an RTX 4090
+        # (its README; other hardware, so no vs_baseline for the headline metric)
+        pts["decode_b1_vs_published_63.8"] = pts["decode_b1"] / 63.8
         out["points"] = pts
     print(json.dumps(out))
     return 0
