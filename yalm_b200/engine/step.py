@@ -51,6 +51,7 @@ class Engine:
         self.cache = Cache(needs, n_slots, self.context, self.rt.dtype, self.rt.device)
         self.vocab = model.spec.vocab_size
         self._graphs: Dict[tuple, dict] = {}
+        self._graph_seen: Dict[tuple, int] = {}
         self._dec: Optional[dict] = None
         self.use_graphs = True
 
@@ -149,6 +150,7 @@ class Engine:
                          want_rows=d["arange"][:B], n_want=B, ctx_bound=self._ctx_bucket(past))
 
     CTX_BUCKET = 512
+    GRAPH_AFTER = 3       # a decode shape is captured on its third step
 
     def _ctx_bucket(self, past: Sequence[int]) -> int:
         """The longest sequence after this step, rounded up: launches sized by it
@@ -181,9 +183,15 @@ class Engine:
             g = self._graphs.get(key)
             if g is not None and g["generation"] != self.rt.buffer_generation:
                 g = None                      # a scratch buffer moved since the capture
-            if g is None:
-                # the first step of this shape runs eagerly (every scratch buffer gets
-                # its final size); then the same launches are captured for replays
+            seen = self._graph_seen.get(key, 0) + 1
+            self._graph_seen[key] = seen
+            if g is None and seen < self.GRAPH_AFTER:
+                # a shape that may not last (a batch that is shrinking step by step): not
+                # worth a capture yet
+                self._decode_body(B, temperature, seed)
+            elif g is None:
+                # this step runs eagerly once more (every scratch buffer has its final
+                # size); then the same launches are captured for replays
                 self._decode_body(B, temperature, seed)
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
