@@ -167,6 +167,40 @@ def test_tcgen05_refuses_what_tma_cannot_address(ops):
                     torch.zeros(2, 4, 128, device=DEV), ops.GEMM_SPLIT, status, splits=2)
 
 
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_rotary_kernel_for_prompts_agrees_with_the_general_one(ops, dt):
+    """With 512 tokens or more in one slice the rotary kernel takes four tokens per block.
+    The same input as two slices (the second one zero) goes through the general kernel:
+    rotated queries, step keys and values and the ring rows must agree to the bit.  The
+    prompts lie on top of earlier positions and one of them overruns its ring."""
+    H, G, hd, cap = 6, 2, 64, 100
+    lens, slots, past = [300, 7, 420], [2, 0, 1], [5, 0, 50]
+    inv = plain_inv_freq(hd, 10000.0, None).to(DEV)
+    b = B(lens, slots)
+    N = b.n_tokens
+    g = torch.Generator(device=DEV).manual_seed(4)
+    qkv = torch.randn(N, (H + 2 * G) * hd, device=DEV, generator=g)
+    two = torch.stack([qkv, torch.zeros_like(qkv)])
+    got = []
+    for src, n in ((qkv, 1), (two, 2)):
+        slot_pos = torch.zeros(3, dtype=torch.int32, device=DEV)
+        for s_, p_ in zip(slots, past):
+            slot_pos[s_] = p_
+        kc = torch.full((3, G, cap, hd), 7.0, device=DEV, dtype=dt)
+        vc = torch.full((3, G, cap, hd), 7.0, device=DEV, dtype=dt)
+        q_out = torch.empty(N, H * hd, device=DEV, dtype=dt)
+        kv_step = torch.empty(N, 2, G, hd, device=DEV, dtype=dt)
+        ops.rope_store(src, n, inv, b, q_out, kv_step, kc, vc, slot_pos, H, G, hd, cap)
+        got.append((q_out, kv_step, kc, vc))
+    for a_, b_ in zip(*got):
+        assert torch.equal(a_, b_)
+    # and against the plain rotation: the last token of the longest prompt
+    t = N - 1
+    pos = torch.tensor([past[2] + lens[2] - 1])
+    ref = plain_rope(qkv[t].cpu().view(1, H + 2 * G, hd)[:, :H], pos, inv.cpu())
+    assert (got[0][0][t].float().cpu().view(H, hd) - ref[0]).abs().max() <= (3e-6 if dt == torch.float32 else 3e-2)
+
+
 def _rope_attend(ops, dt, H, G, hd, cap, window, q_lens, slots, n_slots, steps, nsplit_decode):
     """Drives rope_store + attention over several steps and returns the largest
     error against plain_rope + plain_attention on the whole sequences."""

@@ -199,6 +199,42 @@ template <typename T> struct RopeIO<T, 1> {
   static __device__ __forceinline__ void store(T* p, const float* v) { p[0] = from_float<T>(v[0]); }
 };
 
+// Rotation of one thread's pairs (q and k heads only) and the stores that follow.
+template <typename T, int VEC>
+__device__ __forceinline__ void rope_rotate_store(float* a, float* bb, const float* fr, int t, int head,
+                                                  int i, int pos, bool keep, int slot,
+                                                  T* __restrict__ q_out, T* __restrict__ kv_step,
+                                                  T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                                  int H, int G, int hd, int capacity) {
+  const int half = hd >> 1;
+  if (head < H + G) {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const float ang = (float)pos * fr[v];
+      const float c = cosf(ang), s = sinf(ang);
+      const float r0 = a[v] * c - bb[v] * s, r1 = a[v] * s + bb[v] * c;
+      a[v] = r0;
+      bb[v] = r1;
+    }
+  }
+  if (head < H) {
+    T* o = q_out + ((size_t)t * H + head) * hd + i;
+    RopeIO<T, VEC>::store(o, a);
+    RopeIO<T, VEC>::store(o + half, bb);
+    return;
+  }
+  const bool is_v = head >= H + G;
+  const int g = head - H - (is_v ? G : 0);
+  T* o = kv_step + ((size_t)t * 2 * G + (is_v ? G : 0) + g) * hd + i;
+  RopeIO<T, VEC>::store(o, a);
+  RopeIO<T, VEC>::store(o + half, bb);
+  if (keep) {
+    T* c = (is_v ? v_cache : k_cache) + (((size_t)slot * G + g) * capacity + pos % capacity) * hd + i;
+    RopeIO<T, VEC>::store(c, a);
+    RopeIO<T, VEC>::store(c + half, bb);
+  }
+}
+
 template <typename T, int VEC>
 __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
                                   long long partial_stride, const float* __restrict__ inv_freq,
@@ -257,31 +293,60 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
       bb[0] += pp[half];
     }
   }
-  if (head < H + G) {
+  rope_rotate_store<T, VEC>(a, bb, fr, t, head, i, pos, keep, slot, q_out, kv_step, k_cache, v_cache, H, G, hd,
+                            capacity);
+}
+
+// The same for many tokens whose product is a single slice (a prompt): a block takes
+// TPB tokens, and the index chains and the loads of all of them are in flight together.
+template <typename T, int TPB>
+__global__ void rope_store_many_kernel(const float* __restrict__ qkv, const float* __restrict__ inv_freq,
+                                       const int* __restrict__ token_seq, const int* __restrict__ q_start,
+                                       const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
+                                       T* __restrict__ q_out, T* __restrict__ kv_step,
+                                       T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G,
+                                       int hd, int capacity, int write_cache, int heads_per_block,
+                                       int n_tokens) {
+  pdl_launch_dependents();
+  const int half = hd >> 1;
+  const int lanes = half / 4;
+  const int i = (threadIdx.x % lanes) * 4;
+  const int head = blockIdx.y * heads_per_block + threadIdx.x / lanes;
+  const int t0 = blockIdx.x * TPB;
+  int b[TPB], slot[TPB], qs[TPB], qe[TPB];
 #pragma unroll
-    for (int v = 0; v < VEC; ++v) {
-      const float ang = (float)pos * fr[v];
-      const float c = cosf(ang), s = sinf(ang);
-      const float r0 = a[v] * c - bb[v] * s, r1 = a[v] * s + bb[v] * c;
-      a[v] = r0;
-      bb[v] = r1;
-    }
+  for (int k = 0; k < TPB; ++k) b[k] = token_seq[min(t0 + k, n_tokens - 1)];
+#pragma unroll
+  for (int k = 0; k < TPB; ++k) {
+    slot[k] = seq_slot[b[k]];
+    qs[k] = q_start[b[k]];
+    qe[k] = q_start[b[k] + 1];
   }
-  if (head < H) {
-    T* o = q_out + ((size_t)t * H + head) * hd + i;
-    RopeIO<T, VEC>::store(o, a);
-    RopeIO<T, VEC>::store(o + half, bb);
-    return;
+  float fr[4];
+#pragma unroll
+  for (int v = 0; v < 4; ++v) fr[v] = inv_freq[i + v];
+  pdl_wait();
+  if (head >= H + 2 * G) return;
+  const int row_elems = (H + 2 * G) * hd;
+  int past[TPB];
+  float4 x[TPB], y[TPB];
+#pragma unroll
+  for (int k = 0; k < TPB; ++k) {
+    const float* sp = qkv + (size_t)min(t0 + k, n_tokens - 1) * row_elems + head * hd + i;
+    past[k] = slot_pos[slot[k]];
+    x[k] = *reinterpret_cast<const float4*>(sp);
+    y[k] = *reinterpret_cast<const float4*>(sp + half);
   }
-  const bool is_v = head >= H + G;
-  const int g = head - H - (is_v ? G : 0);
-  T* o = kv_step + ((size_t)t * 2 * G + (is_v ? G : 0) + g) * hd + i;
-  RopeIO<T, VEC>::store(o, a);
-  RopeIO<T, VEC>::store(o + half, bb);
-  if (keep) {
-    T* c = (is_v ? v_cache : k_cache) + (((size_t)slot * G + g) * capacity + pos % capacity) * hd + i;
-    RopeIO<T, VEC>::store(c, a);
-    RopeIO<T, VEC>::store(c + half, bb);
+#pragma unroll
+  for (int k = 0; k < TPB; ++k) {
+    const int t = t0 + k;
+    if (t >= n_tokens) break;
+    const int pos = past[k] + (t - qs[k]);
+    const int end = past[k] + (qe[k] - qs[k]);
+    const bool keep = write_cache && pos >= end - capacity;
+    float a[4] = {x[k].x, x[k].y, x[k].z, x[k].w}, bb[4] = {y[k].x, y[k].y, y[k].z, y[k].w};
+    rope_rotate_store<T, 4>(a, bb, fr, t, head, i, pos, keep, slot[k], q_out, kv_step, k_cache, v_cache, H, G,
+                            hd, capacity);
   }
 }
 
@@ -414,6 +479,21 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
   const dim3 grid(n_tokens, (H + 2 * G + hpb - 1) / hpb);
   const int threads = lanes * hpb;
   if (grid.y > 65535 || threads > 1024) return -4;
+  if (vec && n_partials == 1 && n_tokens >= 512) {
+    constexpr int TPB = 4;
+    const dim3 grid4((n_tokens + TPB - 1) / TPB, grid.y);
+    if (dtype == DT_F32)
+      launch_pdl(rope_store_many_kernel<float, TPB>, grid4, dim3(threads), 0, stream, qkv, inv_freq, token_seq,
+                 q_start, seq_slot, slot_pos, (float*)q_out, (float*)kv_step, (float*)k_cache, (float*)v_cache,
+                 H, G, hd, capacity, write_cache, hpb, n_tokens);
+    else
+      launch_pdl(rope_store_many_kernel<__nv_bfloat16, TPB>, grid4, dim3(threads), 0, stream, qkv, inv_freq,
+                 token_seq, q_start, seq_slot, slot_pos, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_step,
+                 (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, G, hd, capacity, write_cache, hpb,
+                 n_tokens);
+    YALM_LAUNCH_CHECK();
+    return 0;
+  }
 #define YALM_ROPE(T, V)                                                                        \
   launch_pdl(rope_store_kernel<T, V>, grid, dim3(threads), 0, stream, qkv, n_partials,         \
              partial_stride, inv_freq, token_seq, q_start, seq_slot, slot_pos, (T*)q_out,      \
