@@ -319,3 +319,24 @@ def test_both_tensor_core_prefill_attentions_inside_the_engine(attention):
     for i, t in enumerate(toks):
         ref = plain_forward(cfg, w, t)
         assert float((lg[i] - ref[-1]).abs().max() / ref.abs().max()) <= TOL["bfloat16"]
+
+
+def test_a_model_stored_in_float16(tmp_path):
+    """float16 storage: the 32-bit path widens the stored values exactly (its logits match
+    the plain model on those values to 32-bit rounding); the bfloat16 path rounds them to
+    bfloat16 and stays inside its tolerance.  Norm weights stay in 32 bits as stored."""
+    from yalm_b200 import LM
+    cfg, seed = CONFIGS["tiny_a"]
+    w = make_weights(cfg, seed)
+    stored = {k: (v if v.dtype == torch.float32 else (v.float() * 1.001).to(torch.float16))
+              for k, v in w.items()}                            # values that bfloat16 cannot hold
+    assert any(v.dtype == torch.float16 and not torch.equal(v.float(), v.to(torch.bfloat16).float())
+               for v in stored.values())
+    write_model(str(tmp_path / "m"), cfg, stored)
+    toks = random_tokens(40, cfg["vocab_size"], 77)
+    ref = plain_forward(cfg, {k: v.float() for k, v in stored.items()}, toks)
+    for dtype in ("float32", "bfloat16"):
+        lm = LM.from_pretrained(str(tmp_path / "m"), dtype=dtype, max_batch=1)
+        s = lm.acquire(1)
+        lg = lm.step([toks], s, [list(range(40))]).cpu()
+        assert float((lg - ref).abs().max() / ref.abs().max()) <= TOL[dtype], dtype

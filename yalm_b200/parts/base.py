@@ -124,7 +124,8 @@ class Runtime:
 
     def matrix(self, t: torch.Tensor, share: bool = False) -> torch.Tensor:
         """A weight matrix in the type it is multiplied in: the compute type,
-        except that a matrix stored in 32 bits stays 32-bit.  ``share``: parts
+        except that a matrix stored in 32 bits stays 32-bit (float16 storage becomes
+        bfloat16 under bfloat16 compute and is widened exactly under 32-bit compute).  ``share``: parts
         that are bound to the same stored tensor (a tied head) get one copy."""
         dt = torch.float32 if (self.dtype == torch.float32 or t.dtype == torch.float32) else self.dtype
         if share:

@@ -1,8 +1,10 @@
 """Weights by tensor name.
 
 ``load_checkpoint`` reads every ``*.safetensors`` file of a model folder and
-normalises storage types: 16-bit floats are kept as bfloat16, a tensor stored
-in 32-bit floats stays 32-bit, integer tables become int32.  ``check_tensors``
+normalises storage types: bfloat16 and 32-bit floats stay as stored, integer
+tables become int32.  float16 also stays as stored until a part binds it: the
+bfloat16 path then keeps it as bfloat16, the 32-bit path widens it exactly (a
+true 32-bit path must not round its inputs).  ``check_tensors``
 compares what a model declares with what a checkpoint holds and reports every
 problem in ONE error: missing tensors, unexpected tensors and wrong shapes
 (the reference stops at the first missing or mis-shaped tensor,
@@ -35,8 +37,6 @@ class TensorNeed:
 
 
 def _normalise(t: torch.Tensor) -> torch.Tensor:
-    if t.dtype in (torch.float16,):
-        return t.to(torch.bfloat16)
     if t.dtype == torch.float64:
         return t.to(torch.float32)
     if t.dtype in (torch.int64, torch.int16, torch.int8, torch.uint8, torch.bool):
