@@ -117,3 +117,14 @@ def test_sharded_folder_and_duplicate_names(tmp_path):
     with pytest.raises(WeightsError, match="no .safetensors"):
         os.makedirs(tmp_path / "empty")
         load_checkpoint(str(tmp_path / "empty"))
+
+
+def test_tensors_an_exporter_may_add_are_no_error():
+    """Rotary frequency buffers, and a copy of the head beside tied embeddings, are not
+    read and not reported; any other extra tensor still is."""
+    cfg = config_from_dict(dict(TINY_B))
+    assert cfg.tie_word_embeddings
+    assert cfg.ignorable_tensor("model.layers.0.self_attn.rotary_emb.inv_freq")
+    assert cfg.ignorable_tensor("lm_head.weight")
+    assert not cfg.ignorable_tensor("model.layers.0.self_attn.q_proj.bias")
+    assert not config_from_dict(dict(TINY_A)).ignorable_tensor("lm_head.weight")

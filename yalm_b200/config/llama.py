@@ -180,6 +180,13 @@ class LlamaConfig:
             d["torch_dtype"] = self.torch_dtype
         return d
 
+    def ignorable_tensor(self, name: str) -> bool:
+        """Checkpoint tensors that this architecture does not read and that are no
+        error: the rotary frequency buffers some exporters save, and a copy of the
+        head when the embeddings are tied."""
+        return name.endswith("rotary_emb.inv_freq") or (self.tie_word_embeddings
+                                                        and name == "lm_head.weight")
+
     # ---- the architecture as a list of parts -----------------------------
     def to_spec(self) -> ModelSpec:
         """Tensor names are the checkpoint's own (the left column of the

@@ -41,7 +41,8 @@ class LM:
         self.spec = config.to_spec()
         self.rt = Runtime(_dtype(dtype), device, gemm=gemm, attention=attention)
         self.model = Model(self.spec, self.rt)
-        self.model.bind(tensors)
+        ignorable = getattr(config, "ignorable_tensor", None)
+        self.model.bind(tensors, ignore_unexpected=[n for n in tensors if ignorable(n)] if ignorable else ())
         context = self.spec.max_positions if not max_context else min(int(max_context),
                                                                      self.spec.max_positions)
         self.engine = Engine(self.model, max_batch, context)
