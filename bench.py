@@ -176,7 +176,7 @@ def time_decode(lm, batch, steps, warmup, seed, sampler=None, lo=64, hi=2048):
     """Device-timed decode steps of a batch with prompt lengths U[lo, hi]."""
     import torch
     from yalm_b200.csrc import ops
-    lens = prompt_lengths(batch, lo, hi, seed)
+    lens = sorted(prompt_lengths(batch, lo, hi, seed), reverse=True)   # rows longest first, as LM.generate orders them
     prompts = random_prompts(lens, lm.config.vocab_size, seed + 1)
     slots, first = prefill_batch(lm, prompts)
     eng = lm.engine

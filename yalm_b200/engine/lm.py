@@ -159,23 +159,34 @@ class _DeviceBackend:
         self.d2h_bytes = 0
 
     def begin(self, prompts, keys):
+        """Prefill and first tokens.  On the device the batch's rows are ordered longest
+        sequence first (the decode attention's grid takes them in row order, and long
+        blocks that start last leave the SMs idle at the end); `rank` maps the caller's
+        order to that one.  All sequences grow alike, so the order holds for the batch's life."""
         eng = self.engine
-        slots = eng.acquire(len(prompts))
+        B = len(prompts)
+        order = sorted(range(B), key=lambda i: -len(prompts[i]))
+        slots = eng.acquire(B)
         try:
             t0 = time.perf_counter()
-            logits = eng.step(prompts, slots, [[len(p) - 1] for p in prompts])
-            B = len(prompts)
+            rows = [prompts[i] for i in order]
+            logits = eng.step(rows, slots, [[len(p) - 1] for p in rows])
             d = eng._decode_buffers()
             # sample the first token of every sequence into the decode token buffer
-            eng.set_decode_batch([0] * B, slots, keys)
+            eng.set_decode_batch([0] * B, slots, [keys[i] for i in order])
             ops.sample(logits, self.temperature, self.seed, d["row_key"][:B], d["seq_slot"][:B],
                        eng.cache.slot_pos, d["tokens"][:B])
-            first = eng.read_decode_tokens(B)
+            sampled = eng.read_decode_tokens(B)
             self.prefill_seconds += time.perf_counter() - t0
         except Exception:
             eng.release(slots)
             raise
-        handle = {"slots": slots, "keys": list(keys), "active": list(range(len(prompts)))}
+        rank = [0] * B
+        for r, i in enumerate(order):
+            rank[i] = r
+        first = [sampled[rank[i]] for i in range(B)]
+        handle = {"slots": slots, "keys": [keys[i] for i in order], "rank": rank,
+                  "active": list(range(B)), "rows": list(range(B)), "perm": order}
         return handle, first
 
     def decode(self, handle, active, tokens):
@@ -185,15 +196,23 @@ class _DeviceBackend:
         t0 = time.perf_counter()
         B = len(active)
         if active != handle["active"]:
-            eng.set_decode_batch(tokens, [handle["slots"][j] for j in active],
-                                 [handle["keys"][j] for j in active])
-            handle["active"] = list(active)
+            rank = handle["rank"]
+            # perm[r]: which entry of `active` sits in device row r; rows[r]: its row at the start
+            perm = sorted(range(B), key=lambda k: rank[active[k]])
+            rows = [rank[active[k]] for k in perm]
+            handle["active"], handle["perm"], handle["rows"] = list(active), perm, rows
+            eng.set_decode_batch([tokens[k] for k in perm], [handle["slots"][r] for r in rows],
+                                 [handle["keys"][r] for r in rows])
             self.h2d_bytes += 12 * B
         else:
-            eng.set_decode_tokens(tokens)
+            perm = handle["perm"]
+            eng.set_decode_tokens([tokens[k] for k in perm])
             self.h2d_bytes += 4 * B
         eng.decode_step(B, self.temperature, self.seed)
-        out = eng.read_decode_tokens(B)
+        sampled = eng.read_decode_tokens(B)
+        out = [0] * B
+        for r, k in enumerate(perm):
+            out[k] = sampled[r]
         self.d2h_bytes += 4 * B
         self.decode_steps += 1
         dt = time.perf_counter() - t0
