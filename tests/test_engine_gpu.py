@@ -340,3 +340,22 @@ def test_a_model_stored_in_float16(tmp_path):
         s = lm.acquire(1)
         lg = lm.step([toks], s, [list(range(40))]).cpu()
         assert float((lg - ref).abs().max() / ref.abs().max()) <= TOL[dtype], dtype
+
+
+def test_a_packed_one_file_model(tmp_path):
+    """A folder packed into one file (configuration in the metadata) loads to the same model."""
+    from yalm_b200 import LM
+    from yalm_b200.weights import pack_model_dir
+    cfg, seed = CONFIGS["tiny_b"]
+    w = make_weights(cfg, seed)
+    write_model(str(tmp_path / "m"), cfg, w)
+    pack_model_dir(str(tmp_path / "m"), str(tmp_path / "one.safetensors"))
+    toks = random_tokens(30, cfg["vocab_size"], 5)
+    got = []
+    for path in (str(tmp_path / "m"), str(tmp_path / "one.safetensors")):
+        lm = LM.from_pretrained(path, dtype="float32", max_batch=1)
+        s = lm.acquire(1)
+        got.append(lm.step([toks], s, [list(range(30))]).cpu())
+    assert torch.equal(got[0], got[1])
+    ref = plain_forward(cfg, w, toks)
+    assert float((got[1] - ref).abs().max() / ref.abs().max()) <= TOL["float32"]

@@ -128,3 +128,21 @@ def test_tensors_an_exporter_may_add_are_no_error():
     assert cfg.ignorable_tensor("lm_head.weight")
     assert not cfg.ignorable_tensor("model.layers.0.self_attn.q_proj.bias")
     assert not config_from_dict(dict(TINY_A)).ignorable_tensor("lm_head.weight")
+
+
+def test_packed_single_file_round_trip(tmp_path):
+    """A model folder packed into one file: same tensors in their stored types, the
+    configuration in the metadata; a plain safetensors file without it is refused."""
+    from yalm_b200.weights import load_packed, pack_model_dir, read_metadata
+    from yalm_b200.weights.pack import CONFIG_KEY, main
+    cfg = config_from_dict(dict(TINY_B))
+    write_model_dir(str(tmp_path / "m"), cfg, tensor_needs_of(cfg), seed=4, dtype=torch.bfloat16)
+    assert main([str(tmp_path / "m"), str(tmp_path / "one.safetensors")]) == 0
+    d, t = load_packed(str(tmp_path / "one.safetensors"))
+    assert config_from_dict(d) == config_from_dict(dict(cfg.to_dict(), torch_dtype="bfloat16"))
+    ref = load_checkpoint(str(tmp_path / "m"))
+    assert set(t) == set(ref) and all(t[k].dtype == ref[k].dtype and torch.equal(t[k], ref[k]) for k in ref)
+    assert CONFIG_KEY in read_metadata(str(tmp_path / "one.safetensors"))
+    with pytest.raises(WeightsError, match="no configuration"):
+        load_packed(str(tmp_path / "m" / "model.safetensors"))
+    pack_model_dir(str(tmp_path / "m"), str(tmp_path / "two.safetensors"))

@@ -1,7 +1,7 @@
 """Command line in the manner of the reference's ``main`` (main.cpp:17-40,
 334-470): a checkpoint, then one-letter options that each take a value.
 
-    python -m yalm_b200 <model_dir> [options]
+    python -m yalm_b200 <model_dir | packed.safetensors> [options]
 
     -h            this help
     -d cuda       device (only cuda: there is no CPU path)
@@ -75,7 +75,6 @@ def parse(argv):
 
 def main(argv=None) -> int:
     o = parse(list(sys.argv[1:] if argv is None else argv))
-    from .config import load_config
     if o["random_weights"] and not os.path.isfile(os.path.join(o["model"], "config.json")):
         from .engine.lm import LM
         with open(o["random_weights"]) as f:
@@ -83,11 +82,12 @@ def main(argv=None) -> int:
         print(f"wrote a random model to {o['model']}")
     from .engine.lm import LM
     from .tokenizer import Tokenizer
-    cfg = load_config(o["model"])
     lm = LM.from_pretrained(o["model"], dtype=o["dtype"], max_context=o["context"] or None,
                             max_batch=o["max_batch"])
     spec = lm.spec
-    tok = Tokenizer.from_dir(o["model"], spec.vocab_size, spec.bos_token_id, spec.stop_token_ids)
+    # a packed one-file model keeps its tokenizer.json beside it
+    tok_dir = os.path.dirname(os.path.abspath(o["model"])) if os.path.isfile(o["model"]) else o["model"]
+    tok = Tokenizer.from_dir(tok_dir, spec.vocab_size, spec.bos_token_id, spec.stop_token_ids)
     seed = o["seed"] if o["seed"] is not None else int(time.time() * 1000)     # as the reference seeds
     print(f"model: {spec.architecture}, {len(spec.layers)} layers, context {lm.context}, "
           f"{lm.model.weight_bytes() / 1e9:.2f} GB weights, {lm.engine.cache.bytes() / 1e9:.2f} GB cache")

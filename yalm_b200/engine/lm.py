@@ -11,6 +11,7 @@ The reference has no Python interface; its C++ ``main`` is the counterpart
 from __future__ import annotations
 
 import math
+import os
 import time
 from typing import Any, Dict, List, Optional, Sequence, Union
 
@@ -19,7 +20,7 @@ import torch
 from ..config import config_from_dict, load_config
 from ..csrc import ops
 from ..parts import Model, Runtime
-from ..weights import load_checkpoint, random_tensors, write_model_dir
+from ..weights import load_checkpoint, load_packed, random_tensors, write_model_dir
 from .generate import Completion, run_generation
 from .step import Engine
 
@@ -51,6 +52,11 @@ class LM:
     # -- construction ----------------------------------------------------------
     @classmethod
     def from_pretrained(cls, model_dir: str, **kw) -> "LM":
+        """A model folder (config.json and safetensors files), or one packed file
+        (``python -m yalm_b200.weights.pack``) with the configuration in its metadata."""
+        if os.path.isfile(model_dir):
+            config, tensors = load_packed(model_dir)
+            return cls(config_from_dict(config), tensors, **kw)
         config = load_config(model_dir)
         return cls(config, load_checkpoint(model_dir), **kw)
 

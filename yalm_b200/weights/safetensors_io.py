@@ -81,6 +81,23 @@ def read_header(path: str) -> Tuple[Dict[str, dict], int, int]:
     return entries, data_start, size
 
 
+def read_metadata(path: str) -> Dict[str, str]:
+    """The string-to-string ``__metadata__`` of a file ({} if it has none)."""
+    with open(path, "rb") as f:
+        head = f.read(8)
+        if len(head) < 8:
+            raise SafetensorsError(f"{path}: truncated (no header length)")
+        (n,) = struct.unpack("<Q", head)
+        if n <= 0 or 8 + n > os.path.getsize(path):
+            raise SafetensorsError(f"{path}: header length {n} exceeds the file size")
+        try:
+            header = json.loads(f.read(n).decode("utf-8"))
+        except (UnicodeDecodeError, json.JSONDecodeError) as e:
+            raise SafetensorsError(f"{path}: header is not JSON ({e})") from None
+    meta = header.get("__metadata__") or {}
+    return {str(k): str(v) for k, v in meta.items()}
+
+
 def read_file(path: str) -> Dict[str, torch.Tensor]:
     """All tensors of one file, in their stored dtype, as CPU tensors that
     share the file's memory map (copy-on-write: nothing is written back)."""
