@@ -32,3 +32,15 @@ def test_more_than_one_gpu_is_refused(capsys):
     sys.argv = ["bench.py", "--impl", "reference"]
     assert bench.main() == 0
     assert '"unavailable"' in capsys.readouterr().out
+
+
+def test_peaks_come_from_the_measured_file_when_it_is_there(tmp_path, monkeypatch):
+    import json
+    monkeypatch.setattr(bench, "ROOT", str(tmp_path))
+    assert bench.peaks()["source"] == "fallback"
+    (tmp_path / "MEASURED_PEAKS.json").write_text(json.dumps(
+        {"gpu": "B200", "peaks": {"hbm_gbs": 6900.5, "bf16_tflops": 1610, "bf16_tflops_sustained": 1400.0}}))
+    pk = bench.peaks()
+    assert pk == {"hbm_gbs": 6900.5, "bf16_tflops": 1610.0, "bf16_tflops_sustained": 1400.0, "source": "measured"}
+    (tmp_path / "MEASURED_PEAKS.json").write_text("{not json")
+    assert bench.peaks()["source"] == "fallback"
