@@ -39,8 +39,10 @@ def plan_splits(M: int, N: int, K: int, sm_count: int = 148) -> int:
     fit an SM, and a short K slice leaves little to fetch after the hand-over.  So the
     slices fill the 2 x SMs block slots (measured on 7B shapes at batch 8: 6 slices
     instead of 3 for q/k/v, 9 instead of 5 for the down projection: 2.5-3 us per layer).
-    With more tokens the partial sums (written once, read once, 4 bytes each) weigh in,
-    and the count trades idle SMs against that traffic."""
+    That holds up to 64 tokens even where the partial sums (written once, read once, 4
+    bytes each) come to a third of the weights' bytes (batch 32: 159 -> 149 us per layer,
+    batch 64: 194 -> 180); only when they would exceed the weights does the count trade
+    idle SMs against that traffic instead."""
     bt = _token_tile(M)
     tiles = -(-N // 128) * -(-M // bt)
     nkb = -(-K // 64)
@@ -48,7 +50,7 @@ def plan_splits(M: int, N: int, K: int, sm_count: int = 148) -> int:
     s = min(2 * sm_count // max(1, tiles), nkb // 4)
     while s > 1 and not _valid_splits(nkb, s):
         s -= 1
-    if s > 1 and 2.0 * s * M * N * 4.0 <= 0.10 * weight_bytes:
+    if s > 1 and 2.0 * s * M * N * 4.0 <= weight_bytes:
         return s
     best, best_cost = 1, None
     for s in (1, 2, 3, 4, 5, 6, 8, 10, 12, 16):
