@@ -402,7 +402,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   const int nh = min(FD_ROWS, R - hchunk * FD_ROWS);
   const int t = blockIdx.z, part = blockIdx.x;
   const int slot = seq_slot[t];           // written by a host copy, never by a kernel: safe early
-  pdl_wait();
+  // Positions are written by the advance kernel alone, and that kernel lets nothing start
+  // before it has ended: they too may be read while the previous kernel still runs.
   const int pos = slot_pos[slot];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int nkeys = pos - lo + 1;
@@ -429,19 +430,28 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     warp_load_ring_tile<HDP>(dst, n, hd, kc, first, capacity, lane);
     warp_load_ring_tile<HDP>(dst + TILE, n, hd, vc, first, capacity, lane);
   };
-  load_tile<HDP>(q_s, FD_ROWS, hd, q, [&](int r) -> const __nv_bfloat16* {
-    return r < nh ? q + ((size_t)t * H + h0 + r) * hd : nullptr;
-  });
-  cp_async_commit();
-  // FD_STAGES - 1 units are requested before the first is used
+  // FD_STAGES - 1 units are requested before the first is used.  All rows but the newest
+  // position's are older than this step: their units are requested before the wait; the
+  // unit that holds the newest key (the sequence's last) and the queries come after it.
+  const int u_new = (nkeys - 1) / FD_UNIT;
   int u_next = u0 + warp;
 #pragma unroll
   for (int i = 0; i < FD_STAGES - 1; ++i) {
-    if (u_next < u1) load_unit(u_next, i);
+    if (u_next < u1 && u_next != u_new) load_unit(u_next, i);
     u_next += FA_WARPS;
     cp_async_commit();
   }
-  cp_async_wait<FD_STAGES - 1>();                            // this thread's share of Q
+  pdl_wait();
+  load_tile<HDP>(q_s, FD_ROWS, hd, q, [&](int r) -> const __nv_bfloat16* {
+    return r < nh ? q + ((size_t)t * H + h0 + r) * hd : nullptr;
+  });
+#pragma unroll
+  for (int i = 0; i < FD_STAGES - 1; ++i) {
+    const int u = u0 + warp + i * FA_WARPS;
+    if (u < u1 && u == u_new) load_unit(u, i);
+  }
+  cp_async_commit();
+  cp_async_wait<0>();                                        // this thread's share of Q and of the first units
   __syncthreads();                                           // everybody's
   // Q^T as the B operand: per 16-wide step two registers for heads 0-7, two for 8-15
   uint32_t qf[NKS][4];

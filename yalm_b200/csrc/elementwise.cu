@@ -258,9 +258,9 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
   float fr[VEC];
 #pragma unroll
   for (int v = 0; v < VEC; ++v) fr[v] = inv_freq[i + v];
+  const int past = slot_pos[slot];                        // written by the advance kernel alone (see there)
   pdl_wait();
   if (head >= H + 2 * G) return;
-  const int past = slot_pos[slot];
   const int pos = past + (t - qs);
   const int end = past + (q_end - qs);                     // positions after this step
   const bool keep = write_cache && pos >= end - capacity;
@@ -325,15 +325,16 @@ __global__ void rope_store_many_kernel(const float* __restrict__ qkv, const floa
   float fr[4];
 #pragma unroll
   for (int v = 0; v < 4; ++v) fr[v] = inv_freq[i + v];
+  int past[TPB];
+#pragma unroll
+  for (int k = 0; k < TPB; ++k) past[k] = slot_pos[slot[k]];
   pdl_wait();
   if (head >= H + 2 * G) return;
   const int row_elems = (H + 2 * G) * hd;
-  int past[TPB];
   float4 x[TPB], y[TPB];
 #pragma unroll
   for (int k = 0; k < TPB; ++k) {
     const float* sp = qkv + (size_t)min(t0 + k, n_tokens - 1) * row_elems + head * hd + i;
-    past[k] = slot_pos[slot[k]];
     x[k] = *reinterpret_cast<const float4*>(sp);
     y[k] = *reinterpret_cast<const float4*>(sp + half);
   }
@@ -352,7 +353,8 @@ __global__ void rope_store_many_kernel(const float* __restrict__ qkv, const floa
 
 __global__ void advance_kernel(const int* __restrict__ q_start, const int* __restrict__ seq_slot,
                                int* __restrict__ slot_pos, int n_seqs) {
-  pdl_launch_dependents();
+  // No early start for what follows: this is the one kernel that writes the positions, and
+  // other kernels read them before their own dependency wait.
   pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b < n_seqs) slot_pos[seq_slot[b]] += q_start[b + 1] - q_start[b];
