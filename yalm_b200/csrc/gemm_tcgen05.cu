@@ -548,7 +548,26 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     if (lane == 0 && pair < n_tiles) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
-      pdl_wait();
+      // weights do not depend on the previous kernel: the first tile's first stages of them
+      // are requested before the wait, the tokens of those stages after it
+      const int pre = nkb < Cfg::STAGES ? nkb : Cfg::STAGES;
+      {
+        int feat0, tok0;
+        tile_of(pair, feat0, tok0);
+        const int my_feat = feat0 + (int)rank * TC_BM;
+        for (int kb = 0; kb < pre; ++kb) {
+          const uint32_t stage = tiles_smem + kb * Cfg::STAGE_BYTES;
+          const uint32_t bar0 = map_to_rank(smem_u32(&full_bar[kb]), 0);
+          if (leader) mbar_expect_tx(smem_u32(&full_bar[kb]), 2 * Cfg::STAGE_BYTES);
+          tma_load_2d_pair(stage, &map_w, kb * TC_BK, my_feat, bar0);
+          if (NACC == 2) tma_load_2d_pair(stage + Cfg::W_BYTES, &map_w, kb * TC_BK, n_out + my_feat, bar0);
+        }
+        pdl_wait();
+        const int my_tok = tok0 + (int)rank * (BT / 2);
+        for (int kb = 0; kb < pre; ++kb)
+          tma_load_2d_pair(tiles_smem + kb * Cfg::STAGE_BYTES + NACC * Cfg::W_BYTES, &map_a, kb * TC_BK, my_tok,
+                           map_to_rank(smem_u32(&full_bar[kb]), 0));
+      }
       int it = 0;
       bool ok = true;
       for (int t = pair; t < n_tiles && ok; t += n_pairs) {
@@ -557,6 +576,7 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const int my_feat = feat0 + (int)rank * TC_BM;
         const int my_tok = tok0 + (int)rank * (BT / 2);
         for (int kb = 0; kb < nkb; ++kb, ++it) {
+          if (it < pre) continue;                             // requested above
           const int s = it % Cfg::STAGES;
           const uint32_t phase = (it / Cfg::STAGES) & 1;
           ok = mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u, abort_p);
