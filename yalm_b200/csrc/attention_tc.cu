@@ -371,10 +371,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int n_x = my_kb1 - my_kb0;
     for (int it = 0; it < n_x; ++it) {
       const int j0 = (my_kb0 + it) * TA_BN;
-      mbar_wait(bar_s + 8 * (it & 1), (it >> 1) & 1, abort_p);
-      if (x == 0) asm volatile("bar.sync 1, %0;" ::"n"(TA_BM) : "memory");
-      else asm volatile("bar.sync 2, %0;" ::"n"(TA_BM) : "memory");
-      if (*abort_p) { ok = false; break; }
+      // every wait is decided per warp (the loads from tensor memory below are warp-wide)
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_s + 8 * (it & 1), (it >> 1) & 1, abort_p));
+      if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float s[TA_BN];
       {
@@ -407,10 +406,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const bool any_raise = __any_sync(0xffffffffu, raise);
       if (it > 0) {
         // the previous product has read P and written O
-        mbar_wait(bar_pv, (it - 1) & 1, abort_p);
-        if (x == 0) asm volatile("bar.sync 1, %0;" ::"n"(TA_BM) : "memory");
-        else asm volatile("bar.sync 2, %0;" ::"n"(TA_BM) : "memory");
-        if (*abort_p) { ok = false; break; }
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, (it - 1) & 1, abort_p));
+        if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (any_raise) {                                      // uniform over the warp
 #pragma unroll 1
@@ -450,12 +447,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(bar_p);
     }
-    if (ok && n_x > 0) {
-      mbar_wait(bar_pv, (n_x - 1) & 1, abort_p);
-      if (x == 0) asm volatile("bar.sync 1, %0;" ::"n"(TA_BM) : "memory");
-      else asm volatile("bar.sync 2, %0;" ::"n"(TA_BM) : "memory");
-      ok = !*abort_p;
-    }
+    if (ok && n_x > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, (n_x - 1) & 1, abort_p));
     if (ok && n_x > 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = 1.0f / l_run;
