@@ -10,7 +10,8 @@ import torch
 
 from helpers import CONFIGS, TOL, make_weights, random_tokens, write_model
 from plain_model import plain_forward, plain_generate_greedy, plain_perplexity
-from trace_tools import Trace, add_batches, add_tail, add_whole, compare, run_in_process, run_trace_run
+from trace_tools import (Trace, add_batches, add_tail, add_whole, compare, forced_decode, run_in_process,
+                         run_trace_run)
 
 pytestmark = pytest.mark.gpu
 
@@ -158,18 +159,30 @@ def test_greedy_generation_through_the_entry_point():
         assert [c.tokens for c in lm.generate(prompts, 12, 0.0, stop_ids=stop)] == want
 
 
-def test_greedy_generation_in_bfloat16_picks_near_maximal_tokens():
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_e"])
+def test_decode_fast_path_logits_across_graph_keys(name, dtype, monkeypatch):
+    """The path generation runs (device token buffer, captured graphs, sampler in the
+    graph) with the trace's own tokens forced: its logits against the plain model at
+    every step.  Context buckets of 32 positions and a capture on the second step make
+    the sequences cross many graph keys, replay graphs planned for a shorter context,
+    and shrink the batch when a request ends; the same schedule without graphs must
+    give the same bits."""
     from yalm_b200 import LM
     from yalm_b200.config import config_from_dict
-    cfg, seed = CONFIGS["tiny_a"]
-    w = make_weights(cfg, seed)
-    prompts = [random_tokens(n, cfg["vocab_size"], 70 + n) for n in (5, 17, 31)]
-    lm = LM(config_from_dict(cfg), dict(w), dtype="bfloat16", max_batch=4)
-    for p, c in zip(prompts, lm.generate(prompts, max_new_tokens=10, temperature=0.0, ignore_eos=True)):
-        logits = plain_forward(cfg, w, p + c.tokens)
-        for i, t in enumerate(c.tokens):
-            row = logits[len(p) - 1 + i]
-            assert float(row.max() - row[t]) <= 2 * TOL["bfloat16"] * float(logits.abs().max())
+    from yalm_b200.engine.step import Engine
+    monkeypatch.setattr(Engine, "CTX_BUCKET", 32)
+    monkeypatch.setattr(Engine, "GRAPH_AFTER", 2)
+    cfg, w, reqs, refs, _ = setup(name)
+    prompts = dict(REQUESTS[name]["prompts"])
+    ids = REQUESTS[name]["batches"][0]
+    sub = {r: reqs[r] for r in ids}
+    lm = LM(config_from_dict(cfg), dict(w), dtype=dtype, max_batch=len(ids))
+    fast = forced_decode(lm, sub, prompts, refs, TOL[dtype])
+    assert len(lm.engine._graphs) >= (2 if name == "tiny_e" else 1)    # tiny_e crosses a bucket
+    lm.engine.use_graphs = False
+    assert torch.equal(fast, forced_decode(lm, sub, prompts, refs, TOL[dtype]))
+    assert lm.engine.cache.slots.free_count == lm.max_batch
 
 
 def test_temperature_sampling_is_per_request_and_reproducible():

@@ -136,3 +136,45 @@ def compare(tr: Trace, got: Dict[int, torch.Tensor], refs: Dict[str, torch.Tenso
             assert err <= tol, (f"first wrong row: step {step}, request {rid}, position {pos} "
                                 f"(row {i} of {len(rows)}): error {err:.3e} > {tol:.1e}")
     return worst
+
+
+def forced_decode(lm, reqs, prompts, refs, tol, order=None):
+    """Prefill of all prompts in one step, then decode steps through the device-side
+    path with the trace's own next tokens forced; a request leaves the batch when its
+    tokens run out.  Returns every logits row it compared, in order."""
+    eng = lm.engine
+    ids = list(order or reqs)
+    slots = dict(zip(ids, lm.acquire(len(ids))))
+    scale = {r: float(refs[r].abs().max()) for r in ids}
+    seen = []
+
+    def check(rid, pos, row):
+        err = float((row - refs[rid][pos]).abs().max()) / scale[rid]
+        assert err <= tol, f"request {rid}, position {pos}: error {err:.3e} > {tol:.1e}"
+        seen.append(row)
+
+    lg = lm.step([reqs[r][:prompts[r]] for r in ids], [slots[r] for r in ids],
+                 [[prompts[r] - 1] for r in ids]).float().cpu()
+    for i, r in enumerate(ids):
+        check(r, prompts[r] - 1, lg[i])
+    at = dict(prompts)
+    live = [r for r in ids if at[r] < len(reqs[r])]
+    current = None
+    while live:
+        if live != current:
+            eng.set_decode_batch([reqs[r][at[r]] for r in live], [slots[r] for r in live],
+                                 list(range(len(live))))
+            current = list(live)
+        else:
+            eng.set_decode_tokens([reqs[r][at[r]] for r in live])
+        eng.decode_step(len(live), 0.0, 0)
+        lg = eng.decode_logits(len(live)).float().cpu()
+        # the sampler runs inside the same step: greedy picks the row's maximum
+        assert eng.read_decode_tokens(len(live)) == lg.argmax(-1).tolist()
+        for i, r in enumerate(live):
+            check(r, at[r], lg[i])
+            at[r] += 1
+        live = [r for r in live if at[r] < len(reqs[r])]
+    lm.release(list(slots.values()))
+    lm.rt.check_status()
+    return torch.stack(seen)
