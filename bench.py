@@ -271,6 +271,58 @@ def time_prefill(lm, T, reps, pk):
     return out
 
 
+def reference_arm(args):
+    """The unmodified reference on the same layer sizes (see baseline/run_reference.py).
+    It serves one sequence at a time, so the batch's requests run one after another and
+    its decode rate is its batch-1 rate; the prompt has the batch's mean length."""
+    if args.gpus != 1:
+        print(f"bench.py: the reference runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import run_reference
+    base_cfg, context, default_batch, lo, hi = WORKLOADS[args.workload]
+    batch = args.batch or default_batch
+    layers = args.layers or base_cfg["num_hidden_layers"]
+    cfg = dict(base_cfg, num_hidden_layers=layers)
+    cfg = {k: v for k, v in cfg.items() if v is not None}
+    lens = prompt_lengths(batch, lo, hi, 1)                   # the lengths the other arm draws
+    prompt_len = int(round(sum(lens) / len(lens)))
+    W = max(3, args.warmup)
+    try:
+        r = run_reference.run(cfg, context, prompt_len, args.steps, W, sampler=ClockSampler())
+    except run_reference.Unavailable as e:
+        print(json.dumps({"impl": "reference", "unavailable": str(e).replace("\n", " ")[:400]}))
+        return 0
+    out = {
+        "metric": f"decode tokens/s at batch {batch} ({args.workload} shapes, context {context})",
+        "value": r["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": W,
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16", "data": "synthetic", "impl": "reference",
+        "config": {
+            "model": f"{args.workload}-shapes-random", "layers": layers,
+            "layers_of_config": base_cfg["num_hidden_layers"], "hidden": base_cfg["hidden_size"],
+            "ffn": base_cfg["intermediate_size"], "heads": base_cfg["num_attention_heads"],
+            "kv_heads": base_cfg["num_key_value_heads"], "head_dim": base_cfg["head_dim"],
+            "vocab": base_cfg["vocab_size"],
+            "global_batch": f"{batch} requests served one after another (the reference takes one "
+                            f"sequence per forward)",
+            "seq_len": context, "prompt_len": r["prompt_len"], "parallelism": "single-gpu",
+            "timing": "host clock between tokens arriving on the program's output",
+            "weights": "random N(0,0.02) float16, norms 1, packed by the reference's convert.py",
+            "reported_decode_tok_s": r.get("reported_decode_tok_s"),
+            "reported_throughput": r["reported"].get("throughput"),
+            "reported_bandwidth_gbs": r["reported"].get("bandwidth"),
+        },
+        # the program is end to end by construction: the token id goes down as a kernel
+        # argument and the logits come back through mapped host memory every step
+        "e2e": {"value": r["tok_s"], "unit": "tokens/s", "h2d_bytes_per_step": 4,
+                "d2h_bytes_per_step": 4 * base_cfg["vocab_size"], "steps": args.steps},
+        "clocks": r["clocks"],
+    }
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -290,10 +342,7 @@ def main():
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference has no setup.py or pyproject.toml: pip cannot install it "
-                          "offline, and it ships no sm_100 build of its CUDA kernels"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
