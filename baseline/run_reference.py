@@ -120,6 +120,8 @@ def run(cfg: dict, context: int, prompt_len: int, steps: int, warmup: int, sampl
     """Packs a random model of ``cfg`` and times ``steps`` decode steps of the reference
     after ``warmup`` untimed ones, on a prompt of ``prompt_len`` tokens."""
     import torch
+    if not torch.cuda.is_available():
+        raise Unavailable("no CUDA device here: the reference's build/main -d cuda cannot run")
     exe = ensure_built()
     D, F, V, L = (cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"],
                   cfg["num_hidden_layers"])

@@ -3,16 +3,23 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
-Default run: Mistral-7B-v0.2 layer sizes with random weights (bfloat16), a batch
-of 8 sequences with prompt lengths drawn uniformly from [64, 2048] inside a
-context of 4096.  A "step" is one decode step of the batch.  One JSON line:
+Default run: Mistral-7B-v0.2 layer sizes with random float16 weights (--dtype
+bfloat16 for the other 16-bit type), a batch of 8 sequences with prompt lengths
+drawn uniformly from [64, 2048] inside a context of 4096.  A "step" is one decode
+step of the batch.  One JSON line:
 
-  value        decoded tokens per second, K steps timed on the device (CUDA events)
+  value        decoded tokens per second: K steps timed on the device (CUDA events)
+               after W untimed ones that follow the prefill directly
   e2e          the same through LM.generate: every step the host's tokens go down
                from pinned memory and the sampled tokens come back
-  prefill      one prompt of 2,048 tokens: tokens/s, ms, fraction of the bf16 peak
+  prefill      one prompt of 2,048 tokens: tokens/s, ms, fraction of the 16-bit peak
   roofline     bytes the decode step must read (weights once + live cache) / time
-  points       decode tokens/s at batch 1 and 64
+  points       decode tokens/s at batch 1, 8 and 64 in the steady state (after 40
+               untimed steps: the first steps after a prefill run with the SM clock
+               still held down by the power cap), the first 32 steps after a batch
+               of 2,048-token prompts, and the two other workloads
+               (Llama-3.2-1B sizes at batch 64, Mistral-7B-v0.1 sizes at batch 8
+               decoding past its window of 4096)
   clocks       SM clocks and throttle reasons sampled during the timed region
   gpu_launches kernels of this library launched inside the timed region
 
@@ -57,6 +64,7 @@ WORKLOADS = {
     "llama-3.2-1b": (LLAMA32_1B, 8192, 64, 16, 1024),
     "mistral-7b-v0.1": (MISTRAL_7B_V01, 8192, 8, 6000, 6000),     # decodes past the 4096 window
 }
+STEADY = 40          # untimed steps before a steady-state point is timed
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -197,7 +205,8 @@ def prefill_batch(lm, prompts, group=8):
 
 
 def time_decode(lm, batch, steps, warmup, seed, sampler=None, lo=64, hi=2048):
-    """Device-timed decode steps of a batch with prompt lengths U[lo, hi]."""
+    """Device-timed decode steps of a batch with prompt lengths U[lo, hi]; `warmup`
+    untimed steps come first, directly after the prefill."""
     import torch
     from yalm_b200.csrc import ops
     lens = sorted(prompt_lengths(batch, lo, hi, seed), reverse=True)   # rows longest first, as LM.generate orders them
@@ -205,7 +214,7 @@ def time_decode(lm, batch, steps, warmup, seed, sampler=None, lo=64, hi=2048):
     slots, first = prefill_batch(lm, prompts)
     eng = lm.engine
     eng.set_decode_batch(first, slots, list(range(batch)))
-    for _ in range(max(warmup, 3)):
+    for _ in range(warmup):
         eng.decode_step(batch, 0.0, 0)
     torch.cuda.synchronize()
     ctx0 = [eng.cache.host_pos[s] for s in slots]
@@ -331,6 +340,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mistral-7b-v0.2", choices=sorted(WORKLOADS),
                     help="layer sizes, context and prompt lengths (default: the headline one)")
+    ap.add_argument("--dtype", default="float16", choices=["float16", "bfloat16"],
+                    help="the 16-bit type of weights, activations and cache (default: the "
+                         "baseline's float16)")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1/64 and prefill")
@@ -355,26 +367,25 @@ def main():
     args.layers = args.layers or base_cfg["num_hidden_layers"]
     headline = args.workload == "mistral-7b-v0.2"
     cfg = dict(base_cfg, num_hidden_layers=args.layers)
-    t0 = time.time()
-    lm = LM.from_random(cfg, seed=0, dtype="bfloat16", std=0.02, norm_jitter=0.0,
-                        max_context=context,
-                        max_batch=max(64, args.batch) if headline and not (args.no_points or args.prefill_only)
-                        else args.batch)
-    torch.cuda.synchronize()
-    print(f"[bench] model ready in {time.time() - t0:.0f} s "
-          f"({lm.model.weight_bytes() / 1e9:.1f} GB weights, {lm.engine.cache.bytes() / 1e9:.1f} GB cache)",
-          file=sys.stderr, flush=True)
+    points_wanted = headline and not (args.no_points or args.prefill_only)
 
-    if args.no_graphs:
-        lm.engine.use_graphs = False
+    def build(config, ctx, max_batch):
+        t0 = time.time()
+        lm = LM.from_random(config, seed=0, dtype=args.dtype, std=0.02, norm_jitter=0.0,
+                            max_context=ctx, max_batch=max_batch)
+        torch.cuda.synchronize()
+        print(f"[bench] model ready in {time.time() - t0:.0f} s "
+              f"({lm.model.weight_bytes() / 1e9:.1f} GB weights, {lm.engine.cache.bytes() / 1e9:.1f} GB cache)",
+              file=sys.stderr, flush=True)
+        if args.no_graphs:
+            lm.engine.use_graphs = False
+        return lm
+
+    lm = build(cfg, context, max(64, args.batch) if points_wanted else args.batch)
     if args.prefill_only:
         print(json.dumps({"prefill": time_prefill(lm, 2048, 1, pk), "layers": args.layers}))
         return 0
-    # Decode steps right after a prefill run with the SM clocks still held down by the power
-    # cap (the first ~35 steps of a batch-8 run are up to 19 % slower and recover in plateaus);
-    # at least 40 untimed steps let the timed ones see the steady state.  The number used is
-    # the one reported.
-    W = max(40, args.warmup) if not (args.no_points and args.no_e2e) else max(3, args.warmup)
+    W = max(3, args.warmup)
     main_run = time_decode(lm, args.batch, args.steps, W, seed=1, sampler=ClockSampler(), lo=lo, hi=hi)
     by = decode_bytes(lm, main_run["contexts"])
     achieved = by / (main_run["ms_per_step"] / 1e3) / 1e9
@@ -383,7 +394,8 @@ def main():
         "metric": f"decode tokens/s at batch {args.batch} ({args.workload} shapes, context {context})",
         "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": W, "ms_per_step": main_run["ms_per_step"], "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": {"float16": "fp16", "bfloat16": "bf16"}[args.dtype], "data": "synthetic",
         "impl": "ours",
         "config": {
             "model": f"{args.workload}-shapes-random", "layers": args.layers,
@@ -403,18 +415,34 @@ def main():
                      "frac": achieved / pk["hbm_gbs"], "bytes_per_step": by,
                      "of": pk["source"]},
     }
-    if not args.no_points and headline:
+    if points_wanted:
         out["prefill"] = time_prefill(lm, 2048, 5, pk)
-        pts = {}
-        for b in (1, 64):
-            r = time_decode(lm, b, max(16, args.steps // 2), W, seed=10 + b)
-            pts[f"decode_b{b}"] = r["tok_s"]
-            pts[f"decode_b{b}_ms"] = r["ms_per_step"]
-            bb = decode_bytes(lm, r["contexts"])
-            pts[f"decode_b{b}_hbm_frac"] = bb / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"]
+        pts = {"steady_warmup_steps": STEADY}
+
+        def point(name, model, b, steps, warmup, seed, lo_, hi_):
+            r = time_decode(model, b, steps, warmup, seed=seed, lo=lo_, hi=hi_)
+            pts[name] = r["tok_s"]
+            pts[name + "_ms"] = r["ms_per_step"]
+            pts[name + "_hbm_frac"] = (decode_bytes(model, r["contexts"]) / (r["ms_per_step"] / 1e3)
+                                       / 1e9 / pk["hbm_gbs"])
+
+        half = max(16, args.steps // 2)
+        point("decode_b1", lm, 1, half, STEADY, 11, lo, hi)
+        point("decode_b8", lm, 8, half, STEADY, 1, lo, hi)
+        point("decode_b64", lm, 64, half, STEADY, 74, lo, hi)
+        # what a short generate() call sees: the 32 steps right after a batch of long prompts
+        point("decode_b8_first32_after_2048_token_prompts", lm, 8, 32, 0, 5, 2048, 2048)
         # the reference's one published figure: 63.8 tokens/s at batch 1 on an RTX 4090
         # (its README; other hardware, so no vs_baseline for the headline metric)
         pts["decode_b1_vs_published_63.8"] = pts["decode_b1"] / 63.8
+        del lm
+        torch.cuda.empty_cache()
+        for name, key in (("llama-3.2-1b", "llama_3.2_1b_b64"), ("mistral-7b-v0.1", "mistral_7b_v0.1_b8")):
+            c2, ctx2, b2, lo2, hi2 = WORKLOADS[name]
+            other = build(dict(c2), ctx2, b2)
+            point(key, other, b2, half, STEADY, 21, lo2, hi2)
+            del other
+            torch.cuda.empty_cache()
         out["points"] = pts
     print(json.dumps(out))
     return 0

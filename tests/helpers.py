@@ -70,8 +70,10 @@ CONFIGS = {"tiny_a": (TINY_A, 0), "tiny_b": (TINY_B, 1), "tiny_c": (TINY_C, 2), 
 # Tolerances on logits, relative to the largest reference logit in magnitude.
 # float32: FMA chains in another order than the CPU's.  bfloat16: activations are
 # rounded to 8 bits of mantissa between kernels (2^-9 each, a few dozen roundings
-# deep), weights are identical on both sides.
-TOL = {"float32": 1e-5, "bfloat16": 2e-2}
+# deep), weights are identical on both sides.  float16: the same roundings with 11 bits
+# of mantissa, so an eighth of bfloat16's bound.
+TOL = {"float32": 1e-5, "bfloat16": 2e-2, "float16": 2.5e-3}
+DTYPES = ["float32", "bfloat16", "float16"]
 
 
 def make_weights(cfg: dict, seed: int, dtype=torch.bfloat16, std: float = 0.05,

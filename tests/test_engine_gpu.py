@@ -1,14 +1,14 @@
 """The engine against the plain implementation on a GPU: every request alone
 and whole; with the last 32 tokens one by one; in batches of unequal lengths
 whose shorter requests end earlier, batch after batch so that slots are used
-again; in 32-bit and in bfloat16; through bin/trace_run and through the Python
+again; in 32-bit, bfloat16 and float16; through bin/trace_run and through the Python
 entry point."""
 import os
 
 import pytest
 import torch
 
-from helpers import CONFIGS, TOL, make_weights, random_tokens, write_model
+from helpers import CONFIGS, DTYPES, TOL, make_weights, random_tokens, write_model
 from plain_model import plain_forward, plain_generate_greedy, plain_perplexity
 from trace_tools import (Trace, add_batches, add_tail, add_whole, compare, forced_decode, run_in_process,
                          run_trace_run)
@@ -57,7 +57,7 @@ def setup(name):
     return _cache[name]
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
 def test_trace_run_matches_plain_model(name, dtype, tmp_path):
     cfg, w, reqs, refs, tr = setup(name)
@@ -66,7 +66,7 @@ def test_trace_run_matches_plain_model(name, dtype, tmp_path):
     compare(tr, got, refs, cfg["vocab_size"], TOL[dtype])
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e"])
 def test_step_function_matches_plain_model(name, dtype):
     from yalm_b200 import LM
@@ -96,7 +96,7 @@ def test_the_two_ways_of_cutting_agree_beyond_the_plain_models_tolerance():
                 seen[key] = g[i]
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding_past_the_window(dtype):
     """300 tokens decoded one by one through a ring of 32 rows."""
     from yalm_b200 import LM
@@ -116,7 +116,7 @@ def test_long_decoding_past_the_window(dtype):
     assert worst <= TOL[dtype], worst
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_the_first_tokens_of_a_sequence(dtype):
     """A prompt of one token, then positions 1, 2, 3 alone; and steps that want nothing."""
     from yalm_b200 import LM
@@ -159,7 +159,7 @@ def test_greedy_generation_through_the_entry_point():
         assert [c.tokens for c in lm.generate(prompts, 12, 0.0, stop_ids=stop)] == want
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_e"])
 def test_decode_fast_path_logits_across_graph_keys(name, dtype, monkeypatch):
     """The path generation runs (device token buffer, captured graphs, sampler in the
@@ -298,7 +298,7 @@ def test_command_line_completion_and_perplexity(tmp_path):
     assert abs(ppl - plain_perplexity(cfg, w, list(range(3, 40)))[0]) / ppl < 1e-3
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_a_prompt_cut_into_steps_on_a_full_ring(dtype):
     """Several tokens at once on top of a ring that already wrapped (not a
     schedule of the generation loop, but the step function takes it): the ring
@@ -317,8 +317,9 @@ def test_a_prompt_cut_into_steps_on_a_full_ring(dtype):
     assert err <= TOL[dtype], err
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 @pytest.mark.parametrize("attention", ["auto", "mma"])
-def test_both_tensor_core_prefill_attentions_inside_the_engine(attention):
+def test_both_tensor_core_prefill_attentions_inside_the_engine(attention, dtype):
     """Whole prompts go through the TMEM attention kernel by default; attention="mma" keeps
     them on the mma.sync kernel, which otherwise only sees prompts cut into steps."""
     from yalm_b200 import LM
@@ -326,18 +327,19 @@ def test_both_tensor_core_prefill_attentions_inside_the_engine(attention):
     cfg, seed = CONFIGS["tiny_e"]
     w = make_weights(cfg, seed)
     toks = [random_tokens(n, cfg["vocab_size"], 300 + n) for n in (390, 7, 129)]
-    lm = LM(config_from_dict(cfg), dict(w), dtype="bfloat16", max_batch=3, attention=attention)
+    lm = LM(config_from_dict(cfg), dict(w), dtype=dtype, max_batch=3, attention=attention)
     s = lm.acquire(3)
     lg = lm.step(toks, s, [[len(t) - 1] for t in toks]).cpu()
     for i, t in enumerate(toks):
         ref = plain_forward(cfg, w, t)
-        assert float((lg[i] - ref[-1]).abs().max() / ref.abs().max()) <= TOL["bfloat16"]
+        assert float((lg[i] - ref[-1]).abs().max() / ref.abs().max()) <= TOL[dtype]
 
 
 def test_a_model_stored_in_float16(tmp_path):
     """float16 storage: the 32-bit path widens the stored values exactly (its logits match
-    the plain model on those values to 32-bit rounding); the bfloat16 path rounds them to
-    bfloat16 and stays inside its tolerance.  Norm weights stay in 32 bits as stored."""
+    the plain model on those values to 32-bit rounding); the float16 path keeps them as
+    stored; the bfloat16 path rounds them to bfloat16 and stays inside its tolerance.
+    Norm weights stay in 32 bits as stored."""
     from yalm_b200 import LM
     cfg, seed = CONFIGS["tiny_a"]
     w = make_weights(cfg, seed)
@@ -348,8 +350,10 @@ def test_a_model_stored_in_float16(tmp_path):
     write_model(str(tmp_path / "m"), cfg, stored)
     toks = random_tokens(40, cfg["vocab_size"], 77)
     ref = plain_forward(cfg, {k: v.float() for k, v in stored.items()}, toks)
-    for dtype in ("float32", "bfloat16"):
+    for dtype in DTYPES:
         lm = LM.from_pretrained(str(tmp_path / "m"), dtype=dtype, max_batch=1)
+        if dtype == "float16":
+            assert torch.equal(lm.model.head.weight.cpu(), stored["lm_head.weight"])
         s = lm.acquire(1)
         lg = lm.step([toks], s, [list(range(40))]).cpu()
         assert float((lg - ref).abs().max() / ref.abs().max()) <= TOL[dtype], dtype

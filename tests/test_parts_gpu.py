@@ -11,6 +11,8 @@ from plain_model import (plain_attention, plain_block, plain_embedding, plain_fo
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
+# bounds of the 16-bit checks are stated for bfloat16; float16 keeps three more bits
+SCALE = {torch.bfloat16: 1.0, torch.float16: 0.125}
 
 
 def _rt(dtype):
@@ -23,7 +25,7 @@ def _prefill_batch(n):
     return build_batch([[0] * n], [0], [0], [[]], DEV)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_norm_part(dtype):
     from yalm_b200.parts import NORMS, ResidualStream
     rt = _rt(dtype)
@@ -34,11 +36,11 @@ def test_norm_part(dtype):
     x = torch.randn(9, 200, device=DEV)
     h = norm(ResidualStream(rt, x.clone()))
     ref = plain_rmsnorm(x.cpu(), w, 1e-4)
-    tol = 2e-6 if dtype == torch.float32 else 2 ** -8
+    tol = 2e-6 if dtype == torch.float32 else 2 ** -8 * SCALE[dtype]
     assert h.dtype == dtype and (h.float().cpu() - ref).abs().max() <= tol * ref.abs().max()
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_feed_forward_part(dtype):
     from yalm_b200.parts import FEED_FORWARDS, ResidualStream
     rt = _rt(dtype)
@@ -52,11 +54,11 @@ def test_feed_forward_part(dtype):
         ffn.forward(h.to(DEV), _prefill_batch(n), stream)
         got = stream.resolve().cpu()
         ref = 1.0 + plain_swiglu(h.float(), w["gate"], w["up"], w["down"])
-        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        tol = 1e-5 if dtype == torch.float32 else 1e-2 * SCALE[dtype]
         assert (got - ref).abs().max() <= tol * ref.abs().max(), n
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("window", [None, 20])
 def test_attention_part_with_its_position_encoding(dtype, window):
     from yalm_b200.cache import Cache
@@ -87,16 +89,16 @@ def test_attention_part_with_its_position_encoding(dtype, window):
     k = plain_rope((hf @ w["k"].float().T).view(T, G, hd), pos, inv)
     v = (hf @ w["v"].float().T).view(T, G, hd)
     ref = plain_attention(q, k, v, window).reshape(T, H * hd) @ w["o"].float().T
-    tol = 1e-5 if dtype == torch.float32 else 1.5e-2
+    tol = 1e-5 if dtype == torch.float32 else 1.5e-2 * SCALE[dtype]
     assert (got - ref).abs().max() <= tol * ref.abs().max()
     # the ring holds the last `capacity` rotated keys at row pos % capacity
     cap = cache.view(0).capacity
     p = T - 1
     assert (cache.view(0).k[0, 1, p % cap].float().cpu() - k[p, 1]).abs().max() <= (
-        1e-5 if dtype == torch.float32 else 2e-2)
+        1e-5 if dtype == torch.float32 else 2e-2 * SCALE[dtype])
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_block_embedding_and_head(dtype):
     from yalm_b200.cache import Cache
     from yalm_b200.config import config_from_dict
@@ -121,7 +123,7 @@ def test_block_embedding_and_head(dtype):
     block.forward(stream, batch, cache.view(0))
     ref = plain_block(plain_embedding(w["model.embed_tokens.weight"], toks), cfg, w, 1,
                       torch.arange(50))
-    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    tol = 1e-5 if dtype == torch.float32 else 1e-2 * SCALE[dtype]
     got = stream.resolve().cpu()
     assert (got - ref).abs().max() <= tol * ref.abs().max()
     head = HEADS["linear_head"](spec.head.params, rt)

@@ -45,7 +45,7 @@ def test_a_random_configuration_matches_the_plain_model(seed):
     w = make_weights(cfg, 100 + seed)
     toks = [random_tokens(n + 6, cfg["vocab_size"], 7 * seed + i) for i, n in enumerate(lens)]
     refs = [plain_forward(cfg, w, t) for t in toks]
-    for dtype in ("float32", "bfloat16"):
+    for dtype in ("float32", "bfloat16", "float16"):
         lm = LM(config_from_dict(cfg), dict(w), dtype=dtype, max_batch=len(lens), max_context=512)
         s = lm.acquire(len(lens))
         worst = 0.0

@@ -21,7 +21,7 @@ their dependency wait, and a stale read would show here.
 import pytest
 import torch
 
-from helpers import TOL, make_weights, random_tokens
+from helpers import DTYPES, TOL, make_weights, random_tokens
 from plain_model import plain_forward
 from trace_tools import Trace, add_tail, add_whole, compare, forced_decode, run_in_process
 
@@ -73,7 +73,7 @@ def make_lm(cfg, w, dtype, max_batch):
     return LM(config_from_dict(cfg), dict(w), dtype=dtype, max_context=CONTEXT, max_batch=max_batch)
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["mistral_7b", "llama_1b"])
 def test_whole_and_last_32_one_by_one(name, dtype):
     cfg, w, reqs, refs, _ = setup(name)
@@ -86,7 +86,7 @@ def test_whole_and_last_32_one_by_one(name, dtype):
     assert int(lm.rt.status.item()) == 0
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["mistral_7b", "llama_1b"])
 def test_decode_path_with_graphs_and_dependent_launch(name, dtype):
     from yalm_b200.csrc import ops

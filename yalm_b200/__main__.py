@@ -16,7 +16,7 @@
   and beyond the reference:
     --tokens 1,2,3        prompt as token ids (works without tokenizer.json); several
                           prompts separated by ';' run as a batch
-    --dtype bfloat16|float32      --seed N      --max-batch N
+    --dtype bfloat16|float16|float32      --seed N      --max-batch N
     --random-weights CONFIG.json  write <model_dir> (config.json, model.safetensors) from a
                                   configuration and --seed first, if it does not exist
 """

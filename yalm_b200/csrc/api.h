@@ -1,7 +1,8 @@
 // C interface of the sm_100a kernel library.  Every function launches on the
 // given stream and returns 0, a cudaError_t of the launch, or a negative code
 // for arguments it refuses (a size the kernel does not take).  Pointers are
-// device pointers unless said otherwise.  dtype codes: 0 = float32, 1 = bfloat16.
+// device pointers unless said otherwise.  dtype codes: 0 = float32, 1 = bfloat16,
+// 2 = float16.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -42,22 +43,24 @@ int yalm_attention_decode(const void* q, const void* k_cache, const void* v_cach
                           int G, int hd, int capacity, int window, int chunk, int max_context,
                           cudaStream_t stream);
 
-// bfloat16 attention on tensor cores (attention_mma.cu): head sizes in steps of 16 up to 128
+// 16-bit attention on tensor cores (attention_mma.cu; dtype 1 or 2): head sizes in steps of
+// 16 up to 128
 int yalm_attention_prefill_mma(const void* q, const void* kv_step, const void* k_cache,
                                const void* v_cache, const int* q_start, const int* seq_slot,
-                               const int* slot_pos, void* out, int n_seqs, int max_q_len, int H,
-                               int G, int hd, int capacity, int window, cudaStream_t stream);
+                               const int* slot_pos, void* out, int dtype, int n_seqs,
+                               int max_q_len, int H, int G, int hd, int capacity, int window,
+                               cudaStream_t stream);
 int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                               const int* seq_slot, const int* slot_pos, void* out, float* part_o,
-                              float* part_ml, int* counters, int* status, int n_seqs, int H, int G,
-                              int hd, int capacity, int window, int max_context,
+                              float* part_ml, int* counters, int* status, int dtype, int n_seqs,
+                              int H, int G, int hd, int capacity, int window, int max_context,
                               int chunks_per_block, cudaStream_t stream);
 
-// bfloat16 prefill attention on tcgen05 (attention_tc.cu): sequences that start at their
-// first token, head size 64 or 128
+// 16-bit prefill attention on tcgen05 (attention_tc.cu; dtype 1 or 2): sequences that start
+// at their first token, head size 64 or 128
 int yalm_attention_prefill_tc(const void* q, const void* kv_step, const int* q_start, void* out,
-                              int n_tokens, int n_seqs, int max_q_len, int H, int G, int hd,
-                              int window, int* status, cudaStream_t stream);
+                              int dtype, int n_tokens, int n_seqs, int max_q_len, int H, int G,
+                              int hd, int window, int* status, cudaStream_t stream);
 
 int yalm_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* out,
                    int out_dtype, int M, int N, int K, int accumulate, cudaStream_t stream);
@@ -68,20 +71,21 @@ int yalm_sample(const float* logits, int n_rows, int vocab, float temperature,
 
 float yalm_uniform01(unsigned long long seed, unsigned key, unsigned counter);
 
-// tcgen05 / TMA matrix product (bfloat16 operands, 32-bit accumulation in TMEM):
+// tcgen05 / TMA matrix product (operands of ab_dtype 1 or 2, 32-bit accumulation in TMEM;
+// out_dtype is 0 or ab_dtype):
 //   mode 0: out[M,N]  = A W^T             (out_dtype 0 or 1)
 //   mode 1: out[M,N] += A W^T             (out float32: the residual stream)
 //   mode 2: out[M,N/2] = silu(A Wg^T) * (A Wu^T), W = [Wg; Wu] with N rows in all
 //   mode 3: out[s][M,N] = partial products of `splits` slices of K (float32 scratch)
 // status: a device int that receives ERR_WAIT_TIMEOUT if a bounded wait gave up.
-int yalm_gemm_tc(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
-                 int mode, int splits, int* status, cudaStream_t stream);
+int yalm_gemm_tc(const void* A, const void* W, int ab_dtype, void* out, int out_dtype, int M,
+                 int N, int K, int mode, int splits, int* status, cudaStream_t stream);
 // 0 if the driver's tensor-map encoder was found (host-side set-up of yalm_gemm_tc).
 int yalm_gemm_tc_available(void);
 
 // Two-SM (cta_group::2) variant for many tokens: mode 0 store, 1 add, 2 silu(gate)*up.
-int yalm_gemm_2sm(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
-                  int mode, int* status, cudaStream_t stream);
+int yalm_gemm_2sm(const void* A, const void* W, int ab_dtype, void* out, int out_dtype, int M,
+                  int N, int K, int mode, int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

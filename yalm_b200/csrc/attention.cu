@@ -1,5 +1,5 @@
 // Causal grouped-query attention over the cache, one query token per block
-// column, for prefill and decode alike, in 32-bit arithmetic on bfloat16 or
+// column, for prefill and decode alike, in 32-bit arithmetic on bfloat16, float16 or
 // 32-bit storage.
 //
 // The reference computes the same thing for one token of one sequence with
@@ -44,6 +44,23 @@ template <> struct Vec8<__nv_bfloat16> {
   static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
     unpack(load_raw(p), f);
   }
+};
+template <> struct Vec8<__half> {
+  typedef uint4 Raw;
+  static __device__ __forceinline__ Raw zero() { return make_uint4(0u, 0u, 0u, 0u); }
+  static __device__ __forceinline__ Raw load_raw(const __half* p) {
+    return *reinterpret_cast<const uint4*>(p);
+  }
+  static __device__ __forceinline__ void unpack(const Raw& u, float* f) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 v = __half22float2(h[i]);
+      f[2 * i] = v.x;
+      f[2 * i + 1] = v.y;
+    }
+  }
+  static __device__ __forceinline__ void load(const __half* p, float* f) { unpack(load_raw(p), f); }
 };
 template <> struct Vec8<float> {
   struct Raw { float4 a, b; };
@@ -581,6 +598,11 @@ extern "C" int yalm_attention(const void* q, const void* kv_step, const void* k_
     return launch_attention<float>(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot,
                                    slot_pos, out, part_o, part_ml, n_tokens, H, G, hd, capacity,
                                    window, nsplit, stream);
+  if (dtype == DT_F16)
+    return launch_attention<__half>(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot,
+                                    slot_pos, out, part_o, part_ml, n_tokens, H, G, hd, capacity,
+                                    window, nsplit, stream);
+  if (dtype != DT_BF16) return -3;
   return launch_attention<__nv_bfloat16>(q, kv_step, k_cache, v_cache, token_seq, q_start,
                                          seq_slot, slot_pos, out, part_o, part_ml, n_tokens, H, G,
                                          hd, capacity, window, nsplit, stream);
@@ -639,7 +661,9 @@ extern "C" int yalm_attention_decode(const void* q, const void* k_cache, const v
     else YALM_DEC_CASE(T, 32);                         \
   } while (0)
   if (dtype == DT_F32) YALM_DEC_T(float);
-  else YALM_DEC_T(__nv_bfloat16);
+  else if (dtype == DT_F16) YALM_DEC_T(__half);
+  else if (dtype == DT_BF16) YALM_DEC_T(__nv_bfloat16);
+  else return -3;
 #undef YALM_DEC_T
 #undef YALM_DEC_CASE
   YALM_LAUNCH_CHECK();
@@ -664,7 +688,11 @@ extern "C" int yalm_attention_decode(const void* q, const void* k_cache, const v
 //    request is refused with -7 and nothing is launched.
 //  * The first call on a device looks up the array's device address
 //    (cudaGetSymbolAddress, with that device current) and remembers it; make
-//    that first call outside any stream capture.
+//    that first call outside any stream capture.  The address is kept per
+//    device in a plain host table: `stream` must belong to the device that is
+//    current at the call (the array used is the current device's), and when
+//    several host threads make the first call together each may do the look-up
+//    and store the same value, which is harmless.
 //  * All calls share the one array, and it keeps whatever the last call left.
 //    Nothing in it has to start at zero: every slice that is read was written
 //    by the same call (an empty slice writes max = -inf, sum = 0).  Two calls
@@ -689,7 +717,10 @@ extern "C" int yalm_attention_no_alloc(const void* q, const void* kv_step, const
                                        int H, int G, int hd, int capacity, int window, int nsplit,
                                        cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (nsplit < 1 || H <= 0 || hd <= 0) return -4;
+  // the same refusals, in the same order, as yalm_attention; then the capacity
+  if (hd % 8 != 0 || hd > 256 || hd <= 0) return -2;
+  if (G <= 0 || H <= 0 || H % G != 0) return -3;
+  if (nsplit < 1 || nsplit > 65535) return -4;
   const size_t need = (size_t)n_tokens * H * nsplit * ((size_t)hd + 2);
   if (nsplit > 1 && need > yalm::NO_ALLOC_SCRATCH_FLOATS) return -7;
   int dev = -1;

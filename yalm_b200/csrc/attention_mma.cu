@@ -1,10 +1,10 @@
-// Tensor-core attention for bfloat16: prefill (many query tokens per
+// Tensor-core attention for bfloat16 and float16: prefill (many query tokens per
 // sequence) and decode (one query token per sequence).
 //
 // Same mathematics as attention.cu (and as the reference's attn_dot /
 // attn_softmax / att_mix, infer.cu:339-523): scores (q.k)/sqrt(hd) over the
 // visible keys, max-subtracted softmax in 32-bit, weighted sum of values.  Here
-// Q.K^T and P.V run as m16n8k16 bfloat16 tiles with 32-bit accumulators
+// Q.K^T and P.V run as m16n8k16 16-bit tiles with 32-bit accumulators
 // (mma.sync); keys and values are brought into shared memory with cp.async in a
 // 16-byte-chunk XOR swizzle so that ldmatrix is free of bank conflicts; the
 // softmax is the online form (running max and sum per row), so no score matrix
@@ -14,6 +14,8 @@
 // (kv_step [N, 2, G, hd]) when j >= past, else in the cache ring at row
 // j % capacity -- the same rule as attention.cu.
 #include <cuda_bf16.h>
+
+#include <type_traits>
 
 #include "api.h"
 #include "common.cuh"
@@ -27,12 +29,21 @@ constexpr int FP_THREADS = FP_WARPS * 32;        // prefill blocks
 constexpr int FA_BM = FP_WARPS * 16;             // query rows per prefill block (16 per warp)
 constexpr int FA_BN = 64;                        // keys per block iteration
 
-__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, const uint32_t* b) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+template <typename T16>
+__device__ __forceinline__ void mma_16(float* c, const uint32_t* a, const uint32_t* b) {
+  if constexpr (std::is_same<T16, __half>::value) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+  }
 }
 __device__ __forceinline__ void ldsm_x4(uint32_t* r, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -52,12 +63,8 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 
-// A tile of rows x HDP bfloat16 in shared memory; HDP is a multiple of 64, so a
+// A tile of rows x HDP 16-bit elements in shared memory; HDP is a multiple of 64, so a
 // row is a multiple of 128 bytes and the 16-byte chunk index can be XORed with
 // (row & 7) without leaving the row.
 template <int HDP>
@@ -67,13 +74,13 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk)
 
 // Loads `rows` rows of hd elements each into a swizzled tile.  row_ptr(r) gives the
 // global address of row r, or nullptr for a row that is to be zero.
-template <int HDP, int NT = FA_THREADS, typename RowPtr>
+template <int HDP, int NT = FA_THREADS, typename T16, typename RowPtr>
 __device__ __forceinline__ void load_tile(uint32_t base, int rows, int hd,
-                                          const __nv_bfloat16* valid_ptr, RowPtr row_ptr) {
+                                          const T16* valid_ptr, RowPtr row_ptr) {
   const int cpr = hd >> 3;                                    // 16-byte chunks per row
   for (int idx = threadIdx.x; idx < rows * cpr; idx += NT) {
     const int r = idx / cpr, ch = idx - r * cpr;
-    const __nv_bfloat16* p = row_ptr(r);
+    const T16* p = row_ptr(r);
     // a zero-filled chunk still names an address: give it one that exists
     cp_async16(tile_addr<HDP>(base, r, ch), p ? p + ch * 8 : valid_ptr, p != nullptr);
   }
@@ -81,9 +88,9 @@ __device__ __forceinline__ void load_tile(uint32_t base, int rows, int hd,
 
 // Loads `n` rows that lie `stride` elements apart in global memory (rows of this
 // step's own buffers) and zero-fills rows n..rows-1; one 16-byte column per thread.
-template <int HDP, int NT>
+template <int HDP, int NT, typename T16>
 __device__ __forceinline__ void load_strided_tile(uint32_t base, int rows, int n, int hd,
-                                                  const __nv_bfloat16* first, size_t stride) {
+                                                  const T16* first, size_t stride) {
   const int cpr = hd >> 3;
   const int rstep = NT / cpr;
   if ((int)threadIdx.x >= rstep * cpr) return;
@@ -96,13 +103,13 @@ __device__ __forceinline__ void load_strided_tile(uint32_t base, int rows, int n
 // ----------------------------------------------------------------- prefill
 // grid (query tiles of a sequence, heads, sequences); a block takes 64 query
 // tokens of one head.  scale_log2 = log2(e) / sqrt(hd).
-template <int HDP>
+template <int HDP, typename T16>
 __global__ void __launch_bounds__(FP_THREADS, 2)
-attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv_step,
-                        const __nv_bfloat16* __restrict__ k_cache,
-                        const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ q_start,
+attn_prefill_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ kv_step,
+                        const T16* __restrict__ k_cache,
+                        const T16* __restrict__ v_cache, const int* __restrict__ q_start,
                         const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
-                        __nv_bfloat16* __restrict__ out, int H, int G, int hd, int capacity,
+                        T16* __restrict__ out, int H, int G, int hd, int capacity,
                         int window, float scale_log2) {
   constexpr int NKS = HDP / 16, NOT = HDP / 8;
   extern __shared__ __align__(128) uint8_t fa_smem[];
@@ -132,26 +139,26 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int kb0 = k_begin / FA_BN, kb1 = (k_end + FA_BN - 1) / FA_BN;
 
   const size_t step_row = (size_t)2 * G * hd;
-  const __nv_bfloat16* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
-  const __nv_bfloat16* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
+  const T16* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
+  const T16* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
   auto load_kv = [&](int kb, int stage) {
     const int j0 = kb * FA_BN;
     const uint32_t kd = k_s0 + stage * FA_BN * HDP * 2, vd = v_s0 + stage * FA_BN * HDP * 2;
     if (j0 >= past) {
       // the whole block comes from this step's keys and values: rows a fixed stride apart
       const int n = min(FA_BN, k_end - j0);
-      const __nv_bfloat16* k0 = kv_step + (size_t)(qs + j0 - past) * step_row + (size_t)g * hd;
+      const T16* k0 = kv_step + (size_t)(qs + j0 - past) * step_row + (size_t)g * hd;
       load_strided_tile<HDP, FP_THREADS>(kd, FA_BN, n, hd, k0, step_row);
       load_strided_tile<HDP, FP_THREADS>(vd, FA_BN, n, hd, k0 + (size_t)G * hd, step_row);
       return;
     }
-    load_tile<HDP, FP_THREADS>(kd, FA_BN, hd, q, [&](int r) -> const __nv_bfloat16* {
+    load_tile<HDP, FP_THREADS>(kd, FA_BN, hd, q, [&](int r) -> const T16* {
       const int j = j0 + r;
       if (j >= k_end) return nullptr;
       return j >= past ? kv_step + (size_t)(qs + j - past) * step_row + (size_t)g * hd
                        : kc + (size_t)(j % capacity) * hd;
     });
-    load_tile<HDP, FP_THREADS>(vd, FA_BN, hd, q, [&](int r) -> const __nv_bfloat16* {
+    load_tile<HDP, FP_THREADS>(vd, FA_BN, hd, q, [&](int r) -> const T16* {
       const int j = j0 + r;
       if (j >= k_end) return nullptr;
       return j >= past ? kv_step + (size_t)(qs + j - past) * step_row + (size_t)(G + g) * hd
@@ -203,8 +210,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             uint32_t kf[4];
             const int row = half * 32 + np * 16 + (lane & 7) + ((lane >> 4) << 3);
             ldsm_x4(kf, tile_addr<HDP>(k_s, row, ks * 2 + ((lane >> 3) & 1)));
-            mma_bf16(s[2 * np], qf, kf);
-            mma_bf16(s[2 * np + 1], qf, kf + 2);
+            mma_16<T16>(s[2 * np], qf, kf);
+            mma_16<T16>(s[2 * np + 1], qf, kf + 2);
           }
         }
       }
@@ -250,8 +257,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
           p[j] = mr > -INFINITY ? exp2f(s[i][j] - mr) : 0.f;
           l_add[j >> 1] += p[j];
         }
-        pf[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
-        pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+        pf[i >> 1][(i & 1) * 2 + 0] = pack2<T16>(p[0], p[1]);
+        pf[i >> 1][(i & 1) * 2 + 1] = pack2<T16>(p[2], p[3]);
       }
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
@@ -272,8 +279,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             uint32_t vf[4];
             const int row = half * 32 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
             ldsm_x4_t(vf, tile_addr<HDP>(v_s, row, np * 2 + (lane >> 4)));
-            mma_bf16(o[2 * np], pf[kk], vf);
-            mma_bf16(o[2 * np + 1], pf[kk], vf + 2);
+            mma_16<T16>(o[2 * np], pf[kk], vf);
+            mma_16<T16>(o[2 * np + 1], pf[kk], vf + 2);
           }
         }
       }
@@ -293,12 +300,12 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int row = warp * 16 + gid + r * 8;
     if (row < rows) {
       const float inv = 1.0f / l_run[r];
-      __nv_bfloat16* op = out + ((size_t)(qs + m0 + row) * H + h) * hd;
+      T16* op = out + ((size_t)(qs + m0 + row) * H + h) * hd;
 #pragma unroll
       for (int i = 0; i < NOT; ++i) {
         if (i < n_ot) {
           *reinterpret_cast<uint32_t*>(op + i * 8 + tig * 2) =
-              pack_bf16(o[i][r * 2] * inv, o[i][r * 2 + 1] * inv);
+              pack2<T16>(o[i][r * 2] * inv, o[i][r * 2 + 1] * inv);
         }
       }
     }
@@ -346,16 +353,16 @@ __device__ __forceinline__ float ex2_approx(float x) {       // 2^x; 2^-inf = 0
 // zero-fills rows n and up.  Lane l takes rows (l & 7) + 8 rb and the 16-byte
 // columns (l >> 3) + 4 j: its row's swizzle is then one constant, and a full unit
 // that does not wrap needs an add and an exclusive-or per copy.
-template <int HDP>
+template <int HDP, typename T16>
 __device__ __forceinline__ void warp_load_ring_tile(uint32_t base, int n, int hd,
-                                                    const __nv_bfloat16* ring, int first_row,
+                                                    const T16* ring, int first_row,
                                                     int capacity, int lane) {
   const int r7 = lane & 7, cg = lane >> 3;
   const int cpr = hd >> 3;
   const uint32_t s_lane = base + r7 * (HDP * 2) + ((cg ^ (r7 & 3)) << 4);
   const uint32_t x_lane = (uint32_t)(r7 >> 2) << 6;
   if (n == FD_UNIT && first_row + FD_UNIT <= capacity) {
-    const __nv_bfloat16* g = ring + (size_t)(first_row + r7) * hd + cg * 8;
+    const T16* g = ring + (size_t)(first_row + r7) * hd + cg * 8;
 #pragma unroll
     for (int rb = 0; rb < FD_UNIT / 8; ++rb) {
 #pragma unroll
@@ -369,7 +376,7 @@ __device__ __forceinline__ void warp_load_ring_tile(uint32_t base, int n, int hd
 #pragma unroll 1
   for (int rb = 0; rb < FD_UNIT / 8; ++rb) {
     const int r = rb * 8 + r7;
-    const __nv_bfloat16* g = ring + (size_t)((first_row + r) % capacity) * hd + cg * 8;
+    const T16* g = ring + (size_t)((first_row + r) % capacity) * hd + cg * 8;
 #pragma unroll
     for (int j = 0; j < HDP / 32; ++j)
       if (cg + 4 * j < cpr)
@@ -377,11 +384,11 @@ __device__ __forceinline__ void warp_load_ring_tile(uint32_t base, int n, int hd
   }
 }
 
-template <int HDP, int NT>
+template <int HDP, int NT, typename T16>
 __global__ void __launch_bounds__(FA_THREADS)
-attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
-                       const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ seq_slot,
-                       const int* __restrict__ slot_pos, __nv_bfloat16* __restrict__ out,
+attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cache,
+                       const T16* __restrict__ v_cache, const int* __restrict__ seq_slot,
+                       const int* __restrict__ slot_pos, T16* __restrict__ out,
                        float* __restrict__ part_o, float* __restrict__ part_ml,
                        int* __restrict__ counters, int* __restrict__ status, int H, int G, int hd,
                        int capacity, int window, int cpc, int max_parts, float scale_log2) {
@@ -420,8 +427,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   const int gid = lane >> 2, tig = lane & 3;
   const uint32_t q_s = smem_u32(fa_smem);                    // [16 heads][HDP]
   const uint32_t ring_s = q_s + FD_ROWS * HDP * 2 + warp * WARP_RING;
-  const __nv_bfloat16* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
-  const __nv_bfloat16* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
+  const T16* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
+  const T16* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
   auto load_unit = [&](int u, int stage) {
     const int k_lo = lo + u * FD_UNIT;
     const int n = min(FD_UNIT, pos + 1 - k_lo);
@@ -442,7 +449,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     cp_async_commit();
   }
   pdl_wait();
-  load_tile<HDP>(q_s, FD_ROWS, hd, q, [&](int r) -> const __nv_bfloat16* {
+  load_tile<HDP>(q_s, FD_ROWS, hd, q, [&](int r) -> const T16* {
     return r < nh ? q + ((size_t)t * H + h0 + r) * hd : nullptr;
   });
 #pragma unroll
@@ -505,7 +512,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
           uint32_t kf[4];
           ldsm_x4(kf, a + mt * 16 * HDP * 2);
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) mma_bf16(s[mt][nt], kf, &qf[ks][2 * nt]);
+          for (int nt = 0; nt < NT; ++nt) mma_16<T16>(s[mt][nt], kf, &qf[ks][2 * nt]);
         }
       }
     }
@@ -559,8 +566,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
           p[j] = ex2_approx(fmaf(s[mt][nt][j], scale_log2, m_neg[nt][j & 1]));
           l_w[nt][j & 1] += p[j];                            // this lane's keys only
         }
-        pb[mt][nt][0] = movmatrix_t(pack_bf16(p[0], p[1]));
-        pb[mt][nt][1] = movmatrix_t(pack_bf16(p[2], p[3]));
+        pb[mt][nt][0] = movmatrix_t(pack2<T16>(p[0], p[1]));
+        pb[mt][nt][1] = movmatrix_t(pack2<T16>(p[2], p[3]));
       }
 #pragma unroll
     for (int i = 0; i < NKS; ++i) {
@@ -571,7 +578,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
           uint32_t vf[4];
           ldsm_x4_t(vf, a + mt * 16 * HDP * 2);
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) mma_bf16(o[i][nt], vf, pb[mt][nt]);
+          for (int nt = 0; nt < NT; ++nt) mma_16<T16>(o[i][nt], vf, pb[mt][nt]);
         }
       }
     }
@@ -632,7 +639,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 #pragma unroll
     for (int w = 0; w < FA_WARPS; ++w) O += o_s[((size_t)w * hd + d) * FD_OPAD + r] * wm_s[w][r];
     if (n_parts == 1) {
-      out[(qh + r) * hd + d] = __float2bfloat16_rn(O / row_l[r]);
+      out[(qh + r) * hd + d] = from_float<T16>(O / row_l[r]);
     } else {
       const size_t pi = (qh + r) * max_parts + part;
       part_o[pi * hd + d] = O;
@@ -686,11 +693,11 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
       for (int j = 0; j < 8; ++j) O = fmaf(v[j], w_s[(s2 + j) * FD_ROWS + r], O);
     }
     for (; s2 < n_parts; ++s2) O = fmaf(__ldcg(po + (size_t)s2 * hd), w_s[s2 * FD_ROWS + r], O);
-    out[(qh + r) * hd + d] = __float2bfloat16_rn(O / row_l[r]);
+    out[(qh + r) * hd + d] = from_float<T16>(O / row_l[r]);
   }
 }
 
-template <int HDP, int NT>
+template <int HDP, int NT, typename T16>
 static int launch_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                              const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                              float* part_ml, int* counters, int* status, int n_seqs, int H, int G,
@@ -702,7 +709,7 @@ static int launch_decode_mma(const void* q, const void* k_cache, const void* v_c
   if (smem < merge) smem = merge;
   static size_t attr_smem = 0;
   if (smem > attr_smem) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HDP, NT>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HDP, NT, T16>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_smem = smem;
@@ -710,15 +717,15 @@ static int launch_decode_mma(const void* q, const void* k_cache, const void* v_c
   const int nhc = (H / G + FD_ROWS - 1) / FD_ROWS;
   const dim3 grid(max_parts, G * nhc, n_seqs);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
-  launch_pdl(attn_decode_mma_kernel<HDP, NT>, grid, dim3(FA_THREADS), smem, stream,
-             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-             seq_slot, slot_pos, (__nv_bfloat16*)out, part_o, part_ml, counters, status, H, G, hd,
+  launch_pdl(attn_decode_mma_kernel<HDP, NT, T16>, grid, dim3(FA_THREADS), smem, stream,
+             (const T16*)q, (const T16*)k_cache, (const T16*)v_cache,
+             seq_slot, slot_pos, (T16*)out, part_o, part_ml, counters, status, H, G, hd,
              capacity, window, cpc, max_parts, scale_log2);
   YALM_LAUNCH_CHECK();
   return 0;
 }
 
-template <int HDP>
+template <int HDP, typename T16>
 static int launch_prefill(const void* q, const void* kv_step, const void* k_cache,
                           const void* v_cache, const int* q_start, const int* seq_slot,
                           const int* slot_pos, void* out, int n_seqs, int max_q_len, int H, int G,
@@ -726,10 +733,10 @@ static int launch_prefill(const void* q, const void* kv_step, const void* k_cach
   const size_t smem = (size_t)(FA_BM + 4 * FA_BN) * HDP * 2;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HDP>,
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HDP, T16>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HDP>,
+    e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HDP, T16>,
                              cudaFuncAttributePreferredSharedMemoryCarveout,
                              (int)cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return (int)e;
@@ -737,9 +744,9 @@ static int launch_prefill(const void* q, const void* kv_step, const void* k_cach
   }
   const dim3 grid((max_q_len + FA_BM - 1) / FA_BM, H, n_seqs);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
-  launch_pdl(attn_prefill_mma_kernel<HDP>, grid, dim3(FP_THREADS), smem, stream,
-             (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv_step, (const __nv_bfloat16*)k_cache,
-             (const __nv_bfloat16*)v_cache, q_start, seq_slot, slot_pos, (__nv_bfloat16*)out, H, G,
+  launch_pdl(attn_prefill_mma_kernel<HDP, T16>, grid, dim3(FP_THREADS), smem, stream,
+             (const T16*)q, (const T16*)kv_step, (const T16*)k_cache,
+             (const T16*)v_cache, q_start, seq_slot, slot_pos, (T16*)out, H, G,
              hd, capacity, window, scale_log2);
   YALM_LAUNCH_CHECK();
   return 0;
@@ -749,26 +756,32 @@ static int launch_prefill(const void* q, const void* kv_step, const void* k_cach
 
 using namespace yalm;
 
-// Prefill attention on tensor cores (bfloat16).  Sequences are given by q_start
+// Prefill attention on tensor cores (dtype: bfloat16 or float16).  Sequences are given by q_start
 // [n_seqs + 1]; max_q_len is the longest of them (it sizes the grid).  Head sizes:
 // multiples of 16 up to 128 (others: use yalm_attention).
 extern "C" int yalm_attention_prefill_mma(const void* q, const void* kv_step, const void* k_cache,
                                           const void* v_cache, const int* q_start,
                                           const int* seq_slot, const int* slot_pos, void* out,
-                                          int n_seqs, int max_q_len, int H, int G, int hd,
-                                          int capacity, int window, cudaStream_t stream) {
+                                          int dtype, int n_seqs, int max_q_len, int H, int G,
+                                          int hd, int capacity, int window, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return 0;
+  if (dtype != DT_BF16 && dtype != DT_F16) return -3;
   if (hd % 16 != 0 || hd > 128 || hd <= 0) return -2;
   if (G <= 0 || H % G != 0) return -3;
   if (H > 65535 || n_seqs > 65535) return -4;
-  if (hd <= 64)
-    return launch_prefill<64>(q, kv_step, k_cache, v_cache, q_start, seq_slot, slot_pos, out,
-                              n_seqs, max_q_len, H, G, hd, capacity, window, stream);
-  return launch_prefill<128>(q, kv_step, k_cache, v_cache, q_start, seq_slot, slot_pos, out, n_seqs,
-                             max_q_len, H, G, hd, capacity, window, stream);
+#define YALM_FP(HDP, T)                                                                          \
+  return launch_prefill<HDP, T>(q, kv_step, k_cache, v_cache, q_start, seq_slot, slot_pos, out,  \
+                                n_seqs, max_q_len, H, G, hd, capacity, window, stream)
+  if (dtype == DT_F16) {
+    if (hd <= 64) YALM_FP(64, __half);
+    YALM_FP(128, __half);
+  }
+  if (hd <= 64) YALM_FP(64, __nv_bfloat16);
+  YALM_FP(128, __nv_bfloat16);
+#undef YALM_FP
 }
 
-// Decode attention on tensor cores (bfloat16): one query per sequence over the
+// Decode attention on tensor cores (dtype: bfloat16 or float16): one query per sequence over the
 // cache.  A block walks through `chunks_per_block` chunks of 64 positions; a
 // sequence needs parts = ceil(ceil(visible / 64) / chunks_per_block) blocks, with
 // visible = min(max_context, window).  part_o [n, H, parts, hd] and part_ml
@@ -777,10 +790,11 @@ extern "C" int yalm_attention_prefill_mma(const void* q, const void* kv_step, co
 extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                                          const int* seq_slot, const int* slot_pos, void* out,
                                          float* part_o, float* part_ml, int* counters, int* status,
-                                         int n_seqs, int H, int G, int hd, int capacity,
+                                         int dtype, int n_seqs, int H, int G, int hd, int capacity,
                                          int window, int max_context, int chunks_per_block,
                                          cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
+  if (dtype != DT_BF16 && dtype != DT_F16) return -3;
   if (hd % 16 != 0 || hd > 128 || hd <= 0) return -2;
   if (G <= 0 || H % G != 0) return -3;
   if (max_context <= 0 || n_seqs > 65535 || chunks_per_block < 1) return -4;
@@ -789,11 +803,15 @@ extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, con
   const int max_parts = (max_chunks + chunks_per_block - 1) / chunks_per_block;
   if ((size_t)G * ((H / G + FD_ROWS - 1) / FD_ROWS) > 65535) return -4;
   const bool two = H / G > 8;                                 // a second tile of 8 heads
-#define YALM_FD(HDP, NT)                                                                         \
-  launch_decode_mma<HDP, NT>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,      \
-                             counters, status, n_seqs, H, G, hd, capacity, window,               \
-                             chunks_per_block, max_parts, stream)
-  if (hd <= 64) return two ? YALM_FD(64, 2) : YALM_FD(64, 1);
-  return two ? YALM_FD(128, 2) : YALM_FD(128, 1);
+#define YALM_FD(HDP, NT, T)                                                                      \
+  launch_decode_mma<HDP, NT, T>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,   \
+                                counters, status, n_seqs, H, G, hd, capacity, window,            \
+                                chunks_per_block, max_parts, stream)
+  if (dtype == DT_F16) {
+    if (hd <= 64) return two ? YALM_FD(64, 2, __half) : YALM_FD(64, 1, __half);
+    return two ? YALM_FD(128, 2, __half) : YALM_FD(128, 1, __half);
+  }
+  if (hd <= 64) return two ? YALM_FD(64, 2, __nv_bfloat16) : YALM_FD(64, 1, __nv_bfloat16);
+  return two ? YALM_FD(128, 2, __nv_bfloat16) : YALM_FD(128, 1, __nv_bfloat16);
 #undef YALM_FD
 }

@@ -8,7 +8,7 @@
 // and serve both tiles.  Per block of keys and per tile: the MMA thread issues
 // S = Q.K^T into the tile's 64 columns of TMEM; each softmax thread reads its row of
 // S (tcgen05.ld), applies scale and mask, keeps a reference maximum and the sum in
-// 32-bit, and writes exp2(s - reference) as bfloat16 into the tile's swizzled P
+// 32-bit, and writes exp2(s - reference) in the 16-bit type into the tile's swizzled P
 // buffer in shared memory; the MMA thread then issues O += P.V (V is the MN-major B
 // operand, exactly as TMA lays its rows down) into the tile's O columns of TMEM.  The
 // two tiles alternate on the tensor core, so that while one group computes its
@@ -26,6 +26,8 @@
 // barrier is bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
+
+#include <type_traits>
 
 #include "api.h"
 #include "common.cuh"
@@ -152,11 +154,12 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <int HD>
+template <int HD, typename T16>
 __global__ void __launch_bounds__(TA_THREADS)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
-                       const int* __restrict__ q_start, __nv_bfloat16* __restrict__ out, int H, int G,
+                       const int* __restrict__ q_start, T16* __restrict__ out, int H, int G,
                        int window, float scale_log2, int* __restrict__ status) {
+  constexpr uint32_t FMT = std::is_same<T16, __nv_bfloat16>::value ? 1u : 0u;   // operand format
   constexpr int SUB = HD / 64;                     // 64-column sub-tiles of a head
   constexpr int Q_BYTES = TA_BM * HD * 2;          // one query tile
   constexpr int KV_BYTES = TA_BN * HD * 2;         // one block of K or of V
@@ -276,10 +279,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // ---------------- MMA issuer
     if (lane == 0) {
       // S: M = 128 queries, N = 64 keys, both operands K-major
-      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) |
+      const uint32_t idesc_s = (1u << 4) | (FMT << 7) | (FMT << 10) | ((uint32_t)(TA_BN >> 3) << 17) |
                                ((uint32_t)(TA_BM >> 4) << 24);
       // O += P.V: M = 128 queries, N = HD, A (P) K-major, B (V) MN-major
-      const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+      const uint32_t idesc_pv = (1u << 4) | (FMT << 7) | (FMT << 10) | (1u << 16) |
                                 ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
       // descriptors: one per operand tile, advanced by constants inside the loops
       const uint64_t q_desc[2] = {ta_desc_k(q_s), ta_desc_k(q_s + Q_BYTES)};
@@ -431,14 +434,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           e[i] = ta_ex2(fmaf(s[ch * 8 + i], scale_log2, neg));
           ls[i & 3] += e[i];
         }
-        __nv_bfloat162 t0 = __floats2bfloat162_rn(e[0], e[1]);
-        __nv_bfloat162 t1 = __floats2bfloat162_rn(e[2], e[3]);
-        __nv_bfloat162 t2 = __floats2bfloat162_rn(e[4], e[5]);
-        __nv_bfloat162 t3 = __floats2bfloat162_rn(e[6], e[7]);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                     ::"r"(p_row + ((ch ^ (row & 7)) << 4)), "r"(*reinterpret_cast<uint32_t*>(&t0)),
-                       "r"(*reinterpret_cast<uint32_t*>(&t1)), "r"(*reinterpret_cast<uint32_t*>(&t2)),
-                       "r"(*reinterpret_cast<uint32_t*>(&t3))
+                     ::"r"(p_row + ((ch ^ (row & 7)) << 4)), "r"(pack2<T16>(e[0], e[1])),
+                       "r"(pack2<T16>(e[2], e[3])), "r"(pack2<T16>(e[4], e[5])),
+                       "r"(pack2<T16>(e[6], e[7]))
                      : "memory");
       }
       l_run = l_run * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
@@ -451,7 +450,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (ok && n_x > 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = 1.0f / l_run;
-      __nv_bfloat16* op = out + ((size_t)(qs + my_m0 + row) * H + h) * HD;
+      T16* op = out + ((size_t)(qs + my_m0 + row) * H + h) * HD;
 #pragma unroll 1
       for (int c = 0; c < HD; c += 32) {
         float v[32];
@@ -460,14 +459,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int c8 = 0; c8 < 32; c8 += 8) {
             uint4 u;
-            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[c8 + 0] * inv, v[c8 + 1] * inv);
-            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[c8 + 2] * inv, v[c8 + 3] * inv);
-            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[c8 + 4] * inv, v[c8 + 5] * inv);
-            __nv_bfloat162 t3 = __floats2bfloat162_rn(v[c8 + 6] * inv, v[c8 + 7] * inv);
-            u.x = *reinterpret_cast<uint32_t*>(&t0);
-            u.y = *reinterpret_cast<uint32_t*>(&t1);
-            u.z = *reinterpret_cast<uint32_t*>(&t2);
-            u.w = *reinterpret_cast<uint32_t*>(&t3);
+            u.x = pack2<T16>(v[c8 + 0] * inv, v[c8 + 1] * inv);
+            u.y = pack2<T16>(v[c8 + 2] * inv, v[c8 + 3] * inv);
+            u.z = pack2<T16>(v[c8 + 4] * inv, v[c8 + 5] * inv);
+            u.w = pack2<T16>(v[c8 + 6] * inv, v[c8 + 7] * inv);
             *reinterpret_cast<uint4*>(op + c + c8) = u;
           }
         }
@@ -508,44 +503,46 @@ static TaEncodeFn ta_encode_fn() {
   }
   return fn;
 }
-// rows x cols bfloat16, row-major; box = box_rows rows x 64 columns, 128-byte swizzle
+// rows x cols of a 16-bit type, row-major; box = box_rows rows x 64 columns, 128-byte swizzle
 static int ta_make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols,
-                       int box_rows) {
+                       int box_rows, bool half) {
   TaEncodeFn fn = ta_encode_fn();
   if (!fn) return -10;
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
   const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+  CUresult r = fn(map, half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(ptr), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -11;
 }
 
-template <int HD>
+template <int HD, typename T16>
 static int launch_prefill_tc(const void* q, const void* kv_step, const int* q_start, void* out,
                              int n_tokens, int n_seqs, int max_q_len, int H, int G, int window,
                              int* status, cudaStream_t stream) {
   CUtensorMap mq, mkv;
-  int rc = ta_make_map(&mq, q, n_tokens, (long long)H * HD, TA_BM);
+  constexpr bool half = std::is_same<T16, __half>::value;
+  int rc = ta_make_map(&mq, q, n_tokens, (long long)H * HD, TA_BM, half);
   if (rc) return rc;
-  rc = ta_make_map(&mkv, kv_step, n_tokens, (long long)2 * G * HD, TA_BN);
+  rc = ta_make_map(&mkv, kv_step, n_tokens, (long long)2 * G * HD, TA_BN, half);
   if (rc) return rc;
   // two query tiles, the K and V rings, two P tiles, slack to align to 1024
   const size_t smem = (size_t)2 * TA_BM * HD * 2 + (size_t)(TA_KSTAGES + TA_VSTAGES) * TA_BN * HD * 2 +
                       (size_t)2 * TA_BM * TA_BN * 2 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>,
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, T16>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
   const dim3 grid(H, n_seqs, (max_q_len + 2 * TA_BM - 1) / (2 * TA_BM));
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
-  launch_pdl(attn_prefill_tc_kernel<HD>, grid, dim3(TA_THREADS), smem, stream, mq, mkv, q_start,
-             (__nv_bfloat16*)out, H, G, window, scale_log2, status);
+  launch_pdl(attn_prefill_tc_kernel<HD, T16>, grid, dim3(TA_THREADS), smem, stream, mq, mkv, q_start,
+             (T16*)out, H, G, window, scale_log2, status);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -556,20 +553,26 @@ using namespace yalm;
 
 // Prefill attention on tcgen05 for sequences that start at their first token (every
 // key is in kv_step).  q [n_tokens, H*hd], kv_step [n_tokens, 2, G, hd], out like q;
-// bfloat16; hd 64 or 128.  q_start [n_seqs + 1] must be in place before the launch
-// (it is read before the wait on the previous kernel).
+// bfloat16 or float16 (dtype code); hd 64 or 128.  q_start [n_seqs + 1] must be in place
+// before the launch (it is read before the wait on the previous kernel).
 extern "C" int yalm_attention_prefill_tc(const void* q, const void* kv_step, const int* q_start,
-                                         void* out, int n_tokens, int n_seqs, int max_q_len, int H,
-                                         int G, int hd, int window, int* status,
-                                         cudaStream_t stream) {
+                                         void* out, int dtype, int n_tokens, int n_seqs,
+                                         int max_q_len, int H, int G, int hd, int window,
+                                         int* status, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0 || n_tokens <= 0) return 0;
+  if (dtype != DT_BF16 && dtype != DT_F16) return -3;
   if (hd != 64 && hd != 128) return -2;
   if (G <= 0 || H % G != 0) return -3;
   if (n_seqs > 65535 || (max_q_len + 2 * TA_BM - 1) / (2 * TA_BM) > 65535) return -4;
   if (((uintptr_t)q | (uintptr_t)kv_step | (uintptr_t)out) & 15) return -6;
-  if (hd == 64)
-    return launch_prefill_tc<64>(q, kv_step, q_start, out, n_tokens, n_seqs, max_q_len, H, G,
-                                 window, status, stream);
-  return launch_prefill_tc<128>(q, kv_step, q_start, out, n_tokens, n_seqs, max_q_len, H, G,
-                                window, status, stream);
+#define YALM_TA(HD, T) \
+  return launch_prefill_tc<HD, T>(q, kv_step, q_start, out, n_tokens, n_seqs, max_q_len, H, G, \
+                                  window, status, stream)
+  if (dtype == DT_F16) {
+    if (hd == 64) YALM_TA(64, __half);
+    YALM_TA(128, __half);
+  }
+  if (hd == 64) YALM_TA(64, __nv_bfloat16);
+  YALM_TA(128, __nv_bfloat16);
+#undef YALM_TA
 }

@@ -1,16 +1,17 @@
 // Shared device helpers of the sm_100a kernels: storage types, conversions and
 // block reductions.  Every kernel computes in 32-bit floats; only storage is
-// bfloat16 on the 16-bit path.
+// bfloat16 or float16 on the 16-bit paths.
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace yalm {
 
 // dtype codes of the C interface
-enum : int { DT_F32 = 0, DT_BF16 = 1 };
+enum : int { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2 };
 
 // error bits a kernel may set in the status word it is given
 enum : int {
@@ -22,11 +23,32 @@ enum : int {
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
 
 template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
+}
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+
+// Two floats rounded into one 32-bit word of the 16-bit type T (low half first).
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// The same with the type chosen at run time (dtype code DT_BF16 or DT_F16).
+__device__ __forceinline__ uint32_t pack2_rt(int dtype, float lo, float hi) {
+  return dtype == DT_F16 ? pack2<__half>(lo, hi) : pack2<__nv_bfloat16>(lo, hi);
+}
+__device__ __forceinline__ void store16_rt(int dtype, void* base, size_t index, float v) {
+  if (dtype == DT_F16) reinterpret_cast<__half*>(base)[index] = __float2half_rn(v);
+  else reinterpret_cast<__nv_bfloat16*>(base)[index] = __float2bfloat16_rn(v);
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -71,11 +71,11 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
 // every load of a pass is in flight at once, which is what a decode step's
 // handful of rows needs (the kernel is a chain of memory round trips).
 __device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
-__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
-  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+template <typename T16>
+__device__ __forceinline__ void store4(T16* p, float4 v) {
   uint2 u;
-  u.x = *reinterpret_cast<unsigned*>(&lo);
-  u.y = *reinterpret_cast<unsigned*>(&hi);
+  u.x = pack2<T16>(v.x, v.y);
+  u.y = pack2<T16>(v.z, v.w);
   *reinterpret_cast<uint2*>(p) = u;
 }
 
@@ -192,6 +192,11 @@ template <> struct RopeIO<float, 4> {
 };
 template <> struct RopeIO<__nv_bfloat16, 4> {
   static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    store4(p, make_float4(v[0], v[1], v[2], v[3]));
+  }
+};
+template <> struct RopeIO<__half, 4> {
+  static __device__ __forceinline__ void store(__half* p, const float* v) {
     store4(p, make_float4(v[0], v[1], v[2], v[3]));
   }
 };
@@ -389,9 +394,14 @@ extern "C" int yalm_embed(const int* tokens, const void* table, int table_dtype,
   if (table_dtype == DT_F32)
     launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, x, dim,
                                                           vocab, status);
+  else if (table_dtype == DT_BF16)
+    launch_pdl(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream,
+               tokens, (const __nv_bfloat16*)table, x, dim, vocab, status);
+  else if (table_dtype == DT_F16)
+    launch_pdl(embed_kernel<__half>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
+               (const __half*)table, x, dim, vocab, status);
   else
-    launch_pdl(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, 
-        tokens, (const __nv_bfloat16*)table, x, dim, vocab, status);
+    return -3;
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -436,9 +446,14 @@ extern "C" int yalm_rmsnorm(float* x, const float* partials, int n_partials,
   if (out_dtype == DT_F32)
     launch_rmsnorm<float>(x, partials, n_partials, partial_stride, rows, weight, (float*)out,
                           n_rows, dim, eps, stream);
-  else
+  else if (out_dtype == DT_BF16)
     launch_rmsnorm<__nv_bfloat16>(x, partials, n_partials, partial_stride, rows, weight,
                                   (__nv_bfloat16*)out, n_rows, dim, eps, stream);
+  else if (out_dtype == DT_F16)
+    launch_rmsnorm<__half>(x, partials, n_partials, partial_stride, rows, weight, (__half*)out,
+                           n_rows, dim, eps, stream);
+  else
+    return -3;
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -454,9 +469,14 @@ extern "C" int yalm_silu_mul(const float* gu, int n_partials, long long partial_
   if (out_dtype == DT_F32)
     launch_pdl(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, gu, n_partials, partial_stride,
                                                                (float*)out, rows, F, paired);
+  else if (out_dtype == DT_BF16)
+    launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream,
+               gu, n_partials, partial_stride, (__nv_bfloat16*)out, rows, F, paired);
+  else if (out_dtype == DT_F16)
+    launch_pdl(silu_mul_kernel<__half>, dim3((int)blocks), dim3(threads), 0, stream, gu,
+               n_partials, partial_stride, (__half*)out, rows, F, paired);
   else
-    launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, 
-        gu, n_partials, partial_stride, (__nv_bfloat16*)out, rows, F, paired);
+    return -3;
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -469,6 +489,7 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
                                cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (hd % 2 != 0 || hd / 2 > 512 || hd <= 0) return -2;
+  if (dtype != DT_F32 && dtype != DT_BF16 && dtype != DT_F16) return -3;
   const int half = hd / 2;
   const bool vec = half % 4 == 0 && partial_stride % 4 == 0 &&
                    ((((uintptr_t)qkv) | ((uintptr_t)q_out) | ((uintptr_t)kv_step) |
@@ -488,11 +509,15 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
       launch_pdl(rope_store_many_kernel<float, TPB>, grid4, dim3(threads), 0, stream, qkv, inv_freq, token_seq,
                  q_start, seq_slot, slot_pos, (float*)q_out, (float*)kv_step, (float*)k_cache, (float*)v_cache,
                  H, G, hd, capacity, write_cache, hpb, n_tokens);
-    else
+    else if (dtype == DT_BF16)
       launch_pdl(rope_store_many_kernel<__nv_bfloat16, TPB>, grid4, dim3(threads), 0, stream, qkv, inv_freq,
                  token_seq, q_start, seq_slot, slot_pos, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_step,
                  (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, G, hd, capacity, write_cache, hpb,
                  n_tokens);
+    else
+      launch_pdl(rope_store_many_kernel<__half, TPB>, grid4, dim3(threads), 0, stream, qkv, inv_freq,
+                 token_seq, q_start, seq_slot, slot_pos, (__half*)q_out, (__half*)kv_step,
+                 (__half*)k_cache, (__half*)v_cache, H, G, hd, capacity, write_cache, hpb, n_tokens);
     YALM_LAUNCH_CHECK();
     return 0;
   }
@@ -502,8 +527,10 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
              (T*)kv_step, (T*)k_cache, (T*)v_cache, H, G, hd, capacity, write_cache, hpb)
   if (dtype == DT_F32) {
     if (vec) YALM_ROPE(float, 4); else YALM_ROPE(float, 1);
-  } else {
+  } else if (dtype == DT_BF16) {
     if (vec) YALM_ROPE(__nv_bfloat16, 4); else YALM_ROPE(__nv_bfloat16, 1);
+  } else {
+    if (vec) YALM_ROPE(__half, 4); else YALM_ROPE(__half, 1);
   }
 #undef YALM_ROPE
   YALM_LAUNCH_CHECK();

@@ -79,9 +79,14 @@ static int launch_simt(const void* A, const void* W, void* out, int out_dtype, i
   if (out_dtype == DT_F32)
     launch_pdl(gemm_simt_kernel<TA, TW, float>, dim3(grid), dim3(256), 0, stream, (const TA*)A, (const TW*)W,
                                                               (float*)out, M, N, K, accumulate);
+  else if (out_dtype == DT_BF16)
+    launch_pdl(gemm_simt_kernel<TA, TW, __nv_bfloat16>, dim3(grid), dim3(256), 0, stream,
+               (const TA*)A, (const TW*)W, (__nv_bfloat16*)out, M, N, K, accumulate);
+  else if (out_dtype == DT_F16)
+    launch_pdl(gemm_simt_kernel<TA, TW, __half>, dim3(grid), dim3(256), 0, stream, (const TA*)A,
+               (const TW*)W, (__half*)out, M, N, K, accumulate);
   else
-    launch_pdl(gemm_simt_kernel<TA, TW, __nv_bfloat16>, dim3(grid), dim3(256), 0, stream, 
-        (const TA*)A, (const TW*)W, (__nv_bfloat16*)out, M, N, K, accumulate);
+    return -3;
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -104,5 +109,11 @@ extern "C" int yalm_gemm_simt(const void* A, int a_dtype, const void* W, int w_d
     return launch_simt<float, __nv_bfloat16>(A, W, out, out_dtype, M, N, K, accumulate, stream);
   if (a_dtype == DT_BF16 && w_dtype == DT_F32)
     return launch_simt<__nv_bfloat16, float>(A, W, out, out_dtype, M, N, K, accumulate, stream);
+  if (a_dtype == DT_F16 && w_dtype == DT_F16)
+    return launch_simt<__half, __half>(A, W, out, out_dtype, M, N, K, accumulate, stream);
+  if (a_dtype == DT_F32 && w_dtype == DT_F16)
+    return launch_simt<float, __half>(A, W, out, out_dtype, M, N, K, accumulate, stream);
+  if (a_dtype == DT_F16 && w_dtype == DT_F32)
+    return launch_simt<__half, float>(A, W, out, out_dtype, M, N, K, accumulate, stream);
   return -3;
 }

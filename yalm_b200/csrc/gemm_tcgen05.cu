@@ -1,4 +1,4 @@
-// out[M,N] = A[M,K] * W[N,K]^T on the Blackwell tensor cores: bfloat16
+// out[M,N] = A[M,K] * W[N,K]^T on the Blackwell tensor cores: bfloat16 or float16
 // operands brought into shared memory by TMA (128-byte swizzle), tcgen05.mma
 // issued by one thread, 32-bit accumulators in tensor memory (TMEM), read back
 // with tcgen05.ld for a fused epilogue.
@@ -25,7 +25,7 @@
 namespace yalm {
 
 constexpr int TC_BM = 128;      // weight rows (output features) per tile = UMMA M
-constexpr int TC_BK = 64;       // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int TC_BK = 64;       // k per stage: 64 16-bit elements = one 128-byte swizzle row
 constexpr int TC_UMMA_K = 16;
 constexpr int TC_THREADS = 192; // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
 
@@ -38,7 +38,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
-// (64 bf16) with the 128-byte swizzle: 8-row groups 1024 bytes apart.
+// (64 16-bit elements) with the 128-byte swizzle: 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address
@@ -48,7 +48,7 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
   return d;
 }
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                           uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
@@ -74,6 +74,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Instruction descriptor of tcgen05.mma kind::f16: 32-bit accumulator, both operands
+// K-major unless b_mn_major, operand format bfloat16 or float16, N and M of the tile.
+__device__ __forceinline__ uint32_t umma_idesc(int ab_dtype, int n, int m, bool b_mn_major = false) {
+  const uint32_t fmt = ab_dtype == DT_BF16 ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn_major ? (1u << 16) : 0u) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
 template <int BT, int NACC> struct TcCfg {
   static constexpr int W_BYTES = TC_BM * TC_BK * 2;              // 16 KiB per weight tile
   static constexpr int A_BYTES = BT * TC_BK * 2;
@@ -94,8 +102,8 @@ template <int BT, int NACC> struct TcCfg {
 template <int BT, int NACC>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-               void* __restrict__ out, int out_dtype, int M, int N, int K, int mode, int splits,
-               int* __restrict__ status) {
+               void* __restrict__ out, int out_dtype, int ab_dtype, int M, int N, int K, int mode,
+               int splits, int* __restrict__ status) {
   using Cfg = TcCfg<BT, NACC>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[Cfg::STAGES];
@@ -173,8 +181,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else if (warp == 1) {
     // ---------------- MMA issuer
     if (lane == 0 && nk > 0) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BT >> 3) << 17) |
-                             ((uint32_t)(TC_BM >> 4) << 24);
+      const uint32_t idesc = umma_idesc(ab_dtype, BT, TC_BM);
       bool ok = true;
       for (int it = 0; it < nk && ok; ++it) {
         const int s = it % Cfg::STAGES;
@@ -189,10 +196,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
           const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
           const uint64_t koff = (uint64_t)((k * TC_UMMA_K * 2) >> 4);   // 32 bytes per k-step
-          umma_bf16(tmem_base, wdesc + koff, adesc + koff, idesc, acc);
+          umma_f16(tmem_base, wdesc + koff, adesc + koff, idesc, acc);
           if (NACC == 2) {
             const uint64_t w2 = umma_desc_k_sw128(stage + Cfg::W_BYTES);
-            umma_bf16(tmem_base + BT, w2 + koff, adesc + koff, idesc, acc);
+            umma_f16(tmem_base + BT, w2 + koff, adesc + koff, idesc, acc);
           }
         }
         umma_commit(smem_u32(&empty_bar[s]));     // frees the stage once these MMAs are done
@@ -210,7 +217,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (ok) {
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
       float* outf = reinterpret_cast<float*>(out);
-      __nv_bfloat16* outh = reinterpret_cast<__nv_bfloat16*>(out);
 #pragma unroll 1
       for (int c0 = 0; c0 < BT; c0 += 16) {
         if (tok0 + c0 >= M) break;                // uniform over the warp
@@ -242,7 +248,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               const int tok = tok0 + c0 + j;
               if (tok < M) {
                 if (out_dtype == DT_F32) outf[(size_t)tok * (N >> 1) + fo] = v[j];
-                else outh[(size_t)tok * (N >> 1) + fo] = __float2bfloat16_rn(v[j]);
+                else store16_rt(out_dtype, out, (size_t)tok * (N >> 1) + fo, v[j]);
               }
             }
           }
@@ -271,7 +277,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               } else if (out_dtype == DT_F32) {
                 outf[(size_t)tok * n_out + f] = v[j];
               } else {
-                outh[(size_t)tok * n_out + f] = __float2bfloat16_rn(v[j]);
+                store16_rt(out_dtype, out, (size_t)tok * n_out + f, v[j]);
               }
             }
           }
@@ -316,27 +322,28 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// rows x K bfloat16, row-major; box = box_rows x 64 with the 128-byte swizzle
-static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+// rows x K of a 16-bit type, row-major; box = box_rows x 64 with the 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows, int dtype) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -10;
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
   const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+  CUresult r = fn(map, dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                  2, const_cast<void*>(ptr), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -11;
 }
 
 template <int BT, int NACC>
-static int launch_tc(const CUtensorMap& mw, const void* A, void* out, int out_dtype, int M, int N,
-                     int K, int mode, int splits, int* status, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& mw, const void* A, void* out, int out_dtype, int ab_dtype,
+                     int M, int N, int K, int mode, int splits, int* status, cudaStream_t stream) {
   using Cfg = TcCfg<BT, NACC>;
   static_assert(Cfg::STAGES >= 2, "pipeline needs two stages");
   CUtensorMap ma;
-  int rc = make_map(&ma, A, M, K, BT);
+  int rc = make_map(&ma, A, M, K, BT, ab_dtype);
   if (rc) return rc;
   static bool attr_set = false;
   if (!attr_set) {
@@ -348,8 +355,8 @@ static int launch_tc(const CUtensorMap& mw, const void* A, void* out, int out_dt
   const int n_out = mode == 2 ? N / 2 : N;
   const dim3 grid((n_out + TC_BM - 1) / TC_BM, (M + BT - 1) / BT, splits);
   if (grid.y > 65535 || grid.z > 65535) return -4;
-  launch_pdl(gemm_tc_kernel<BT, NACC>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM, stream, mw, ma, out, out_dtype, M, N,
-                                                                   K, mode, splits, status);
+  launch_pdl(gemm_tc_kernel<BT, NACC>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM, stream, mw, ma, out,
+             out_dtype, ab_dtype, M, N, K, mode, splits, status);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -366,7 +373,6 @@ __device__ __forceinline__ void sk_store_chunk(int mode, int out_dtype, void* __
                                                const float* v, int f, int tok_first, int M,
                                                int n_out) {
   float* outf = reinterpret_cast<float*>(out);
-  __nv_bfloat16* outh = reinterpret_cast<__nv_bfloat16*>(out);
   if (f >= n_out) return;
   if (mode == 1) {
     float old[16];
@@ -390,7 +396,7 @@ __device__ __forceinline__ void sk_store_chunk(int mode, int out_dtype, void* __
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       const int tok = tok_first + j;
-      if (tok < M) outh[(size_t)tok * n_out + f] = __float2bfloat16_rn(v[j]);
+      if (tok < M) store16_rt(out_dtype, out, (size_t)tok * n_out + f, v[j]);
     }
   }
 }
@@ -460,7 +466,7 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar_cluster_addr)
       : "memory");
 }
-__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                                uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
@@ -485,7 +491,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
 template <int BT, int NACC>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS)
 gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-                void* __restrict__ out, int out_dtype, int M, int N, int K, int mode,
+                void* __restrict__ out, int out_dtype, int ab_dtype, int M, int N, int K, int mode,
                 int* __restrict__ status) {
   using Cfg = G2Cfg<BT, NACC>;
   extern __shared__ uint8_t smem_raw[];
@@ -594,8 +600,7 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   } else if (warp == 1) {
     // ---------------- MMA issuer: one thread of the first block, for the pair
     if (lane == 0 && leader && pair < n_tiles) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BT >> 3) << 17) |
-                             ((uint32_t)((2 * TC_BM) >> 4) << 24);
+      const uint32_t idesc = umma_idesc(ab_dtype, BT, 2 * TC_BM);
       bool ok = true;
       int it = 0, part = 0;
       for (int t = pair; t < n_tiles && ok; t += n_pairs, ++part) {
@@ -617,10 +622,10 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
             const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
             const uint64_t koff = (uint64_t)((k * TC_UMMA_K * 2) >> 4);
-            umma_bf16_pair(acc_addr, wdesc + koff, adesc + koff, idesc, acc);
+            umma_f16_pair(acc_addr, wdesc + koff, adesc + koff, idesc, acc);
             if (NACC == 2) {
               const uint64_t w2 = umma_desc_k_sw128(stage + Cfg::W_BYTES);
-              umma_bf16_pair(acc_addr + BT, w2 + koff, adesc + koff, idesc, acc);
+              umma_f16_pair(acc_addr + BT, w2 + koff, adesc + koff, idesc, acc);
             }
           }
           umma_commit_pair(smem_u32(&empty_bar[s]));           // frees the stage in both blocks
@@ -693,14 +698,14 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 }
 
 template <int BT, int NACC>
-static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
-                      int mode, int* status, cudaStream_t stream) {
+static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, int ab_dtype, int M,
+                      int N, int K, int mode, int* status, cudaStream_t stream) {
   using Cfg = G2Cfg<BT, NACC>;
   static_assert(Cfg::STAGES >= 3, "pipeline depth");
   CUtensorMap mw, ma;
-  int rc = make_map(&mw, W, N, K, TC_BM);
+  int rc = make_map(&mw, W, N, K, TC_BM, ab_dtype);
   if (rc) return rc;
-  rc = make_map(&ma, A, M, K, BT / 2);
+  rc = make_map(&ma, A, M, K, BT / 2, ab_dtype);
   if (rc) return rc;
   static bool attr_set = false;
   if (!attr_set) {
@@ -715,7 +720,7 @@ static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, in
   if (pairs > tiles) pairs = tiles;
   if (pairs < 1) return -4;
   launch_pdl(gemm_2sm_kernel<BT, NACC>, dim3((unsigned)(2 * pairs)), dim3(TC_THREADS), Cfg::SMEM,
-             stream, mw, ma, out, out_dtype, M, N, K, mode, status);
+             stream, mw, ma, out, out_dtype, ab_dtype, M, N, K, mode, status);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -726,9 +731,12 @@ using namespace yalm;
 
 extern "C" int yalm_gemm_tc_available(void) { return encode_fn() ? 0 : -10; }
 
-extern "C" int yalm_gemm_tc(const void* A, const void* W, void* out, int out_dtype, int M, int N,
-                            int K, int mode, int splits, int* status, cudaStream_t stream) {
+extern "C" int yalm_gemm_tc(const void* A, const void* W, int ab_dtype, void* out, int out_dtype,
+                            int M, int N, int K, int mode, int splits, int* status,
+                            cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  if (ab_dtype != DT_BF16 && ab_dtype != DT_F16) return -3;
+  if (out_dtype != DT_F32 && out_dtype != ab_dtype) return -3;
   if (K <= 0 || K % 8 != 0) return -2;               // TMA: rows must be 16-byte multiples
   if (((uintptr_t)A | (uintptr_t)W) & 15) return -6; // TMA: 16-byte aligned bases
   if (mode < 0 || mode > 4) return -3;
@@ -743,10 +751,10 @@ extern "C" int yalm_gemm_tc(const void* A, const void* W, void* out, int out_dty
     if ((splits - 1) * per >= nkb) return -5;        // no empty slice of K
   }
   CUtensorMap mw;
-  int rc = make_map(&mw, W, N, K, TC_BM);
+  int rc = make_map(&mw, W, N, K, TC_BM, ab_dtype);
   if (rc) return rc;
 #define YALM_TC(BT, NACC) \
-  return launch_tc<BT, NACC>(mw, A, out, out_dtype, M, N, K, mode, splits, status, stream)
+  return launch_tc<BT, NACC>(mw, A, out, out_dtype, ab_dtype, M, N, K, mode, splits, status, stream)
   if (mode == 2) {
     if (M <= 16) YALM_TC(16, 2);
     if (M <= 32) YALM_TC(32, 2);
@@ -764,15 +772,18 @@ extern "C" int yalm_gemm_tc(const void* A, const void* W, void* out, int out_dty
 
 // Two-SM variant for many tokens (see gemm_2sm_kernel): mode 0 store, 1 add into
 // float32 out, 2 silu(gate)*up, 4 the same with interleaved rows.
-extern "C" int yalm_gemm_2sm(const void* A, const void* W, void* out, int out_dtype, int M, int N,
-                             int K, int mode, int* status, cudaStream_t stream) {
+extern "C" int yalm_gemm_2sm(const void* A, const void* W, int ab_dtype, void* out, int out_dtype,
+                             int M, int N, int K, int mode, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  if (ab_dtype != DT_BF16 && ab_dtype != DT_F16) return -3;
+  if (out_dtype != DT_F32 && out_dtype != ab_dtype) return -3;
   if (K <= 0 || K % 8 != 0) return -2;
   if (((uintptr_t)A | (uintptr_t)W) & 15) return -6;
   if (mode < 0 || mode == 3 || mode > 4) return -3;
   if (mode == 2 && (N % 2 != 0)) return -3;
   if (mode == 4 && (N % 32 != 0)) return -3;
   if (mode == 1 && out_dtype != DT_F32) return -3;
-  if (mode == 2) return launch_2sm<128, 2>(A, W, out, out_dtype, M, N, K, mode, status, stream);
-  return launch_2sm<256, 1>(A, W, out, out_dtype, M, N, K, mode, status, stream);
+  if (mode == 2)
+    return launch_2sm<128, 2>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, status, stream);
+  return launch_2sm<256, 1>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, status, stream);
 }

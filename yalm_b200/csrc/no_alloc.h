@@ -13,9 +13,13 @@
 // Returns 0, a cudaError_t, or a refusal: -7 if n_tokens * H * nsplit *
 // (hd + 2) floats exceed the capacity, -8 for a device index beyond 63, the
 // codes of yalm_attention otherwise.  The first call on a device looks up the
-// array's address and should come before any stream capture.  Calls share the
-// array: calls that overlap on the GPU race.  See the comment at the
-// definition in attention.cu for the full rules.
+// array's address and should come before any stream capture; `stream` must
+// belong to the device that is current at the call, because the array used is
+// the current device's.  The addresses are kept in a host table without a
+// lock: host threads that make a device's first call together may each do the
+// look-up and store the same value.  Calls share the array: calls that overlap
+// on the GPU race.  See the comment at the definition in attention.cu for the
+// full rules.
 #pragma once
 #include <cuda_runtime.h>
 

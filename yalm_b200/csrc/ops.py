@@ -14,7 +14,8 @@ import torch
 
 from . import build
 
-F32, BF16 = 0, 1
+F32, BF16, F16 = 0, 1, 2
+HALF_TYPES = (torch.bfloat16, torch.float16)
 
 ERR_TOKEN_RANGE, ERR_WAIT_TIMEOUT, ERR_SLOT_RANGE, ERR_CONTEXT_RANGE = 1, 2, 4, 8
 
@@ -38,7 +39,9 @@ def dtype_code(dt: torch.dtype) -> int:
         return F32
     if dt == torch.bfloat16:
         return BF16
-    raise KernelError(f"the kernels take float32 and bfloat16 tensors, not {dt}")
+    if dt == torch.float16:
+        return F16
+    raise KernelError(f"the kernels take float32, bfloat16 and float16 tensors, not {dt}")
 
 
 _c = ctypes
@@ -57,15 +60,15 @@ _SIGNATURES = {
     "yalm_attention_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                               _i, _i, _i, _i, _vp],
     "yalm_attention_prefill_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                   _i, _vp],
-    "yalm_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+                                   _i, _i, _vp],
+    "yalm_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_attention_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
-                                  _i, _i, _i, _i, _vp],
+                                  _i, _i, _i, _i, _i, _vp],
     "yalm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp],
-    "yalm_gemm_tc": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "yalm_gemm_tc": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_gemm_tc_available": [],
-    "yalm_gemm_2sm": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "yalm_gemm_2sm": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp],
 }
 
 _lib = None
@@ -245,35 +248,38 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 
 
 def mma_attention_usable(dtype: torch.dtype, hd: int) -> bool:
-    """The tensor-core attention kernels take bfloat16 and head sizes in steps of 16 up to 128."""
-    return dtype == torch.bfloat16 and hd % 16 == 0 and 0 < hd <= 128
+    """The tensor-core attention kernels take bfloat16 or float16 and head sizes in steps of
+    16 up to 128."""
+    return dtype in HALF_TYPES and hd % 16 == 0 and 0 < hd <= 128
 
 
 def attention_prefill_mma(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
                           v_cache: torch.Tensor, batch, slot_pos: torch.Tensor, out: torch.Tensor,
                           H: int, G: int, hd: int, capacity: int, window: Optional[int]) -> None:
-    _need(q.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16,
-          "attention_prefill_mma: bfloat16 only")
+    _need(q.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == out.dtype
+          and q.dtype in HALF_TYPES, "attention_prefill_mma: one 16-bit type throughout")
     _check(lib().yalm_attention_prefill_mma(_p(q), _p(kv_step), _p(k_cache), _p(v_cache),
                                             _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos),
-                                            _p(out), batch.n_seqs, max(batch.q_lens), H, G, hd,
+                                            _p(out), dtype_code(q.dtype), batch.n_seqs,
+                                            max(batch.q_lens), H, G, hd,
                                             capacity, int(window or 0), _stream()),
            "attention_prefill_mma")
 
 
 def tc_attention_usable(dtype: torch.dtype, hd: int, past) -> bool:
-    """The tcgen05 prefill attention takes bfloat16, head size 64 or 128, and sequences
-    that start at their first token (every key is one of this step's)."""
-    return dtype == torch.bfloat16 and hd in (64, 128) and all(p == 0 for p in past)
+    """The tcgen05 prefill attention takes bfloat16 or float16, head size 64 or 128, and
+    sequences that start at their first token (every key is one of this step's)."""
+    return dtype in HALF_TYPES and hd in (64, 128) and all(p == 0 for p in past)
 
 
 def attention_prefill_tc(q: torch.Tensor, kv_step: torch.Tensor, batch, out: torch.Tensor,
                          H: int, G: int, hd: int, window: Optional[int],
                          status: torch.Tensor) -> None:
-    _need(q.dtype == kv_step.dtype == out.dtype == torch.bfloat16 and q.is_contiguous()
-          and kv_step.is_contiguous() and out.is_contiguous(), "attention_prefill_tc: bfloat16")
+    _need(q.dtype == kv_step.dtype == out.dtype and q.dtype in HALF_TYPES and q.is_contiguous()
+          and kv_step.is_contiguous() and out.is_contiguous(),
+          "attention_prefill_tc: one 16-bit type throughout")
     _check(lib().yalm_attention_prefill_tc(_p(q), _p(kv_step), _p(batch.q_start), _p(out),
-                                           q.shape[0], batch.n_seqs, max(batch.q_lens), H, G, hd,
+                                           dtype_code(q.dtype), q.shape[0], batch.n_seqs, max(batch.q_lens), H, G, hd,
                                            int(window or 0), _p(status), _stream()),
            "attention_prefill_tc")
 
@@ -290,8 +296,8 @@ def attention_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          status: torch.Tensor, H: int, G: int, hd: int, capacity: int,
                          window: Optional[int], max_context: int, chunks_per_block: int) -> None:
     n = q.shape[0]
-    _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16,
-          "attention_decode_mma: bfloat16 only")
+    _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype and q.dtype in HALF_TYPES,
+          "attention_decode_mma: one 16-bit type throughout")
     parts = decode_mma_parts(max_context, window, chunks_per_block)
     hc = -(-(H // G) // 16)
     _need(part_o.numel() >= n * H * parts * hd and part_ml.numel() >= n * H * parts * 2
@@ -299,8 +305,9 @@ def attention_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
           "attention_decode_mma: workspace")
     _check(lib().yalm_attention_decode_mma(_p(q), _p(k_cache), _p(v_cache), _p(seq_slot),
                                            _p(slot_pos), _p(out), _p(part_o), _p(part_ml),
-                                           _p(counters), _p(status), n, H, G, hd, capacity,
-                                           int(window or 0), max_context, chunks_per_block,
+                                           _p(counters), _p(status), dtype_code(q.dtype), n, H, G,
+                                           hd, capacity, int(window or 0), max_context,
+                                           chunks_per_block,
                                            _stream()),
            "attention_decode_mma")
 
@@ -320,7 +327,7 @@ GEMM_STORE, GEMM_ADD, GEMM_SILU_MUL, GEMM_SPLIT, GEMM_SILU_PAIRED = 0, 1, 2, 3, 
 
 
 def gemm_tc_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
-    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
+    return (a.dtype == w.dtype and a.dtype in HALF_TYPES and a.shape[1] % 8 == 0
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
@@ -328,7 +335,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, stat
             splits: int = 1) -> None:
     M, K = a.shape
     N = w.shape[0]
-    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+    _need(a.dtype == w.dtype and a.dtype in HALF_TYPES and w.shape[1] == K
           and a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "gemm_tc: operands")
     if mode in (GEMM_SILU_MUL, GEMM_SILU_PAIRED):
         _need(tuple(out.shape) == (M, N // 2), "gemm_tc: silu-mul out is [M, N/2]")
@@ -336,8 +343,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, stat
         _need(out.dtype == torch.float32 and out.numel() >= splits * M * N, "gemm_tc: split scratch")
     else:
         _need(tuple(out.shape) == (M, N), "gemm_tc: out is [M, N]")
-    _check(lib().yalm_gemm_tc(_p(a), _p(w), _p(out), dtype_code(out.dtype), M, N, K, mode, splits,
-                              _p(status), _stream()), "gemm_tc")
+    _check(lib().yalm_gemm_tc(_p(a), _p(w), dtype_code(a.dtype), _p(out), dtype_code(out.dtype), M,
+                              N, K, mode, splits, _p(status), _stream()), "gemm_tc")
 
 
 def gemm_2sm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
@@ -345,12 +352,12 @@ def gemm_2sm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
     """Two-SM tcgen05 product (pairs of blocks on one 256-feature tile) with a fused epilogue."""
     M, K = a.shape
     N = w.shape[0]
-    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+    _need(a.dtype == w.dtype and a.dtype in HALF_TYPES and w.shape[1] == K
           and a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "gemm_2sm: operands")
     _need(tuple(out.shape) == ((M, N // 2) if mode in (GEMM_SILU_MUL, GEMM_SILU_PAIRED) else (M, N)),
           "gemm_2sm: out shape")
-    _check(lib().yalm_gemm_2sm(_p(a), _p(w), _p(out), dtype_code(out.dtype), M, N, K, mode,
-                               _p(status), _stream()), "gemm_2sm")
+    _check(lib().yalm_gemm_2sm(_p(a), _p(w), dtype_code(a.dtype), _p(out), dtype_code(out.dtype), M,
+                               N, K, mode, _p(status), _stream()), "gemm_2sm")
 
 
 def sample(logits: torch.Tensor, temperature: float, seed: int, row_key: torch.Tensor,

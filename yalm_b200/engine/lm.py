@@ -24,23 +24,26 @@ from ..weights import load_checkpoint, load_packed, random_tensors, write_model_
 from .generate import Completion, run_generation
 from .step import Engine
 
-_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
-           "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.float16,
+           "fp16": torch.float16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float16: torch.float16,
+           torch.float32: torch.float32}
 
 
 def _dtype(d) -> torch.dtype:
     if d not in _DTYPES:
-        raise ValueError(f"dtype must be 'bfloat16' or 'float32', got {d!r}")
+        raise ValueError(f"dtype must be 'bfloat16', 'float16' or 'float32', got {d!r}")
     return _DTYPES[d]
 
 
 class LM:
     def __init__(self, config: Any, tensors: Dict[str, torch.Tensor], dtype="bfloat16",
                  max_context: Optional[int] = None, max_batch: int = 8, device="cuda:0",
-                 gemm: str = "auto", attention: str = "auto"):
+                 gemm: str = "auto", attention: str = "auto", float32_matrices: str = "keep"):
         self.config = config
         self.spec = config.to_spec()
-        self.rt = Runtime(_dtype(dtype), device, gemm=gemm, attention=attention)
+        self.rt = Runtime(_dtype(dtype), device, gemm=gemm, attention=attention,
+                          float32_matrices=float32_matrices)
         self.model = Model(self.spec, self.rt)
         ignorable = getattr(config, "ignorable_tensor", None)
         self.model.bind(tensors, ignore_unexpected=[n for n in tensors if ignorable(n)] if ignorable else ())

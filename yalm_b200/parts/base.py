@@ -65,9 +65,11 @@ class Runtime:
     CUDA graph relies on that)."""
 
     def __init__(self, dtype: torch.dtype, device="cuda:0", gemm: str = "auto",
-                 attention: str = "auto"):
-        if dtype not in (torch.float32, torch.bfloat16):
-            raise ValueError(f"compute type must be float32 or bfloat16, not {dtype}")
+                 attention: str = "auto", float32_matrices: str = "keep"):
+        if dtype not in (torch.float32, torch.bfloat16, torch.float16):
+            raise ValueError(f"compute type must be float32, bfloat16 or float16, not {dtype}")
+        if float32_matrices not in ("keep", "round"):
+            raise ValueError("float32_matrices is 'keep' or 'round'")
         self.dtype = dtype
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -76,6 +78,10 @@ class Runtime:
         ops.lib()   # builds/loads the kernels now: a missing library fails here, loudly
         self.gemm = gemm                      # "auto" | "simt" (debugging aid: no tensor cores)
         self.attention = attention            # "auto" | "mma" (no tcgen05 prefill attention) | "simt"
+        # a matrix stored in 32 bits under 16-bit compute: "keep" it (it is then multiplied by
+        # the FMA kernel, without tensor cores) or "round" it to the compute type
+        self.float32_matrices = float32_matrices
+        self.kept_float32 = 0
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._buffers: Dict[str, torch.Tensor] = {}
         self._shared = []
@@ -89,6 +95,7 @@ class Runtime:
         tensors they need (random-weights mode, checks), but not run."""
         rt = cls.__new__(cls)
         rt.dtype, rt.device, rt.gemm, rt.attention = dtype, torch.device("cpu"), "auto", "auto"
+        rt.float32_matrices, rt.kept_float32 = "keep", 0
         rt.status, rt._buffers, rt._shared = None, {}, []
         rt.frozen, rt.sm_count, rt.buffer_generation = True, 148, 0
         return rt
@@ -123,11 +130,15 @@ class Runtime:
         return buf
 
     def matrix(self, t: torch.Tensor, share: bool = False) -> torch.Tensor:
-        """A weight matrix in the type it is multiplied in: the compute type,
-        except that a matrix stored in 32 bits stays 32-bit (float16 storage becomes
-        bfloat16 under bfloat16 compute and is widened exactly under 32-bit compute).  ``share``: parts
-        that are bound to the same stored tensor (a tied head) get one copy."""
-        dt = torch.float32 if (self.dtype == torch.float32 or t.dtype == torch.float32) else self.dtype
+        """A weight matrix in the type it is multiplied in: the compute type (a 16-bit
+        matrix stored in the other 16-bit type is rounded to it; 32-bit compute widens
+        16-bit storage exactly), except that a matrix stored in 32 bits stays 32-bit unless
+        ``float32_matrices="round"``.  ``share``: parts that are bound to the same stored
+        tensor (a tied head) get one copy."""
+        keep32 = t.dtype == torch.float32 and self.float32_matrices == "keep"
+        dt = torch.float32 if (self.dtype == torch.float32 or keep32) else self.dtype
+        if keep32 and self.dtype != torch.float32:
+            self.kept_float32 += 1
         if share:
             for src, dev in self._shared:
                 if src is t:
@@ -139,6 +150,12 @@ class Runtime:
 
     def end_binding(self) -> None:
         self._shared.clear()
+        if self.kept_float32:
+            import warnings
+            warnings.warn(f"{self.kept_float32} weight matrices are stored in float32 and stay so: "
+                          f"their products run on the FMA kernel, not on tensor cores "
+                          f"(float32_matrices='round' converts them to {self.dtype})", stacklevel=3)
+            self.kept_float32 = 0
 
     def vector(self, t: torch.Tensor) -> torch.Tensor:
         return t.to(device=self.device, dtype=torch.float32).contiguous()

@@ -1,12 +1,12 @@
 """Matrix products of the parts: which kernel, which epilogue, how many K
 slices.
 
-bfloat16 operands go to the tcgen05 kernel.  When the token count is small the
+16-bit operands (bfloat16 or float16) go to the tcgen05 kernel.  When the token count is small the
 grid of 128-row weight tiles is too small to pull from HBM with every SM, so K
 is split and each slice writes a 32-bit partial product; the consumer (norm,
 rotary or SiLU kernel) sums the slices while it reads them.  With many tokens
 the epilogue is fused instead (store, residual add, SiLU*up).  32-bit operands,
-mixed operands (a matrix stored in 32 bits under bfloat16 compute) and shapes
+mixed operands (a matrix stored in 32 bits under 16-bit compute) and shapes
 TMA cannot address go to the FMA kernel.
 """
 from __future__ import annotations

@@ -2,9 +2,9 @@
 
 ``load_checkpoint`` reads every ``*.safetensors`` file of a model folder and
 normalises storage types: bfloat16 and 32-bit floats stay as stored, integer
-tables become int32.  float16 also stays as stored until a part binds it: the
-bfloat16 path then keeps it as bfloat16, the 32-bit path widens it exactly (a
-true 32-bit path must not round its inputs).  ``check_tensors``
+tables become int32.  float16 also stays as stored: a part that binds it keeps
+it under float16 compute, rounds it to bfloat16 under bfloat16 compute, and widens
+it exactly under 32-bit compute (a true 32-bit path must not round its inputs).  ``check_tensors``
 compares what a model declares with what a checkpoint holds and reports every
 problem in ONE error: missing tensors, unexpected tensors and wrong shapes
 (the reference stops at the first missing or mis-shaped tensor,
