@@ -170,24 +170,12 @@ def random_prompts(lengths, vocab, seed):
 def decode_bytes(lm, contexts):
     """Bytes one decode step has to read: every weight once (the embedding
     table only one row per sequence) plus the keys and values of the live
-    sequences."""
-    cfg = lm.config
-    esz = 2
-    D, F, V, L = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
-    H, G, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-    per_layer = ((H + 2 * G) * hd * D + D * H * hd + 3 * F * D) * esz + 2 * D * 4
-    weights = L * per_layer + V * D * esz + D * 4 + len(contexts) * D * esz
-    window = cfg.sliding_window
-    kv = sum(min(c, window) if window else c for c in contexts) * L * 2 * G * hd * esz
-    return weights + kv
+    sequences.  The model's parts do the counting."""
+    return lm.model.step_bytes(contexts)
 
 
-def prefill_flops(cfg, T):
-    D, F, V, L = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
-    H, G, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-    linear = 2.0 * T * L * ((H + 2 * G) * hd * D + D * H * hd + 3 * F * D) + 2.0 * V * D
-    attn = L * 2.0 * 2.0 * H * hd * (T * (T + 1) / 2.0)
-    return linear + attn
+def prefill_flops(lm, T):
+    return lm.model.step_flops([T], [0], n_want=1)
 
 
 def prefill_batch(lm, prompts, group=8):
@@ -272,7 +260,7 @@ def time_prefill(lm, T, reps, pk):
         if i >= 2:
             times.append(a.elapsed_time(b))
     ms = sorted(times)[len(times) // 2]
-    fl = prefill_flops(lm.config, T)
+    fl = prefill_flops(lm, T)
     out = {"value": T / (ms / 1e3), "tokens": T, "ms": ms,
            "frac": fl / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), "of": pk["source"]}
     if "bf16_tflops_sustained" in pk:       # the step is short; the burst figure is the denominator

@@ -10,19 +10,28 @@ import bench  # noqa: E402
 from yalm_b200.config import config_from_dict  # noqa: E402
 
 
+def _model_without_device(cfg_dict):
+    import torch
+    from yalm_b200.parts import Model, Runtime
+    cfg = config_from_dict(dict(cfg_dict))
+    return cfg, SimpleNamespace(config=cfg, model=Model(cfg.to_spec(), Runtime.shapes_only(torch.float16)))
+
+
 def test_decode_bytes_and_prefill_flops():
-    cfg = config_from_dict(dict(bench.MISTRAL_7B))
-    lm = SimpleNamespace(config=cfg)
+    cfg, lm = _model_without_device(bench.MISTRAL_7B)
     weights_only = bench.decode_bytes(lm, [])
     assert abs(weights_only - 14.22e9) / 14.22e9 < 0.01
     per_position = bench.decode_bytes(lm, [1]) - weights_only - cfg.hidden_size * 2
     assert per_position == 128 * 1024
     b64 = bench.decode_bytes(lm, [1056] * 64)
     assert abs(b64 - 23.08e9) / 23.08e9 < 0.01
-    assert abs(bench.prefill_flops(cfg, 2048) - 29.7e12) / 29.7e12 < 0.01
+    assert abs(bench.prefill_flops(lm, 2048) - 29.7e12) / 29.7e12 < 0.01
     # under a window only the ring is read
-    v01 = SimpleNamespace(config=config_from_dict(dict(bench.WORKLOADS["mistral-7b-v0.1"][0])))
+    _, v01 = _model_without_device(bench.WORKLOADS["mistral-7b-v0.1"][0])
     assert bench.decode_bytes(v01, [6000]) == bench.decode_bytes(v01, [4096])
+    # a tied head: the table is read whole once, as the head
+    _, l1b = _model_without_device(bench.LLAMA32_1B)
+    assert abs(bench.decode_bytes(l1b, []) - 2.47e9) / 2.47e9 < 0.01
 
 
 def test_more_than_one_gpu_is_refused(capsys):

@@ -75,7 +75,7 @@ def test_registry_maps_both_names_and_takes_new_ones(tmp_path):
 def test_spec_lists_parts_layer_by_layer():
     s = config_from_dict(TINY_B).to_spec()
     assert len(s.layers) == 3 and [e.layer for e in s.run_order] == [0, 1, 2]
-    m = s.layers[1].mixer
+    m = s.layers[1].part("mixer")
     assert m.kind == "gqa_attention" and m.params["window"] == 32
     assert m.params["position"].kind == "rope" and m.params["position"].params["scaling"]["factor"] == 4.0
     assert m.tensors["q"] == "model.layers.1.self_attn.q_proj.weight"

@@ -376,3 +376,108 @@ def test_a_packed_one_file_model(tmp_path):
     assert torch.equal(got[0], got[1])
     ref = plain_forward(cfg, w, toks)
     assert float((got[1] - ref).abs().max() / ref.abs().max()) <= TOL["float32"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_window_imposed_on_a_model_that_has_none(dtype):
+    """window_override=24 on tiny-A (no window in its config.json): generation goes on
+    past 24 positions in a ring of 24 rows, and the logits are those of the plain model
+    with sliding_window = 24."""
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, seed = CONFIGS["tiny_a"]
+    w = make_weights(cfg, seed)
+    toks = random_tokens(100, cfg["vocab_size"], 31)
+    ref = plain_forward(dict(cfg, sliding_window=24), w, toks)
+    assert float((ref - plain_forward(cfg, w, toks)).abs().max()) > 1e-3     # the window matters
+    lm = LM(config_from_dict(cfg), dict(w), dtype=dtype, max_batch=2, window_override=24)
+    assert lm.engine.cache.groups[0]["capacity"] == 24 and lm.context == 128
+    s = lm.acquire(1)
+    lg = lm.step([toks[:40]], s, [list(range(40))]).cpu()      # a prompt longer than the ring
+    worst = float((lg - ref[:40]).abs().max())
+    for p in range(40, 100):
+        worst = max(worst, float((lm.step([[toks[p]]], s, [[0]])[0].cpu() - ref[p]).abs().max()))
+    assert worst / float(ref.abs().max()) <= TOL[dtype]
+
+
+def test_context_option_of_the_command_line_is_a_window_and_batch_file(tmp_path):
+    """-T 24 on the command line: 60 greedy tokens past a ring of 24 rows equal the plain
+    model's with sliding_window = 24; --batch-file gives several prompts."""
+    import subprocess
+    import sys
+    from trace_tools import ROOT
+    cfg, seed = CONFIGS["tiny_a"]
+    w = make_weights(cfg, seed)
+    model = write_model(str(tmp_path / "m"), cfg, w)
+    prompts = [random_tokens(9, cfg["vocab_size"], 50), random_tokens(30, cfg["vocab_size"], 51)]
+    (tmp_path / "batch.txt").write_text("\n".join(",".join(map(str, p)) for p in prompts) + "\n")
+    r = subprocess.run([sys.executable, "-m", "yalm_b200", model, "--dtype", "float32", "-T", "24",
+                        "--batch-file", str(tmp_path / "batch.txt"), "-n", "60", "-t", "0"],
+                       capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.startswith("tokens:")]
+    assert len(lines) == 2
+    windowed = dict(cfg, sliding_window=24)
+    for line, p in zip(lines, prompts):
+        got = [int(t) for t in line.split("(")[0].split()[1:]]
+        assert got == plain_generate_greedy(windowed, w, p, 60, stop=[2])
+
+
+def test_perplexity_of_a_text_longer_than_the_context():
+    """The text is cut into sequences of `context` tokens that overlap by one token, and
+    each runs in portions: every token but the first is predicted once."""
+    import math
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, seed = CONFIGS["tiny_a"]                               # context 128
+    w = make_weights(cfg, seed)
+    toks = random_tokens(300, cfg["vocab_size"], 8)
+    lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=1)
+    ppl, err = lm.perplexity(toks, chunk=50)
+    vals = []
+    for a in (0, 127, 254):
+        seg = toks[a:a + 128]
+        lp = torch.log_softmax(plain_forward(cfg, w, seg).double(), -1)
+        vals += [lp[i, seg[i + 1]].item() for i in range(len(seg) - 1)]
+    assert len(vals) == 299
+    want = math.exp(-sum(vals) / len(vals))
+    assert abs(ppl - want) / want < 1e-4 and err > 0
+    assert lm.engine.cache.slots.free_count == 1
+
+
+def test_trace_run_takes_random_weights_of_a_configuration(tmp_path):
+    """--model random:<config.json>:<seed> is the model that LM.from_random draws."""
+    import json
+    from yalm_b200 import LM
+    cfg, _ = CONFIGS["tiny_c"]
+    (tmp_path / "cfg.json").write_text(json.dumps(cfg))
+    toks = random_tokens(45, cfg["vocab_size"], 3)
+    tr = Trace()
+    add_whole(tr, {"r": toks})
+    got = run_trace_run(f"random:{tmp_path / 'cfg.json'}:5", "float32", tr, str(tmp_path / "out"))
+    lm = LM.from_random(cfg, seed=5, dtype="float32", max_batch=1)
+    s = lm.acquire(1)
+    want = lm.step([toks], s, [list(range(45))]).cpu()
+    assert torch.equal(got[0].reshape(45, -1), want)
+
+
+def test_seeds_and_temperatures_share_the_captured_decode_steps():
+    """Seed and temperature are read from device memory, so a new seed costs no new
+    graph; the number of kept graphs is bounded."""
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, seed = CONFIGS["tiny_a"]
+    w = make_weights(cfg, seed)
+    prompts = [random_tokens(n, cfg["vocab_size"], 80 + n) for n in (6, 11)]
+    lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=2)
+    outs = {}
+    for sd in range(6):
+        outs[sd] = [c.tokens for c in lm.generate(prompts, 10, temperature=0.8 + 0.1 * sd, seed=sd,
+                                                  ignore_eos=True)]
+    assert len(lm.engine._graphs) == 1
+    lm.engine.use_graphs = False
+    for sd in (0, 5):
+        again = [c.tokens for c in lm.generate(prompts, 10, temperature=0.8 + 0.1 * sd, seed=sd,
+                                               ignore_eos=True)]
+        assert again == outs[sd]
+    assert lm.engine.MAX_GRAPHS >= 1

@@ -340,6 +340,53 @@ def test_sampling_greedy_and_temperature(ops):
     assert out[3].item() == one
     us = [ops.uniform01(9, 1, i) for i in range(2000)]
     assert 0.45 < sum(us) / len(us) < 0.55 and len(set(us)) > 1990
+    # seed and temperature read from device memory (what a captured step does) give the
+    # same tokens as the same values passed as arguments
+    for temp, seed in ((0.0, 5), (0.7, 2 ** 63 + 11), (1.9, 3)):
+        ops.sample(logits, temp, seed, keys, seq_slot, slot_pos, out)
+        want = out.tolist()
+        params = torch.tensor(ops.sampling_params(temp, seed), dtype=torch.int64, device=DEV)
+        ops.sample(logits, 123.0, 999, keys, seq_slot, slot_pos, out, params=params)
+        assert out.tolist() == want, (temp, seed)
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable(ops):
+    """A kernel waits on a barrier that nobody arrives on, gives up after a millisecond
+    and raises the status bit; the runtime turns it into an error and clears it."""
+    from yalm_b200.parts import Runtime
+    rt = Runtime(torch.float32, DEV)
+    ops.wait_probe(1_000_000, rt.status)
+    with pytest.raises(ops.KernelError, match="bounded barrier wait"):
+        rt.check_status()
+    rt.check_status()                                           # cleared
+    with pytest.raises(ops.KernelError, match="refused"):
+        ops.wait_probe(10 ** 10, rt.status)                     # limits beyond 100 ms are refused
+    x = torch.arange(8, device=DEV).sum().item()                # the context still works
+    assert x == 28
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.float16])
+def test_ring_rows_written_from_the_step_buffer(ops, dt):
+    """cache_write puts a step's keys and values where rope_store would have put them:
+    only the positions the ring keeps, at row position % capacity, other rows untouched."""
+    G, hd, cap, n_slots = 3, 24, 16, 4
+    for hd in (24, 20):                                         # 16-byte rows and odd ones
+        b = B([21, 1, 5], [2, 0, 3])
+        slot_pos = torch.tensor([30, 0, 7, 13], dtype=torch.int32, device=DEV)
+        kv = torch.randn(b.n_tokens, 2, G, hd, device=DEV).to(dt)
+        kc = torch.full((n_slots, G, cap, hd), 7.0, device=DEV, dtype=dt)
+        vc = torch.full_like(kc, 7.0)
+        ops.cache_write(kv, b, kc, vc, slot_pos, G, hd, cap)
+        want_k, want_v = torch.full_like(kc, 7.0), torch.full_like(vc, 7.0)
+        qs = b.q_start.tolist()
+        for i, slot in enumerate(b.slots):
+            past, n = int(slot_pos[slot]), b.q_lens[i]
+            for j in range(n):
+                pos = past + j
+                if pos >= past + n - cap:
+                    want_k[slot, :, pos % cap] = kv[qs[i] + j, 0]
+                    want_v[slot, :, pos % cap] = kv[qs[i] + j, 1]
+        assert torch.equal(kc, want_k) and torch.equal(vc, want_v)
 
 
 @pytest.mark.parametrize("dt, tol", [(torch.float32, 3e-6), (torch.bfloat16, 1.6e-2), (torch.float16, 2e-3)])

@@ -120,7 +120,7 @@ def test_block_embedding_and_head(dtype):
     cache = Cache({0: block.mixer.cache_need()}, 1, 160, dtype, DEV)
     cache.acquire(1)
     stream = ResidualStream(rt, x)
-    block.forward(stream, batch, cache.view(0))
+    block.forward(stream, batch, {"mixer": cache.view(0)})
     ref = plain_block(plain_embedding(w["model.embed_tokens.weight"], toks), cfg, w, 1,
                       torch.arange(50))
     tol = 1e-5 if dtype == torch.float32 else 1e-2 * SCALE[dtype]
@@ -191,7 +191,7 @@ def _register_toy():
             spec = super().to_spec()
             toy = PartSpec("toy_decay", {"size": self.hidden_size, "decay": 0.5},
                            {"w": "model.layers.0.toy.weight"})
-            layers = [dataclasses.replace(spec.layers[0], mixer=toy)] + spec.layers[1:]
+            layers = [spec.layers[0].with_parts(mixer=toy)] + spec.layers[1:]
             return dataclasses.replace(spec, layers=layers)
 
     register_architecture("ToyForCausalLM", ToyConfig)
@@ -257,7 +257,7 @@ def test_a_layer_named_twice_and_a_layer_reading_anothers_cache():
     rt = Runtime(torch.float32, DEV)
     m = Model(dataclasses.replace(spec, run_order=[RunEntry(0), RunEntry(1), RunEntry(0)]), rt)
     m.bind(dict(w))
-    assert sorted(m.cache_needs()) == [0, 1, 2]
+    assert sorted(k[0] for k in m.cache_needs()) == [0, 1, 2]
     eng = Engine(m, 1, 128)
     s = eng.acquire(1)
     ref = plain_forward(cfg, w, toks, run_order=[0, 1, 0])
@@ -269,7 +269,7 @@ def test_a_layer_named_twice_and_a_layer_reading_anothers_cache():
     # sharing: the reader's keys/values are the owner's, so its own k/v projections are unused
     m2 = Model(dataclasses.replace(spec, run_order=[RunEntry(0), RunEntry(1), RunEntry(1, 1)]), rt)
     m2.bind(dict(w))
-    assert sorted(m2.cache_needs()) == [0, 1]
+    assert sorted(k[0] for k in m2.cache_needs()) == [0, 1]
     eng2 = Engine(m2, 1, 128)
     s = eng2.acquire(1)
     whole = eng2.step([toks], s, [list(range(40))]).cpu()
@@ -343,14 +343,14 @@ def _register_toy_position_and_routing():
         def to_spec(self):
             spec = super().to_spec()
             l0 = spec.layers[0]
-            mixer = dataclasses.replace(l0.mixer, params=dict(
-                l0.mixer.params, position=PartSpec("no_position", {"head_dim": self.head_dim})))
+            mixer = dataclasses.replace(l0.part("mixer"), params=dict(
+                l0.part("mixer").params, position=PartSpec("no_position", {"head_dim": self.head_dim})))
             names = {"router": "model.layers.0.moe.router.weight"}
             for e in range(2):
                 for k in ("gate", "up", "down"):
                     names[f"{k}{e}"] = f"model.layers.0.moe.experts.{e}.{k}.weight"
             ffn = PartSpec("toy_top1", {"size": self.hidden_size, "ffn": 40, "experts": 2}, names)
-            return dataclasses.replace(spec, layers=[dataclasses.replace(l0, mixer=mixer, feed_forward=ffn)]
+            return dataclasses.replace(spec, layers=[l0.with_parts(mixer=mixer, feed_forward=ffn)]
                                        + spec.layers[1:])
 
     register_architecture("ToyRoutedForCausalLM", ToyRoutedConfig)
@@ -403,3 +403,181 @@ def test_toy_position_encoding_and_routed_feed_forward():
     for p in range(35, 50):
         lg = lm.step([[toks[p]]], s, [[0]]).cpu()
         assert (lg[0] - ref[p]).abs().max() <= 1e-5 * ref.abs().max(), p
+
+
+# ---------------------------------------------------------------------------
+# Two more arrangements that only this file defines: a block with four norms (one
+# before and one after each of mixer and feed-forward), and a mixer that asks the cache
+# for keys/values AND a state of its own (attention plus a decaying sum).
+
+def _register_sandwich_and_kv_state():
+    from yalm_b200.cache import CacheNeed
+    from yalm_b200.config import LayerSpec, LlamaConfig, PartSpec, register_architecture
+    from yalm_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, ResidualStream, make_part,
+                                 register_block, register_mixer)
+    from yalm_b200.weights import TensorNeed
+    if "sandwich" in BLOCKS:
+        return
+
+    @register_block("sandwich")
+    class SandwichBlock:
+        NAMES = ("pre_mixer_norm", "mixer", "post_mixer_norm", "pre_ffn_norm", "feed_forward",
+                 "post_ffn_norm")
+
+        def __init__(self, layer_spec, rt):
+            self.rt, self.spec = rt, layer_spec
+            table = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS}
+            self.p = {n: make_part(table.get(n, NORMS), layer_spec.part(n), rt) for n in self.NAMES}
+
+        def parts(self):
+            return [(self.p[n], self.spec.part(n)) for n in self.NAMES]
+
+        def mixers(self):
+            return {"mixer": self.p["mixer"]}
+
+        def _branch(self, stream, pre, run, post):
+            h = self.p[pre](stream)
+            side = ResidualStream(self.rt, torch.zeros_like(stream.x))
+            later = run(h, side)
+            side.resolve()
+            stream.add_tensor(self.p[post](side, name=post))
+            return later
+
+        def forward(self, stream, batch, views, shared=False):
+            later = self._branch(stream, "pre_mixer_norm",
+                                 lambda h, side: self.p["mixer"].forward(h, batch, side, views["mixer"], shared=shared),
+                                 "post_mixer_norm")
+            self._branch(stream, "pre_ffn_norm",
+                         lambda h, side: self.p["feed_forward"].forward(h, batch, side), "post_ffn_norm")
+            return later
+
+    @register_mixer("toy_kv_state")
+    class AttentionPlusDecay:
+        def __init__(self, params, rt):
+            self.rt, self.D = rt, int(params["hidden_size"])
+            self.attn = MIXERS["gqa_attention"](params, rt)
+
+        def tensor_needs(self):
+            return dict(self.attn.tensor_needs(), s=TensorNeed((self.D, self.D)))
+
+        def bind(self, tensors):
+            self.attn.bind({k: v for k, v in tensors.items() if k != "s"})
+            self.ws = tensors["s"].to(self.rt.device, torch.float32)
+
+        def cache_need(self):
+            return {"kv": self.attn.cache_need(),
+                    "state": CacheNeed("state", state_shape=(self.D,), state_dtype=torch.float32)}
+
+        def forward(self, h, batch, stream, view, shared=False):
+            later = self.attn.forward(h, batch, stream, view["kv"], shared=shared)
+            out = torch.empty(batch.n_tokens, self.D, device=self.rt.device)
+            t = 0
+            for slot, n in zip(batch.slots, batch.q_lens):
+                s = view["state"].state[slot]
+                for _ in range(n):
+                    s = 0.5 * s + h[t].float()
+                    out[t] = self.ws @ s
+                    t += 1
+                view["state"].state[slot] = s
+            stream.add_tensor(out)
+            return later
+
+    class SandwichConfig(LlamaConfig):
+        def to_spec(self):
+            spec = super().to_spec()
+            norm = lambda n: PartSpec("rmsnorm", {"size": self.hidden_size, "eps": self.rms_norm_eps},
+                                      {"weight": n})
+            l0 = spec.layers[0]
+            mixer = dataclasses.replace(l0.part("mixer"), kind="toy_kv_state",
+                                        tensors=dict(l0.part("mixer").tensors, s="model.layers.0.decay.weight"))
+            layer0 = LayerSpec("sandwich", {
+                "pre_mixer_norm": l0.part("mixer_norm"), "mixer": mixer,
+                "post_mixer_norm": norm("model.layers.0.post_mixer_norm.weight"),
+                "pre_ffn_norm": l0.part("feed_forward_norm"), "feed_forward": l0.part("feed_forward"),
+                "post_ffn_norm": norm("model.layers.0.post_ffn_norm.weight")})
+            return dataclasses.replace(spec, layers=[layer0] + spec.layers[1:])
+
+    register_architecture("SandwichForCausalLM", SandwichConfig)
+
+
+def test_a_block_with_four_norms_and_a_mixer_with_keys_values_and_a_state():
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    _register_sandwich_and_kv_state()
+    cfg = dict(TINY_C, architectures=["SandwichForCausalLM"])       # window 40: the kv part is a ring
+    D, H, G, hd, eps = cfg["hidden_size"], 6, 2, 48, cfg["rms_norm_eps"]
+    w = make_weights(cfg, 8)
+    g = torch.Generator().manual_seed(3)
+    w["model.layers.0.decay.weight"] = (0.05 * torch.randn(D, D, generator=g)).to(torch.bfloat16)
+    w["model.layers.0.post_mixer_norm.weight"] = 1.0 + 0.1 * torch.randn(D, generator=g)
+    w["model.layers.0.post_ffn_norm.weight"] = 1.0 + 0.1 * torch.randn(D, generator=g)
+
+    def plain(toks):
+        T = len(toks)
+        p = "model.layers.0"
+        x = plain_embedding(w["model.embed_tokens.weight"], toks)
+        h = plain_rmsnorm(x, w[f"{p}.input_layernorm.weight"], eps)
+        inv = plain_inv_freq(hd, cfg["rope_theta"], None)
+        pos = torch.arange(T)
+        q = plain_rope((h @ w[f"{p}.self_attn.q_proj.weight"].float().T).view(T, H, hd), pos, inv)
+        k = plain_rope((h @ w[f"{p}.self_attn.k_proj.weight"].float().T).view(T, G, hd), pos, inv)
+        v = (h @ w[f"{p}.self_attn.v_proj.weight"].float().T).view(T, G, hd)
+        y = plain_attention(q, k, v, cfg["sliding_window"]).reshape(T, H * hd) @ \
+            w[f"{p}.self_attn.o_proj.weight"].float().T
+        s = torch.zeros(D)
+        for t in range(T):
+            s = 0.5 * s + h[t]
+            y[t] += w[f"{p}.decay.weight"].float() @ s
+        x = x + plain_rmsnorm(y, w[f"{p}.post_mixer_norm.weight"], eps)
+        h = plain_rmsnorm(x, w[f"{p}.post_attention_layernorm.weight"], eps)
+        y = plain_swiglu(h, w[f"{p}.mlp.gate_proj.weight"], w[f"{p}.mlp.up_proj.weight"],
+                         w[f"{p}.mlp.down_proj.weight"])
+        x = x + plain_rmsnorm(y, w[f"{p}.post_ffn_norm.weight"], eps)
+        x = plain_block(x, cfg, w, 1, pos)
+        return plain_rmsnorm(x, w["model.norm.weight"], eps) @ w["lm_head.weight"].float().T
+
+    lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=2)
+    kinds = sorted(g_["need"].kind for g_ in lm.engine.cache.groups)
+    assert kinds == ["kv", "state"]
+    assert sorted(k[2] for k in lm.model.cache_needs() if k[0] == 0) == ["kv", "state"]
+    ta, tb = random_tokens(90, cfg["vocab_size"], 1), random_tokens(33, cfg["vocab_size"], 2)
+    ra, rb = plain(ta), plain(tb)
+    sa, sb = lm.acquire(2)
+    lg = lm.step([ta[:60], tb[:20]], [sa, sb], [[59], [19]]).cpu()
+    assert (lg[0] - ra[59]).abs().max() <= 1e-5 * ra.abs().max()
+    assert (lg[1] - rb[19]).abs().max() <= 1e-5 * rb.abs().max()
+    for p in range(20, 33):                                     # past the ring of 40 for request a
+        lg = lm.step([[ta[40 + p]], [tb[p]]], [sa, sb], [[0], [0]]).cpu()
+        assert (lg[0] - ra[40 + p]).abs().max() <= 1e-5 * ra.abs().max(), p
+        assert (lg[1] - rb[p]).abs().max() <= 1e-5 * rb.abs().max(), p
+    lm.release([sa, sb])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_reader_of_a_windowed_cache_sees_the_old_rows_when_a_prompt_is_cut(dtype):
+    """Run order [0, 1, 2, 2<-2] on a ring of 32 rows: the last entry reads entry 2's
+    keys and values.  A prompt given as 30 + 25 + 1 tokens makes the second portion land
+    on a full ring; the owner's ring write must wait until the reader has run, or the
+    reader's first tokens would find their oldest keys replaced.  Whole and cut agree."""
+    from yalm_b200.config import RunEntry, config_from_dict
+    from yalm_b200.engine.step import Engine
+    from yalm_b200.parts import Model, Runtime
+    from helpers import TINY_B, TOL
+    cfg = dict(TINY_B, tie_word_embeddings=False)
+    w = make_weights(cfg, 21)
+    toks = random_tokens(56, cfg["vocab_size"], 4)
+    spec = config_from_dict(cfg).to_spec()
+    rt = Runtime({"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype], DEV)
+    m = Model(dataclasses.replace(spec, run_order=[RunEntry(0), RunEntry(1), RunEntry(2),
+                                                   RunEntry(2, 2)]), rt)
+    m.bind(dict(w))
+    eng = Engine(m, 1, 96)
+    s = eng.acquire(1)
+    whole = eng.step([toks], s, [list(range(56))]).cpu()
+    eng.release(s)
+    s = eng.acquire(1)
+    cut = torch.cat([eng.step([toks[a:b]], s, [list(range(b - a))]).cpu()
+                     for a, b in ((0, 30), (30, 55), (55, 56))])
+    tol = 2e-5 if dtype == "float32" else TOL[dtype]
+    assert float((cut - whole).abs().max() / whole.abs().max()) <= tol
+    rt.check_status()

@@ -6,8 +6,10 @@
     -h            this help
     -d cuda       device (only cuda: there is no CPU path)
     -m MODE       completion | passkey | perplexity (any prefix; default completion)
-    -T N          context length (0 = the model's); with no window in config.json
-                  the cache still ends there
+    -T N          context length (0 = the model's): the cache keeps the last N positions
+                  of each sequence as a ring (a window of N where config.json sets none or
+                  a longer one) and generation goes on past N, as the reference's -T does,
+                  without its two sink tokens
     -i TEXT       prompt          -f FILE   prompt file   (exactly one of -i, -f, --tokens)
     -n N          completion: tokens to generate (default 256, 0 = up to the context, -1 = no limit
                   but the context); passkey: number of filler lines (default 250)
@@ -16,6 +18,9 @@
   and beyond the reference:
     --tokens 1,2,3        prompt as token ids (works without tokenizer.json); several
                           prompts separated by ';' run as a batch
+    --batch-file FILE     one prompt per line (token ids separated by commas or blanks, or
+                          text if the model folder has a tokenizer.json): they run as a batch
+    --max-context N       the most positions a sequence may take (default: the model's)
     --dtype bfloat16|float16|float32      --seed N      --max-batch N
     --random-weights CONFIG.json  write <model_dir> (config.json, model.safetensors) from a
                                   configuration and --seed first, if it does not exist
@@ -43,12 +48,14 @@ def parse(argv):
         usage(0 if argv else 1)
     o = {"model": argv[0], "device": "cuda", "mode": "completion", "context": 0, "prompt": None,
          "file": None, "n": None, "temperature": 1.0, "line": -1, "tokens": None,
-         "dtype": "bfloat16", "seed": None, "max_batch": 8, "random_weights": None}
+         "dtype": "bfloat16", "seed": None, "max_batch": 8, "random_weights": None,
+         "batch_file": None, "max_context": 0}
     i = 1
     short = {"-d": "device", "-m": "mode", "-T": "context", "-i": "prompt", "-f": "file", "-n": "n",
              "-t": "temperature", "-l": "line"}
     long = {"--tokens": "tokens", "--dtype": "dtype", "--seed": "seed", "--max-batch": "max_batch",
-            "--random-weights": "random_weights", "--max-new-tokens": "n"}
+            "--random-weights": "random_weights", "--max-new-tokens": "n",
+            "--batch-file": "batch_file", "--max-context": "max_context"}
     while i < len(argv):
         flag = argv[i]
         if flag == "-h":
@@ -57,7 +64,7 @@ def parse(argv):
         if key is None or i + 1 >= len(argv):          # every option takes a value
             usage()
         val = argv[i + 1]
-        if key in ("context", "n", "line", "seed", "max_batch"):
+        if key in ("context", "n", "line", "seed", "max_batch", "max_context"):
             val = int(val)
         elif key == "temperature":
             val = float(val)
@@ -82,8 +89,8 @@ def main(argv=None) -> int:
         print(f"wrote a random model to {o['model']}")
     from .engine.lm import LM
     from .tokenizer import Tokenizer
-    lm = LM.from_pretrained(o["model"], dtype=o["dtype"], max_context=o["context"] or None,
-                            max_batch=o["max_batch"])
+    lm = LM.from_pretrained(o["model"], dtype=o["dtype"], max_context=o["max_context"] or None,
+                            window_override=o["context"] or None, max_batch=o["max_batch"])
     spec = lm.spec
     # a packed one-file model keeps its tokenizer.json beside it
     tok_dir = os.path.dirname(os.path.abspath(o["model"])) if os.path.isfile(o["model"]) else o["model"]
@@ -92,10 +99,22 @@ def main(argv=None) -> int:
     print(f"model: {spec.architecture}, {len(spec.layers)} layers, context {lm.context}, "
           f"{lm.model.weight_bytes() / 1e9:.2f} GB weights, {lm.engine.cache.bytes() / 1e9:.2f} GB cache")
 
+    def ids_or_text(line):
+        parts = line.replace(",", " ").split()
+        if parts and all(p.lstrip("-").isdigit() for p in parts):
+            return [int(p) for p in parts]
+        if tok is None:
+            sys.stderr.write("no tokenizer.json in the model folder: give prompts as token ids\n")
+            sys.exit(1)
+        return tok.encode(line, bos=True)
+
     def prompts_from_options():
-        given = [x is not None for x in (o["prompt"], o["file"], o["tokens"])]
+        given = [x is not None for x in (o["prompt"], o["file"], o["tokens"], o["batch_file"])]
         if sum(given) != 1:
             usage()
+        if o["batch_file"] is not None:
+            with open(o["batch_file"]) as f:
+                return [ids_or_text(l.rstrip("\n")) for l in f if l.strip()]
         if o["tokens"] is not None:
             return [[int(t) for t in part.replace(",", " ").split()] for part in o["tokens"].split(";")]
         text = o["prompt"] if o["prompt"] is not None else open(o["file"]).read()
@@ -108,7 +127,7 @@ def main(argv=None) -> int:
         prompts = prompts_from_options()
         n = 256 if o["n"] is None else o["n"]
         if n == 0:
-            n = lm.context
+            n = o["context"] or lm.context              # "-n 0": as many steps as the context (-T) is long
         stop = tok.stop_ids if tok is not None else list(spec.stop_token_ids)
         last = {}
 

@@ -1,8 +1,9 @@
 """The cache: per-sequence slots, keys and values per layer run, each
 sequence's own length, and fixed-size per-sequence state beside them.
 
-What a mixer needs is declared by the mixer (``CacheNeed``); run entries with
-equal needs share one *group*, which has storage of its own:
+What a mixer needs is declared by the mixer (one ``CacheNeed``, or several by
+name: keys and values AND a state, two states of different types); needs that are
+equal share one *group*, which has storage of its own:
 
 * ``kv`` groups hold ``K, V : [entries, slots, kv_heads, capacity, head_dim]``.
   ``capacity`` is the window when the mixer has one (the slot is then a ring:
@@ -60,12 +61,27 @@ class CacheView:
     kv_step: Optional[torch.Tensor] = None     # this step's keys/values, kept for a reader entry
 
 
+def normalise_needs(need) -> Dict[str, CacheNeed]:
+    """What a mixer's ``cache_need()`` may return -- nothing, one need, or several by
+    name -- as a dict.  A single need goes by the name "cache"."""
+    if need is None:
+        return {}
+    if isinstance(need, CacheNeed):
+        return {"cache": need}
+    out = dict(need)
+    for name, n in out.items():
+        if not isinstance(n, CacheNeed):
+            raise TypeError(f"cache need {name!r} is a {type(n).__name__}, not a CacheNeed")
+    return out
+
+
 class Cache:
-    def __init__(self, needs: Dict[int, CacheNeed], n_slots: int, context: int,
+    def __init__(self, needs: Dict[object, CacheNeed], n_slots: int, context: int,
                  dtype: torch.dtype, device):
-        """``needs`` maps a run-entry index to its need (entries that read
-        another entry's cache are absent).  ``context`` is the most positions
-        one sequence may take."""
+        """``needs`` maps a key to a need.  The model's keys are (run entry, mixer
+        name, need name); any hashable, sortable key will do (entries that read
+        another entry's cache are absent).  ``context`` is the most positions one
+        sequence may take."""
         self.n_slots = n_slots
         self.context = context
         self.dtype = dtype
@@ -74,7 +90,7 @@ class Cache:
         self.slot_pos = torch.zeros(n_slots, dtype=torch.int32, device=self.device)
         self.host_pos = [0] * n_slots          # the host's copy of slot_pos
         self.groups: List[dict] = []
-        self._entry: Dict[int, Tuple[int, int]] = {}
+        self._entry: Dict[object, Tuple[int, int]] = {}
         by_key: Dict[tuple, int] = {}
         for entry in sorted(needs):
             need = needs[entry]
@@ -109,7 +125,7 @@ class Cache:
         return total
 
     @staticmethod
-    def bytes_needed(needs: Dict[int, CacheNeed], n_slots: int, context: int,
+    def bytes_needed(needs: Dict[object, CacheNeed], n_slots: int, context: int,
                      dtype: torch.dtype) -> int:
         esz = torch.empty((), dtype=dtype).element_size()
         total = 0
@@ -139,9 +155,9 @@ class Cache:
         self.slots.release(slots)
 
     # -- views ---------------------------------------------------------------
-    def view(self, entry: int) -> CacheView:
+    def view(self, entry) -> CacheView:
         if entry not in self._entry:
-            raise KeyError(f"run entry {entry} owns no cache")
+            raise KeyError(f"{entry!r} owns no cache")
         gi, i = self._entry[entry]
         g = self.groups[gi]
         if g["need"].kind == "kv":

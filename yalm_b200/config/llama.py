@@ -10,7 +10,7 @@ and ``tie_word_embeddings``.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field, asdict
+from dataclasses import asdict, dataclass, field, replace
 from typing import Any, Dict, List, Optional
 
 from .spec import LayerSpec, ModelSpec, PartSpec, RunEntry
@@ -180,6 +180,17 @@ class LlamaConfig:
             d["torch_dtype"] = self.torch_dtype
         return d
 
+    def with_window(self, n: int) -> "LlamaConfig":
+        """The same model with its attention bounded to the last ``n`` positions where
+        the checkpoint sets no window (or a longer one): the role of the reference's
+        ``-T n``, whose cache is a ring of n rows (model.cpp:28-32, infer.cu:1160-1165),
+        here as a pure window without its two sink tokens."""
+        n = int(n)
+        if n <= 0:
+            raise ConfigError(f"a window must be positive, got {n}")
+        own = self.sliding_window
+        return replace(self, sliding_window=n if own is None else min(own, n))
+
     def ignorable_tensor(self, name: str) -> bool:
         """Checkpoint tensors that this architecture does not read and that are no
         error: the rotary frequency buffers some exporters save, and a copy of the
@@ -223,10 +234,10 @@ class LlamaConfig:
                 "up": f"{p}.mlp.up_proj.weight",
                 "down": f"{p}.mlp.down_proj.weight",
             })
-            layers.append(LayerSpec(
-                block="prenorm", mixer=mixer, feed_forward=ffn,
-                mixer_norm=norm(f"{p}.input_layernorm.weight"),
-                feed_forward_norm=norm(f"{p}.post_attention_layernorm.weight")))
+            layers.append(LayerSpec("prenorm", {
+                "mixer_norm": norm(f"{p}.input_layernorm.weight"), "mixer": mixer,
+                "feed_forward_norm": norm(f"{p}.post_attention_layernorm.weight"),
+                "feed_forward": ffn}))
         head_tensors = ({"weight": "model.embed_tokens.weight"} if self.tie_word_embeddings
                         else {"weight": "lm_head.weight"})
         spec = ModelSpec(

@@ -25,14 +25,24 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """A residual block: arrangement ``block`` (a key of the block registry)
-    of a mixer, a feed-forward and their two norms."""
+    """A residual block: an arrangement ``block`` (a key of the block registry)
+    and the parts it arranges, by the names that arrangement gives them.  The
+    ``prenorm`` arrangement has ``mixer_norm``, ``mixer``, ``feed_forward_norm``
+    and ``feed_forward``; another arrangement (four norms, two mixers side by
+    side) names its own."""
 
     block: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    parts: Dict[str, PartSpec]
+
+    def part(self, name: str) -> PartSpec:
+        if name not in self.parts:
+            raise KeyError(f"block {self.block!r} needs a part named {name!r}; "
+                           f"the layer has {sorted(self.parts)}")
+        return self.parts[name]
+
+    def with_parts(self, **parts: PartSpec) -> "LayerSpec":
+        """A copy with some parts replaced or added."""
+        return LayerSpec(self.block, {**self.parts, **parts})
 
 
 @dataclass(frozen=True)

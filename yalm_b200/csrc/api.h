@@ -10,6 +10,9 @@
 extern "C" {
 #endif
 
+// a kernel whose bounded barrier wait runs out after limit_ns (<= 100 ms) and raises
+// ERR_WAIT_TIMEOUT in *status: the status path, for tests
+int yalm_wait_probe(unsigned long long limit_ns, int* status, cudaStream_t stream);
 int yalm_copy_async(void* dst, const void* src, long long bytes, int to_device, cudaStream_t stream);
 int yalm_stream_wait(cudaStream_t stream);
 int yalm_embed(const int* tokens, const void* table, int table_dtype, float* x, int n_tokens,
@@ -27,6 +30,13 @@ int yalm_rope_store(const float* qkv, int n_partials, long long partial_stride,
                     const int* seq_slot, const int* slot_pos, void* q_out, void* kv_step,
                     void* k_cache, void* v_cache, int dtype, int n_tokens, int H, int G, int hd,
                     int capacity, int write_cache, cudaStream_t stream);
+
+// kv_step [N, 2, G, hd] -> the ring rows of the positions the ring keeps (the cache
+// write of yalm_rope_store, on its own: for a ring that may only be written after the
+// attention has read the rows that are replaced)
+int yalm_cache_write(const void* kv_step, const int* token_seq, const int* q_start,
+                     const int* seq_slot, const int* slot_pos, void* k_cache, void* v_cache,
+                     int dtype, int n_tokens, int G, int hd, int capacity, cudaStream_t stream);
 
 int yalm_advance(const int* q_start, const int* seq_slot, int* slot_pos, int n_seqs,
                  cudaStream_t stream);
@@ -65,9 +75,11 @@ int yalm_attention_prefill_tc(const void* q, const void* kv_step, const int* q_s
 int yalm_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* out,
                    int out_dtype, int M, int N, int K, int accumulate, cudaStream_t stream);
 
+// params: null, or two 64-bit words on the device that replace `seed` and `temperature`
+// (the temperature's float bits in the low half of the second word)
 int yalm_sample(const float* logits, int n_rows, int vocab, float temperature,
-                unsigned long long seed, const int* row_key, const int* seq_slot,
-                const int* slot_pos, int* out_tokens, cudaStream_t stream);
+                unsigned long long seed, const unsigned long long* params, const int* row_key,
+                const int* seq_slot, const int* slot_pos, int* out_tokens, cudaStream_t stream);
 
 float yalm_uniform01(unsigned long long seed, unsigned key, unsigned counter);
 

@@ -116,7 +116,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
                : "memory");
 }
 // Bounded wait; false after the time limit or once another role has given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
   unsigned long long t0 = 0;
   for (uint32_t it = 0;; ++it) {
     uint32_t ok;
@@ -132,7 +133,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       const unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+      else if (now - t0 > limit_ns) { *abort_flag = 1; return false; }
     }
   }
 }

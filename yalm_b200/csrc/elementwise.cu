@@ -356,6 +356,46 @@ __global__ void rope_store_many_kernel(const float* __restrict__ qkv, const floa
   }
 }
 
+// ------------------------------------------------- ring rows from the step's buffer
+// Copies this step's keys and values (kv_step [N, 2, G, hd], already rotated) into
+// the cache ring for the positions the ring keeps: what rope_store does on the way
+// when it may write at once.  Used when the ring may only be written after the
+// attention (several tokens on top of a ring that already wrapped).  One block per
+// token; 16-byte copies when rows allow it.
+template <typename T>
+__global__ void cache_write_kernel(const T* __restrict__ kv_step, const int* __restrict__ token_seq,
+                                   const int* __restrict__ q_start, const int* __restrict__ seq_slot,
+                                   const int* __restrict__ slot_pos, T* __restrict__ k_cache,
+                                   T* __restrict__ v_cache, int G, int hd, int capacity, int vec) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int b = token_seq[t];
+  const int slot = seq_slot[b];
+  const int qs = q_start[b], q_end = q_start[b + 1];
+  const int past = slot_pos[slot];
+  const int pos = past + (t - qs);
+  if (pos < past + (q_end - qs) - capacity) return;          // the ring keeps only the last rows
+  const size_t row = (size_t)(pos % capacity) * hd;
+  const T* src = kv_step + (size_t)t * 2 * G * hd;
+  if (vec) {
+    constexpr int E = 16 / sizeof(T);
+    const int per_head = hd / E;
+    for (int i = threadIdx.x; i < 2 * G * per_head; i += blockDim.x) {
+      const int kv = i / (G * per_head), g = (i / per_head) % G, c = i % per_head;
+      T* dst = (kv ? v_cache : k_cache) + ((size_t)slot * G + g) * capacity * hd + row;
+      reinterpret_cast<uint4*>(dst)[c] =
+          reinterpret_cast<const uint4*>(src + ((size_t)kv * G + g) * hd)[c];
+    }
+  } else {
+    for (int i = threadIdx.x; i < 2 * G * hd; i += blockDim.x) {
+      const int kv = i / (G * hd), g = (i / hd) % G, c = i % hd;
+      T* dst = (kv ? v_cache : k_cache) + ((size_t)slot * G + g) * capacity * hd + row;
+      dst[c] = src[((size_t)kv * G + g) * hd + c];
+    }
+  }
+}
+
 __global__ void advance_kernel(const int* __restrict__ q_start, const int* __restrict__ seq_slot,
                                int* __restrict__ slot_pos, int n_seqs) {
   // No early start for what follows: this is the one kernel that writes the positions, and
@@ -365,9 +405,34 @@ __global__ void advance_kernel(const int* __restrict__ q_start, const int* __res
   if (b < n_seqs) slot_pos[seq_slot[b]] += q_start[b + 1] - q_start[b];
 }
 
+// The bounded wait of common.cuh on its own: one thread waits on a barrier that nobody
+// arrives on, gives up after limit_ns, and raises ERR_WAIT_TIMEOUT in the status word,
+// exactly as a kernel's role does when a copy or a product never completes.  It returns by
+// itself; nothing is trapped and nothing waits without a limit.
+__global__ void wait_probe_kernel(unsigned long long limit_ns, int* __restrict__ status) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    volatile int* abort_p = &abort_flag;
+    if (!mbar_wait(smem_u32(&bar), 0, abort_p, limit_ns)) atomicOr(status, ERR_WAIT_TIMEOUT);
+  }
+}
+
 }  // namespace yalm
 
 using namespace yalm;
+
+// For tests of the status path: a kernel whose bounded wait runs out after limit_ns
+// (at most 100 ms) and reports it in `status`.
+extern "C" int yalm_wait_probe(unsigned long long limit_ns, int* status, cudaStream_t stream) {
+  if (limit_ns == 0 || limit_ns > 100000000ull) return -2;
+  wait_probe_kernel<<<1, 32, 0, stream>>>(limit_ns, status);
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
 
 // Programmatic dependent launch on (1, the default) or off (0: every kernel starts
 // only after the previous one has ended, as a plain stream launch does).
@@ -533,6 +598,29 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
     if (vec) YALM_ROPE(__half, 4); else YALM_ROPE(__half, 1);
   }
 #undef YALM_ROPE
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int yalm_cache_write(const void* kv_step, const int* token_seq, const int* q_start,
+                                const int* seq_slot, const int* slot_pos, void* k_cache,
+                                void* v_cache, int dtype, int n_tokens, int G, int hd,
+                                int capacity, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (G <= 0 || hd <= 0 || capacity <= 0) return -2;
+  const int esz = dtype == DT_F32 ? 4 : 2;
+  const int vec = (hd * esz) % 16 == 0 &&
+                  ((((uintptr_t)kv_step) | ((uintptr_t)k_cache) | ((uintptr_t)v_cache)) & 15) == 0;
+  const dim3 grid(n_tokens), block(128);
+  if (dtype == DT_F32)
+    launch_pdl(cache_write_kernel<float>, grid, block, 0, stream, (const float*)kv_step, token_seq,
+               q_start, seq_slot, slot_pos, (float*)k_cache, (float*)v_cache, G, hd, capacity, vec);
+  else if (dtype == DT_BF16 || dtype == DT_F16)          // 16-bit rows are copied as they are
+    launch_pdl(cache_write_kernel<uint16_t>, grid, block, 0, stream, (const uint16_t*)kv_step,
+               token_seq, q_start, seq_slot, slot_pos, (uint16_t*)k_cache, (uint16_t*)v_cache, G,
+               hd, capacity, vec);
+  else
+    return -3;
   YALM_LAUNCH_CHECK();
   return 0;
 }

@@ -50,11 +50,13 @@ _SIGNATURES = {
     "yalm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp],
     "yalm_rmsnorm": [_vp, _vp, _i, _ll, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "yalm_copy_async": [_vp, _vp, _ll, _i, _vp],
+    "yalm_wait_probe": [_ull, _vp, _vp],
     "yalm_stream_wait": [_vp],
     "yalm_silu_mul": [_vp, _i, _ll, _vp, _i, _i, _i, _i, _vp],
     "yalm_rope_store": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                         _i, _i, _i, _vp],
     "yalm_advance": [_vp, _vp, _vp, _i, _vp],
+    "yalm_cache_write": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "yalm_attention": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                        _i, _i, _i, _vp],
     "yalm_attention_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
@@ -65,7 +67,7 @@ _SIGNATURES = {
     "yalm_attention_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _i, _vp],
     "yalm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
-    "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp],
+    "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp, _vp],
     "yalm_gemm_tc": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_gemm_tc_available": [],
     "yalm_gemm_2sm": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp],
@@ -167,6 +169,12 @@ def copy_async(dst_ptr: int, src_ptr: int, n_bytes: int, to_device: bool) -> Non
            "copy_async", kernels=0)
 
 
+def wait_probe(limit_ns: int, status: torch.Tensor) -> None:
+    """Launches a kernel whose bounded barrier wait runs out after ``limit_ns`` and raises
+    ERR_WAIT_TIMEOUT in ``status`` (the path a stuck copy or product would take)."""
+    _check(lib().yalm_wait_probe(int(limit_ns), _p(status), _stream()), "wait_probe")
+
+
 def stream_wait() -> None:
     _check(lib().yalm_stream_wait(_stream()), "stream_wait", kernels=0)
 
@@ -198,6 +206,20 @@ def rope_store(qkv: torch.Tensor, n_partials: int, inv_freq: torch.Tensor, batch
                                  _p(slot_pos), _p(q_out), _p(kv_step), _p(k_cache), _p(v_cache),
                                  dtype_code(q_out.dtype), n, H, G, hd, capacity,
                                  1 if write_cache else 0, _stream()), "rope_store")
+
+
+def cache_write(kv_step: torch.Tensor, batch, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                slot_pos: torch.Tensor, G: int, hd: int, capacity: int) -> None:
+    """This step's keys and values (kv_step [N, 2, G, hd]) into the ring rows of the
+    positions the ring keeps; positions are those before the step's advance."""
+    n = kv_step.shape[0]
+    _need(kv_step.dtype == k_cache.dtype == v_cache.dtype and kv_step.is_contiguous()
+          and k_cache.is_contiguous() and v_cache.is_contiguous()
+          and kv_step.numel() == n * 2 * G * hd, "cache_write: kv_step [N, 2, G, hd] and the cache")
+    _check(lib().yalm_cache_write(_p(kv_step), _p(batch.token_seq), _p(batch.q_start),
+                                  _p(batch.seq_slot), _p(slot_pos), _p(k_cache), _p(v_cache),
+                                  dtype_code(kv_step.dtype), n, G, hd, capacity, _stream()),
+           "cache_write")
 
 
 def advance(batch, slot_pos: torch.Tensor) -> None:
@@ -361,13 +383,28 @@ def gemm_2sm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
 
 
 def sample(logits: torch.Tensor, temperature: float, seed: int, row_key: torch.Tensor,
-           seq_slot: torch.Tensor, slot_pos: torch.Tensor, out_tokens: torch.Tensor) -> None:
+           seq_slot: torch.Tensor, slot_pos: torch.Tensor, out_tokens: torch.Tensor,
+           params: Optional[torch.Tensor] = None) -> None:
+    """``params``: int64 [2] on the device holding (seed, temperature bits), which then
+    replace the two arguments (see ``sampling_params``)."""
     rows, vocab = logits.shape
     _need(logits.dtype == torch.float32 and logits.is_contiguous() and out_tokens.dtype == torch.int32
           and row_key.dtype == torch.int32, "sample: types")
+    _need(params is None or (params.dtype == torch.int64 and params.numel() >= 2),
+          "sample: params is int64 [2]")
     _check(lib().yalm_sample(_p(logits), rows, vocab, float(temperature), int(seed) & (2 ** 64 - 1),
-                             _p(row_key), _p(seq_slot), _p(slot_pos), _p(out_tokens), _stream()),
-           "sample")
+                             _p(params), _p(row_key), _p(seq_slot), _p(slot_pos), _p(out_tokens),
+                             _stream()), "sample")
+
+
+def sampling_params(temperature: float, seed: int):
+    """The two 64-bit words ``sample`` reads from ``params`` (as signed Python ints)."""
+    import struct
+    if temperature < 0:
+        raise KernelError("sample: the temperature must not be negative")
+    s = int(seed) & (2 ** 64 - 1)
+    s = s - 2 ** 64 if s >= 2 ** 63 else s
+    return s, struct.unpack("<I", struct.pack("<f", float(temperature)))[0]
 
 
 def set_pdl(on: bool) -> None:

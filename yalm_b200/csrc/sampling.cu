@@ -30,11 +30,17 @@ static_assert(SAMPLE_THREADS == 1024, "the scan over the warps' sums assumes 32 
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int vocab, float temperature,
-              unsigned long long seed, const int* __restrict__ row_key,
-              const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
-              int* __restrict__ out_tokens) {
+              unsigned long long seed, const unsigned long long* __restrict__ params,
+              const int* __restrict__ row_key, const int* __restrict__ seq_slot,
+              const int* __restrict__ slot_pos, int* __restrict__ out_tokens) {
   pdl_launch_dependents();
   pdl_wait();
+  if (params != nullptr) {
+    // seed and temperature from device memory (written by a host copy): a captured
+    // launch then serves every seed and temperature
+    seed = params[0];
+    temperature = __uint_as_float((unsigned)params[1]);
+  }
   __shared__ float red_v[SAMPLE_THREADS];
   __shared__ int red_i[SAMPLE_THREADS];
   __shared__ int result;
@@ -131,13 +137,16 @@ sample_kernel(const float* __restrict__ logits, int vocab, float temperature,
 
 using namespace yalm;
 
+// params: null, or two 64-bit words on the device that replace the arguments: the seed, and
+// the temperature's 32 bits in the low half of the second word.
 extern "C" int yalm_sample(const float* logits, int n_rows, int vocab, float temperature,
-                           unsigned long long seed, const int* row_key, const int* seq_slot,
-                           const int* slot_pos, int* out_tokens, cudaStream_t stream) {
+                           unsigned long long seed, const unsigned long long* params,
+                           const int* row_key, const int* seq_slot, const int* slot_pos,
+                           int* out_tokens, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (vocab <= 0 || temperature < 0.f) return -2;
-  launch_pdl(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, vocab, temperature, seed, row_key,
-                                                      seq_slot, slot_pos, out_tokens);
+  launch_pdl(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, vocab,
+             temperature, seed, params, row_key, seq_slot, slot_pos, out_tokens);
   YALM_LAUNCH_CHECK();
   return 0;
 }

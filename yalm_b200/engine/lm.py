@@ -39,7 +39,17 @@ def _dtype(d) -> torch.dtype:
 class LM:
     def __init__(self, config: Any, tensors: Dict[str, torch.Tensor], dtype="bfloat16",
                  max_context: Optional[int] = None, max_batch: int = 8, device="cuda:0",
-                 gemm: str = "auto", attention: str = "auto", float32_matrices: str = "keep"):
+                 gemm: str = "auto", attention: str = "auto", float32_matrices: str = "keep",
+                 window_override: Optional[int] = None):
+        """``max_context``: the most positions a sequence may take (at most the model's).
+        ``window_override=n``: attention parts without a window (or with a longer one)
+        see only the last n positions, so the cache is a ring of n rows per sequence
+        and generation goes on past n: the role of the reference's ``-T n``
+        (model.cpp:28-32), as a pure window."""
+        if window_override:
+            if not hasattr(config, "with_window"):
+                raise ValueError(f"{type(config).__name__} has no window to impose")
+            config = config.with_window(int(window_override))
         self.config = config
         self.spec = config.to_spec()
         self.rt = Runtime(_dtype(dtype), device, gemm=gemm, attention=attention,
@@ -124,23 +134,36 @@ class LM:
                            "h2d_bytes": backend.h2d_bytes, "d2h_bytes": backend.d2h_bytes}
         return out
 
-    def perplexity(self, tokens: Sequence[int]):
-        """exp(-mean log p(next token)) over one sequence and its error
-        estimate, as the reference's perplexity mode (main.cpp:201-218)."""
+    def perplexity(self, tokens: Sequence[int], chunk: int = 2048):
+        """exp(-mean log p(next token)) over one text and its error estimate, as the
+        reference's perplexity mode (main.cpp:150-235), which walks a text of any length."""
+        tokens = list(tokens)
         if len(tokens) < 2:
             raise ValueError("perplexity needs at least two tokens")
-        if len(tokens) > self.context:
-            raise ValueError(f"{len(tokens)} tokens exceed the context {self.context}")
-        slot = self.acquire(1)
-        try:
-            logits = self.step([list(tokens)], slot, [list(range(len(tokens) - 1))])
-        finally:
-            self.release(slot)
-        lp = torch.log_softmax(logits.double(), -1)
-        nxt = torch.tensor(list(tokens[1:]), device=lp.device)
-        vals = lp.gather(1, nxt[:, None])[:, 0]
-        n = vals.numel()
-        s, ss = vals.sum().item(), (vals * vals).sum().item()
+        # The text runs through the step function in portions of at most `chunk` tokens
+        # (that bounds the logits held at once).  A text longer than the context is cut
+        # into sequences of `context` tokens that overlap by one token, so that every
+        # token but the first is predicted exactly once; each starts from an empty cache.
+        C = self.context
+        s = ss = 0.0
+        n = 0
+        start = 0
+        while start < len(tokens) - 1:
+            seg = tokens[start:start + C]
+            slot = self.acquire(1)
+            try:
+                for a in range(0, len(seg) - 1, chunk):
+                    b = min(len(seg) - 1, a + chunk)
+                    logits = self.step([seg[a:b]], slot, [list(range(b - a))])
+                    lp = torch.log_softmax(logits.double(), -1)
+                    nxt = torch.tensor(seg[a + 1:b + 1], device=lp.device)
+                    vals = lp.gather(1, nxt[:, None])[:, 0]
+                    s += vals.sum().item()
+                    ss += (vals * vals).sum().item()
+                    n += vals.numel()
+            finally:
+                self.release(slot)
+            start += len(seg) - 1
         ppl = math.exp(-s / n)
         return ppl, ppl * math.sqrt(max(0.0, (ss - s * s / n) / n / n))
 
@@ -168,13 +191,13 @@ class _DeviceBackend:
         self.d2h_bytes = 0
 
     def begin(self, prompts, keys):
-        """Prefill and first tokens.  On the device the batch's rows are ordered longest
-        sequence first (the decode attention's grid takes them in row order, and long
-        blocks that start last leave the SMs idle at the end); `rank` maps the caller's
-        order to that one.  All sequences grow alike, so the order holds for the batch's life."""
+        """Prefill and first tokens.  The batch's rows sit on the device in the order the
+        model's mixers ask for (the attention part: longest sequence first); `rank` maps
+        the caller's order to that one.  All sequences grow alike, so the order holds for
+        the batch's life."""
         eng = self.engine
         B = len(prompts)
-        order = sorted(range(B), key=lambda i: -len(prompts[i]))
+        order = self.lm.model.row_order([len(p) for p in prompts])
         slots = eng.acquire(B)
         try:
             t0 = time.perf_counter()

@@ -14,6 +14,7 @@ host only reads tokens back.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -50,8 +51,9 @@ class Engine:
                     f"ask for fewer sequences (max_batch) or a shorter context (max_context)")
         self.cache = Cache(needs, n_slots, self.context, self.rt.dtype, self.rt.device)
         self.vocab = model.spec.vocab_size
-        self._graphs: Dict[tuple, dict] = {}
+        self._graphs: "OrderedDict[tuple, dict]" = OrderedDict()    # least recently used first
         self._graph_seen: Dict[tuple, int] = {}
+        self._sampling = None                 # (temperature, seed) now on the device
         self._dec: Optional[dict] = None
         self.use_graphs = True
 
@@ -107,6 +109,8 @@ class Engine:
                 "row_key": torch.zeros(n, dtype=torch.int32, device=dev),
                 "arange": torch.arange(n + 1, dtype=torch.int32, device=dev),
                 "logits": torch.empty((n, self.vocab), dtype=torch.float32, device=dev),
+                "sample_params": torch.zeros(2, dtype=torch.int64, device=dev),
+                "host_params": torch.zeros(2, dtype=torch.int64).pin_memory(),
                 "host": torch.zeros(3 * n, dtype=torch.int32).pin_memory(),
                 "host_out": torch.zeros(n, dtype=torch.int32).pin_memory(),
             }
@@ -114,7 +118,8 @@ class Engine:
             self._dec["host_np"] = self._dec["host"].numpy()
             self._dec["host_out_np"] = self._dec["host_out"].numpy()
             self._dec["ptr"] = {k: self._dec[k].data_ptr()
-                                for k in ("tokens", "seq_slot", "row_key", "host", "host_out")}
+                                for k in ("tokens", "seq_slot", "row_key", "host", "host_out",
+                                          "sample_params", "host_params")}
         return self._dec
 
     def set_decode_batch(self, tokens: Sequence[int], slots: Sequence[int],
@@ -151,6 +156,18 @@ class Engine:
 
     CTX_BUCKET = 512
     GRAPH_AFTER = 3       # a decode shape is captured on its third step
+    MAX_GRAPHS = 16       # captured decode shapes kept (the least recently used goes first)
+
+    def _set_sampling(self, temperature: float, seed: int) -> None:
+        """Seed and temperature live on the device, where the sampling kernel reads them:
+        a captured step serves every seed and temperature."""
+        if self._sampling == (temperature, seed):
+            return
+        d = self._decode_buffers()
+        d["host_params"][0], d["host_params"][1] = ops.sampling_params(temperature, seed)
+        ops.copy_async(d["ptr"]["sample_params"], d["ptr"]["host_params"], 16, True)
+        ops.stream_wait()                     # the pinned words may change again right away
+        self._sampling = (temperature, seed)
 
     def _ctx_bucket(self, past: Sequence[int]) -> int:
         """The longest sequence after this step, rounded up: launches sized by it
@@ -158,14 +175,14 @@ class Engine:
         longest = max(past) + 1
         return min(self.context, -(-longest // self.CTX_BUCKET) * self.CTX_BUCKET)
 
-    def _decode_body(self, B: int, temperature: float, seed: int) -> None:
+    def _decode_body(self, B: int) -> None:
         d = self._decode_buffers()
         batch = self._decode_batch(B)
         logits = self.model.forward(batch, self.cache, batch.want_rows, B, logits_out=d["logits"][:B])
         ops.advance(batch, self.cache.slot_pos)
         # the new token goes where the next step's embedding reads it
-        ops.sample(logits, temperature, seed, d["row_key"][:B], batch.seq_slot,
-                   self.cache.slot_pos, d["tokens"][:B])
+        ops.sample(logits, 0.0, 0, d["row_key"][:B], batch.seq_slot, self.cache.slot_pos,
+                   d["tokens"][:B], params=d["sample_params"])
 
     def decode_step(self, B: int, temperature: float, seed: int) -> None:
         """One decode step of the B sequences set by ``set_decode_batch``: their
@@ -175,38 +192,43 @@ class Engine:
         for s in d["slots_host"][:B]:
             if self.cache.host_pos[s] + 1 > self.context:
                 raise StepError(f"the sequence in slot {s} is at the context's end ({self.context})")
+        self._set_sampling(float(temperature), int(seed))
         if not self.use_graphs:
-            self._decode_body(B, temperature, seed)
+            self._decode_body(B)
         else:
-            key = (B, float(temperature), int(seed),
-                   self._ctx_bucket([self.cache.host_pos[s] for s in d["slots_host"][:B]]))
+            key = (B, self._ctx_bucket([self.cache.host_pos[s] for s in d["slots_host"][:B]]))
             g = self._graphs.get(key)
             if g is not None and g["generation"] != self.rt.buffer_generation:
-                g = None                      # a scratch buffer moved since the capture
+                del self._graphs[key]         # a scratch buffer moved since the capture
+                g = None
             seen = self._graph_seen.get(key, 0) + 1
             self._graph_seen[key] = seen
             if g is None and seen < self.GRAPH_AFTER:
                 # a shape that may not last (a batch that is shrinking step by step): not
                 # worth a capture yet
-                self._decode_body(B, temperature, seed)
+                self._decode_body(B)
             elif g is None:
                 # this step runs eagerly once more (every scratch buffer has its final
                 # size); then the same launches are captured for replays
-                self._decode_body(B, temperature, seed)
+                self._decode_body(B)
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
                 self.rt.frozen = True
                 before = ops.LAUNCHES
                 try:
                     with torch.cuda.graph(graph):
-                        self._decode_body(B, temperature, seed)
+                        self._decode_body(B)
                 finally:
                     self.rt.frozen = False
                 captured = ops.LAUNCHES - before
                 ops.LAUNCHES = before             # capturing launches nothing
                 self._graphs[key] = {"graph": graph, "generation": self.rt.buffer_generation,
                                      "kernels": captured}
+                while len(self._graphs) > self.MAX_GRAPHS:
+                    old, _ = self._graphs.popitem(last=False)
+                    self._graph_seen.pop(old, None)
             else:
+                self._graphs.move_to_end(key)
                 g["graph"].replay()
                 ops.LAUNCHES += g["kernels"]
         for s in d["slots_host"][:B]:

@@ -77,7 +77,27 @@ class GQAAttention:
             cpc += 1
         return cpc
 
-    def forward(self, h, batch, stream, view, shared: bool = False) -> None:
+    # The decode kernel's grid takes sequences in row order, and long blocks that start
+    # last leave the SMs idle at the end: the generation loop orders a batch by this.
+    prefers_longest_first = True
+
+    def cache_read_bytes(self, contexts, element_size: int) -> int:
+        """Bytes of keys and values one decode step reads for sequences of these lengths."""
+        seen = sum(min(c, self.window) if self.window else c for c in contexts)
+        return seen * 2 * self.G * self.hd * element_size
+
+    def flops(self, q_lens, past) -> float:
+        """Multiply-adds times two of a step: the four projections and, for each query,
+        scores and value mix over the keys it sees."""
+        n = sum(q_lens)
+        linear = 2.0 * n * ((self.H + 2 * self.G) * self.hd * self.D + self.D * self.H * self.hd)
+        pairs = 0
+        for q, p in zip(q_lens, past):
+            for pos in range(p, p + q):
+                pairs += min(pos + 1, self.window) if self.window else pos + 1
+        return linear + 4.0 * self.H * self.hd * pairs
+
+    def forward(self, h, batch, stream, view, shared: bool = False):
         rt, H, G, hd = self.rt, self.H, self.G, self.hd
         n = batch.n_tokens
         qkv, S = matmul_partials(rt, h, self.w_qkv, "qkv")
@@ -87,7 +107,8 @@ class GQAAttention:
             rt.buffer("kv_step", (n, 2, G, hd), rt.dtype)
         # Several tokens on top of a ring that is already full: their rows would
         # replace keys that the first of them still has to see, so the ring is
-        # written after the attention instead of before it.
+        # written after the attention instead of before it -- and after every later
+        # run entry that reads this cache: then the write is handed back to the model.
         late_write = (not shared) and any(
             p > 0 and ql > 1 and p + ql > view.capacity for p, ql in zip(batch.past, batch.q_lens))
         if shared:
@@ -132,6 +153,11 @@ class GQAAttention:
         else:
             ops.attention(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
                           view.capacity, self.window, 1, None, None)
-        if late_write:
-            self.position.rotate_and_store(qkv, S, batch, view, q, kv_step, H, G, write_cache=True)
         stream.add_linear(o, self.w_o)
+        if late_write:
+            def write_ring():
+                ops.cache_write(kv_step, batch, view.k, view.v, view.slot_pos, G, hd, view.capacity)
+            if getattr(view, "kv_step", None) is not None:
+                return write_ring                  # other run entries still read the old rows
+            write_ring()
+        return None

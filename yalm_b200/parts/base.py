@@ -9,12 +9,21 @@ about the model it sits in.  Interfaces (duck-typed):
   device in the type it computes with);
 * norm: ``__call__(stream, rows=None) -> h`` (normalised rows in the compute
   type; folds the stream's pending partial sums in);
-* mixer: ``cache_need() -> CacheNeed | None`` and
-  ``forward(h, batch, stream, cache_view, shared=False)``, which must add its
-  output to ``stream`` (``stream.add_linear`` or ``stream.add_tensor``);
+* mixer: ``cache_need() -> None | CacheNeed | {name: CacheNeed}`` (several needs:
+  keys and values and a state, say) and ``forward(h, batch, stream, view,
+  shared=False)``, which must add its output to ``stream`` (``stream.add_linear``
+  or ``stream.add_tensor``).  ``view`` is one ``CacheView`` for a single need, a
+  dict of them by need name for several, None for none.  ``forward`` returns
+  None, or a function that writes the cache and that the model calls once every
+  run entry that reads this entry's cache has run;
 * feed-forward: ``forward(h, batch, stream)``, likewise;
 * position encoding: owned by the mixer that uses it (see ``position.py``);
-* block: ``forward(stream, batch, cache_view, shared)`` arranging the four.
+* block: ``parts()``, ``mixers() -> {name: mixer}`` and
+  ``forward(stream, batch, views, shared)`` with ``views[name]`` the view of the
+  mixer of that name;
+* optional, for roofline figures: ``flops(q_lens, past)`` on any part and
+  ``cache_read_bytes(contexts, element_size)`` on a mixer; and
+  ``prefers_longest_first`` on a mixer that wants a batch's rows in that order.
 """
 from __future__ import annotations
 

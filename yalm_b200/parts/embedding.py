@@ -44,6 +44,9 @@ class LinearHead:
     def bind(self, tensors) -> None:
         self.weight = self.rt.matrix(tensors["weight"], share=True)
 
+    def flops(self, q_lens, past) -> float:
+        return 2.0 * sum(q_lens) * self.vocab * self.size
+
     def forward(self, h: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         matmul_store(self.rt, h, self.weight, out)
         return out

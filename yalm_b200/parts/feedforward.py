@@ -40,6 +40,9 @@ class SwiGLU:
             self.w_gate_up = self.rt.matrix(torch.cat(parts, 0))
         self.w_down = self.rt.matrix(tensors["down"])
 
+    def flops(self, q_lens, past) -> float:
+        return 2.0 * sum(q_lens) * 3 * self.F * self.D
+
     def forward(self, h, batch, stream) -> None:
         act = self.rt.buffer("ffn_act", (h.shape[0], self.F), self.rt.dtype)
         matmul_silu_mul(self.rt, h, self.w_gate_up, act, self.paired)

@@ -15,6 +15,7 @@ from typing import Dict, Optional
 import torch
 
 from ..cache import Cache, CacheNeed
+from ..cache.storage import normalise_needs
 from ..config import ModelSpec
 from ..weights import TensorNeed, check_tensors
 from .base import (BLOCKS, EMBEDDINGS, HEADS, NORMS, ResidualStream, Runtime, make_part)
@@ -37,6 +38,8 @@ class Model:
         self.head = make_part(HEADS, spec.head, rt)
         self.run_order = list(spec.run_order)
         self._readers = {e.reads_cache_of for e in self.run_order if e.reads_cache_of is not None}
+        self._last_reader = {e.reads_cache_of: i for i, e in enumerate(self.run_order)
+                             if e.reads_cache_of is not None}
 
     # -- weights -------------------------------------------------------------
     def _bound_parts(self):
@@ -70,17 +73,84 @@ class Model:
         self.rt.end_binding()
 
     # -- cache ---------------------------------------------------------------
-    def cache_needs(self) -> Dict[int, CacheNeed]:
-        """Run-entry index -> what its mixer asks of the cache (entries that
-        read another entry's cache own none)."""
+    def cache_needs(self) -> Dict[tuple, CacheNeed]:
+        """(run entry, mixer name, need name) -> what that mixer asks of the cache.  A
+        mixer may declare one need or several by name; entries that read another
+        entry's cache own none."""
         needs = {}
         for i, e in enumerate(self.run_order):
             if e.reads_cache_of is not None:
                 continue
-            need = self.layers[e.layer].mixer.cache_need()
-            if need is not None:
-                needs[i] = need
+            for mname, mixer in self.layers[e.layer].mixers().items():
+                for nname, need in normalise_needs(mixer.cache_need()).items():
+                    needs[(i, mname, nname)] = need
         return needs
+
+    def _views_of(self, owner: int, batch, cache: Cache):
+        """mixer name -> what that mixer sees of run entry ``owner``'s cache: one view,
+        a dict of views by need name, or None."""
+        rt = self.rt
+        out = {}
+        for mname, mixer in self.layers[self.run_order[owner].layer].mixers().items():
+            needs = normalise_needs(mixer.cache_need())
+            got = {}
+            for nname, need in needs.items():
+                view = cache.view((owner, mname, nname))
+                if view.kind == "kv" and owner in self._readers:
+                    # this step's keys and values are kept apart for the entries that read them
+                    view = dataclasses.replace(view, kv_step=rt.buffer(
+                        f"kv_step_{owner}_{mname}_{nname}",
+                        (batch.n_tokens, 2, need.kv_heads, need.head_dim), rt.dtype))
+                got[nname] = view
+            out[mname] = None if not got else (got["cache"] if list(got) == ["cache"] else got)
+        return out
+
+    # -- what a step costs (for roofline figures) ------------------------------
+    def step_bytes(self, contexts) -> int:
+        """Bytes a decode step of sequences with these context lengths has to read:
+        every weight once (of the embedding table one row per sequence) and the cache
+        of the live sequences."""
+        esz = torch.empty((), dtype=self.rt.dtype).element_size()
+        needs = self.tensor_needs()                  # declared shapes: no device needed
+        table_name = self.spec.embedding.tensors.get("weight")
+        tied = table_name in self.spec.head.tensors.values()
+        total = 0
+        for name, need in needs.items():
+            n = 1
+            for d in need.shape:
+                n *= int(d)
+            if name == table_name and not tied:
+                n = len(contexts) * int(need.shape[-1])      # an untied table is read by rows only
+            elif name == table_name:
+                n += len(contexts) * int(need.shape[-1])
+            total += n * (4 if need.init == "ones" else esz)
+        for e in self.run_order:
+            for mixer in self.layers[e.layer].mixers().values():
+                f = getattr(mixer, "cache_read_bytes", None)
+                if f is not None:
+                    total += f(contexts, esz)
+        return total
+
+    def step_flops(self, q_lens, past=None, n_want: int = 1) -> float:
+        """Floating-point operations of one step (products and attention)."""
+        past = [0] * len(q_lens) if past is None else list(past)
+        total = 0.0
+        for e in self.run_order:
+            for part, _ in self.layers[e.layer].parts():
+                f = getattr(part, "flops", None)
+                if f is not None:
+                    total += f(q_lens, past)
+        f = getattr(self.head, "flops", None)
+        return total + (f([n_want], [0]) if f is not None else 0.0)
+
+    def row_order(self, lengths) -> list:
+        """The order in which a batch's sequences should sit in the step's rows: longest
+        first if a mixer asks for it (``prefers_longest_first``), else as given."""
+        idx = list(range(len(lengths)))
+        if any(getattr(m, "prefers_longest_first", False)
+               for layer in self.layers for m in layer.mixers().values()):
+            idx.sort(key=lambda i: -lengths[i])
+        return idx
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
@@ -101,18 +171,18 @@ class Model:
         x = self.embedding.forward(batch)
         stream = ResidualStream(rt, x)
         views = {}
+        deferred: Dict[int, list] = {}      # run entry -> cache writes to make once it has run
         for i, e in enumerate(self.run_order):
             layer = self.layers[e.layer]
             owner = i if e.reads_cache_of is None else e.reads_cache_of
             if owner not in views:
-                need = self.layers[self.run_order[owner].layer].mixer.cache_need()
-                view = cache.view(owner) if need is not None else None
-                if view is not None and view.kind == "kv" and owner in self._readers:
-                    view = dataclasses.replace(view, kv_step=rt.buffer(
-                        f"kv_step_{owner}", (batch.n_tokens, 2, need.kv_heads, need.head_dim),
-                        rt.dtype))
-                views[owner] = view
-            layer.forward(stream, batch, views[owner], shared=e.reads_cache_of is not None)
+                views[owner] = self._views_of(owner, batch, cache)
+            later = layer.forward(stream, batch, views[owner], shared=e.reads_cache_of is not None)
+            if later is not None:
+                # a write the mixer may only make after every entry that reads its cache
+                deferred.setdefault(self._last_reader.get(i, i), []).append(later)
+            for write in deferred.pop(i, []):
+                write()
         if n_want == 0:
             return None
         h = self.final_norm(stream, rows=want_rows, n_rows=n_want, name="final_normed")
