@@ -60,8 +60,9 @@ def test_groups_have_storage_of_their_own_and_state_is_zeroed():
     c = Cache(needs, n_slots=3, context=32, dtype=torch.float32, device="cpu")
     assert len(c.groups) == 3
     full, ring, state = c.view(0), c.view(1), c.view(3)
-    assert full.k.shape == (3, 2, 32, 16) and ring.k.shape == (3, 2, 8, 16)
-    assert full.capacity == 32 and ring.capacity == 8
+    # pages of 64 positions: [kv heads, pages, 64, head size]; one page per slot covers 32 rows
+    assert full.k.shape == (2, 3, 64, 16) and ring.k.shape == (2, 3, 64, 16)
+    assert full.capacity == 32 and ring.capacity == 8 and full.pages.shape == (3, 1)
     assert c.view(2).k.data_ptr() != full.k.data_ptr()          # same group, own layer plane
     assert state.state.shape == (3, 4, 3)
     assert c.bytes() == Cache.bytes_needed(needs, 3, 32, torch.float32)
@@ -78,3 +79,66 @@ def test_groups_have_storage_of_their_own_and_state_is_zeroed():
         c.acquire(1)
     with pytest.raises(KeyError):
         Cache({0: needs[0]}, 1, 8, torch.float32, "cpu").view(5)
+
+
+def test_pages_follow_the_tokens_and_come_back():
+    """A sequence takes a page when it grows into it; a windowed group never takes more
+    than its ring needs; release returns every page; a request beyond the pool changes
+    nothing and says so."""
+    from yalm_b200.cache import CacheFull, PAGE
+    needs = {0: CacheNeed("kv", kv_heads=1, head_dim=8),
+             1: CacheNeed("kv", kv_heads=1, head_dim=8, window=100)}
+    c = Cache(needs, n_slots=4, context=1000, dtype=torch.float32, device="cpu", max_tokens=640)
+    assert c.free_pages() == [10, 8]              # 640 tokens; four rings of two pages
+    a, b = c.acquire(2)
+    c.ensure([a, b], [1, 130])
+    assert c.free_pages() == [10 - 1 - 3, 8 - 1 - 2]
+    c.ensure([a, b], [64, 192])                   # still inside the pages they hold
+    assert c.free_pages() == [6, 5]
+    c.ensure([a], [65])
+    assert c.free_pages() == [5, 4]
+    c.sync_tables()
+    full = c.view(0)
+    held = c.groups[0]["held"]
+    assert full.pages[a, :2].tolist() == held[a] and full.pages[b, :3].tolist() == held[b]
+    assert len(set(held[a]) | set(held[b])) == 5  # no page held twice
+    with pytest.raises(CacheFull, match="more pages"):
+        c.ensure([a, b], [200, 450])              # 2 + 5 more of the first group: only 5 are free
+    assert c.free_pages() == [5, 4]               # nothing was taken
+    c.release([a])
+    assert c.free_pages() == [7, 6]
+    (d,) = c.acquire(1)
+    c.ensure([d], [PAGE * 7])
+    assert c.free_pages() == [0, 4]
+    c.release([b, d])
+    assert c.free_pages() == [10, 8]
+    for g in c.groups:
+        g["pool"].check()
+
+
+def test_random_page_traffic_never_loses_or_duplicates_a_page():
+    rng = random.Random(1)
+    needs = {0: CacheNeed("kv", kv_heads=1, head_dim=8)}
+    c = Cache(needs, n_slots=5, context=640, dtype=torch.float32, device="cpu", max_tokens=1600)
+    from yalm_b200.cache import CacheFull
+    live = {}
+    for _ in range(600):
+        if live and rng.random() < 0.3:
+            s = rng.choice(sorted(live))
+            c.release([s])
+            del live[s]
+        elif len(live) < 5 and rng.random() < 0.4:
+            (s,) = c.acquire(1)
+            live[s] = 0
+        elif live:
+            s = rng.choice(sorted(live))
+            n = min(640, live[s] + rng.randint(1, 200))
+            try:
+                c.ensure([s], [n])
+                live[s] = n
+            except CacheFull:
+                pass
+        held = [p for s in live for p in c.groups[0]["held"][s]]
+        assert len(held) == len(set(held)) == 25 - c.free_pages()[0]
+        assert all(len(c.groups[0]["held"][s]) == -(-live[s] // 64) for s in live)
+        c.groups[0]["pool"].check()

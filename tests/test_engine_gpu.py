@@ -481,3 +481,57 @@ def test_seeds_and_temperatures_share_the_captured_decode_steps():
                                                ignore_eos=True)]
         assert again == outs[sd]
     assert lm.engine.MAX_GRAPHS >= 1
+
+
+def test_pages_are_taken_as_sequences_grow_and_a_full_pool_refuses():
+    """max_tokens = 256 gives four pages of 64 positions to four slots of 128: what fits
+    is decided by the tokens held (each count rounded up to 64), not by slots x context;
+    pages come back when a sequence ends and serve the next one."""
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    from yalm_b200.engine.step import StepError
+    cfg, seed = CONFIGS["tiny_a"]
+    w = make_weights(cfg, seed)
+    V = cfg["vocab_size"]
+    ta, tb, tc = (random_tokens(n, V, 300 + n) for n in (128, 60, 70))
+    ra, rb, rc = (plain_forward(cfg, w, t) for t in (ta, tb, tc))
+    lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=4, max_tokens=256)
+    cache = lm.engine.cache
+    assert cache.free_pages() == [4]
+    sa, sb, sc = lm.acquire(3)
+    lg = lm.step([ta[:100], tb[:60]], [sa, sb], [[99], [59]]).cpu()      # 2 + 1 pages
+    assert cache.free_pages() == [1]
+    assert float((lg[0] - ra[99]).abs().max() / ra.abs().max()) <= TOL["float32"]
+    with pytest.raises(StepError, match="more pages"):
+        lm.step([tc], [sc], [[69]])                                      # would need 2
+    assert cache.free_pages() == [1] and cache.host_pos[sc] == 0         # nothing happened
+    lm.release([sb])                                                     # b's page comes back
+    assert cache.free_pages() == [2]
+    lg = lm.step([tc, ta[100:128]], [sc, sa], [[69], [27]]).cpu()        # c takes both; a stays in its two
+    assert cache.free_pages() == [0]
+    assert float((lg[0] - rc[69]).abs().max() / rc.abs().max()) <= TOL["float32"]
+    assert float((lg[1] - ra[127]).abs().max() / ra.abs().max()) <= TOL["float32"]
+    lm.release([sa, sc])
+    assert cache.free_pages() == [4]
+
+
+def test_every_page_of_every_layer_counts():
+    """Spoiling one page of one layer's keys moves the next token's logits: the compared
+    logits depend on each page that the table names."""
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, seed = CONFIGS["tiny_a"]
+    w = make_weights(cfg, seed)
+    toks = random_tokens(101, cfg["vocab_size"], 17)
+    ref = plain_forward(cfg, w, toks)
+    for layer in range(cfg["num_hidden_layers"]):
+        for which in (0, 1):
+            lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=2)
+            lm.acquire(1)                                                # the request sits in the second slot
+            (s,) = lm.acquire(1)
+            lm.step([toks[:100]], [s], [[]])
+            g = lm.engine.cache.groups[0]
+            page = g["held"][s][which]
+            g["k"][layer, :, page] += 0.5
+            lg = lm.step([toks[100:]], [s], [[0]])[0].cpu()
+            assert float((lg - ref[100]).abs().max() / ref.abs().max()) > 100 * TOL["float32"], (layer, which)

@@ -615,3 +615,101 @@ def test_tcgen05_prefill_attention(ops, H, G, hd, window, dt, eps):
             ref = plain_attention(qq, kk, vv, window)
             got = out[qs[i]:qs[i + 1]].float().cpu().view(-1, H, hd)
             assert (got - ref).abs().max().item() <= 6.4 * eps, (rep, i)
+
+
+def _paged(kc, vc, seed):
+    """The same cache as pages of 64 positions in a shuffled pool: (k pages, v pages, table)."""
+    n_slots, G, cap, hd = kc.shape
+    pps = -(-cap // 64)
+    n_pages = n_slots * pps + 3
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g)[:n_slots * pps].reshape(n_slots, pps)
+    kp = torch.full((G, n_pages, 64, hd), 5.0, device=DEV, dtype=kc.dtype)
+    vp = torch.full_like(kp, 5.0)
+    for s in range(n_slots):
+        for p in range(pps):
+            n = min(64, cap - p * 64)
+            kp[:, perm[s, p], :n] = kc[s, :, p * 64:p * 64 + n]
+            vp[:, perm[s, p], :n] = vc[s, :, p * 64:p * 64 + n]
+    return kp, vp, perm.to(torch.int32).to(DEV).contiguous()
+
+
+def _unpaged(kp, table, cap):
+    n_slots, pps = table.shape
+    out = torch.cat([kp[:, table[s].long()].reshape(1, kp.shape[0], pps * 64, kp.shape[3])
+                     for s in range(n_slots)])
+    return out[:, :, :cap]
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("H, G, hd, cap, window", [(8, 2, 128, 300, None), (6, 3, 48, 100, 100),
+                                                   (4, 4, 16, 70, 33)])
+def test_every_cache_kernel_reads_and_writes_pages_like_rows(ops, dt, H, G, hd, cap, window):
+    """A cache of shuffled 64-position pages behind a page table gives, bit for bit, what
+    the same rows give as one block per sequence: rotary write, ring write, and the four
+    attention kernels (prompts on top of a cache, decode; SIMT and tensor cores)."""
+    from plain_model import plain_inv_freq
+    inv = plain_inv_freq(hd, 10000.0, None).to(DEV)
+    n_slots, slots = 4, [2, 0, 3]
+    g = torch.Generator(device=DEV).manual_seed(cap + hd)
+    kc = torch.randn(n_slots, G, cap, hd, device=DEV, generator=g).to(dt)
+    vc = torch.randn(n_slots, G, cap, hd, device=DEV, generator=g).to(dt)
+    kp, vp, table = _paged(kc, vc, 3)
+    past = [cap - 5, 17, 64] if window else [cap - 40, 17, 64]
+    slot_pos = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+    for s, p in zip(slots, past):
+        slot_pos[s] = p
+    lens = [30, 1, 9] if window else [35, 1, 9]
+    b = B(lens, slots)
+    N = b.n_tokens
+    qkv = torch.randn(N, (H + 2 * G) * hd, device=DEV, generator=g)
+    outs = []
+    for paged in (False, True):
+        K, V, pg = (kp.clone(), vp.clone(), table) if paged else (kc.clone(), vc.clone(), None)
+        q = torch.empty(N, H * hd, device=DEV, dtype=dt)
+        kv = torch.empty(N, 2, G, hd, device=DEV, dtype=dt)
+        ops.rope_store(qkv, 1, inv, b, q, kv, K, V, slot_pos, H, G, hd, cap, write_cache=False, pages=pg)
+        res = []
+        o = torch.empty(N, H * hd, device=DEV, dtype=dt)
+        ops.attention(q, kv, K, V, b, slot_pos, o, H, G, hd, cap, window, 1, pages=pg)
+        res.append(o.clone())
+        if ops.mma_attention_usable(dt, hd):
+            o2 = torch.empty_like(o)
+            ops.attention_prefill_mma(q, kv, K, V, b, slot_pos, o2, H, G, hd, cap, window, pages=pg)
+            res.append(o2)
+        ops.cache_write(kv, b, K, V, slot_pos, G, hd, cap, pages=pg)          # the late ring write
+        K2, V2 = K.clone(), V.clone()
+        ops.rope_store(qkv, 1, inv, b, q, kv, K2, V2, slot_pos, H, G, hd, cap, pages=pg)
+        res += [(_unpaged(K, table, cap) if paged else K), (_unpaged(K2, table, cap) if paged else K2),
+                (_unpaged(V2, table, cap) if paged else V2)]
+        # decode: one more token per sequence on top of what is now cached
+        sp = slot_pos.clone()
+        for s, p, n in zip(slots, past, lens):
+            sp[s] = p + n - 1                                                  # the newest row is cached
+        bd = B([1, 1, 1], slots)
+        qd = torch.randn(3, H * hd, device=DEV, generator=torch.Generator(device=DEV).manual_seed(1)).to(dt)
+        bound = max(p + n for p, n in zip(past, lens))
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        chunk = 32
+        mc = -(-(min(bound, window) if window else bound) // chunk)
+        od = torch.empty(3, H * hd, device=DEV, dtype=dt)
+        ops.attention_decode(qd, K2, V2, bd.seq_slot, sp, od, torch.empty(3 * H * mc * hd, device=DEV),
+                             torch.empty(3 * H * mc * 2, device=DEV),
+                             torch.zeros(3 * G * -(-(H // G) // 4), dtype=torch.int32, device=DEV), status,
+                             H, G, hd, cap, window, chunk, bound, pages=pg)
+        res.append(od)
+        if ops.mma_attention_usable(dt, hd):
+            for cpc in (1, 1000):
+                mp = ops.decode_mma_parts(bound, window, cpc)
+                om = torch.empty(3, H * hd, device=DEV, dtype=dt)
+                ops.attention_decode_mma(qd, K2, V2, bd.seq_slot, sp, om, torch.empty(3 * H * mp * hd, device=DEV),
+                                         torch.empty(3 * H * mp * 2, device=DEV),
+                                         torch.zeros(3 * G * -(-(H // G) // 16), dtype=torch.int32, device=DEV),
+                                         status, H, G, hd, cap, window, bound, cpc, pages=pg)
+                res.append(om)
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        outs.append(res)
+    assert len(outs[0]) == len(outs[1])
+    for i, (a, c) in enumerate(zip(*outs)):
+        assert torch.equal(a, c), i

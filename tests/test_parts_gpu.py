@@ -78,6 +78,8 @@ def test_attention_part_with_its_position_encoding(dtype, window):
     assert (need.kind, need.kv_heads, need.head_dim, need.window) == ("kv", G, hd, window)
     cache = Cache({0: need}, n_slots=1, context=96, dtype=dtype, device=DEV)
     cache.acquire(1)
+    cache.ensure([0], [T])
+    cache.sync_tables()
     h = torch.randn(T, D).to(dtype)
     stream = ResidualStream(rt, torch.zeros(T, D, device=DEV))
     mixer.forward(h.to(DEV), _prefill_batch(T), stream, cache.view(0))
@@ -94,7 +96,7 @@ def test_attention_part_with_its_position_encoding(dtype, window):
     # the ring holds the last `capacity` rotated keys at row pos % capacity
     cap = cache.view(0).capacity
     p = T - 1
-    assert (cache.view(0).k[0, 1, p % cap].float().cpu() - k[p, 1]).abs().max() <= (
+    assert (cache.rows(0, 0)[0][1, p % cap].float().cpu() - k[p, 1]).abs().max() <= (
         1e-5 if dtype == torch.float32 else 2e-2 * SCALE[dtype])
 
 
@@ -119,6 +121,8 @@ def test_block_embedding_and_head(dtype):
         part.bind({k: w[pspec.tensors[k]] for k in part.tensor_needs()})
     cache = Cache({0: block.mixer.cache_need()}, 1, 160, dtype, DEV)
     cache.acquire(1)
+    cache.ensure([0], [50])
+    cache.sync_tables()
     stream = ResidualStream(rt, x)
     block.forward(stream, batch, {"mixer": cache.view(0)})
     ref = plain_block(plain_embedding(w["model.embed_tokens.weight"], toks), cfg, w, 1,
@@ -309,7 +313,7 @@ def _register_toy_position_and_routing():
         def rotate_and_store(self, qkv, n_partials, batch, view, q_out, kv_step, H, G,
                              write_cache=True):
             ops.rope_store(qkv, n_partials, self.zero, batch, q_out, kv_step, view.k, view.v,
-                           view.slot_pos, H, G, self.hd, view.capacity, write_cache)
+                           view.slot_pos, H, G, self.hd, view.capacity, write_cache, pages=view.pages)
 
     @register_feed_forward("toy_top1")
     class ToyTop1:

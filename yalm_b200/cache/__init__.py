@@ -1,4 +1,4 @@
 from .slots import SlotAllocator, SlotError
-from .storage import Cache, CacheNeed, CacheView
+from .storage import PAGE, Cache, CacheFull, CacheNeed, CacheView
 
-__all__ = ["SlotAllocator", "SlotError", "Cache", "CacheNeed", "CacheView"]
+__all__ = ["SlotAllocator", "SlotError", "Cache", "CacheFull", "CacheNeed", "CacheView", "PAGE"]

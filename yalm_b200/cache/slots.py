@@ -13,9 +13,12 @@ class SlotError(RuntimeError):
 
 
 class SlotAllocator:
-    def __init__(self, n_slots: int):
+    def __init__(self, n_slots: int, what: str = "slot"):
+        """``what`` names the thing in messages: the same bookkeeping hands out the
+        cache's pages."""
+        self.what = what
         if n_slots <= 0:
-            raise SlotError(f"a cache needs at least one slot, got {n_slots}")
+            raise SlotError(f"a cache needs at least one {what}, got {n_slots}")
         self.n_slots = n_slots
         self._free: List[int] = list(range(n_slots - 1, -1, -1))   # pop() gives the lowest
         self._held = [False] * n_slots
@@ -30,7 +33,7 @@ class SlotAllocator:
 
     def acquire(self, n: int = 1) -> List[int]:
         if n > len(self._free):
-            raise SlotError(f"{n} slots wanted but only {len(self._free)} of {self.n_slots} are free")
+            raise SlotError(f"{n} {self.what}s wanted but only {len(self._free)} of {self.n_slots} are free")
         out = []
         for _ in range(n):
             s = self._free.pop()
@@ -43,11 +46,11 @@ class SlotAllocator:
         slots = list(slots)
         for s in slots:
             if not 0 <= s < self.n_slots:
-                raise SlotError(f"slot {s} does not exist (0..{self.n_slots - 1})")
+                raise SlotError(f"{self.what} {s} does not exist (0..{self.n_slots - 1})")
             if not self._held[s]:
-                raise SlotError(f"slot {s} is released but not held")
+                raise SlotError(f"{self.what} {s} is released but not held")
         if len(set(slots)) != len(slots):
-            raise SlotError(f"a slot is released twice in one call: {slots}")
+            raise SlotError(f"a {self.what} is released twice in one call: {slots}")
         for s in slots:
             self._held[s] = False
             self._free.append(s)
@@ -58,4 +61,4 @@ class SlotAllocator:
         free = sorted(self._free)
         held = self.held
         if sorted(free + held) != list(range(self.n_slots)) or len(set(free)) != len(free):
-            raise SlotError(f"slot table corrupt: free={free} held={held}")
+            raise SlotError(f"{self.what} table corrupt: free={free} held={held}")

@@ -5,9 +5,14 @@ What a mixer needs is declared by the mixer (one ``CacheNeed``, or several by
 name: keys and values AND a state, two states of different types); needs that are
 equal share one *group*, which has storage of its own:
 
-* ``kv`` groups hold ``K, V : [entries, slots, kv_heads, capacity, head_dim]``.
-  ``capacity`` is the window when the mixer has one (the slot is then a ring:
-  position p lives at row p % capacity), else the context length.
+* ``kv`` groups hold keys and values in pages of ``PAGE`` = 64 positions,
+  ``K, V : [entries, kv_heads, pages, PAGE, head_dim]``, and a table
+  ``[slots, pages_per_slot]`` that names the page of rows 64 p .. 64 p + 63 of each
+  sequence.  A sequence's rows are numbered 0 .. capacity - 1; ``capacity`` is the
+  window when the mixer has one (the rows are then a ring: position p lives at row
+  p % capacity), else the context length.  Pages come from a pool of the group: a
+  sequence takes one when it grows into it and gives all back when it ends, so the
+  memory follows the tokens that are held, not slots x capacity.
 * ``state`` groups hold ``[entries, slots, *shape]`` of fixed size per
   sequence; it is zeroed when a slot is acquired.  The Llama / Mistral decoder
   declares none; the storage exists for mixers that carry a recurrent state.
@@ -15,9 +20,9 @@ equal share one *group*, which has storage of its own:
 The per-sequence record on the device is ``slot_pos[slot]``: the number of
 positions the sequence has taken so far (its next position).  Ring offset and
 valid length follow from it (pos % capacity, min(pos, capacity)).  Kernels read
-it on the device, so a captured decode step needs no new arguments per step.
-The reference keeps one sequence's cache inside each block, f16[S, G*hd]
-(model.h:241-243, model.cpp:201-202) and passes kv_pos/kv_len per call
+it, and the page table, on the device, so a captured decode step needs no new
+arguments per step.  The reference keeps one sequence's cache inside each block,
+f16[S, G*hd] (model.h:241-243, model.cpp:201-202) and passes kv_pos/kv_len per call
 (infer.cpp:486-488).
 """
 from __future__ import annotations
@@ -27,7 +32,13 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from .slots import SlotAllocator
+from .slots import SlotAllocator, SlotError
+
+PAGE = 64      # positions per page (the kernels' KV_PAGE)
+
+
+class CacheFull(SlotError):
+    """The pool of pages cannot hold the tokens that were asked for."""
 
 
 @dataclass(frozen=True)
@@ -54,8 +65,9 @@ class CacheView:
     """What a mixer sees of the cache for one run entry."""
     kind: str
     capacity: int = 0
-    k: Optional[torch.Tensor] = None           # [slots, kv_heads, capacity, head_dim]
+    k: Optional[torch.Tensor] = None           # [kv_heads, pages, PAGE, head_dim]
     v: Optional[torch.Tensor] = None
+    pages: Optional[torch.Tensor] = None       # int32 [slots, pages_per_slot] on the device
     state: Optional[torch.Tensor] = None       # [slots, *shape]
     slot_pos: Optional[torch.Tensor] = None    # int32 [slots]
     kv_step: Optional[torch.Tensor] = None     # this step's keys/values, kept for a reader entry
@@ -75,20 +87,35 @@ def normalise_needs(need) -> Dict[str, CacheNeed]:
     return out
 
 
+def _pool_pages(need: CacheNeed, n_slots: int, context: int, max_tokens: Optional[int]) -> int:
+    """Pages in a kv group's pool: enough for every slot to fill up, or, when the tokens
+    that live sequences hold together are bounded (each count rounded up to a page),
+    enough for those."""
+    per_slot = -(-need.capacity(context) // PAGE)
+    full = n_slots * per_slot
+    if max_tokens is None:
+        return full
+    return max(1, min(full, -(-int(max_tokens) // PAGE)))
+
+
 class Cache:
     def __init__(self, needs: Dict[object, CacheNeed], n_slots: int, context: int,
-                 dtype: torch.dtype, device):
+                 dtype: torch.dtype, device, max_tokens: Optional[int] = None):
         """``needs`` maps a key to a need.  The model's keys are (run entry, mixer
         name, need name); any hashable, sortable key will do (entries that read
         another entry's cache are absent).  ``context`` is the most positions one
-        sequence may take."""
+        sequence may take; ``max_tokens``, if given, the most tokens all live sequences
+        hold together (each sequence's count rounded up to a multiple of 64): it sizes
+        the page pools."""
         self.n_slots = n_slots
         self.context = context
         self.dtype = dtype
         self.device = torch.device(device)
+        self.on_gpu = self.device.type == "cuda"
         self.slots = SlotAllocator(n_slots)
         self.slot_pos = torch.zeros(n_slots, dtype=torch.int32, device=self.device)
         self.host_pos = [0] * n_slots          # the host's copy of slot_pos
+        self._covered = [0] * n_slots          # positions each slot can hold with the pages it has
         self.groups: List[dict] = []
         self._entry: Dict[object, Tuple[int, int]] = {}
         by_key: Dict[tuple, int] = {}
@@ -105,10 +132,18 @@ class Cache:
             need, n = g["need"], len(g["entries"])
             if need.kind == "kv":
                 cap = need.capacity(context)
-                shape = (n, n_slots, need.kv_heads, cap, need.head_dim)
+                n_pages = _pool_pages(need, n_slots, context, max_tokens)
+                shape = (n, need.kv_heads, n_pages, PAGE, need.head_dim)
                 g["capacity"] = cap
+                g["pages_per_slot"] = -(-cap // PAGE)
                 g["k"] = torch.zeros(shape, dtype=dtype, device=self.device)
                 g["v"] = torch.zeros(shape, dtype=dtype, device=self.device)
+                g["pool"] = SlotAllocator(n_pages, what="page")
+                g["held"] = [[] for _ in range(n_slots)]           # a slot's pages, in row order
+                table = torch.zeros((n_slots, g["pages_per_slot"]), dtype=torch.int32)
+                g["table_host"] = table.pin_memory() if self.on_gpu else table
+                g["table"] = torch.zeros_like(table, device=self.device)
+                g["dirty"] = set()                                 # slots whose row must go down
             elif need.kind == "state":
                 g["state"] = torch.zeros((n, n_slots) + tuple(need.state_shape),
                                          dtype=need.state_dtype, device=self.device)
@@ -126,12 +161,13 @@ class Cache:
 
     @staticmethod
     def bytes_needed(needs: Dict[object, CacheNeed], n_slots: int, context: int,
-                     dtype: torch.dtype) -> int:
+                     dtype: torch.dtype, max_tokens: Optional[int] = None) -> int:
         esz = torch.empty((), dtype=dtype).element_size()
         total = 0
         for need in needs.values():
             if need.kind == "kv":
-                total += 2 * n_slots * need.kv_heads * need.capacity(context) * need.head_dim * esz
+                pages = _pool_pages(need, n_slots, context, max_tokens)
+                total += 2 * pages * need.kv_heads * PAGE * need.head_dim * esz
             else:
                 n = 1
                 for s in need.state_shape:
@@ -152,7 +188,74 @@ class Cache:
         return slots
 
     def release(self, slots: Sequence[int]) -> None:
+        """Gives the slots and their pages back.  Work that is still queued on the
+        device for these sequences ends first: their pages may be handed out at once."""
+        slots = list(slots)
         self.slots.release(slots)
+        if self.on_gpu:
+            torch.cuda.current_stream(self.device).synchronize()
+        for g in self.groups:
+            if "pool" in g:
+                for s in slots:
+                    if g["held"][s]:
+                        g["pool"].release(g["held"][s])
+                        g["held"][s] = []
+        for s in slots:
+            self._covered[s] = 0
+
+    # -- pages ---------------------------------------------------------------
+    def free_pages(self) -> List[int]:
+        """Free pages of each kv group, in group order."""
+        return [g["pool"].free_count for g in self.groups if "pool" in g]
+
+    def ensure(self, slots: Sequence[int], lengths: Sequence[int]) -> None:
+        """Pages for the sequences in ``slots`` to hold ``lengths`` positions.  Either
+        all of them are found or nothing changes and ``CacheFull`` is raised."""
+        if all(n <= self._covered[s] for s, n in zip(slots, lengths)):
+            return                              # the usual case of a decode step
+        plan = []
+        for g in self.groups:
+            if "pool" not in g:
+                continue
+            want = []
+            for s, n in zip(slots, lengths):
+                need = -(-min(int(n), g["capacity"]) // PAGE) - len(g["held"][s])
+                if need > 0:
+                    want.append((s, need))
+            total = sum(n for _, n in want)
+            if total > g["pool"].free_count:
+                raise CacheFull(
+                    f"{total} more pages of {PAGE} positions are needed and {g['pool'].free_count} of "
+                    f"{g['pool'].n_slots} are free: the live sequences hold more tokens than the "
+                    f"cache was sized for (max_tokens / max_batch x max_context)")
+            plan.append((g, want))
+        for g, want in plan:
+            for s, n in want:
+                pages = g["pool"].acquire(n)
+                at = len(g["held"][s])
+                g["held"][s].extend(pages)
+                g["table_host"][s, at:at + n] = torch.tensor(pages, dtype=torch.int32)
+                g["dirty"].add(s)
+        for s in slots:
+            self._covered[s] = min([self.context] + [
+                len(g["held"][s]) * PAGE for g in self.groups
+                if "pool" in g and len(g["held"][s]) < g["pages_per_slot"]])
+
+    def sync_tables(self) -> None:
+        """The changed rows of the page tables go to the device, in stream order before
+        the kernels that read them."""
+        for g in self.groups:
+            if "pool" not in g or not g["dirty"]:
+                continue
+            if self.on_gpu:
+                from ..csrc import ops
+                row = g["pages_per_slot"] * 4
+                for s in sorted(g["dirty"]):
+                    ops.copy_async(g["table"].data_ptr() + s * row, g["table_host"].data_ptr() + s * row,
+                                   row, True)
+            else:
+                g["table"].copy_(g["table_host"])
+            g["dirty"].clear()
 
     # -- views ---------------------------------------------------------------
     def view(self, entry) -> CacheView:
@@ -162,8 +265,21 @@ class Cache:
         g = self.groups[gi]
         if g["need"].kind == "kv":
             return CacheView("kv", capacity=g["capacity"], k=g["k"][i], v=g["v"][i],
-                             slot_pos=self.slot_pos)
+                             slot_pos=self.slot_pos, pages=g["table"])
         return CacheView("state", state=g["state"][i], slot_pos=self.slot_pos)
+
+    def rows(self, entry, slot: int, first: int = 0, count: Optional[int] = None):
+        """Keys and values of rows ``first .. first + count - 1`` of the sequence in
+        ``slot`` as two tensors [kv_heads, count, head_dim] (a gather through the page
+        table, for inspection and tests)."""
+        gi, i = self._entry[entry]
+        g = self.groups[gi]
+        held = g["held"][slot]
+        count = len(held) * PAGE - first if count is None else count
+        idx = torch.tensor([held[r // PAGE] * PAGE + r % PAGE for r in range(first, first + count)],
+                           dtype=torch.long, device=self.device)
+        flat = lambda t: t[i].reshape(t.shape[1], -1, t.shape[4])
+        return flat(g["k"])[:, idx], flat(g["v"])[:, idx]
 
     def room(self, slot: int) -> int:
         """Positions the sequence in ``slot`` may still take."""

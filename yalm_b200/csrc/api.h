@@ -25,18 +25,24 @@ int yalm_rmsnorm(float* x, const float* partials, int n_partials, long long part
 int yalm_silu_mul(const float* gu, int n_partials, long long partial_stride, void* out,
                   int out_dtype, int rows, int F, int paired, cudaStream_t stream);
 
+// The cache of a layer run, wherever it is an argument: contiguous per sequence,
+// [slots][G][capacity][hd] (page_table null), or pages of 64 positions,
+// [pages][G][64][hd], with page_table [slots][pages_per_slot] naming the page of rows
+// 64 p .. 64 p + 63 of each sequence.  A row is a position modulo the capacity.
 int yalm_rope_store(const float* qkv, int n_partials, long long partial_stride,
                     const float* inv_freq, const int* token_seq, const int* q_start,
                     const int* seq_slot, const int* slot_pos, void* q_out, void* kv_step,
                     void* k_cache, void* v_cache, int dtype, int n_tokens, int H, int G, int hd,
-                    int capacity, int write_cache, cudaStream_t stream);
+                    int capacity, int write_cache, const int* page_table, int pages_per_slot, int n_pages,
+                    cudaStream_t stream);
 
 // kv_step [N, 2, G, hd] -> the ring rows of the positions the ring keeps (the cache
 // write of yalm_rope_store, on its own: for a ring that may only be written after the
 // attention has read the rows that are replaced)
 int yalm_cache_write(const void* kv_step, const int* token_seq, const int* q_start,
                      const int* seq_slot, const int* slot_pos, void* k_cache, void* v_cache,
-                     int dtype, int n_tokens, int G, int hd, int capacity, cudaStream_t stream);
+                     int dtype, int n_tokens, int G, int hd, int capacity, const int* page_table,
+                     int pages_per_slot, int n_pages, cudaStream_t stream);
 
 int yalm_advance(const int* q_start, const int* seq_slot, int* slot_pos, int n_seqs,
                  cudaStream_t stream);
@@ -45,13 +51,13 @@ int yalm_attention(const void* q, const void* kv_step, const void* k_cache, cons
                    const int* token_seq, const int* q_start, const int* seq_slot,
                    const int* slot_pos, void* out, float* part_o, float* part_ml, int dtype,
                    int n_tokens, int H, int G, int hd, int capacity, int window, int nsplit,
-                   cudaStream_t stream);
+                   const int* page_table, int pages_per_slot, int n_pages, cudaStream_t stream);
 
 int yalm_attention_decode(const void* q, const void* k_cache, const void* v_cache,
                           const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                           float* part_ml, int* counters, int* status, int dtype, int n_seqs, int H,
                           int G, int hd, int capacity, int window, int chunk, int max_context,
-                          cudaStream_t stream);
+                          const int* page_table, int pages_per_slot, int n_pages, cudaStream_t stream);
 
 // 16-bit attention on tensor cores (attention_mma.cu; dtype 1 or 2): head sizes in steps of
 // 16 up to 128
@@ -59,12 +65,13 @@ int yalm_attention_prefill_mma(const void* q, const void* kv_step, const void* k
                                const void* v_cache, const int* q_start, const int* seq_slot,
                                const int* slot_pos, void* out, int dtype, int n_seqs,
                                int max_q_len, int H, int G, int hd, int capacity, int window,
-                               cudaStream_t stream);
+                               const int* page_table, int pages_per_slot, int n_pages, cudaStream_t stream);
 int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                               const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                               float* part_ml, int* counters, int* status, int dtype, int n_seqs,
                               int H, int G, int hd, int capacity, int window, int max_context,
-                              int chunks_per_block, cudaStream_t stream);
+                              int chunks_per_block, const int* page_table, int pages_per_slot, int n_pages,
+                              cudaStream_t stream);
 
 // 16-bit prefill attention on tcgen05 (attention_tc.cu; dtype 1 or 2): sequences that start
 // at their first token, head size 64 or 128

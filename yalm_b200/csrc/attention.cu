@@ -91,7 +91,8 @@ attn_token_kernel(const T* __restrict__ q, const T* __restrict__ kv_step,
                   const int* __restrict__ token_seq, const int* __restrict__ q_start,
                   const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
                   T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-                  int H, int G, int hd, int capacity, int window, int nsplit, float scale, int t0) {
+                  int H, int G, int hd, int capacity, int window, int nsplit, float scale, int t0,
+                  const int* __restrict__ page_table, int pps, int n_pages) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int KPW = 32 / LPK;                 // keys per warp per iteration
@@ -145,8 +146,6 @@ attn_token_kernel(const T* __restrict__ q, const T* __restrict__ kv_step,
   }
 
   const size_t step_row = (size_t)2 * G * hd;
-  const T* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
-  const T* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
 
   // ATT_U keys per lane group are loaded before any is used: the loop is a
   // stream of independent 16-byte loads, which is what hides HBM latency
@@ -163,9 +162,9 @@ attn_token_kernel(const T* __restrict__ q, const T* __restrict__ kv_step,
           kp = kv_step + (size_t)(qs + key - past) * step_row + (size_t)g * hd + e0;
           vp = kp + (size_t)G * hd;
         } else {
-          const size_t row = (size_t)(key % capacity) * hd + e0;
-          kp = kc + row;
-          vp = vc + row;
+          const size_t row = kv_row_offset(page_table, pps, n_pages, slot, g, G, capacity, key % capacity, hd) + e0;
+          kp = k_cache + row;
+          vp = v_cache + row;
         }
         kraw[u] = Vec8<T>::load_raw(kp);
         vraw[u] = Vec8<T>::load_raw(vp);
@@ -295,7 +294,8 @@ attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
                    const int* __restrict__ slot_pos, T* __restrict__ out,
                    float* __restrict__ part_o, float* __restrict__ part_ml,
                    int* __restrict__ counters, int* __restrict__ status, int H, int G, int hd,
-                   int capacity, int window, int chunk, int max_chunks, float scale) {
+                   int capacity, int window, int chunk, int max_chunks, float scale,
+                   const int* __restrict__ page_table, int pps, int n_pages) {
   static_assert(ATT_WARPS == ATT_RT, "one warp per query head in the softmax pass");
   constexpr int KPW = 32 / LPK;
   constexpr int GROUPS = ATT_WARPS * KPW;
@@ -337,18 +337,18 @@ attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     const size_t row_bytes = (size_t)hd * sizeof(T);
-    const T* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
-    const T* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
-    const int r0 = k_lo % capacity;
-    const int n1 = min(n, capacity - r0);                   // rows before the ring wraps
+    // consecutive rows in runs that end where the ring wraps or a page ends
     mbar_expect_tx(smem_u32(&bar), (uint32_t)(2 * n * row_bytes));
-    bulk_load(smem_u32(ks), kc + (size_t)r0 * hd, (uint32_t)(n1 * row_bytes), smem_u32(&bar));
-    bulk_load(smem_u32(vs), vc + (size_t)r0 * hd, (uint32_t)(n1 * row_bytes), smem_u32(&bar));
-    if (n1 < n) {
-      bulk_load(smem_u32(ks + (size_t)n1 * hd), kc, (uint32_t)((n - n1) * row_bytes),
+    for (int done = 0; done < n;) {
+      const int row = (k_lo + done) % capacity;
+      int run = min(n - done, capacity - row);
+      if (page_table != nullptr) run = min(run, KV_PAGE - row % KV_PAGE);
+      const size_t off = kv_row_offset(page_table, pps, n_pages, slot, g, G, capacity, row, hd);
+      bulk_load(smem_u32(ks + (size_t)done * hd), k_cache + off, (uint32_t)(run * row_bytes),
                 smem_u32(&bar));
-      bulk_load(smem_u32(vs + (size_t)n1 * hd), vc, (uint32_t)((n - n1) * row_bytes),
+      bulk_load(smem_u32(vs + (size_t)done * hd), v_cache + off, (uint32_t)(run * row_bytes),
                 smem_u32(&bar));
+      done += run;
     }
   }
 
@@ -549,7 +549,8 @@ static int launch_attention(const void* q, const void* kv_step, const void* k_ca
                             const void* v_cache, const int* token_seq, const int* q_start,
                             const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                             float* part_ml, int n_tokens, int H, int G, int hd, int capacity,
-                            int window, int nsplit, cudaStream_t stream) {
+                            int window, int nsplit, const int* page_table, int pps, int n_pages,
+                            cudaStream_t stream) {
   const int R = H / G;
   const int nchunks = (R + ATT_RT - 1) / ATT_RT;
   const dim3 block(ATT_WARPS * 32);
@@ -560,7 +561,8 @@ static int launch_attention(const void* q, const void* kv_step, const void* k_ca
 #define YALM_ATT_CASE(LPK)                                                                      \
   launch_pdl(attn_token_kernel<T, LPK>, dim3(grid), dim3(block), 0, stream,                                         \
       (const T*)q, (const T*)kv_step, (const T*)k_cache, (const T*)v_cache, token_seq, q_start, \
-      seq_slot, slot_pos, (T*)out, part_o, part_ml, H, G, hd, capacity, window, nsplit, scale, t0)
+      seq_slot, slot_pos, (T*)out, part_o, part_ml, H, G, hd, capacity, window, nsplit, scale, t0, \
+      page_table, pps, n_pages)
   if (hd <= 16) YALM_ATT_CASE(2);
   else if (hd <= 32) YALM_ATT_CASE(4);
   else if (hd <= 64) YALM_ATT_CASE(8);
@@ -588,7 +590,8 @@ extern "C" int yalm_attention(const void* q, const void* kv_step, const void* k_
                               const void* v_cache, const int* token_seq, const int* q_start,
                               const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                               float* part_ml, int dtype, int n_tokens, int H, int G, int hd,
-                              int capacity, int window, int nsplit, cudaStream_t stream) {
+                              int capacity, int window, int nsplit, const int* page_table,
+                              int pages_per_slot, int n_pages, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (hd % 8 != 0 || hd > 256 || hd <= 0) return -2;     // head sizes: multiples of 8 up to 256
   if (G <= 0 || H % G != 0) return -3;
@@ -597,15 +600,16 @@ extern "C" int yalm_attention(const void* q, const void* kv_step, const void* k_
   if (dtype == DT_F32)
     return launch_attention<float>(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot,
                                    slot_pos, out, part_o, part_ml, n_tokens, H, G, hd, capacity,
-                                   window, nsplit, stream);
+                                   window, nsplit, page_table, pages_per_slot, n_pages, stream);
   if (dtype == DT_F16)
     return launch_attention<__half>(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot,
                                     slot_pos, out, part_o, part_ml, n_tokens, H, G, hd, capacity,
-                                    window, nsplit, stream);
+                                    window, nsplit, page_table, pages_per_slot, n_pages, stream);
   if (dtype != DT_BF16) return -3;
   return launch_attention<__nv_bfloat16>(q, kv_step, k_cache, v_cache, token_seq, q_start,
                                          seq_slot, slot_pos, out, part_o, part_ml, n_tokens, H, G,
-                                         hd, capacity, window, nsplit, stream);
+                                         hd, capacity, window, nsplit, page_table, pages_per_slot, n_pages,
+                                         stream);
 }
 
 // Decode attention (see attn_decode_kernel).  Every query is the newest token of
@@ -619,6 +623,7 @@ extern "C" int yalm_attention_decode(const void* q, const void* k_cache, const v
                                      float* part_o, float* part_ml, int* counters, int* status,
                                      int dtype, int n_seqs, int H, int G, int hd, int capacity,
                                      int window, int chunk, int max_context,
+                                     const int* page_table, int pages_per_slot, int n_pages,
                                      cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (hd % 8 != 0 || hd > 256 || hd <= 0) return -2;
@@ -650,7 +655,7 @@ extern "C" int yalm_attention_decode(const void* q, const void* k_cache, const v
     launch_pdl(attn_decode_kernel<T, LPK>, grid, block, smem, stream, (const T*)q,             \
                (const T*)k_cache, (const T*)v_cache, seq_slot, slot_pos, (T*)out, part_o,      \
                part_ml, counters, status, H, G, hd, capacity, window, chunk, max_chunks,       \
-               scale);                                                                         \
+               scale, page_table, pages_per_slot, n_pages);                                             \
   } while (0)
 #define YALM_DEC_T(T)                                  \
   do {                                                 \
@@ -740,5 +745,5 @@ extern "C" int yalm_attention_no_alloc(const void* q, const void* kv_step, const
   float* part_ml = base + (size_t)n_tokens * H * nsplit * hd;        // [tokens, H, nsplit, 2]
   return yalm_attention(q, kv_step, k_cache, v_cache, token_seq, q_start, seq_slot, slot_pos, out,
                         part_o, part_ml, dtype, n_tokens, H, G, hd, capacity, window, nsplit,
-                        stream);
+                        nullptr, 0, 0, stream);            // a contiguous cache only
 }

@@ -110,7 +110,7 @@ attn_prefill_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ kv_st
                         const T16* __restrict__ v_cache, const int* __restrict__ q_start,
                         const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
                         T16* __restrict__ out, int H, int G, int hd, int capacity,
-                        int window, float scale_log2) {
+                        int window, float scale_log2, const int* __restrict__ page_table, int pps, int n_pages) {
   constexpr int NKS = HDP / 16, NOT = HDP / 8;
   extern __shared__ __align__(128) uint8_t fa_smem[];
   pdl_launch_dependents();
@@ -139,8 +139,6 @@ attn_prefill_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ kv_st
   const int kb0 = k_begin / FA_BN, kb1 = (k_end + FA_BN - 1) / FA_BN;
 
   const size_t step_row = (size_t)2 * G * hd;
-  const T16* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
-  const T16* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
   auto load_kv = [&](int kb, int stage) {
     const int j0 = kb * FA_BN;
     const uint32_t kd = k_s0 + stage * FA_BN * HDP * 2, vd = v_s0 + stage * FA_BN * HDP * 2;
@@ -156,13 +154,13 @@ attn_prefill_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ kv_st
       const int j = j0 + r;
       if (j >= k_end) return nullptr;
       return j >= past ? kv_step + (size_t)(qs + j - past) * step_row + (size_t)g * hd
-                       : kc + (size_t)(j % capacity) * hd;
+                       : k_cache + kv_row_offset(page_table, pps, n_pages, slot, g, G, capacity, j % capacity, hd);
     });
     load_tile<HDP, FP_THREADS>(vd, FA_BN, hd, q, [&](int r) -> const T16* {
       const int j = j0 + r;
       if (j >= k_end) return nullptr;
       return j >= past ? kv_step + (size_t)(qs + j - past) * step_row + (size_t)(G + g) * hd
-                       : vc + (size_t)(j % capacity) * hd;
+                       : v_cache + kv_row_offset(page_table, pps, n_pages, slot, g, G, capacity, j % capacity, hd);
     });
   };
 
@@ -348,21 +346,40 @@ __device__ __forceinline__ float ex2_approx(float x) {       // 2^x; 2^-inf = 0
   return y;
 }
 
+// Where the rows of one (sequence, kv head) of a cache live (see kv_row_offset).  `pages`
+// is the sequence's own row of the page table (in shared or global memory), or null for
+// a cache that is one block per sequence.
+struct KvRows {
+  const int* pages;
+  int n_pages, slot, g, G, capacity, hd;
+  __device__ __forceinline__ size_t offset(int row) const {
+    if (pages == nullptr) return (((size_t)slot * G + g) * capacity + row) * hd;
+    return (((size_t)g * n_pages + pages[row / KV_PAGE]) * KV_PAGE + (row % KV_PAGE)) * hd;
+  }
+  // rows first .. first + n - 1 lie one after another in memory
+  __device__ __forceinline__ bool consecutive(int first, int n) const {
+    if (first + n > capacity) return false;
+    if (pages == nullptr || first / KV_PAGE == (first + n - 1) / KV_PAGE) return true;
+    return pages[(first + n - 1) / KV_PAGE] == pages[first / KV_PAGE] + 1;   // n <= KV_PAGE
+  }
+};
+constexpr int FD_TABLE = 512;      // page-table entries of a sequence kept in shared memory
+
 // One warp loads `n` consecutive positions of a cache ring (rows first_row,
 // first_row + 1, ... modulo capacity) into a swizzled tile of FD_UNIT rows and
 // zero-fills rows n and up.  Lane l takes rows (l & 7) + 8 rb and the 16-byte
 // columns (l >> 3) + 4 j: its row's swizzle is then one constant, and a full unit
-// that does not wrap needs an add and an exclusive-or per copy.
+// that neither wraps nor crosses a page needs an add and an exclusive-or per copy.
 template <int HDP, typename T16>
 __device__ __forceinline__ void warp_load_ring_tile(uint32_t base, int n, int hd,
-                                                    const T16* ring, int first_row,
-                                                    int capacity, int lane) {
+                                                    const T16* cache, const KvRows& rows,
+                                                    int first_row, int lane) {
   const int r7 = lane & 7, cg = lane >> 3;
   const int cpr = hd >> 3;
   const uint32_t s_lane = base + r7 * (HDP * 2) + ((cg ^ (r7 & 3)) << 4);
   const uint32_t x_lane = (uint32_t)(r7 >> 2) << 6;
-  if (n == FD_UNIT && first_row + FD_UNIT <= capacity) {
-    const T16* g = ring + (size_t)(first_row + r7) * hd + cg * 8;
+  if (n == FD_UNIT && rows.consecutive(first_row, FD_UNIT)) {
+    const T16* g = cache + rows.offset(first_row) + (size_t)r7 * hd + cg * 8;
 #pragma unroll
     for (int rb = 0; rb < FD_UNIT / 8; ++rb) {
 #pragma unroll
@@ -376,7 +393,9 @@ __device__ __forceinline__ void warp_load_ring_tile(uint32_t base, int n, int hd
 #pragma unroll 1
   for (int rb = 0; rb < FD_UNIT / 8; ++rb) {
     const int r = rb * 8 + r7;
-    const T16* g = ring + (size_t)((first_row + r) % capacity) * hd + cg * 8;
+    int row = first_row + r;
+    if (row >= rows.capacity) row = rows.capacity >= FD_UNIT ? row - rows.capacity : row % rows.capacity;
+    const T16* g = cache + rows.offset(row) + cg * 8;
 #pragma unroll
     for (int j = 0; j < HDP / 32; ++j)
       if (cg + 4 * j < cpr)
@@ -391,7 +410,8 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
                        const int* __restrict__ slot_pos, T16* __restrict__ out,
                        float* __restrict__ part_o, float* __restrict__ part_ml,
                        int* __restrict__ counters, int* __restrict__ status, int H, int G, int hd,
-                       int capacity, int window, int cpc, int max_parts, float scale_log2) {
+                       int capacity, int window, int cpc, int max_parts, float scale_log2,
+                       const int* __restrict__ page_table, int pps, int n_pages) {
   constexpr int NKS = HDP / 16;                              // 16-wide steps over the head size
   constexpr int TILE = FD_UNIT * HDP * 2;                    // K (or V) of one unit, bytes
   constexpr int WARP_RING = FD_STAGES * 2 * TILE;
@@ -401,6 +421,7 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   __shared__ float wl_s[FA_WARPS][FD_ROWS];
   __shared__ float row_m[FD_ROWS], row_l[FD_ROWS];
   __shared__ int last_flag;
+  __shared__ int pages_s[FD_TABLE];                          // this sequence's row of the page table
   pdl_launch_dependents();
   const int R = H / G;
   const int nhc = (R + FD_ROWS - 1) / FD_ROWS;
@@ -409,6 +430,18 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   const int nh = min(FD_ROWS, R - hchunk * FD_ROWS);
   const int t = blockIdx.z, part = blockIdx.x;
   const int slot = seq_slot[t];           // written by a host copy, never by a kernel: safe early
+  // The page table is written by host copies before the step's first kernel, like the
+  // batch's index arrays: it may be read before the dependency wait too.  The sequence's
+  // row of it is asked for now, together with its position, and kept in shared memory
+  // (a row longer than FD_TABLE entries is read in place).
+  const int* my_pages = page_table ? page_table + (size_t)slot * pps : nullptr;
+  const bool table_in_smem = page_table != nullptr && pps <= FD_TABLE;
+  int entries[FD_TABLE / FA_THREADS];
+#pragma unroll
+  for (int k = 0; k < FD_TABLE / FA_THREADS; ++k) {
+    const int idx = threadIdx.x + k * FA_THREADS;
+    entries[k] = (table_in_smem && idx < pps) ? my_pages[idx] : 0;
+  }
   // Positions are written by the advance kernel alone, and that kernel lets nothing start
   // before it has ended: they too may be read while the previous kernel still runs.
   const int pos = slot_pos[slot];
@@ -427,15 +460,20 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   const int gid = lane >> 2, tig = lane & 3;
   const uint32_t q_s = smem_u32(fa_smem);                    // [16 heads][HDP]
   const uint32_t ring_s = q_s + FD_ROWS * HDP * 2 + warp * WARP_RING;
-  const T16* kc = k_cache + ((size_t)slot * G + g) * capacity * hd;
-  const T16* vc = v_cache + ((size_t)slot * G + g) * capacity * hd;
+  if (table_in_smem) {
+#pragma unroll
+    for (int k = 0; k < FD_TABLE / FA_THREADS; ++k) pages_s[threadIdx.x + k * FA_THREADS] = entries[k];
+    my_pages = pages_s;
+    __syncthreads();
+  }
+  const KvRows rows{my_pages, n_pages, slot, g, G, capacity, hd};
   auto load_unit = [&](int u, int stage) {
     const int k_lo = lo + u * FD_UNIT;
     const int n = min(FD_UNIT, pos + 1 - k_lo);
     const uint32_t dst = ring_s + stage * 2 * TILE;
     const int first = k_lo % capacity;
-    warp_load_ring_tile<HDP>(dst, n, hd, kc, first, capacity, lane);
-    warp_load_ring_tile<HDP>(dst + TILE, n, hd, vc, first, capacity, lane);
+    warp_load_ring_tile<HDP>(dst, n, hd, k_cache, rows, first, lane);
+    warp_load_ring_tile<HDP>(dst + TILE, n, hd, v_cache, rows, first, lane);
   };
   // FD_STAGES - 1 units are requested before the first is used.  All rows but the newest
   // position's are older than this step: their units are requested before the wait; the
@@ -702,7 +740,7 @@ static int launch_decode_mma(const void* q, const void* k_cache, const void* v_c
                              const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                              float* part_ml, int* counters, int* status, int n_seqs, int H, int G,
                              int hd, int capacity, int window, int cpc, int max_parts,
-                             cudaStream_t stream) {
+                             const int* page_table, int pps, int n_pages, cudaStream_t stream) {
   // Q, then every warp's ring of (K, V) stages; the merge buffer lies over them
   size_t smem = (size_t)(FD_ROWS + FA_WARPS * FD_STAGES * 2 * FD_UNIT) * HDP * 2;
   const size_t merge = (size_t)FA_WARPS * hd * FD_OPAD * 4;
@@ -720,7 +758,7 @@ static int launch_decode_mma(const void* q, const void* k_cache, const void* v_c
   launch_pdl(attn_decode_mma_kernel<HDP, NT, T16>, grid, dim3(FA_THREADS), smem, stream,
              (const T16*)q, (const T16*)k_cache, (const T16*)v_cache,
              seq_slot, slot_pos, (T16*)out, part_o, part_ml, counters, status, H, G, hd,
-             capacity, window, cpc, max_parts, scale_log2);
+             capacity, window, cpc, max_parts, scale_log2, page_table, pps, n_pages);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -729,7 +767,8 @@ template <int HDP, typename T16>
 static int launch_prefill(const void* q, const void* kv_step, const void* k_cache,
                           const void* v_cache, const int* q_start, const int* seq_slot,
                           const int* slot_pos, void* out, int n_seqs, int max_q_len, int H, int G,
-                          int hd, int capacity, int window, cudaStream_t stream) {
+                          int hd, int capacity, int window, const int* page_table, int pps, int n_pages,
+                          cudaStream_t stream) {
   const size_t smem = (size_t)(FA_BM + 4 * FA_BN) * HDP * 2;
   static bool attr_set = false;
   if (!attr_set) {
@@ -747,7 +786,7 @@ static int launch_prefill(const void* q, const void* kv_step, const void* k_cach
   launch_pdl(attn_prefill_mma_kernel<HDP, T16>, grid, dim3(FP_THREADS), smem, stream,
              (const T16*)q, (const T16*)kv_step, (const T16*)k_cache,
              (const T16*)v_cache, q_start, seq_slot, slot_pos, (T16*)out, H, G,
-             hd, capacity, window, scale_log2);
+             hd, capacity, window, scale_log2, page_table, pps, n_pages);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -763,7 +802,8 @@ extern "C" int yalm_attention_prefill_mma(const void* q, const void* kv_step, co
                                           const void* v_cache, const int* q_start,
                                           const int* seq_slot, const int* slot_pos, void* out,
                                           int dtype, int n_seqs, int max_q_len, int H, int G,
-                                          int hd, int capacity, int window, cudaStream_t stream) {
+                                          int hd, int capacity, int window, const int* page_table,
+                                          int pages_per_slot, int n_pages, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return 0;
   if (dtype != DT_BF16 && dtype != DT_F16) return -3;
   if (hd % 16 != 0 || hd > 128 || hd <= 0) return -2;
@@ -771,7 +811,8 @@ extern "C" int yalm_attention_prefill_mma(const void* q, const void* kv_step, co
   if (H > 65535 || n_seqs > 65535) return -4;
 #define YALM_FP(HDP, T)                                                                          \
   return launch_prefill<HDP, T>(q, kv_step, k_cache, v_cache, q_start, seq_slot, slot_pos, out,  \
-                                n_seqs, max_q_len, H, G, hd, capacity, window, stream)
+                                n_seqs, max_q_len, H, G, hd, capacity, window, page_table,        \
+                                pages_per_slot, n_pages, stream)
   if (dtype == DT_F16) {
     if (hd <= 64) YALM_FP(64, __half);
     YALM_FP(128, __half);
@@ -792,6 +833,7 @@ extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, con
                                          float* part_o, float* part_ml, int* counters, int* status,
                                          int dtype, int n_seqs, int H, int G, int hd, int capacity,
                                          int window, int max_context, int chunks_per_block,
+                                         const int* page_table, int pages_per_slot, int n_pages,
                                          cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (dtype != DT_BF16 && dtype != DT_F16) return -3;
@@ -806,7 +848,7 @@ extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, con
 #define YALM_FD(HDP, NT, T)                                                                      \
   launch_decode_mma<HDP, NT, T>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,   \
                                 counters, status, n_seqs, H, G, hd, capacity, window,            \
-                                chunks_per_block, max_parts, stream)
+                                chunks_per_block, max_parts, page_table, pages_per_slot, n_pages, stream)
   if (dtype == DT_F16) {
     if (hd <= 64) return two ? YALM_FD(64, 2, __half) : YALM_FD(64, 1, __half);
     return two ? YALM_FD(128, 2, __half) : YALM_FD(128, 1, __half);

@@ -97,6 +97,23 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return scratch[32];
 }
 
+// ---- where a cached row lives --------------------------------------------
+// The cache of one layer run is either contiguous per sequence,
+// [slots][kv heads][capacity][head size], or made of pages of KV_PAGE positions,
+// [kv heads][pages][KV_PAGE][head size], with a table [slots][pages_per_slot] that
+// names the page of rows 64 p .. 64 p + 63 of each sequence (page_table != null).
+// Row r is a position modulo the capacity in both.  With the kv head outermost the
+// rows of one head in pages that follow one another are one run of memory, which is
+// what a sequence that grew without interruption has.
+constexpr int KV_PAGE = 64;
+__device__ __forceinline__ size_t kv_row_offset(const int* __restrict__ page_table,
+                                                int pages_per_slot, int n_pages, int slot, int g,
+                                                int G, int capacity, int row, int hd) {
+  if (page_table == nullptr) return (((size_t)slot * G + g) * capacity + row) * hd;
+  const int page = page_table[(size_t)slot * pages_per_slot + (row / KV_PAGE)];
+  return (((size_t)g * n_pages + page) * KV_PAGE + (row % KV_PAGE)) * hd;
+}
+
 // ---- shared-memory barriers with bounded waits --------------------------
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 

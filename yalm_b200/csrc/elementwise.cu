@@ -210,7 +210,8 @@ __device__ __forceinline__ void rope_rotate_store(float* a, float* bb, const flo
                                                   int i, int pos, bool keep, int slot,
                                                   T* __restrict__ q_out, T* __restrict__ kv_step,
                                                   T* __restrict__ k_cache, T* __restrict__ v_cache,
-                                                  int H, int G, int hd, int capacity) {
+                                                  int H, int G, int hd, int capacity,
+                                                  const int* __restrict__ page_table, int pps, int n_pages) {
   const int half = hd >> 1;
   if (head < H + G) {
 #pragma unroll
@@ -234,7 +235,8 @@ __device__ __forceinline__ void rope_rotate_store(float* a, float* bb, const flo
   RopeIO<T, VEC>::store(o, a);
   RopeIO<T, VEC>::store(o + half, bb);
   if (keep) {
-    T* c = (is_v ? v_cache : k_cache) + (((size_t)slot * G + g) * capacity + pos % capacity) * hd + i;
+    T* c = (is_v ? v_cache : k_cache) +
+           kv_row_offset(page_table, pps, n_pages, slot, g, G, capacity, pos % capacity, hd) + i;
     RopeIO<T, VEC>::store(c, a);
     RopeIO<T, VEC>::store(c + half, bb);
   }
@@ -247,7 +249,8 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
                                   const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
                                   T* __restrict__ q_out, T* __restrict__ kv_step,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G,
-                                  int hd, int capacity, int write_cache, int heads_per_block) {
+                                  int hd, int capacity, int write_cache, int heads_per_block,
+                                  const int* __restrict__ page_table, int pps, int n_pages) {
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int half = hd >> 1;
@@ -299,7 +302,7 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
     }
   }
   rope_rotate_store<T, VEC>(a, bb, fr, t, head, i, pos, keep, slot, q_out, kv_step, k_cache, v_cache, H, G, hd,
-                            capacity);
+                            capacity, page_table, pps, n_pages);
 }
 
 // The same for many tokens whose product is a single slice (a prompt): a block takes
@@ -311,7 +314,7 @@ __global__ void rope_store_many_kernel(const float* __restrict__ qkv, const floa
                                        T* __restrict__ q_out, T* __restrict__ kv_step,
                                        T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G,
                                        int hd, int capacity, int write_cache, int heads_per_block,
-                                       int n_tokens) {
+                                       int n_tokens, const int* __restrict__ page_table, int pps, int n_pages) {
   pdl_launch_dependents();
   const int half = hd >> 1;
   const int lanes = half / 4;
@@ -352,7 +355,7 @@ __global__ void rope_store_many_kernel(const float* __restrict__ qkv, const floa
     const bool keep = write_cache && pos >= end - capacity;
     float a[4] = {x[k].x, x[k].y, x[k].z, x[k].w}, bb[4] = {y[k].x, y[k].y, y[k].z, y[k].w};
     rope_rotate_store<T, 4>(a, bb, fr, t, head, i, pos, keep, slot[k], q_out, kv_step, k_cache, v_cache, H, G,
-                            hd, capacity);
+                            hd, capacity, page_table, pps, n_pages);
   }
 }
 
@@ -366,7 +369,8 @@ template <typename T>
 __global__ void cache_write_kernel(const T* __restrict__ kv_step, const int* __restrict__ token_seq,
                                    const int* __restrict__ q_start, const int* __restrict__ seq_slot,
                                    const int* __restrict__ slot_pos, T* __restrict__ k_cache,
-                                   T* __restrict__ v_cache, int G, int hd, int capacity, int vec) {
+                                   T* __restrict__ v_cache, int G, int hd, int capacity, int vec,
+                                   const int* __restrict__ page_table, int pps, int n_pages) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -376,21 +380,21 @@ __global__ void cache_write_kernel(const T* __restrict__ kv_step, const int* __r
   const int past = slot_pos[slot];
   const int pos = past + (t - qs);
   if (pos < past + (q_end - qs) - capacity) return;          // the ring keeps only the last rows
-  const size_t row = (size_t)(pos % capacity) * hd;
+  const int row = pos % capacity;
   const T* src = kv_step + (size_t)t * 2 * G * hd;
   if (vec) {
     constexpr int E = 16 / sizeof(T);
     const int per_head = hd / E;
     for (int i = threadIdx.x; i < 2 * G * per_head; i += blockDim.x) {
       const int kv = i / (G * per_head), g = (i / per_head) % G, c = i % per_head;
-      T* dst = (kv ? v_cache : k_cache) + ((size_t)slot * G + g) * capacity * hd + row;
+      T* dst = (kv ? v_cache : k_cache) + kv_row_offset(page_table, pps, n_pages, slot, g, G, capacity, row, hd);
       reinterpret_cast<uint4*>(dst)[c] =
           reinterpret_cast<const uint4*>(src + ((size_t)kv * G + g) * hd)[c];
     }
   } else {
     for (int i = threadIdx.x; i < 2 * G * hd; i += blockDim.x) {
       const int kv = i / (G * hd), g = (i / hd) % G, c = i % hd;
-      T* dst = (kv ? v_cache : k_cache) + ((size_t)slot * G + g) * capacity * hd + row;
+      T* dst = (kv ? v_cache : k_cache) + kv_row_offset(page_table, pps, n_pages, slot, g, G, capacity, row, hd);
       dst[c] = src[((size_t)kv * G + g) * hd + c];
     }
   }
@@ -551,7 +555,7 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
                                const int* seq_slot, const int* slot_pos, void* q_out,
                                void* kv_step, void* k_cache, void* v_cache, int dtype,
                                int n_tokens, int H, int G, int hd, int capacity, int write_cache,
-                               cudaStream_t stream) {
+                               const int* page_table, int pages_per_slot, int n_pages, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (hd % 2 != 0 || hd / 2 > 512 || hd <= 0) return -2;
   if (dtype != DT_F32 && dtype != DT_BF16 && dtype != DT_F16) return -3;
@@ -573,23 +577,25 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
     if (dtype == DT_F32)
       launch_pdl(rope_store_many_kernel<float, TPB>, grid4, dim3(threads), 0, stream, qkv, inv_freq, token_seq,
                  q_start, seq_slot, slot_pos, (float*)q_out, (float*)kv_step, (float*)k_cache, (float*)v_cache,
-                 H, G, hd, capacity, write_cache, hpb, n_tokens);
+                 H, G, hd, capacity, write_cache, hpb, n_tokens, page_table, pages_per_slot, n_pages);
     else if (dtype == DT_BF16)
       launch_pdl(rope_store_many_kernel<__nv_bfloat16, TPB>, grid4, dim3(threads), 0, stream, qkv, inv_freq,
                  token_seq, q_start, seq_slot, slot_pos, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_step,
                  (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, G, hd, capacity, write_cache, hpb,
-                 n_tokens);
+                 n_tokens, page_table, pages_per_slot, n_pages);
     else
       launch_pdl(rope_store_many_kernel<__half, TPB>, grid4, dim3(threads), 0, stream, qkv, inv_freq,
                  token_seq, q_start, seq_slot, slot_pos, (__half*)q_out, (__half*)kv_step,
-                 (__half*)k_cache, (__half*)v_cache, H, G, hd, capacity, write_cache, hpb, n_tokens);
+                 (__half*)k_cache, (__half*)v_cache, H, G, hd, capacity, write_cache, hpb, n_tokens,
+                 page_table, pages_per_slot, n_pages);
     YALM_LAUNCH_CHECK();
     return 0;
   }
 #define YALM_ROPE(T, V)                                                                        \
   launch_pdl(rope_store_kernel<T, V>, grid, dim3(threads), 0, stream, qkv, n_partials,         \
              partial_stride, inv_freq, token_seq, q_start, seq_slot, slot_pos, (T*)q_out,      \
-             (T*)kv_step, (T*)k_cache, (T*)v_cache, H, G, hd, capacity, write_cache, hpb)
+             (T*)kv_step, (T*)k_cache, (T*)v_cache, H, G, hd, capacity, write_cache, hpb,      \
+             page_table, pages_per_slot, n_pages)
   if (dtype == DT_F32) {
     if (vec) YALM_ROPE(float, 4); else YALM_ROPE(float, 1);
   } else if (dtype == DT_BF16) {
@@ -605,7 +611,8 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
 extern "C" int yalm_cache_write(const void* kv_step, const int* token_seq, const int* q_start,
                                 const int* seq_slot, const int* slot_pos, void* k_cache,
                                 void* v_cache, int dtype, int n_tokens, int G, int hd,
-                                int capacity, cudaStream_t stream) {
+                                int capacity, const int* page_table, int pages_per_slot, int n_pages,
+                                cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (G <= 0 || hd <= 0 || capacity <= 0) return -2;
   const int esz = dtype == DT_F32 ? 4 : 2;
@@ -614,11 +621,12 @@ extern "C" int yalm_cache_write(const void* kv_step, const int* token_seq, const
   const dim3 grid(n_tokens), block(128);
   if (dtype == DT_F32)
     launch_pdl(cache_write_kernel<float>, grid, block, 0, stream, (const float*)kv_step, token_seq,
-               q_start, seq_slot, slot_pos, (float*)k_cache, (float*)v_cache, G, hd, capacity, vec);
+               q_start, seq_slot, slot_pos, (float*)k_cache, (float*)v_cache, G, hd, capacity, vec,
+               page_table, pages_per_slot, n_pages);
   else if (dtype == DT_BF16 || dtype == DT_F16)          // 16-bit rows are copied as they are
     launch_pdl(cache_write_kernel<uint16_t>, grid, block, 0, stream, (const uint16_t*)kv_step,
                token_seq, q_start, seq_slot, slot_pos, (uint16_t*)k_cache, (uint16_t*)v_cache, G,
-               hd, capacity, vec);
+               hd, capacity, vec, page_table, pages_per_slot, n_pages);
   else
     return -3;
   YALM_LAUNCH_CHECK();

@@ -7,7 +7,8 @@
 // its own arena at start-up, or one running inside another runtime's callback
 // where cudaMalloc is forbidden because it synchronises the device -- can call
 // yalm_attention_no_alloc instead: the arguments are those of yalm_attention
-// (api.h) without the two scratch pointers, and the scratch is a fixed array
+// (api.h) without the two scratch pointers and without a page table (the cache
+// is one block per sequence, [slots][G][capacity][hd]), and the scratch is a fixed array
 // of yalm_attention_no_alloc_capacity() floats (8 MiB) inside the library.
 //
 // Returns 0, a cudaError_t, or a refusal: -7 if n_tokens * H * nsplit *

@@ -54,18 +54,18 @@ _SIGNATURES = {
     "yalm_stream_wait": [_vp],
     "yalm_silu_mul": [_vp, _i, _ll, _vp, _i, _i, _i, _i, _vp],
     "yalm_rope_store": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
-                        _i, _i, _i, _vp],
+                        _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_advance": [_vp, _vp, _vp, _i, _vp],
-    "yalm_cache_write": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "yalm_cache_write": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_attention": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-                       _i, _i, _i, _vp],
+                       _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_attention_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-                              _i, _i, _i, _i, _vp],
+                              _i, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_attention_prefill_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                   _i, _i, _vp],
+                                   _i, _i, _vp, _i, _i, _vp],
     "yalm_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_attention_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
-                                  _i, _i, _i, _i, _i, _vp],
+                                  _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp, _vp],
     "yalm_gemm_tc": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
@@ -127,6 +127,22 @@ def _stream() -> int:
 def _need(cond: bool, msg: str) -> None:
     if not cond:
         raise KernelError(msg)
+
+
+KV_PAGE = 64     # positions per page of a paged cache
+
+
+def _pages(pages, cache: torch.Tensor, G: int, hd: int):
+    """(page_table pointer, pages per slot, pages) of a cache argument.  ``pages`` None: the
+    cache is contiguous per sequence, [slots, G, capacity, hd].  Else ``pages`` is the int32
+    table [slots, pages_per_slot] and the cache is [G, pages, 64, hd]."""
+    if pages is None:
+        return None, 0, 0
+    _need(pages.dtype == torch.int32 and pages.dim() == 2 and pages.is_contiguous(),
+          "page table: int32 [slots, pages_per_slot]")
+    _need(cache.dim() == 4 and cache.shape[0] == G and tuple(cache.shape[2:]) == (KV_PAGE, hd),
+          f"a paged cache is [{G}, pages, {KV_PAGE}, {hd}]")
+    return pages.data_ptr(), pages.shape[1], cache.shape[1]
 
 
 # --------------------------------------------------------------------------
@@ -193,8 +209,9 @@ def silu_mul(gu: torch.Tensor, out: torch.Tensor, n_partials: int = 1, paired: b
 def rope_store(qkv: torch.Tensor, n_partials: int, inv_freq: torch.Tensor, batch,
                q_out: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
                v_cache: torch.Tensor, slot_pos: torch.Tensor, H: int, G: int, hd: int,
-               capacity: int, write_cache: bool = True) -> None:
+               capacity: int, write_cache: bool = True, pages=None) -> None:
     n = q_out.shape[0]
+    pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(qkv.dtype == torch.float32 and qkv.shape[-1] == (H + 2 * G) * hd
           and qkv.shape[-2] == n and qkv.is_contiguous(), "rope_store: qkv float32 [(s,) N, (H+2G)hd]")
     _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == hd // 2, "rope_store: inv_freq")
@@ -205,20 +222,21 @@ def rope_store(qkv: torch.Tensor, n_partials: int, inv_freq: torch.Tensor, batch
                                  _p(batch.token_seq), _p(batch.q_start), _p(batch.seq_slot),
                                  _p(slot_pos), _p(q_out), _p(kv_step), _p(k_cache), _p(v_cache),
                                  dtype_code(q_out.dtype), n, H, G, hd, capacity,
-                                 1 if write_cache else 0, _stream()), "rope_store")
+                                 1 if write_cache else 0, pt, pps, npg, _stream()), "rope_store")
 
 
 def cache_write(kv_step: torch.Tensor, batch, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                slot_pos: torch.Tensor, G: int, hd: int, capacity: int) -> None:
+                slot_pos: torch.Tensor, G: int, hd: int, capacity: int, pages=None) -> None:
     """This step's keys and values (kv_step [N, 2, G, hd]) into the ring rows of the
     positions the ring keeps; positions are those before the step's advance."""
     n = kv_step.shape[0]
     _need(kv_step.dtype == k_cache.dtype == v_cache.dtype and kv_step.is_contiguous()
           and k_cache.is_contiguous() and v_cache.is_contiguous()
           and kv_step.numel() == n * 2 * G * hd, "cache_write: kv_step [N, 2, G, hd] and the cache")
+    pt, pps, npg = _pages(pages, k_cache, G, hd)
     _check(lib().yalm_cache_write(_p(kv_step), _p(batch.token_seq), _p(batch.q_start),
                                   _p(batch.seq_slot), _p(slot_pos), _p(k_cache), _p(v_cache),
-                                  dtype_code(kv_step.dtype), n, G, hd, capacity, _stream()),
+                                  dtype_code(kv_step.dtype), n, G, hd, capacity, pt, pps, npg, _stream()),
            "cache_write")
 
 
@@ -230,8 +248,10 @@ def advance(batch, slot_pos: torch.Tensor) -> None:
 def attention(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               batch, slot_pos: torch.Tensor, out: torch.Tensor, H: int, G: int, hd: int,
               capacity: int, window: Optional[int], nsplit: int = 1,
-              part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> None:
+              part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+              pages=None) -> None:
     n = q.shape[0]
+    pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(q.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == out.dtype,
           "attention: dtypes")
     _need(hd % 8 == 0 and 0 < hd <= 256,
@@ -244,7 +264,7 @@ def attention(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor, v_c
     _check(lib().yalm_attention(_p(q), _p(kv_step), _p(k_cache), _p(v_cache), _p(batch.token_seq),
                                 _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos), _p(out),
                                 _p(part_o), _p(part_ml), dtype_code(q.dtype), n, H, G, hd,
-                                capacity, int(window or 0), nsplit, _stream()), "attention",
+                                capacity, int(window or 0), nsplit, pt, pps, npg, _stream()), "attention",
            kernels=2 if nsplit > 1 else 1)
 
 
@@ -252,9 +272,10 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      seq_slot: torch.Tensor, slot_pos: torch.Tensor, out: torch.Tensor,
                      part_o: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
                      status: torch.Tensor, H: int, G: int, hd: int, capacity: int,
-                     window: Optional[int], chunk: int, max_context: int) -> None:
+                     window: Optional[int], chunk: int, max_context: int, pages=None) -> None:
     """One query per sequence over the cache (the query's own row included)."""
     n = q.shape[0]
+    pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype, "attention_decode: dtypes")
     visible = min(max_context, window) if window else max_context
     max_chunks = -(-visible // chunk)
@@ -265,7 +286,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     _check(lib().yalm_attention_decode(_p(q), _p(k_cache), _p(v_cache), _p(seq_slot), _p(slot_pos),
                                        _p(out), _p(part_o), _p(part_ml), _p(counters), _p(status),
                                        dtype_code(q.dtype), n, H, G, hd, capacity,
-                                       int(window or 0), chunk, max_context, _stream()),
+                                       int(window or 0), chunk, max_context, pt, pps, npg, _stream()),
            "attention_decode")
 
 
@@ -277,14 +298,16 @@ def mma_attention_usable(dtype: torch.dtype, hd: int) -> bool:
 
 def attention_prefill_mma(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
                           v_cache: torch.Tensor, batch, slot_pos: torch.Tensor, out: torch.Tensor,
-                          H: int, G: int, hd: int, capacity: int, window: Optional[int]) -> None:
+                          H: int, G: int, hd: int, capacity: int, window: Optional[int],
+                          pages=None) -> None:
+    pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(q.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == out.dtype
           and q.dtype in HALF_TYPES, "attention_prefill_mma: one 16-bit type throughout")
     _check(lib().yalm_attention_prefill_mma(_p(q), _p(kv_step), _p(k_cache), _p(v_cache),
                                             _p(batch.q_start), _p(batch.seq_slot), _p(slot_pos),
                                             _p(out), dtype_code(q.dtype), batch.n_seqs,
                                             max(batch.q_lens), H, G, hd,
-                                            capacity, int(window or 0), _stream()),
+                                            capacity, int(window or 0), pt, pps, npg, _stream()),
            "attention_prefill_mma")
 
 
@@ -316,8 +339,10 @@ def attention_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          seq_slot: torch.Tensor, slot_pos: torch.Tensor, out: torch.Tensor,
                          part_o: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
                          status: torch.Tensor, H: int, G: int, hd: int, capacity: int,
-                         window: Optional[int], max_context: int, chunks_per_block: int) -> None:
+                         window: Optional[int], max_context: int, chunks_per_block: int,
+                         pages=None) -> None:
     n = q.shape[0]
+    pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype and q.dtype in HALF_TYPES,
           "attention_decode_mma: one 16-bit type throughout")
     parts = decode_mma_parts(max_context, window, chunks_per_block)
@@ -329,7 +354,7 @@ def attention_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                                            _p(slot_pos), _p(out), _p(part_o), _p(part_ml),
                                            _p(counters), _p(status), dtype_code(q.dtype), n, H, G,
                                            hd, capacity, int(window or 0), max_context,
-                                           chunks_per_block,
+                                           chunks_per_block, pt, pps, npg,
                                            _stream()),
            "attention_decode_mma")
 

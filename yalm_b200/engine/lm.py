@@ -40,8 +40,11 @@ class LM:
     def __init__(self, config: Any, tensors: Dict[str, torch.Tensor], dtype="bfloat16",
                  max_context: Optional[int] = None, max_batch: int = 8, device="cuda:0",
                  gemm: str = "auto", attention: str = "auto", float32_matrices: str = "keep",
-                 window_override: Optional[int] = None):
+                 window_override: Optional[int] = None, max_tokens: Optional[int] = None):
         """``max_context``: the most positions a sequence may take (at most the model's).
+        ``max_tokens``: the most tokens all live sequences hold together (each count
+        rounded up to 64), when that is less than max_batch x max_context: the cache's
+        pages are sized by it.
         ``window_override=n``: attention parts without a window (or with a longer one)
         see only the last n positions, so the cache is a ring of n rows per sequence
         and generation goes on past n: the role of the reference's ``-T n``
@@ -59,7 +62,7 @@ class LM:
         self.model.bind(tensors, ignore_unexpected=[n for n in tensors if ignorable(n)] if ignorable else ())
         context = self.spec.max_positions if not max_context else min(int(max_context),
                                                                      self.spec.max_positions)
-        self.engine = Engine(self.model, max_batch, context)
+        self.engine = Engine(self.model, max_batch, context, max_tokens)
         self._next_key = 0
 
     # -- construction ----------------------------------------------------------
@@ -218,7 +221,8 @@ class _DeviceBackend:
             rank[i] = r
         first = [sampled[rank[i]] for i in range(B)]
         handle = {"slots": slots, "keys": [keys[i] for i in order], "rank": rank,
-                  "active": list(range(B)), "rows": list(range(B)), "perm": order}
+                  "active": list(range(B)), "rows": list(range(B)), "perm": order,
+                  "held": set(slots)}
         return handle, first
 
     def decode(self, handle, active, tokens):
@@ -229,6 +233,10 @@ class _DeviceBackend:
         B = len(active)
         if active != handle["active"]:
             rank = handle["rank"]
+            # sequences that ended give their slot and pages back now, not at the batch's end
+            gone = [handle["slots"][rank[j]] for j in handle["active"] if j not in set(active)]
+            eng.release(gone)
+            handle["held"] -= set(gone)
             # perm[r]: which entry of `active` sits in device row r; rows[r]: its row at the start
             perm = sorted(range(B), key=lambda k: rank[active[k]])
             rows = [rank[active[k]] for k in perm]
@@ -253,4 +261,5 @@ class _DeviceBackend:
         return out
 
     def end(self, handle):
-        self.engine.release(handle["slots"])
+        self.engine.release(sorted(handle["held"]))
+        handle["held"] = set()

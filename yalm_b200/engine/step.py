@@ -19,7 +19,7 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
-from ..cache import Cache
+from ..cache import Cache, CacheFull
 from ..csrc import ops
 from ..parts import Model
 from .batch import StepBatch, build_batch
@@ -34,22 +34,27 @@ class CacheMemoryError(StepError):
 
 
 class Engine:
-    def __init__(self, model: Model, n_slots: int, context: int):
+    def __init__(self, model: Model, n_slots: int, context: int, max_tokens: Optional[int] = None):
+        """``n_slots`` sequences may be live at once, each up to ``context`` positions.
+        ``max_tokens``: the most tokens they hold together (each count rounded up to 64),
+        if that is less than n_slots x context: the cache's pages are sized by it."""
         self.model = model
         self.rt = model.rt
         self.context = int(context)
         if self.context > model.spec.max_positions:
             raise StepError(f"context {context} exceeds the model's {model.spec.max_positions} positions")
         needs = model.cache_needs()
-        want = Cache.bytes_needed(needs, n_slots, self.context, self.rt.dtype)
+        want = Cache.bytes_needed(needs, n_slots, self.context, self.rt.dtype, max_tokens)
         if torch.device(self.rt.device).type == "cuda":
             free, _ = torch.cuda.mem_get_info(self.rt.device)
             if want > free:
                 raise CacheMemoryError(
-                    f"the cache for {n_slots} sequences of {self.context} positions needs "
+                    f"the cache for {n_slots} sequences of {self.context} positions"
+                    + (f" ({max_tokens} tokens in all)" if max_tokens else "") + f" needs "
                     f"{want / 2**30:.1f} GiB; {free / 2**30:.1f} GiB are free on {self.rt.device}: "
-                    f"ask for fewer sequences (max_batch) or a shorter context (max_context)")
-        self.cache = Cache(needs, n_slots, self.context, self.rt.dtype, self.rt.device)
+                    f"ask for fewer sequences (max_batch), a shorter context (max_context) or "
+                    f"fewer tokens in all (max_tokens)")
+        self.cache = Cache(needs, n_slots, self.context, self.rt.dtype, self.rt.device, max_tokens)
         self.vocab = model.spec.vocab_size
         self._graphs: "OrderedDict[tuple, dict]" = OrderedDict()    # least recently used first
         self._graph_seen: Dict[tuple, int] = {}
@@ -90,6 +95,11 @@ class Engine:
                     raise StepError(f"sequence {b}: token {t} is outside the vocabulary "
                                     f"(0..{self.vocab - 1})")
             past.append(self.cache.host_pos[s])
+        try:
+            self.cache.ensure(slots, [p + len(t) for p, t in zip(past, token_lists)])
+        except CacheFull as e:
+            raise StepError(str(e)) from None
+        self.cache.sync_tables()
         batch = build_batch(token_lists, slots, past, want, self.rt.device)
         logits = self.model.forward(batch, self.cache, batch.want_rows, batch.n_want)
         ops.advance(batch, self.cache.slot_pos)
@@ -189,9 +199,15 @@ class Engine:
         tokens are read from, and their sampled successors written to, the
         device token buffer.  Nothing crosses to the host."""
         d = self._decode_buffers()
-        for s in d["slots_host"][:B]:
+        live = d["slots_host"][:B]
+        for s in live:
             if self.cache.host_pos[s] + 1 > self.context:
                 raise StepError(f"the sequence in slot {s} is at the context's end ({self.context})")
+        try:
+            self.cache.ensure(live, [self.cache.host_pos[s] + 1 for s in live])
+        except CacheFull as e:
+            raise StepError(str(e)) from None
+        self.cache.sync_tables()
         self._set_sampling(float(temperature), int(seed))
         if not self.use_graphs:
             self._decode_body(B)

@@ -137,11 +137,11 @@ class GQAAttention:
             if tensor_cores:
                 ops.attention_decode_mma(q, view.k, view.v, batch.seq_slot, view.slot_pos, o,
                                          part_o, part_ml, counters, rt.status, H, G, hd,
-                                         view.capacity, self.window, bound, cpc)
+                                         view.capacity, self.window, bound, cpc, pages=view.pages)
             else:
                 ops.attention_decode(q, view.k, view.v, batch.seq_slot, view.slot_pos, o, part_o,
                                      part_ml, counters, rt.status, H, G, hd, view.capacity,
-                                     self.window, chunk, bound)
+                                     self.window, chunk, bound, pages=view.pages)
         elif rt.attention in ("auto", "tcgen05") and ops.tc_attention_usable(rt.dtype, hd, batch.past):
             # whole prompts: S and O in tensor memory, two query tiles per block in
             # ping-pong (99 us against 357 us for the mma.sync kernel per layer at
@@ -149,14 +149,15 @@ class GQAAttention:
             ops.attention_prefill_tc(q, kv_step, batch, o, H, G, hd, self.window, rt.status)
         elif tensor_cores:
             ops.attention_prefill_mma(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G,
-                                      hd, view.capacity, self.window)
+                                      hd, view.capacity, self.window, pages=view.pages)
         else:
             ops.attention(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
-                          view.capacity, self.window, 1, None, None)
+                          view.capacity, self.window, 1, None, None, pages=view.pages)
         stream.add_linear(o, self.w_o)
         if late_write:
             def write_ring():
-                ops.cache_write(kv_step, batch, view.k, view.v, view.slot_pos, G, hd, view.capacity)
+                ops.cache_write(kv_step, batch, view.k, view.v, view.slot_pos, G, hd, view.capacity,
+                                pages=view.pages)
             if getattr(view, "kv_step", None) is not None:
                 return write_ring                  # other run entries still read the old rows
             write_ring()

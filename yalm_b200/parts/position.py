@@ -54,4 +54,5 @@ class Rope:
     def rotate_and_store(self, qkv, n_partials, batch, view, q_out, kv_step, H, G,
                          write_cache=True) -> None:
         ops.rope_store(qkv, n_partials, self.inv_freq, batch, q_out, kv_step, view.k, view.v,
-                       view.slot_pos, H, G, self.head_dim, view.capacity, write_cache)
+                       view.slot_pos, H, G, self.head_dim, view.capacity, write_cache,
+                       pages=view.pages)
