@@ -109,8 +109,9 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partials,
     const int c = threadIdx.x + k * blockDim.x;
     v[k] = c < nvec ? xr[c] : zero;
   }
-  // four slices at a time, so that their loads are in flight together
-  constexpr int SB = 4;
+  // several slices at a time, so that their loads are in flight together: a decode
+  // step's row (one or two vectors per thread) takes up to eight slices in one round trip
+  constexpr int SB = VPT <= 2 ? 8 : 4;
   for (int s0 = 0; s0 < n_partials; s0 += SB) {
     float4 p[SB][VPT];
 #pragma unroll
@@ -210,8 +211,7 @@ __device__ __forceinline__ void rope_rotate_store(float* a, float* bb, const flo
                                                   int i, int pos, bool keep, int slot,
                                                   T* __restrict__ q_out, T* __restrict__ kv_step,
                                                   T* __restrict__ k_cache, T* __restrict__ v_cache,
-                                                  int H, int G, int hd, int capacity,
-                                                  const int* __restrict__ page_table, int pps, int n_pages) {
+                                                  int H, int G, int hd, size_t cache_row) {
   const int half = hd >> 1;
   if (head < H + G) {
 #pragma unroll
@@ -235,8 +235,7 @@ __device__ __forceinline__ void rope_rotate_store(float* a, float* bb, const flo
   RopeIO<T, VEC>::store(o, a);
   RopeIO<T, VEC>::store(o + half, bb);
   if (keep) {
-    T* c = (is_v ? v_cache : k_cache) +
-           kv_row_offset(page_table, pps, n_pages, slot, g, G, capacity, pos % capacity, hd) + i;
+    T* c = (is_v ? v_cache : k_cache) + cache_row + i;
     RopeIO<T, VEC>::store(c, a);
     RopeIO<T, VEC>::store(c + half, bb);
   }
@@ -267,29 +266,35 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
 #pragma unroll
   for (int v = 0; v < VEC; ++v) fr[v] = inv_freq[i + v];
   const int past = slot_pos[slot];                        // written by the advance kernel alone (see there)
-  pdl_wait();
-  if (head >= H + 2 * G) return;
   const int pos = past + (t - qs);
   const int end = past + (q_end - qs);                     // positions after this step
   const bool keep = write_cache && pos >= end - capacity;
+  // where the row goes in the cache (the page table too is written by host copies only)
+  size_t cache_row = 0;
+  if (keep && head >= H && head < H + 2 * G)
+    cache_row = kv_row_offset(page_table, pps, n_pages, slot, (head - H) % G, G, capacity,
+                              pos % capacity, hd);
+  pdl_wait();
+  if (head >= H + 2 * G) return;
   const int row_elems = (H + 2 * G) * hd;
   const float* sp = qkv + (size_t)t * row_elems + head * hd + i;
   float a[VEC], bb[VEC];
 #pragma unroll
   for (int v = 0; v < VEC; ++v) { a[v] = 0.f; bb[v] = 0.f; }
   if (VEC == 4) {
-    // four slices at a time, so that their loads are in flight together
-    for (int p0 = 0; p0 < n_partials; p0 += 4) {
-      float4 x[4], y[4];
+    // eight slices at a time, so that their loads are in flight together
+    constexpr int SB = 8;
+    for (int p0 = 0; p0 < n_partials; p0 += SB) {
+      float4 x[SB], y[SB];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < SB; ++j) {
         const float* pp = sp + (size_t)(p0 + j) * partial_stride;
         const bool live = p0 + j < n_partials;
         x[j] = live ? *reinterpret_cast<const float4*>(pp) : make_float4(0.f, 0.f, 0.f, 0.f);
         y[j] = live ? *reinterpret_cast<const float4*>(pp + half) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < SB; ++j) {
         a[0] += x[j].x; a[VEC > 1 ? 1 : 0] += x[j].y; a[VEC > 2 ? 2 : 0] += x[j].z; a[VEC > 3 ? 3 : 0] += x[j].w;
         bb[0] += y[j].x; bb[VEC > 1 ? 1 : 0] += y[j].y; bb[VEC > 2 ? 2 : 0] += y[j].z; bb[VEC > 3 ? 3 : 0] += y[j].w;
       }
@@ -302,7 +307,7 @@ __global__ void rope_store_kernel(const float* __restrict__ qkv, int n_partials,
     }
   }
   rope_rotate_store<T, VEC>(a, bb, fr, t, head, i, pos, keep, slot, q_out, kv_step, k_cache, v_cache, H, G, hd,
-                            capacity, page_table, pps, n_pages);
+                            cache_row);
 }
 
 // The same for many tokens whose product is a single slice (a prompt): a block takes
@@ -354,8 +359,12 @@ __global__ void rope_store_many_kernel(const float* __restrict__ qkv, const floa
     const int end = past[k] + (qe[k] - qs[k]);
     const bool keep = write_cache && pos >= end - capacity;
     float a[4] = {x[k].x, x[k].y, x[k].z, x[k].w}, bb[4] = {y[k].x, y[k].y, y[k].z, y[k].w};
+    size_t cache_row = 0;
+    if (keep && head >= H)
+      cache_row = kv_row_offset(page_table, pps, n_pages, slot[k], (head - H) % G, G, capacity,
+                                pos % capacity, hd);
     rope_rotate_store<T, 4>(a, bb, fr, t, head, i, pos, keep, slot[k], q_out, kv_step, k_cache, v_cache, H, G,
-                            hd, capacity, page_table, pps, n_pages);
+                            hd, cache_row);
   }
 }
 
