@@ -713,3 +713,43 @@ def test_every_cache_kernel_reads_and_writes_pages_like_rows(ops, dt, H, G, hd, 
     assert len(outs[0]) == len(outs[1])
     for i, (a, c) in enumerate(zip(*outs)):
         assert torch.equal(a, c), i
+
+
+@pytest.mark.parametrize("dt, eps", HALF)
+@pytest.mark.parametrize("H, G, hd, lens", [(4, 2, 128, [300, 1, 150]), (6, 2, 64, [129]), (5, 1, 32, [200, 260]),
+                                            (3, 3, 16, [700])])
+def test_many_token_product_with_rotary_epilogue(ops, H, G, hd, lens, dt, eps):
+    """gemm_2sm_rope against the two-SM product followed by the rotary kernel, bit for bit:
+    ragged prompts on top of filled slots, a ring that wraps, a paged cache."""
+    from plain_model import plain_inv_freq
+    D, cap, n_slots = 192, 96, 4
+    N = (H + 2 * G) * hd
+    inv = plain_inv_freq(hd, 10000.0, None).to(DEV)
+    slots = [2, 0, 3][:len(lens)]
+    b = B(lens, slots)
+    M = b.n_tokens
+    slot_pos = torch.tensor([30, 0, 70, 5], dtype=torch.int32, device=DEV)
+    a = torch.randn(M, D, device=DEV).to(dt)
+    w = (torch.randn(N, D, device=DEV) * 0.1).to(dt)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kc0 = torch.full((n_slots, G, cap, hd), 3.0, device=DEV, dtype=dt)
+    kp0, vp0, table = _paged(kc0, kc0, 5)
+    for pages in (None, table):
+        for write_cache in (True, False):
+            def fresh():
+                kc = (kp0 if pages is not None else kc0).clone()
+                return [torch.zeros(M, H * hd, device=DEV, dtype=dt), torch.zeros(M, 2, G, hd, device=DEV, dtype=dt),
+                        kc, kc.clone()]
+            want, got = fresh(), fresh()
+            full = torch.empty(M, N, device=DEV)
+            ops.gemm_2sm(a, w, full, ops.GEMM_STORE, status)
+            ops.rope_store(full, 1, inv, b, want[0], want[1], want[2], want[3], slot_pos, H, G, hd, cap,
+                           write_cache=write_cache, pages=pages)
+            table = torch.empty(M, hd // 2, 2, device=DEV)
+            ops.rope_table(inv, b, slot_pos, table)
+            ops.gemm_2sm_rope(a, w, table, b, got[0], got[1], got[2], got[3], slot_pos, H, G, hd, cap, status,
+                              write_cache=write_cache, pages=pages)
+            torch.cuda.synchronize()
+            assert status.item() == 0
+            for i, (g_, w_) in enumerate(zip(got, want)):
+                assert torch.equal(g_, w_), (i, write_cache, pages is not None)

@@ -102,9 +102,37 @@ int yalm_gemm_tc(const void* A, const void* W, int ab_dtype, void* out, int out_
 // 0 if the driver's tensor-map encoder was found (host-side set-up of yalm_gemm_tc).
 int yalm_gemm_tc_available(void);
 
+// cos_sin[t][i] = (cos, sin) of position(t) * inv_freq[i], positions as yalm_rope_store
+// derives them: the table that yalm_gemm_2sm_rope reads, made once per step for all layers
+int yalm_rope_table(const float* inv_freq, const int* token_seq, const int* q_start,
+                    const int* seq_slot, const int* slot_pos, float* cos_sin, int n_tokens, int half,
+                    cudaStream_t stream);
+
+// What the rotary epilogue of yalm_gemm_2sm_rope needs: the arguments of yalm_rope_store,
+// with the table of yalm_rope_table in place of the frequencies.
+typedef struct yalm_rope_args {
+  const float* cos_sin;      // [M][hd/2][2]
+  const int* token_seq;      // [M]
+  const int* q_start;        // [n_seqs + 1]
+  const int* seq_slot;       // [n_seqs]
+  const int* slot_pos;       // [slots]
+  void* q_out;               // [M, H*hd]
+  void* kv_step;             // [M, 2, G, hd]
+  void* k_cache;
+  void* v_cache;
+  const int* page_table;     // null: a cache that is one block per sequence
+  int pages_per_slot, n_pages;
+  int H, G, hd, capacity, write_cache;
+} yalm_rope_args;
+
 // Two-SM (cta_group::2) variant for many tokens: mode 0 store, 1 add, 2 silu(gate)*up.
 int yalm_gemm_2sm(const void* A, const void* W, int ab_dtype, void* out, int out_dtype, int M,
                   int N, int K, int mode, int* status, cudaStream_t stream);
+
+// The q/k/v product of many tokens with rotary encoding and cache write in its epilogue
+// (head sizes that divide 128).
+int yalm_gemm_2sm_rope(const void* A, const void* W, int ab_dtype, int M, int N, int K,
+                       const yalm_rope_args* rope, int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

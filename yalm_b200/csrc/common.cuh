@@ -97,6 +97,16 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return scratch[32];
 }
 
+// ---- the rotation of one pair ----------------------------------------------
+// (a, b) -> (a c - b s, a s + b c) with the roundings spelled out, so that every kernel
+// that rotates gives the same bits whatever the compiler would have fused.
+__device__ __forceinline__ float rotate_lo(float a, float b, float c, float s) {
+  return __fmaf_rn(a, c, -__fmul_rn(b, s));
+}
+__device__ __forceinline__ float rotate_hi(float a, float b, float c, float s) {
+  return __fmaf_rn(a, s, __fmul_rn(b, c));
+}
+
 // ---- where a cached row lives --------------------------------------------
 // The cache of one layer run is either contiguous per sequence,
 // [slots][kv heads][capacity][head size], or made of pages of KV_PAGE positions,

@@ -218,7 +218,7 @@ __device__ __forceinline__ void rope_rotate_store(float* a, float* bb, const flo
     for (int v = 0; v < VEC; ++v) {
       const float ang = (float)pos * fr[v];
       const float c = cosf(ang), s = sinf(ang);
-      const float r0 = a[v] * c - bb[v] * s, r1 = a[v] * s + bb[v] * c;
+      const float r0 = rotate_lo(a[v], bb[v], c, s), r1 = rotate_hi(a[v], bb[v], c, s);
       a[v] = r0;
       bb[v] = r1;
     }
@@ -365,6 +365,23 @@ __global__ void rope_store_many_kernel(const float* __restrict__ qkv, const floa
                                 pos % capacity, hd);
     rope_rotate_store<T, 4>(a, bb, fr, t, head, i, pos, keep, slot[k], q_out, kv_step, k_cache, v_cache, H, G,
                             hd, cache_row);
+  }
+}
+
+// cos_sin[t][i] = (cos, sin)(pos(t) * inv_freq[i]) with the angle in 32 bits, exactly as
+// rope_store_kernel computes it: the table a product with a rotary epilogue reads.
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, const int* __restrict__ token_seq,
+                                  const int* __restrict__ q_start, const int* __restrict__ seq_slot,
+                                  const int* __restrict__ slot_pos, float2* __restrict__ cos_sin,
+                                  int n_tokens, int half) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int b = token_seq[t];
+  const int pos = slot_pos[seq_slot[b]] + (t - q_start[b]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float ang = (float)pos * inv_freq[i];
+    cos_sin[(size_t)t * half + i] = make_float2(cosf(ang), sinf(ang));
   }
 }
 
@@ -613,6 +630,17 @@ extern "C" int yalm_rope_store(const float* qkv, int n_partials, long long parti
     if (vec) YALM_ROPE(__half, 4); else YALM_ROPE(__half, 1);
   }
 #undef YALM_ROPE
+  YALM_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int yalm_rope_table(const float* inv_freq, const int* token_seq, const int* q_start,
+                               const int* seq_slot, const int* slot_pos, float* cos_sin,
+                               int n_tokens, int half, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (half <= 0 || (((uintptr_t)cos_sin) & 7)) return -2;
+  launch_pdl(rope_table_kernel, dim3(n_tokens), dim3(half >= 64 ? 64 : 32), 0, stream, inv_freq, token_seq,
+             q_start, seq_slot, slot_pos, reinterpret_cast<float2*>(cos_sin), n_tokens, half);
   YALM_LAUNCH_CHECK();
   return 0;
 }

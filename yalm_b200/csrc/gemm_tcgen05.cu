@@ -492,7 +492,7 @@ template <int BT, int NACC>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS)
 gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                 void* __restrict__ out, int out_dtype, int ab_dtype, int M, int N, int K, int mode,
-                int* __restrict__ status) {
+                int* __restrict__ status, const yalm_rope_args rope) {
   using Cfg = G2Cfg<BT, NACC>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[Cfg::STAGES];
@@ -501,6 +501,10 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  // mode 5 (rotary epilogue): a 16-token chunk of the block's 128 features, so that a
+  // feature finds its rotation partner, and each token's position and cache row
+  __shared__ float rope_ex[NACC == 1 ? TC_BM : 1][17];
+  __shared__ int rope_row[NACC == 1 ? BT : 1], rope_where[NACC == 1 ? BT : 1];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
@@ -652,6 +656,76 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
                              (uint32_t)(buf * Cfg::ACC_COLS);
       const int ncols = min(BT, M - tok0);
+      if (NACC == 1 && mode == 5) {
+        // ---- rotary encoding and cache write on the way out (rows are q, k, v heads)
+        for (int j = row; j < ncols; j += SK_EPI_THREADS) {
+          const int tok = tok0 + j;
+          const int b = rope.token_seq[tok];
+          const int slot = rope.seq_slot[b];
+          const int qs = rope.q_start[b], qe = rope.q_start[b + 1];
+          const int past = rope.slot_pos[slot];
+          const int pos = past + (tok - qs);
+          const bool keep = rope.write_cache && pos >= past + (qe - qs) - rope.capacity;
+          const int r = pos % rope.capacity;
+          rope_row[j] = keep ? r : -1;
+          rope_where[j] = rope.page_table ? rope.page_table[(size_t)slot * rope.pages_per_slot + r / KV_PAGE]
+                                          : slot;
+        }
+        const int hd = rope.hd, half = hd >> 1, H = rope.H, G = rope.G;
+        const bool live = f < N;
+        const int head = live ? f / hd : 0, i = live ? f - head * hd : 0;
+        const bool upper = i >= half, rotates = head < H + G, is_v = head >= H + G;
+        const int partner = upper ? row - half : row + half;
+        // cosine and sine of (token, pair) come from a table made once per step for all layers
+        const float2* cs_col = reinterpret_cast<const float2*>(rope.cos_sin) + (upper ? i - half : i);
+        const int g = head - H - (is_v ? G : 0);
+        asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
+#pragma unroll 1
+        for (int c0 = 0; c0 < ncols; c0 += 16) {
+          float v[16];
+          tmem_ld16(taddr + c0, v);
+          // the chunk's cosines and sines: sixteen loads in flight across the barrier
+          float2 cs[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            cs[j] = (live && rotates && c0 + j < ncols)
+                        ? __ldg(cs_col + (size_t)(tok0 + c0 + j) * half) : make_float2(1.f, 0.f);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) rope_ex[row][j] = v[j];
+          asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
+          if (live) {
+            if (rotates) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float o = rope_ex[partner][j];
+                v[j] = upper ? rotate_hi(o, v[j], cs[j].x, cs[j].y) : rotate_lo(v[j], o, cs[j].x, cs[j].y);
+              }
+            }
+            const int n_here = min(16, ncols - c0);
+            if (head < H) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (j < n_here) store16_rt(ab_dtype, rope.q_out, (size_t)(tok0 + c0 + j) * H * hd + f, v[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (j >= n_here) break;
+                const int tok = tok0 + c0 + j;
+                store16_rt(ab_dtype, rope.kv_step, ((size_t)tok * 2 * G + (is_v ? G : 0) + g) * hd + i, v[j]);
+                const int r = rope_row[c0 + j];
+                if (r >= 0) {
+                  const int w = rope_where[c0 + j];
+                  const size_t at = rope.page_table
+                      ? (((size_t)g * rope.n_pages + w) * KV_PAGE + (r % KV_PAGE)) * hd + i
+                      : (((size_t)w * G + g) * rope.capacity + r) * hd + i;
+                  store16_rt(ab_dtype, is_v ? rope.v_cache : rope.k_cache, at, v[j]);
+                }
+              }
+            }
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
+        }
+      } else
 #pragma unroll 1
       for (int c0 = 0; c0 < ncols; c0 += 16) {
         float v[16];
@@ -699,7 +773,8 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
 template <int BT, int NACC>
 static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, int ab_dtype, int M,
-                      int N, int K, int mode, int* status, cudaStream_t stream) {
+                      int N, int K, int mode, int* status, cudaStream_t stream,
+                      const yalm_rope_args& rope) {
   using Cfg = G2Cfg<BT, NACC>;
   static_assert(Cfg::STAGES >= 3, "pipeline depth");
   CUtensorMap mw, ma;
@@ -720,7 +795,7 @@ static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, in
   if (pairs > tiles) pairs = tiles;
   if (pairs < 1) return -4;
   launch_pdl(gemm_2sm_kernel<BT, NACC>, dim3((unsigned)(2 * pairs)), dim3(TC_THREADS), Cfg::SMEM,
-             stream, mw, ma, out, out_dtype, ab_dtype, M, N, K, mode, status);
+             stream, mw, ma, out, out_dtype, ab_dtype, M, N, K, mode, status, rope);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -783,7 +858,27 @@ extern "C" int yalm_gemm_2sm(const void* A, const void* W, int ab_dtype, void* o
   if (mode == 2 && (N % 2 != 0)) return -3;
   if (mode == 4 && (N % 32 != 0)) return -3;
   if (mode == 1 && out_dtype != DT_F32) return -3;
+  yalm_rope_args none = {};
   if (mode == 2)
-    return launch_2sm<128, 2>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, status, stream);
-  return launch_2sm<256, 1>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, status, stream);
+    return launch_2sm<128, 2>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, status, stream, none);
+  return launch_2sm<256, 1>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, status, stream, none);
+}
+
+// The q/k/v product of a prompt with the rotary encoding and the cache write in its
+// epilogue: W's rows are the q heads, then the k heads, then the v heads; nothing but
+// rotated q (q_out), this step's keys and values (kv_step) and the cache rows is written.
+extern "C" int yalm_gemm_2sm_rope(const void* A, const void* W, int ab_dtype, int M, int N, int K,
+                                  const yalm_rope_args* rope, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (rope == nullptr) return -3;
+  if (ab_dtype != DT_BF16 && ab_dtype != DT_F16) return -3;
+  if (K <= 0 || K % 8 != 0) return -2;
+  if (((uintptr_t)A | (uintptr_t)W) & 15) return -6;
+  const int hd = rope->hd;
+  if (hd <= 0 || hd % 2 != 0 || TC_BM % hd != 0) return -2;        // a block's 128 rows hold whole heads
+  if (N != (rope->H + 2 * rope->G) * hd || rope->capacity <= 0) return -2;
+  if (!rope->cos_sin || !rope->token_seq || !rope->q_start || !rope->seq_slot || !rope->slot_pos ||
+      !rope->q_out || !rope->kv_step || !rope->k_cache || !rope->v_cache)
+    return -3;
+  return launch_2sm<256, 1>(A, W, nullptr, ab_dtype, ab_dtype, M, N, K, 5, status, stream, *rope);
 }

@@ -71,6 +71,8 @@ _SIGNATURES = {
     "yalm_gemm_tc": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_gemm_tc_available": [],
     "yalm_gemm_2sm": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "yalm_gemm_2sm_rope": [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
+    "yalm_rope_table": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
 }
 
 _lib = None
@@ -405,6 +407,57 @@ def gemm_2sm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
           "gemm_2sm: out shape")
     _check(lib().yalm_gemm_2sm(_p(a), _p(w), dtype_code(a.dtype), _p(out), dtype_code(out.dtype), M,
                                N, K, mode, _p(status), _stream()), "gemm_2sm")
+
+
+class _RopeArgs(ctypes.Structure):
+    _fields_ = [("cos_sin", _vp), ("token_seq", _vp), ("q_start", _vp), ("seq_slot", _vp),
+                ("slot_pos", _vp), ("q_out", _vp), ("kv_step", _vp), ("k_cache", _vp),
+                ("v_cache", _vp), ("page_table", _vp), ("pages_per_slot", _i), ("n_pages", _i),
+                ("H", _i), ("G", _i), ("hd", _i), ("capacity", _i), ("write_cache", _i)]
+
+
+def gemm_2sm_rope_usable(a: torch.Tensor, w: torch.Tensor, hd: int) -> bool:
+    """The q/k/v product with the rotary epilogue takes what the tcgen05 product takes and
+    head sizes that divide 128 (a block's 128 rows then hold whole heads)."""
+    return gemm_tc_usable(a, w) and hd % 2 == 0 and 128 % hd == 0
+
+
+def rope_table(inv_freq: torch.Tensor, batch, slot_pos: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = (cos, sin) of position(t) * inv_freq[i] for the batch's tokens."""
+    n, half = batch.n_tokens, inv_freq.numel()
+    _need(inv_freq.dtype == torch.float32 and out.dtype == torch.float32 and out.is_contiguous()
+          and tuple(out.shape) == (n, half, 2), "rope_table: out is float32 [tokens, hd/2, 2]")
+    _check(lib().yalm_rope_table(_p(inv_freq), _p(batch.token_seq), _p(batch.q_start),
+                                 _p(batch.seq_slot), _p(slot_pos), _p(out), n, half, _stream()),
+           "rope_table")
+
+
+def gemm_2sm_rope(a: torch.Tensor, w: torch.Tensor, cos_sin: torch.Tensor, batch,
+                  q_out: torch.Tensor, kv_step: torch.Tensor, k_cache: torch.Tensor,
+                  v_cache: torch.Tensor, slot_pos: torch.Tensor, H: int, G: int, hd: int,
+                  capacity: int, status: torch.Tensor, write_cache: bool = True, pages=None) -> None:
+    """rope_store(a @ w.T) in one launch: the two-SM product of many tokens whose epilogue
+    rotates q and k and writes q_out, kv_step and the cache rows (no 32-bit q/k/v in between).
+    ``cos_sin`` is the table of ``rope_table`` for this batch."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(a.dtype == w.dtype and a.dtype in HALF_TYPES and w.shape[1] == K and a.is_contiguous()
+          and w.is_contiguous() and N == (H + 2 * G) * hd, "gemm_2sm_rope: operands")
+    _need(q_out.dtype == kv_step.dtype == k_cache.dtype == v_cache.dtype == a.dtype
+          and q_out.is_contiguous() and kv_step.is_contiguous() and k_cache.is_contiguous()
+          and v_cache.is_contiguous() and q_out.numel() == M * H * hd
+          and kv_step.numel() == M * 2 * G * hd and cos_sin.dtype == torch.float32
+          and cos_sin.is_contiguous() and tuple(cos_sin.shape) == (M, hd // 2, 2),
+          "gemm_2sm_rope: buffers")
+    pt, pps, npg = _pages(pages, k_cache, G, hd)
+    r = _RopeArgs()
+    r.cos_sin, r.token_seq, r.q_start = _p(cos_sin), _p(batch.token_seq), _p(batch.q_start)
+    r.seq_slot, r.slot_pos = _p(batch.seq_slot), _p(slot_pos)
+    r.q_out, r.kv_step, r.k_cache, r.v_cache = _p(q_out), _p(kv_step), _p(k_cache), _p(v_cache)
+    r.page_table, r.pages_per_slot, r.n_pages = pt, pps, npg
+    r.H, r.G, r.hd, r.capacity, r.write_cache = H, G, hd, capacity, 1 if write_cache else 0
+    _check(lib().yalm_gemm_2sm_rope(_p(a), _p(w), dtype_code(a.dtype), M, N, K, ctypes.byref(r),
+                                    _p(status), _stream()), "gemm_2sm_rope")
 
 
 def sample(logits: torch.Tensor, temperature: float, seed: int, row_key: torch.Tensor,

@@ -9,7 +9,7 @@ decode steps of the same sequences except ``tokens``.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
 import torch
@@ -29,6 +29,7 @@ class StepBatch:
     want_rows: Optional[torch.Tensor] = None   # int32 flat token indices whose logits are wanted
     n_want: int = 0
     ctx_bound: int = 0                    # no sequence exceeds this many positions after the step
+    notes: dict = field(default_factory=dict)  # what parts make once per step and share between layers
 
     @property
     def is_decode(self) -> bool:

@@ -100,8 +100,13 @@ class GQAAttention:
     def forward(self, h, batch, stream, view, shared: bool = False):
         rt, H, G, hd = self.rt, self.H, self.G, self.hd
         n = batch.n_tokens
-        qkv, S = matmul_partials(rt, h, self.w_qkv, "qkv")
         q = rt.buffer("q_rot", (n, H * hd), rt.dtype)
+        # many tokens: the q/k/v product rotates and stores in its own epilogue
+        table = getattr(self.position, "step_table", None)
+        fused = (not shared and n > 128 and table is not None and rt.gemm != "simt"
+                 and ops.gemm_2sm_rope_usable(h, self.w_qkv, hd))
+        if not fused:
+            qkv, S = matmul_partials(rt, h, self.w_qkv, "qkv")
         # a layer whose cache another run entry reads keeps its step keys apart
         kv_step = view.kv_step if getattr(view, "kv_step", None) is not None else \
             rt.buffer("kv_step", (n, 2, G, hd), rt.dtype)
@@ -111,7 +116,12 @@ class GQAAttention:
         # run entry that reads this cache: then the write is handed back to the model.
         late_write = (not shared) and any(
             p > 0 and ql > 1 and p + ql > view.capacity for p, ql in zip(batch.past, batch.q_lens))
-        if shared:
+        if fused:
+            ops.gemm_2sm_rope(h, self.w_qkv, table(batch, view.slot_pos), batch, q, kv_step, view.k,
+                              view.v, view.slot_pos,
+                              H, G, hd, view.capacity, rt.status, write_cache=not late_write,
+                              pages=view.pages)
+        elif shared:
             # this run reads the owner's keys and values: rotate q only
             scratch = rt.buffer("kv_step_unused", (n, 2, G, hd), rt.dtype)
             self.position.rotate_and_store(qkv, S, batch, view, q, scratch, H, G,

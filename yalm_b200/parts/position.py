@@ -50,6 +50,23 @@ class Rope:
             raise ValueError(f"rope needs an even head size, got {self.head_dim}")
         self.inv_freq = llama3_inv_freq(self.head_dim, float(params["theta"]),
                                         params.get("scaling")).to(rt.device)
+        scaling = params.get("scaling")
+        self._table_key = "rope_table_%d_%r_%r" % (
+            self.head_dim, float(params["theta"]),
+            None if scaling is None else tuple(sorted((k, str(v)) for k, v in scaling.items())))
+
+    def step_table(self, batch, slot_pos) -> torch.Tensor:
+        """(cos, sin) of every token's angle for every pair, float32 [tokens, head_dim/2, 2]:
+        made once per step and shared by the layers whose encoding has the same constants,
+        for a q/k/v product that rotates and stores in its own epilogue (an encoding
+        without this method always gets ``rotate_and_store``)."""
+        table = batch.notes.get(self._table_key)
+        if table is None:
+            table = self.rt.buffer(self._table_key, (batch.n_tokens, self.head_dim // 2, 2),
+                                   torch.float32)
+            ops.rope_table(self.inv_freq, batch, slot_pos, table)
+            batch.notes[self._table_key] = table
+        return table
 
     def rotate_and_store(self, qkv, n_partials, batch, view, q_out, kv_step, H, G,
                          write_cache=True) -> None:
