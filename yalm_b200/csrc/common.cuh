@@ -46,6 +46,10 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
 __device__ __forceinline__ uint32_t pack2_rt(int dtype, float lo, float hi) {
   return dtype == DT_F16 ? pack2<__half>(lo, hi) : pack2<__nv_bfloat16>(lo, hi);
 }
+__device__ __forceinline__ uint16_t bits16_rt(int dtype, float v) {
+  return dtype == DT_F16 ? __half_as_ushort(__float2half_rn(v))
+                         : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
 __device__ __forceinline__ void store16_rt(int dtype, void* base, size_t index, float v) {
   if (dtype == DT_F16) reinterpret_cast<__half*>(base)[index] = __float2half_rn(v);
   else reinterpret_cast<__nv_bfloat16*>(base)[index] = __float2bfloat16_rn(v);

@@ -504,6 +504,7 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   // mode 5 (rotary epilogue): a 16-token chunk of the block's 128 features, so that a
   // feature finds its rotation partner, and each token's position and cache row
   __shared__ float rope_ex[NACC == 1 ? TC_BM : 1][17];
+  __shared__ __align__(16) uint16_t rope_out[NACC == 1 ? 16 : 1][TC_BM + 8];   // a rotated chunk, token-major
   __shared__ int rope_row[NACC == 1 ? BT : 1], rope_where[NACC == 1 ? BT : 1];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -674,11 +675,10 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const int hd = rope.hd, half = hd >> 1, H = rope.H, G = rope.G;
         const bool live = f < N;
         const int head = live ? f / hd : 0, i = live ? f - head * hd : 0;
-        const bool upper = i >= half, rotates = head < H + G, is_v = head >= H + G;
+        const bool upper = i >= half, rotates = head < H + G;
         const int partner = upper ? row - half : row + half;
         // cosine and sine of (token, pair) come from a table made once per step for all layers
         const float2* cs_col = reinterpret_cast<const float2*>(rope.cos_sin) + (upper ? i - half : i);
-        const int g = head - H - (is_v ? G : 0);
         asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
 #pragma unroll 1
         for (int c0 = 0; c0 < ncols; c0 += 16) {
@@ -701,26 +701,41 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 v[j] = upper ? rotate_hi(o, v[j], cs[j].x, cs[j].y) : rotate_lo(v[j], o, cs[j].x, cs[j].y);
               }
             }
-            const int n_here = min(16, ncols - c0);
-            if (head < H) {
+          }
+          // token-major in shared memory, so that a thread stores 16 features of one token
+          // (32 bytes) instead of one feature of 16 tokens
 #pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (j < n_here) store16_rt(ab_dtype, rope.q_out, (size_t)(tok0 + c0 + j) * H * hd + f, v[j]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (j >= n_here) break;
-                const int tok = tok0 + c0 + j;
-                store16_rt(ab_dtype, rope.kv_step, ((size_t)tok * 2 * G + (is_v ? G : 0) + g) * hd + i, v[j]);
+          for (int j = 0; j < 16; ++j) rope_out[j][row] = bits16_rt(ab_dtype, v[j]);
+          asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
+          {
+            const int j = row >> 3, fl = (row & 7) * 16;        // this thread's token and features
+            const int f0 = feat0 + (int)rank * TC_BM + fl;
+            if (c0 + j < ncols && f0 < N) {
+              const int tok = tok0 + c0 + j;
+              const int head0 = f0 / hd, i0 = f0 - head0 * hd;
+              const uint4 lo = *reinterpret_cast<const uint4*>(&rope_out[j][fl]);
+              const uint4 hi = *reinterpret_cast<const uint4*>(&rope_out[j][fl + 8]);
+              uint16_t* dst;
+              if (head0 < H) {
+                dst = reinterpret_cast<uint16_t*>(rope.q_out) + (size_t)tok * H * hd + f0;
+              } else {
+                const bool v_row = head0 >= H + G;
+                const int g0 = head0 - H - (v_row ? G : 0);
+                dst = reinterpret_cast<uint16_t*>(rope.kv_step) +
+                      ((size_t)tok * 2 * G + (v_row ? G : 0) + g0) * hd + i0;
                 const int r = rope_row[c0 + j];
                 if (r >= 0) {
                   const int w = rope_where[c0 + j];
                   const size_t at = rope.page_table
-                      ? (((size_t)g * rope.n_pages + w) * KV_PAGE + (r % KV_PAGE)) * hd + i
-                      : (((size_t)w * G + g) * rope.capacity + r) * hd + i;
-                  store16_rt(ab_dtype, is_v ? rope.v_cache : rope.k_cache, at, v[j]);
+                      ? (((size_t)g0 * rope.n_pages + w) * KV_PAGE + (r % KV_PAGE)) * hd + i0
+                      : (((size_t)w * G + g0) * rope.capacity + r) * hd + i0;
+                  uint16_t* c = reinterpret_cast<uint16_t*>(v_row ? rope.v_cache : rope.k_cache) + at;
+                  reinterpret_cast<uint4*>(c)[0] = lo;
+                  reinterpret_cast<uint4*>(c)[1] = hi;
                 }
               }
+              reinterpret_cast<uint4*>(dst)[0] = lo;
+              reinterpret_cast<uint4*>(dst)[1] = hi;
             }
           }
           asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
