@@ -339,6 +339,9 @@ def main():
                     help="only the 2,048-token prefill, once (profiling); prints its record alone")
     ap.add_argument("--no-graphs", action="store_true",
                     help="launch decode kernels one by one instead of replaying a CUDA graph")
+    ap.add_argument("--max-tokens", type=int, default=None,
+                    help="a cache pool of this many tokens in pages of 64 behind a page table, "
+                         "instead of one block of the context length per sequence")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -360,7 +363,7 @@ def main():
     def build(config, ctx, max_batch):
         t0 = time.time()
         lm = LM.from_random(config, seed=0, dtype=args.dtype, std=0.02, norm_jitter=0.0,
-                            max_context=ctx, max_batch=max_batch)
+                            max_context=ctx, max_batch=max_batch, max_tokens=args.max_tokens)
         torch.cuda.synchronize()
         print(f"[bench] model ready in {time.time() - t0:.0f} s "
               f"({lm.model.weight_bytes() / 1e9:.1f} GB weights, {lm.engine.cache.bytes() / 1e9:.1f} GB cache)",

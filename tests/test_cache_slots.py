@@ -60,9 +60,14 @@ def test_groups_have_storage_of_their_own_and_state_is_zeroed():
     c = Cache(needs, n_slots=3, context=32, dtype=torch.float32, device="cpu")
     assert len(c.groups) == 3
     full, ring, state = c.view(0), c.view(1), c.view(3)
-    # pages of 64 positions: [kv heads, pages, 64, head size]; one page per slot covers 32 rows
-    assert full.k.shape == (2, 3, 64, 16) and ring.k.shape == (2, 3, 64, 16)
-    assert full.capacity == 32 and ring.capacity == 8 and full.pages.shape == (3, 1)
+    # no bound on the tokens held: one block per sequence, [slots, kv heads, capacity, head size]
+    assert full.k.shape == (3, 2, 32, 16) and ring.k.shape == (3, 2, 8, 16)
+    assert full.capacity == 32 and ring.capacity == 8 and full.pages is None
+    # a bound below slots x capacity: pages of 64 positions, [kv heads, pages, 64, head size]
+    p = Cache({0: CacheNeed("kv", kv_heads=2, head_dim=16)}, 3, 256, torch.float32, "cpu", max_tokens=320)
+    assert p.view(0).k.shape == (2, 5, 64, 16) and p.view(0).pages.shape == (3, 4)
+    assert p.bytes() == Cache.bytes_needed({0: CacheNeed("kv", kv_heads=2, head_dim=16)}, 3, 256,
+                                           torch.float32, 320)
     assert c.view(2).k.data_ptr() != full.k.data_ptr()          # same group, own layer plane
     assert state.state.shape == (3, 4, 3)
     assert c.bytes() == Cache.bytes_needed(needs, 3, 32, torch.float32)
@@ -89,14 +94,15 @@ def test_pages_follow_the_tokens_and_come_back():
     needs = {0: CacheNeed("kv", kv_heads=1, head_dim=8),
              1: CacheNeed("kv", kv_heads=1, head_dim=8, window=100)}
     c = Cache(needs, n_slots=4, context=1000, dtype=torch.float32, device="cpu", max_tokens=640)
-    assert c.free_pages() == [10, 8]              # 640 tokens; four rings of two pages
+    assert c.free_pages() == [10]                 # 640 tokens; the four rings of 100 rows fit whole
+    assert c.view(1).pages is None and c.view(1).k.shape == (4, 1, 100, 8)
     a, b = c.acquire(2)
     c.ensure([a, b], [1, 130])
-    assert c.free_pages() == [10 - 1 - 3, 8 - 1 - 2]
+    assert c.free_pages() == [10 - 1 - 3]
     c.ensure([a, b], [64, 192])                   # still inside the pages they hold
-    assert c.free_pages() == [6, 5]
+    assert c.free_pages() == [6]
     c.ensure([a], [65])
-    assert c.free_pages() == [5, 4]
+    assert c.free_pages() == [5]
     c.sync_tables()
     full = c.view(0)
     held = c.groups[0]["held"]
@@ -104,16 +110,15 @@ def test_pages_follow_the_tokens_and_come_back():
     assert len(set(held[a]) | set(held[b])) == 5  # no page held twice
     with pytest.raises(CacheFull, match="more pages"):
         c.ensure([a, b], [200, 450])              # 2 + 5 more of the first group: only 5 are free
-    assert c.free_pages() == [5, 4]               # nothing was taken
+    assert c.free_pages() == [5]                  # nothing was taken
     c.release([a])
-    assert c.free_pages() == [7, 6]
+    assert c.free_pages() == [7]
     (d,) = c.acquire(1)
     c.ensure([d], [PAGE * 7])
-    assert c.free_pages() == [0, 4]
+    assert c.free_pages() == [0]
     c.release([b, d])
-    assert c.free_pages() == [10, 8]
-    for g in c.groups:
-        g["pool"].check()
+    assert c.free_pages() == [10]
+    c.groups[0]["pool"].check()
 
 
 def test_random_page_traffic_never_loses_or_duplicates_a_page():

@@ -72,10 +72,15 @@ def test_step_function_matches_plain_model(name, dtype):
     from yalm_b200 import LM
     from yalm_b200.config import config_from_dict
     cfg, w, reqs, refs, tr = setup(name)
-    lm = LM(config_from_dict(cfg), dict(w), dtype=dtype, max_batch=max(1, tr.max_tokens // 64))
+    # the cache is sized by the tokens held, so its rows live in pages wherever that is
+    # less than slots x context (the same sizing as bin/trace_run's)
+    lm = LM(config_from_dict(cfg), dict(w), dtype=dtype, max_batch=max(1, tr.max_tokens // 64),
+            max_tokens=tr.max_tokens)
     got = run_in_process(lm, tr)
     compare(tr, got, refs, cfg["vocab_size"], TOL[dtype])
     assert lm.engine.cache.slots.free_count == lm.max_batch
+    assert all(f == g["pool"].n_slots for f, g in zip(lm.engine.cache.free_pages(),
+                                                      [g for g in lm.engine.cache.groups if "pool" in g]))
 
 
 def test_the_two_ways_of_cutting_agree_beyond_the_plain_models_tolerance():
@@ -526,7 +531,7 @@ def test_every_page_of_every_layer_counts():
     ref = plain_forward(cfg, w, toks)
     for layer in range(cfg["num_hidden_layers"]):
         for which in (0, 1):
-            lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=2)
+            lm = LM(config_from_dict(cfg), dict(w), dtype="float32", max_batch=2, max_tokens=192)
             lm.acquire(1)                                                # the request sits in the second slot
             (s,) = lm.acquire(1)
             lm.step([toks[:100]], [s], [[]])

@@ -67,10 +67,11 @@ def setup(name):
     return _cache[name]
 
 
-def make_lm(cfg, w, dtype, max_batch):
+def make_lm(cfg, w, dtype, max_batch, max_tokens=None):
     from yalm_b200 import LM
     from yalm_b200.config import config_from_dict
-    return LM(config_from_dict(cfg), dict(w), dtype=dtype, max_context=CONTEXT, max_batch=max_batch)
+    return LM(config_from_dict(cfg), dict(w), dtype=dtype, max_context=CONTEXT, max_batch=max_batch,
+              max_tokens=max_tokens)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -80,7 +81,8 @@ def test_whole_and_last_32_one_by_one(name, dtype):
     tr = Trace()
     add_whole(tr, reqs)
     add_tail(tr, reqs, tail=32)
-    lm = make_lm(cfg, w, dtype, 1)
+    lm = make_lm(cfg, w, dtype, 1, max_tokens=448)           # seven pages of 64: a paged cache
+    assert lm.engine.cache.free_pages() == [7]
     got = run_in_process(lm, tr)
     compare(tr, got, refs, cfg["vocab_size"], TOL[dtype])
     assert int(lm.rt.status.item()) == 0

@@ -59,6 +59,15 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool p
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n)
                : "memory");
 }
+// The same under a predicate of the instruction itself (never a branch around it): `live`
+// false zero-fills, `issue` false leaves the 16 bytes alone.
+__device__ __forceinline__ void cp_async16_if(uint32_t dst, const void* src, bool live, bool issue) {
+  const int n = live ? 16 : 0;
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %3, 0;\n\t"
+               "@p cp.async.cg.shared.global [%0], [%1], 16, %2;\n\t}" ::"r"(dst), "l"(src), "r"(n),
+               "r"((int)issue)
+               : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -110,7 +119,8 @@ attn_prefill_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ kv_st
                         const T16* __restrict__ v_cache, const int* __restrict__ q_start,
                         const int* __restrict__ seq_slot, const int* __restrict__ slot_pos,
                         T16* __restrict__ out, int H, int G, int hd, int capacity,
-                        int window, float scale_log2, const int* __restrict__ page_table, int pps, int n_pages) {
+                        int window, float scale_log2, const int* __restrict__ page_table,
+                        int pps, int n_pages) {
   constexpr int NKS = HDP / 16, NOT = HDP / 8;
   extern __shared__ __align__(128) uint8_t fa_smem[];
   pdl_launch_dependents();
@@ -346,56 +356,50 @@ __device__ __forceinline__ float ex2_approx(float x) {       // 2^x; 2^-inf = 0
   return y;
 }
 
-// Where the rows of one (sequence, kv head) of a cache live (see kv_row_offset).  `pages`
-// is the sequence's own row of the page table (in shared or global memory), or null for
-// a cache that is one block per sequence.
-struct KvRows {
-  const int* pages;
-  int n_pages, slot, g, G, capacity, hd;
-  __device__ __forceinline__ size_t offset(int row) const {
-    if (pages == nullptr) return (((size_t)slot * G + g) * capacity + row) * hd;
-    return (((size_t)g * n_pages + pages[row / KV_PAGE]) * KV_PAGE + (row % KV_PAGE)) * hd;
-  }
-  // rows first .. first + n - 1 lie one after another in memory
-  __device__ __forceinline__ bool consecutive(int first, int n) const {
-    if (first + n > capacity) return false;
-    if (pages == nullptr || first / KV_PAGE == (first + n - 1) / KV_PAGE) return true;
-    return pages[(first + n - 1) / KV_PAGE] == pages[first / KV_PAGE] + 1;   // n <= KV_PAGE
-  }
-};
-constexpr int FD_TABLE = 512;      // page-table entries of a sequence kept in shared memory
-
-// One warp loads `n` consecutive positions of a cache ring (rows first_row,
-// first_row + 1, ... modulo capacity) into a swizzled tile of FD_UNIT rows and
-// zero-fills rows n and up.  Lane l takes rows (l & 7) + 8 rb and the 16-byte
-// columns (l >> 3) + 4 j: its row's swizzle is then one constant, and a full unit
-// that neither wraps nor crosses a page needs an add and an exclusive-or per copy.
+// One warp loads the first `n` of FD_UNIT positions into a swizzled tile of FD_UNIT rows and
+// zero-fills rows n and up.  Lane l takes rows (l & 7) + 8 rb and the 16-byte columns
+// (l >> 3) + 4 j: its row's swizzle is then one constant, and a copy needs an add and an
+// exclusive-or.  (A warp is alone on its scheduler here, so every instruction of the address
+// arithmetic is paid in full.)
+//
+// warp_load_run: the unit's rows follow one another in memory from `first` on.
 template <int HDP, typename T16>
-__device__ __forceinline__ void warp_load_ring_tile(uint32_t base, int n, int hd,
-                                                    const T16* cache, const KvRows& rows,
-                                                    int first_row, int lane) {
+__device__ __forceinline__ void warp_load_run(uint32_t base, int n, int hd, const T16* first,
+                                              int lane) {
   const int r7 = lane & 7, cg = lane >> 3;
   const int cpr = hd >> 3;
   const uint32_t s_lane = base + r7 * (HDP * 2) + ((cg ^ (r7 & 3)) << 4);
   const uint32_t x_lane = (uint32_t)(r7 >> 2) << 6;
-  if (n == FD_UNIT && rows.consecutive(first_row, FD_UNIT)) {
-    const T16* g = cache + rows.offset(first_row) + (size_t)r7 * hd + cg * 8;
+  const T16* g = first + (size_t)r7 * hd + cg * 8;
 #pragma unroll
-    for (int rb = 0; rb < FD_UNIT / 8; ++rb) {
+  for (int rb = 0; rb < FD_UNIT / 8; ++rb) {
+    const bool live = rb * 8 + r7 < n;
 #pragma unroll
-      for (int j = 0; j < HDP / 32; ++j)
-        if (cg + 4 * j < cpr)
-          cp_async16(s_lane + rb * 8 * HDP * 2 + ((uint32_t)(j << 6) ^ x_lane), g + j * 32, true);
-      g += (size_t)8 * hd;
-    }
-    return;
+    for (int j = 0; j < HDP / 32; ++j)
+      cp_async16_if(s_lane + rb * 8 * HDP * 2 + ((uint32_t)(j << 6) ^ x_lane), g + j * 32, live,
+                    cg + 4 * j < cpr);
+    g += (size_t)8 * hd;
   }
+}
+
+// warp_load_rows: a unit that wraps around the ring's end or crosses a page; every row is
+// looked up (rows first_row, first_row + 1, ... modulo capacity of the kv head's rows at
+// `head`; through the sequence's row of the page table if there is one).  Rare, and kept
+// out of line so that it does not shape the code around the common path.
+template <int HDP, typename T16>
+__device__ __noinline__ void warp_load_rows(uint32_t base, int n, int hd, const T16* head,
+                                            const int* __restrict__ pages, int first_row,
+                                            int capacity, int lane) {
+  const int r7 = lane & 7, cg = lane >> 3;
+  const int cpr = hd >> 3;
+  const uint32_t s_lane = base + r7 * (HDP * 2) + ((cg ^ (r7 & 3)) << 4);
+  const uint32_t x_lane = (uint32_t)(r7 >> 2) << 6;
 #pragma unroll 1
   for (int rb = 0; rb < FD_UNIT / 8; ++rb) {
     const int r = rb * 8 + r7;
-    int row = first_row + r;
-    if (row >= rows.capacity) row = rows.capacity >= FD_UNIT ? row - rows.capacity : row % rows.capacity;
-    const T16* g = cache + rows.offset(row) + cg * 8;
+    int row = (first_row + r) % capacity;
+    if (pages != nullptr) row = pages[row / KV_PAGE] * KV_PAGE + (row % KV_PAGE);
+    const T16* g = head + (size_t)row * hd + cg * 8;
 #pragma unroll
     for (int j = 0; j < HDP / 32; ++j)
       if (cg + 4 * j < cpr)
@@ -403,7 +407,7 @@ __device__ __forceinline__ void warp_load_ring_tile(uint32_t base, int n, int hd
   }
 }
 
-template <int HDP, int NT, typename T16>
+template <int HDP, int NT, typename T16, bool PAGED>
 __global__ void __launch_bounds__(FA_THREADS)
 attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cache,
                        const T16* __restrict__ v_cache, const int* __restrict__ seq_slot,
@@ -421,7 +425,6 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   __shared__ float wl_s[FA_WARPS][FD_ROWS];
   __shared__ float row_m[FD_ROWS], row_l[FD_ROWS];
   __shared__ int last_flag;
-  __shared__ int pages_s[FD_TABLE];                          // this sequence's row of the page table
   pdl_launch_dependents();
   const int R = H / G;
   const int nhc = (R + FD_ROWS - 1) / FD_ROWS;
@@ -430,18 +433,6 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   const int nh = min(FD_ROWS, R - hchunk * FD_ROWS);
   const int t = blockIdx.z, part = blockIdx.x;
   const int slot = seq_slot[t];           // written by a host copy, never by a kernel: safe early
-  // The page table is written by host copies before the step's first kernel, like the
-  // batch's index arrays: it may be read before the dependency wait too.  The sequence's
-  // row of it is asked for now, together with its position, and kept in shared memory
-  // (a row longer than FD_TABLE entries is read in place).
-  const int* my_pages = page_table ? page_table + (size_t)slot * pps : nullptr;
-  const bool table_in_smem = page_table != nullptr && pps <= FD_TABLE;
-  int entries[FD_TABLE / FA_THREADS];
-#pragma unroll
-  for (int k = 0; k < FD_TABLE / FA_THREADS; ++k) {
-    const int idx = threadIdx.x + k * FA_THREADS;
-    entries[k] = (table_in_smem && idx < pps) ? my_pages[idx] : 0;
-  }
   // Positions are written by the advance kernel alone, and that kernel lets nothing start
   // before it has ended: they too may be read while the previous kernel still runs.
   const int pos = slot_pos[slot];
@@ -460,30 +451,59 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   const int gid = lane >> 2, tig = lane & 3;
   const uint32_t q_s = smem_u32(fa_smem);                    // [16 heads][HDP]
   const uint32_t ring_s = q_s + FD_ROWS * HDP * 2 + warp * WARP_RING;
-  if (table_in_smem) {
-#pragma unroll
-    for (int k = 0; k < FD_TABLE / FA_THREADS; ++k) pages_s[threadIdx.x + k * FA_THREADS] = entries[k];
-    my_pages = pages_s;
+  // A head size below HDP: the tiles' columns from hd on are zeroed once (no copy ever writes
+  // them), and the products below run over all HDP columns without a test per step.
+  if (hd < HDP) {
+    constexpr int WORDS = (FD_ROWS * HDP * 2 + FA_WARPS * WARP_RING) / 16;
+    for (int i = threadIdx.x; i < WORDS; i += FA_THREADS)
+      reinterpret_cast<uint4*>(fa_smem)[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
   }
-  const KvRows rows{my_pages, n_pages, slot, g, G, capacity, hd};
-  auto load_unit = [&](int u, int stage) {
-    const int k_lo = lo + u * FD_UNIT;
-    const int n = min(FD_UNIT, pos + 1 - k_lo);
+  // The page table is written by host copies before the step's first kernel, like the
+  // batch's index arrays: it may be read before the dependency wait too.
+  const int* my_pages = PAGED ? page_table + (size_t)slot * pps : nullptr;
+  const size_t head_off = PAGED ? (size_t)g * n_pages * KV_PAGE * hd
+                                : ((size_t)slot * G + g) * capacity * hd;
+  const T16* kc = k_cache + head_off;
+  const T16* vc = v_cache + head_off;
+  // A unit's place in the ring is carried from unit to unit (no division in the loop), and
+  // the page that holds its first row is asked for one unit ahead of its use.
+  const int ring_step = (FA_WARPS * FD_UNIT) % capacity;
+  auto page_of = [&](int u, int row) { return (PAGED && u < u1) ? my_pages[row / KV_PAGE] : 0; };
+  auto load_unit = [&](int u, int stage, int first, int page) {
+    const int n = min(FD_UNIT, pos + 1 - (lo + u * FD_UNIT));
     const uint32_t dst = ring_s + stage * 2 * TILE;
-    const int first = k_lo % capacity;
-    warp_load_ring_tile<HDP>(dst, n, hd, k_cache, rows, first, lane);
-    warp_load_ring_tile<HDP>(dst + TILE, n, hd, v_cache, rows, first, lane);
+    const int in_page = first & (KV_PAGE - 1);
+    const bool run = first + FD_UNIT <= capacity && (!PAGED || in_page + FD_UNIT <= KV_PAGE);
+    if (run) {
+      const size_t off = (PAGED ? (size_t)page * KV_PAGE + in_page : (size_t)first) * hd;
+      warp_load_run<HDP>(dst, n, hd, kc + off, lane);
+      warp_load_run<HDP>(dst + TILE, n, hd, vc + off, lane);
+    } else {
+      warp_load_rows<HDP>(dst, n, hd, kc, my_pages, first, capacity, lane);
+      warp_load_rows<HDP>(dst + TILE, n, hd, vc, my_pages, first, capacity, lane);
+    }
   };
   // FD_STAGES - 1 units are requested before the first is used.  All rows but the newest
   // position's are older than this step: their units are requested before the wait; the
   // unit that holds the newest key (the sequence's last) and the queries come after it.
   const int u_new = (nkeys - 1) / FD_UNIT;
   int u_next = u0 + warp;
+  int row_next = (lo + u_next * FD_UNIT) % capacity;
+  int row_first[FD_STAGES - 1], page_first[FD_STAGES - 1];
 #pragma unroll
   for (int i = 0; i < FD_STAGES - 1; ++i) {
-    if (u_next < u1 && u_next != u_new) load_unit(u_next, i);
+    row_first[i] = row_next;
+    page_first[i] = page_of(u_next, row_next);
     u_next += FA_WARPS;
+    row_next += ring_step;
+    if (row_next >= capacity) row_next -= capacity;
+  }
+  int page_next = page_of(u_next, row_next);
+#pragma unroll
+  for (int i = 0; i < FD_STAGES - 1; ++i) {
+    const int u = u0 + warp + i * FA_WARPS;
+    if (u < u1 && u != u_new) load_unit(u, i, row_first[i], page_first[i]);
     cp_async_commit();
   }
   pdl_wait();
@@ -493,7 +513,7 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
 #pragma unroll
   for (int i = 0; i < FD_STAGES - 1; ++i) {
     const int u = u0 + warp + i * FA_WARPS;
-    if (u < u1 && u == u_new) load_unit(u, i);
+    if (u < u1 && u == u_new) load_unit(u, i, row_first[i], page_first[i]);
   }
   cp_async_commit();
   cp_async_wait<0>();                                        // this thread's share of Q and of the first units
@@ -502,7 +522,6 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   uint32_t qf[NKS][4];
 #pragma unroll
   for (int ks = 0; ks < NKS; ++ks)
-    if (ks < nks)
       ldsm_x4(qf[ks], tile_addr<HDP>(q_s, (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
 
   float o[NKS][NT][4];                                       // O^T: 16 features x 8 heads per tile
@@ -528,8 +547,11 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
     const int stage = it % FD_STAGES;
     cp_async_wait<FD_STAGES - 2>();                          // unit u has landed (this lane's share)
     __syncwarp();                                            // ... every lane's; unit u-1 is read out
-    if (u_next < u1) load_unit(u_next, (it + FD_STAGES - 1) % FD_STAGES);
+    if (u_next < u1) load_unit(u_next, (it + FD_STAGES - 1) % FD_STAGES, row_next, page_next);
     u_next += FA_WARPS;
+    row_next += ring_step;
+    if (row_next >= capacity) row_next -= capacity;
+    page_next = page_of(u_next, row_next);
     cp_async_commit();
     const uint32_t k_s = ring_s + stage * 2 * TILE + k_lane, v_s = ring_s + stage * 2 * TILE + TILE + v_lane;
     const int n = min(FD_UNIT, pos + 1 - (lo + u * FD_UNIT));
@@ -543,7 +565,7 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
         for (int j = 0; j < 4; ++j) s[mt][nt][j] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < NKS; ++ks) {
-      if (ks < nks) {
+      {
         const uint32_t a = k_s + ((uint32_t)(ks << 5) ^ k_x);
 #pragma unroll
         for (int mt = 0; mt < FD_MT; ++mt) {
@@ -609,7 +631,7 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
       }
 #pragma unroll
     for (int i = 0; i < NKS; ++i) {
-      if (i < nks) {
+      {
         const uint32_t a = v_s + ((uint32_t)(i << 5) ^ v_x);
 #pragma unroll
         for (int mt = 0; mt < FD_MT; ++mt) {
@@ -735,7 +757,7 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   }
 }
 
-template <int HDP, int NT, typename T16>
+template <int HDP, int NT, typename T16, bool PAGED>
 static int launch_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                              const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                              float* part_ml, int* counters, int* status, int n_seqs, int H, int G,
@@ -747,7 +769,7 @@ static int launch_decode_mma(const void* q, const void* k_cache, const void* v_c
   if (smem < merge) smem = merge;
   static size_t attr_smem = 0;
   if (smem > attr_smem) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HDP, NT, T16>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HDP, NT, T16, PAGED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_smem = smem;
@@ -755,7 +777,7 @@ static int launch_decode_mma(const void* q, const void* k_cache, const void* v_c
   const int nhc = (H / G + FD_ROWS - 1) / FD_ROWS;
   const dim3 grid(max_parts, G * nhc, n_seqs);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
-  launch_pdl(attn_decode_mma_kernel<HDP, NT, T16>, grid, dim3(FA_THREADS), smem, stream,
+  launch_pdl(attn_decode_mma_kernel<HDP, NT, T16, PAGED>, grid, dim3(FA_THREADS), smem, stream,
              (const T16*)q, (const T16*)k_cache, (const T16*)v_cache,
              seq_slot, slot_pos, (T16*)out, part_o, part_ml, counters, status, H, G, hd,
              capacity, window, cpc, max_parts, scale_log2, page_table, pps, n_pages);
@@ -767,8 +789,8 @@ template <int HDP, typename T16>
 static int launch_prefill(const void* q, const void* kv_step, const void* k_cache,
                           const void* v_cache, const int* q_start, const int* seq_slot,
                           const int* slot_pos, void* out, int n_seqs, int max_q_len, int H, int G,
-                          int hd, int capacity, int window, const int* page_table, int pps, int n_pages,
-                          cudaStream_t stream) {
+                          int hd, int capacity, int window, const int* page_table, int pps,
+                          int n_pages, cudaStream_t stream) {
   const size_t smem = (size_t)(FA_BM + 4 * FA_BN) * HDP * 2;
   static bool attr_set = false;
   if (!attr_set) {
@@ -845,10 +867,12 @@ extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, con
   const int max_parts = (max_chunks + chunks_per_block - 1) / chunks_per_block;
   if ((size_t)G * ((H / G + FD_ROWS - 1) / FD_ROWS) > 65535) return -4;
   const bool two = H / G > 8;                                 // a second tile of 8 heads
-#define YALM_FD(HDP, NT, T)                                                                      \
-  launch_decode_mma<HDP, NT, T>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,   \
-                                counters, status, n_seqs, H, G, hd, capacity, window,            \
-                                chunks_per_block, max_parts, page_table, pages_per_slot, n_pages, stream)
+#define YALM_FD_(HDP, NT, T, PAGED)                                                              \
+  launch_decode_mma<HDP, NT, T, PAGED>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o,     \
+                                       part_ml, counters, status, n_seqs, H, G, hd, capacity,    \
+                                       window, chunks_per_block, max_parts, page_table,          \
+                                       pages_per_slot, n_pages, stream)
+#define YALM_FD(HDP, NT, T) (page_table ? YALM_FD_(HDP, NT, T, true) : YALM_FD_(HDP, NT, T, false))
   if (dtype == DT_F16) {
     if (hd <= 64) return two ? YALM_FD(64, 2, __half) : YALM_FD(64, 1, __half);
     return two ? YALM_FD(128, 2, __half) : YALM_FD(128, 1, __half);
@@ -856,4 +880,5 @@ extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, con
   if (hd <= 64) return two ? YALM_FD(64, 2, __nv_bfloat16) : YALM_FD(64, 1, __nv_bfloat16);
   return two ? YALM_FD(128, 2, __nv_bfloat16) : YALM_FD(128, 1, __nv_bfloat16);
 #undef YALM_FD
+#undef YALM_FD_
 }

@@ -12,6 +12,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -50,15 +51,19 @@ def build_batch(token_lists: Sequence[Sequence[int]], slots: Sequence[int], past
     q_start = [0]
     for q in q_lens:
         q_start.append(q_start[-1] + q)
-    flat, tseq, rows = [], [], []
+    pieces, rows = [], []
     for b, toks in enumerate(token_lists):
-        flat.extend(int(t) for t in toks)
-        tseq.extend([b] * len(toks))
-        for w in want[b]:
-            if not 0 <= w < len(toks):
-                raise IndexError(f"sequence {b}: wanted place {w} is outside its {len(toks)} tokens")
-            rows.append(q_start[b] + w)
-    host = torch.tensor(flat + tseq + q_start + list(slots) + rows, dtype=torch.int32)
+        pieces.append(np.asarray(toks, dtype=np.int32))
+        w = np.asarray(want[b], dtype=np.int64)
+        if w.size:
+            if int(w.min()) < 0 or int(w.max()) >= len(toks):
+                bad = next(x for x in want[b] if not 0 <= x < len(toks))
+                raise IndexError(f"sequence {b}: wanted place {bad} is outside its {len(toks)} tokens")
+            rows.append((w + q_start[b]).astype(np.int32))
+    rows = np.concatenate(rows) if rows else np.zeros(0, dtype=np.int32)
+    tseq = np.repeat(np.arange(B, dtype=np.int32), q_lens)
+    host = torch.from_numpy(np.concatenate(
+        pieces + [tseq, np.asarray(q_start, dtype=np.int32), np.asarray(list(slots), dtype=np.int32), rows]))
     if torch.device(device).type == "cuda":
         host = host.pin_memory()
     dev = host.to(device, non_blocking=True)

@@ -17,6 +17,7 @@ from __future__ import annotations
 from collections import OrderedDict
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import Cache, CacheFull
@@ -90,10 +91,11 @@ class Engine:
                 raise StepError(
                     f"sequence {b} would reach {self.cache.host_pos[s] + len(toks)} positions; "
                     f"the context is {self.context}")
-            for t in toks:
-                if not 0 <= int(t) < self.vocab:
-                    raise StepError(f"sequence {b}: token {t} is outside the vocabulary "
-                                    f"(0..{self.vocab - 1})")
+            ids = np.asarray(toks, dtype=np.int64)
+            if ids.ndim != 1 or int(ids.min()) < 0 or int(ids.max()) >= self.vocab:
+                bad = next((t for t in toks if not 0 <= int(t) < self.vocab), toks[0])
+                raise StepError(f"sequence {b}: token {bad} is outside the vocabulary "
+                                f"(0..{self.vocab - 1})")
             past.append(self.cache.host_pos[s])
         try:
             self.cache.ensure(slots, [p + len(t) for p, t in zip(past, token_lists)])
