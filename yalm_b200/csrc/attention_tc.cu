@@ -2,23 +2,31 @@
 // accumulators in tensor memory, operands brought by TMA.
 //
 // A block takes 256 query tokens of one head of one sequence as two tiles of 128
-// rows, A and B.  Warp 0 is the TMA producer, warp 1 issues the MMAs, warps 2-5 are
-// the softmax group of tile A and warps 6-9 that of tile B: one query row per
-// thread.  Keys and values come in blocks of 64 through rings of three stages each
-// and serve both tiles.  Per block of keys and per tile: the MMA thread issues
-// S = Q.K^T into the tile's 64 columns of TMEM; each softmax thread reads its row of
-// S (tcgen05.ld), applies scale and mask, keeps a reference maximum and the sum in
-// 32-bit, and writes exp2(s - reference) in the 16-bit type into the tile's swizzled P
-// buffer in shared memory; the MMA thread then issues O += P.V (V is the MN-major B
-// operand, exactly as TMA lays its rows down) into the tile's O columns of TMEM.  The
-// two tiles alternate on the tensor core, so that while one group computes its
-// softmax the other tile's products run.
+// rows, A and B.  Warp 0 is the TMA producer, warps 1 and 10 issue the products of tile
+// A and of tile B, warps 2-5 are the softmax group of tile A and warps 6-9 that of tile
+// B: one query row per thread.  Keys and values come in blocks of 64 through rings of
+// three stages each and serve both tiles.  Per block of keys and per tile: the tile's
+// issuer puts S = Q.K^T into one of the tile's two buffers of 64 columns of TMEM (two
+// blocks ahead of the softmax); each softmax thread reads its row of S (tcgen05.ld),
+// applies scale and mask, keeps a reference maximum and the sum in 32-bit, and writes
+// exp2(s - reference) in the 16-bit type back over the first 32 columns of that S buffer
+// (tcgen05.st, two keys per column); the issuer then puts O += P.V (P as the A operand
+// from tensor memory, V as the MN-major B operand exactly as TMA lays its rows down)
+// into the tile's O columns.  Nothing of P touches shared memory: at 128 bytes a clock
+// shared memory is what bounds these products (Q and K for S alone are 6 KB per 32
+// clocks of arithmetic), and P there cost a fifth of the kernel's time.
+//
+// Each issuer is a whole warp that runs the (uniform) loop, with lane 0 issuing under a
+// predicate: the descriptors then stay in uniform registers.  One issuer for both tiles,
+// and in a branch that a single lane takes, was what bounded the kernel (about 80 clocks
+// per instruction, 23 % tensor pipe); a stage of K or V is free once both have committed it.
 //
 // O stays in TMEM for the whole row of blocks.  Its reference maximum is raised
 // only when a block's maximum exceeds it by more than 8 (in log2 units, so
-// probabilities stay below 256): then the warp reads its O rows, scales them and
-// writes them back (tcgen05.st) before the next product is issued.  The final
-// division by the sum uses the same reference, so the result is the plain softmax.
+// probabilities stay below 256): then the warp waits for the previous block's product,
+// reads its O rows, scales them and writes them back (tcgen05.st) before the next
+// product is issued.  The final division by the sum uses the same reference, so the
+// result is the plain softmax.
 //
 // Same mathematics as the reference's attn_dot / attn_softmax / att_mix
 // (infer.cu:339-523) and as attention.cu.  Takes the case "all keys are this step's
@@ -36,7 +44,8 @@ namespace yalm {
 
 constexpr int TA_BM = 128;     // query rows per tile; a block takes two tiles
 constexpr int TA_BN = 64;      // keys per iteration
-constexpr int TA_THREADS = 320;
+constexpr int TA_THREADS = 352;
+constexpr int TA_MMA_B = 10;   // the warp that issues tile B's products (warp 1: tile A's)
 constexpr int TA_KSTAGES = 3;
 constexpr int TA_VSTAGES = 3;
 constexpr float TA_RAISE = 8.f;   // a block's maximum may exceed the reference by this much (log2)
@@ -70,17 +79,32 @@ __device__ __forceinline__ uint64_t ta_desc_mn(uint32_t addr, uint32_t lbo) {
   d |= (uint64_t)2 << 61;
   return d;
 }
-__device__ __forceinline__ void ta_umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                        uint32_t idesc, uint32_t accumulate) {
+// A product issued from a whole warp: every lane runs the (uniform) descriptor arithmetic, so
+// it can stay in uniform registers, and the instruction itself is issued by the lane whose
+// `leader` is set.  (Inside a branch that one lane takes, every operand goes from a vector
+// register to a uniform one, one transfer after the other: about 80 clocks per instruction.)
+__device__ __forceinline__ void ta_umma_by(uint32_t leader, uint32_t tmem_d, uint64_t adesc,
+                                           uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      "{\n.reg .pred p, q;\nsetp.ne.b32 p, %4, 0;\nsetp.ne.b32 q, %5, 0;\n"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)
       : "memory");
 }
-__device__ __forceinline__ void ta_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-               ::"r"(bar) : "memory");
+// ... with the A operand in tensor memory (row m in lane m, two 16-bit elements per column)
+__device__ __forceinline__ void ta_umma_tmem_a_by(uint32_t leader, uint32_t tmem_d, uint32_t tmem_a,
+                                                  uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p, q;\nsetp.ne.b32 p, %4, 0;\nsetp.ne.b32 q, %5, 0;\n"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)
+      : "memory");
+}
+__device__ __forceinline__ void ta_commit_by(uint32_t leader, uint32_t bar) {
+  asm volatile(
+      "{\n.reg .pred q;\nsetp.ne.b32 q, %1, 0;\n"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}"
+      ::"r"(bar), "r"(leader) : "memory");
 }
 __device__ __forceinline__ void ta_ld32(uint32_t taddr, float* v) {
   uint32_t r[32];
@@ -163,21 +187,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   constexpr int SUB = HD / 64;                     // 64-column sub-tiles of a head
   constexpr int Q_BYTES = TA_BM * HD * 2;          // one query tile
   constexpr int KV_BYTES = TA_BN * HD * 2;         // one block of K or of V
-  constexpr int P_BYTES = TA_BM * TA_BN * 2;
   constexpr int TMEM_COLS = 512;                   // S: 2 tiles x 2 buffers x 64; O: 2 tiles x HD
   extern __shared__ uint8_t ta_smem[];
-  __shared__ __align__(8) uint64_t q_full, s_full[2][2], p_ready[2], pv_done[2];
+  __shared__ __align__(8) uint64_t q_full, s_full[2][2], p_ready[2][2], pv_done[2][2];
   __shared__ __align__(8) uint64_t k_full[TA_KSTAGES], k_empty[TA_KSTAGES];
   __shared__ __align__(8) uint64_t v_full[TA_VSTAGES], v_empty[TA_VSTAGES];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   // heads run fastest in the grid, then sequences, and a sequence's blocks come from its
   // end: the long blocks of every head and sequence start before any short one
   const int b = blockIdx.y, h = blockIdx.x;
   const int g = h / (H / G);
-  const int qs = q_start[b], q_len = q_start[b + 1] - qs;       // written by a host copy: safe early
+  // (broadcast from lane 0: the same value in every lane, and known to be)
+  const int qs = __shfl_sync(0xffffffffu, q_start[b], 0);      // written by a host copy: safe early
+  const int q_len = __shfl_sync(0xffffffffu, q_start[b + 1], 0) - qs;
   const int n_blocks = (q_len + 2 * TA_BM - 1) / (2 * TA_BM);
   if ((int)blockIdx.z >= n_blocks) return;
   const int m0 = (n_blocks - 1 - (int)blockIdx.z) * 2 * TA_BM;
@@ -201,7 +226,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t q_s = base;                                    // tiles A and B
   const uint32_t k_s = q_s + 2 * Q_BYTES;
   const uint32_t v_s = k_s + TA_KSTAGES * KV_BYTES;
-  const uint32_t p_s = v_s + TA_VSTAGES * KV_BYTES;             // tiles A and B
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -209,16 +233,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int x = 0; x < 2; ++x) {
       mbar_init(smem_u32(&s_full[x][0]), 1);
       mbar_init(smem_u32(&s_full[x][1]), 1);
-      mbar_init(smem_u32(&p_ready[x]), TA_BM);
-      mbar_init(smem_u32(&pv_done[x]), 1);
+      for (int buf = 0; buf < 2; ++buf) {
+        mbar_init(smem_u32(&p_ready[x][buf]), TA_BM);
+        mbar_init(smem_u32(&pv_done[x][buf]), 1);
+      }
     }
     for (int s = 0; s < TA_KSTAGES; ++s) {
       mbar_init(smem_u32(&k_full[s]), 1);
-      mbar_init(smem_u32(&k_empty[s]), 1);
+      mbar_init(smem_u32(&k_empty[s]), 2);
     }
     for (int s = 0; s < TA_VSTAGES; ++s) {
       mbar_init(smem_u32(&v_full[s]), 1);
-      mbar_init(smem_u32(&v_empty[s]), 1);
+      mbar_init(smem_u32(&v_empty[s]), 2);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -231,7 +257,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_slot, 0);
   // columns: two S buffers of tile A, two of tile B, O of tile A, O of tile B
   const uint32_t tmem_s[2] = {tmem_base, tmem_base + 2 * TA_BN};
   const uint32_t tmem_o[2] = {tmem_base + 4 * TA_BN, tmem_base + 4 * TA_BN + HD};
@@ -275,9 +301,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer
-    if (lane == 0) {
+  } else if (warp == 1 || warp == TA_MMA_B) {
+    // ---------------- MMA issuers, one per tile: the whole warp runs the loop, lane 0 issues
+    {
+      const int x = warp == 1 ? 0 : 1;
+      const uint32_t leader = lane == 0 ? 1u : 0u;
       // S: M = 128 queries, N = 64 keys, both operands K-major
       const uint32_t idesc_s = (1u << 4) | (FMT << 7) | (FMT << 10) | ((uint32_t)(TA_BN >> 3) << 17) |
                                ((uint32_t)(TA_BM >> 4) << 24);
@@ -285,71 +313,74 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const uint32_t idesc_pv = (1u << 4) | (FMT << 7) | (FMT << 10) | (1u << 16) |
                                 ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
       // descriptors: one per operand tile, advanced by constants inside the loops
-      const uint64_t q_desc[2] = {ta_desc_k(q_s), ta_desc_k(q_s + Q_BYTES)};
-      const uint64_t p_desc[2] = {ta_desc_k(p_s), ta_desc_k(p_s + P_BYTES)};
-      auto issue_s = [&](int x, int stage, int buf) {         // buf: the block's parity for this tile
+      // this issuer's tile: its queries, its columns of tensor memory, its barriers
+      const uint64_t q_desc = ta_desc_k(q_s + x * Q_BYTES);
+      const uint32_t my_s = x ? tmem_s[1] : tmem_s[0], my_o = x ? tmem_o[1] : tmem_o[0];
+      const int my_kb0 = x ? t_kb0[1] : t_kb0[0], my_kb1 = x ? t_kb1[1] : t_kb1[0];
+      const uint32_t bar_s = smem_u32(x ? &s_full[1][0] : &s_full[0][0]);   // [1] is 8 bytes on
+      const uint32_t bar_p = smem_u32(x ? &p_ready[1][0] : &p_ready[0][0]);
+      const uint32_t bar_pv = smem_u32(x ? &pv_done[1][0] : &pv_done[0][0]);
+      auto mine = [&](int kb) { return kb >= my_kb0 && kb < my_kb1; };
+      auto issue_s = [&](int stage, int buf) {                // buf: the block's parity for this tile
         const uint64_t k_desc = ta_desc_k(k_s + stage * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          ta_umma(tmem_s[x] + buf * TA_BN,
-                  q_desc[x] + (uint64_t)(((ks / 4) * (TA_BM * 128) + (ks % 4) * 32) >> 4),
-                  k_desc + (uint64_t)(((ks / 4) * (TA_BN * 128) + (ks % 4) * 32) >> 4), idesc_s,
-                  ks > 0 ? 1u : 0u);
-        ta_commit(smem_u32(&s_full[x][buf]));
+          ta_umma_by(leader, my_s + buf * TA_BN,
+                     q_desc + (uint64_t)(((ks / 4) * (TA_BM * 128) + (ks % 4) * 32) >> 4),
+                     k_desc + (uint64_t)(((ks / 4) * (TA_BN * 128) + (ks % 4) * 32) >> 4), idesc_s,
+                     ks > 0 ? 1u : 0u);
+        ta_commit_by(leader, bar_s + 8 * buf);
       };
-      auto issue_pv = [&](int x, int stage, bool first) {
+      auto issue_pv = [&](int stage, int blk) {               // blk: the tile's own count of blocks
         const uint64_t v_desc = ta_desc_mn(v_s + stage * KV_BYTES, TA_BN * 128);
 #pragma unroll
         for (int kk = 0; kk < TA_BN / 16; ++kk)
-          ta_umma(tmem_o[x], p_desc[x] + (uint64_t)((kk * 32) >> 4),
-                  v_desc + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv,
-                  (first && kk == 0) ? 0u : 1u);
-        ta_commit(smem_u32(&pv_done[x]));
+          ta_umma_tmem_a_by(leader, my_o, my_s + (blk & 1) * TA_BN + kk * 8,
+                            v_desc + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv,
+                            (blk == 0 && kk == 0) ? 0u : 1u);
+        ta_commit_by(leader, bar_pv + 8 * (blk & 1));
       };
       // S runs two blocks of keys ahead of the softmax: each tile has two S buffers, and
       // a buffer is free again once the row threads have signalled the block that used it.
-      bool ok = mbar_wait(smem_u32(&q_full), 0, abort_p);
+      // A stage of K or V is free once both issuers have committed it (also the one whose
+      // tile does not see that block: its commit has nothing to wait for).
+      bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&q_full), 0, abort_p));
       for (int pre = 0; pre < 2 && pre < n_it && ok; ++pre) {
-        ok = mbar_wait(smem_u32(&k_full[pre]), 0, abort_p);
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&k_full[pre]), 0, abort_p));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-        for (int x = 0; x < 2; ++x)
-          if (active(x, kb_lo + pre)) issue_s(x, pre, (kb_lo + pre - t_kb0[x]) & 1);
-        ta_commit(smem_u32(&k_empty[pre]));
+        if (mine(kb_lo + pre)) issue_s(pre, (kb_lo + pre - my_kb0) & 1);
+        ta_commit_by(leader, smem_u32(&k_empty[pre]));
       }
       for (int it = 0; it < n_it && ok; ++it) {
         const int kb = kb_lo + it;
         const int sv = it % TA_VSTAGES, sk = (it + 2) % TA_KSTAGES;
         const bool more = it + 2 < n_it;
-        bool v_here = false, k_here = false;
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
+        // (an issuer whose tile does not see a block still waits for the block's stage before
+        // it commits it: one arrival per issuer and filling, or the producer would run ahead)
+        const bool pv = mine(kb);
+        if (pv) {
+          // P of this block is in tensor memory, S has been read, O is rescaled
+          const int blk = kb - my_kb0;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_p + 8 * (blk & 1), (uint32_t)(blk >> 1) & 1u, abort_p));
           if (!ok) break;
-          if (active(x, kb)) {
-            // P of this block is in shared memory, S has been read, O is rescaled
-            ok = mbar_wait(smem_u32(&p_ready[x]), (uint32_t)(kb - t_kb0[x]) & 1u, abort_p);
-            if (ok && !v_here) {
-              ok = mbar_wait(smem_u32(&v_full[sv]), (it / TA_VSTAGES) & 1, abort_p);
-              v_here = true;
-            }
-            if (!ok) break;
+        }
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&v_full[sv]), (it / TA_VSTAGES) & 1, abort_p));
+        if (!ok) break;
+        if (pv) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_pv(sv, kb - my_kb0);
+        }
+        if (more) {
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&k_full[sk]), ((it + 2) / TA_KSTAGES) & 1, abort_p));
+          if (!ok) break;
+          if (mine(kb + 2)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_pv(x, sv, kb == t_kb0[x]);
-          }
-          if (more && active(x, kb + 2)) {
-            if (!k_here) {
-              ok = mbar_wait(smem_u32(&k_full[sk]), ((it + 2) / TA_KSTAGES) & 1, abort_p);
-              k_here = true;
-              if (!ok) break;
-              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
-            issue_s(x, sk, (kb + 2 - t_kb0[x]) & 1);          // into the buffer just read out
+            issue_s(sk, (kb + 2 - my_kb0) & 1);
           }
         }
-        if (!ok) break;
-        ta_commit(smem_u32(&v_empty[sv]));                    // V of this block is consumed
-        if (more) ta_commit(smem_u32(&k_empty[sk]));          // and K of the block after next
+        ta_commit_by(leader, smem_u32(&v_empty[sv]));         // V of this block is consumed
+        if (more) ta_commit_by(leader, smem_u32(&k_empty[sk]));   // and K of the block after next
       }
     }
   } else {
@@ -365,9 +396,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t my_s = (x ? tmem_s[1] : tmem_s[0]) + lane_addr;
     const uint32_t my_o = (x ? tmem_o[1] : tmem_o[0]) + lane_addr;
     const uint32_t bar_s = smem_u32(x ? &s_full[1][0] : &s_full[0][0]);   // [1] is 8 bytes on
-    const uint32_t bar_p = smem_u32(x ? &p_ready[1] : &p_ready[0]);
-    const uint32_t bar_pv = smem_u32(x ? &pv_done[1] : &pv_done[0]);
-    const uint32_t p_row = p_s + x * P_BYTES + row * 128;
+    const uint32_t bar_p = smem_u32(x ? &p_ready[1][0] : &p_ready[0][0]);   // likewise
+    const uint32_t bar_pv = smem_u32(x ? &pv_done[1][0] : &pv_done[0][0]);
     float m_ref = -INFINITY, l_run = 0.f;
     pdl_wait();
     bool ok = true;
@@ -407,46 +437,44 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const float m_new = raise ? m_blk : m_ref;
       const float corr = raise ? ta_ex2(m_ref - m_new) : 1.f;
       const bool any_raise = __any_sync(0xffffffffu, raise);
-      if (it > 0) {
-        // the previous product has read P and written O
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, (it - 1) & 1, abort_p));
+      if (it > 0 && any_raise) {                              // uniform over the warp; rare
+        // O is rescaled once the previous block's product has been added to it
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_pv + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1, abort_p));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (any_raise) {                                      // uniform over the warp
 #pragma unroll 1
-          for (int c = 0; c < HD; c += 32) {
-            float v[32];
-            ta_ld32(my_o + c, v);
+        for (int c = 0; c < HD; c += 32) {
+          float v[32];
+          ta_ld32(my_o + c, v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= corr;
-            ta_st32(my_o + c, v);
-          }
+          for (int i = 0; i < 32; ++i) v[i] *= corr;
+          ta_st32(my_o + c, v);
         }
       }
       m_ref = m_new;
       const float neg = m_ref > -INFINITY ? -m_ref : 0.f;
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      float2 ls[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      const float2 scale2 = make_float2(scale_log2, scale_log2), neg2 = make_float2(neg, neg);
 #pragma unroll
-      for (int ch = 0; ch < TA_BN / 8; ++ch) {                // 16-byte chunks of 8 keys
-        float e[8];
+      float pk[TA_BN / 2];                                    // P, two keys per 32-bit column
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          e[i] = ta_ex2(fmaf(s[ch * 8 + i], scale_log2, neg));
-          ls[i & 3] += e[i];
-        }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                     ::"r"(p_row + ((ch ^ (row & 7)) << 4)), "r"(pack2<T16>(e[0], e[1])),
-                       "r"(pack2<T16>(e[2], e[3])), "r"(pack2<T16>(e[4], e[5])),
-                       "r"(pack2<T16>(e[6], e[7]))
-                     : "memory");
+      for (int j = 0; j < TA_BN / 2; ++j) {                   // pairs of keys, in packed arithmetic
+        const float2 x = __ffma2_rn(make_float2(s[2 * j], s[2 * j + 1]), scale2, neg2);
+        const float2 e = make_float2(ta_ex2(x.x), ta_ex2(x.y));
+        ls[j & 1] = __fadd2_rn(ls[j & 1], e);
+        pk[j] = __uint_as_float(pack2<T16>(e.x, e.y));
       }
-      l_run = l_run * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
+      // P takes the place of the first half of the S columns it came from: the product
+      // reads it from tensor memory, and S of the block after next overwrites it only
+      // after that product (the tensor core runs its instructions in order)
+      ta_st32(my_s + (it & 1) * TA_BN, pk);
+      l_run = l_run * corr + ((ls[0].x + ls[0].y) + (ls[1].x + ls[1].y));
       // P is complete for this row, S has been read, O is rescaled: the MMA thread may go on
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(bar_p);
+      mbar_arrive(bar_p + 8 * (it & 1));
     }
-    if (ok && n_x > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, (n_x - 1) & 1, abort_p));
+    if (ok && n_x > 0)
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_pv + 8 * ((n_x - 1) & 1), ((n_x - 1) >> 1) & 1, abort_p));
     if (ok && n_x > 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = 1.0f / l_run;
@@ -529,9 +557,8 @@ static int launch_prefill_tc(const void* q, const void* kv_step, const int* q_st
   if (rc) return rc;
   rc = ta_make_map(&mkv, kv_step, n_tokens, (long long)2 * G * HD, TA_BN, half);
   if (rc) return rc;
-  // two query tiles, the K and V rings, two P tiles, slack to align to 1024
-  const size_t smem = (size_t)2 * TA_BM * HD * 2 + (size_t)(TA_KSTAGES + TA_VSTAGES) * TA_BN * HD * 2 +
-                      (size_t)2 * TA_BM * TA_BN * 2 + 1024;
+  // two query tiles, the K and V rings, slack to align to 1024
+  const size_t smem = (size_t)2 * TA_BM * HD * 2 + (size_t)(TA_KSTAGES + TA_VSTAGES) * TA_BN * HD * 2 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, T16>,
