@@ -48,17 +48,23 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
   return d;
 }
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                          uint32_t idesc, uint32_t accumulate) {
+// A product issued from a whole warp: every lane runs the (uniform) descriptor arithmetic,
+// which can then stay in uniform registers, and the lane whose `issue` is set issues the
+// instruction.  (In a branch that one lane takes, each operand goes from a vector register
+// to a uniform one, a transfer at a time: about 80 clocks per instruction.)
+__device__ __forceinline__ void umma_f16_by(uint32_t issue, uint32_t tmem_d, uint64_t adesc,
+                                             uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      "{\n.reg .pred p, q;\nsetp.ne.b32 p, %4, 0;\nsetp.ne.b32 q, %5, 0;\n"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(issue)
       : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-               ::"r"(bar) : "memory");
+__device__ __forceinline__ void umma_commit_by(uint32_t issue, uint32_t bar) {
+  asm volatile(
+      "{\n.reg .pred q;\nsetp.ne.b32 q, %1, 0;\n"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}"
+      ::"r"(bar), "r"(issue) : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   uint32_t r[16];
@@ -112,7 +118,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // (broadcasts from lane 0: the compiler then knows these are the same in every lane)
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int n_out = mode == 2 ? N / 2 : N;                   // features this grid covers
   const int feat0 = blockIdx.x * TC_BM;
@@ -141,7 +148,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_slot, 0);
   volatile int* abort_p = &abort_flag;
   pdl_launch_dependents();
 
@@ -179,14 +186,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer
-    if (lane == 0 && nk > 0) {
+    // ---------------- MMA issuer: the whole warp runs the loop, lane 0 issues
+    if (nk > 0) {
+      const uint32_t issue = lane == 0 ? 1u : 0u;
       const uint32_t idesc = umma_idesc(ab_dtype, BT, TC_BM);
       bool ok = true;
       for (int it = 0; it < nk && ok; ++it) {
         const int s = it % Cfg::STAGES;
         const uint32_t phase = (it / Cfg::STAGES) & 1;
-        ok = mbar_wait(smem_u32(&full_bar[s]), phase, abort_p);
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s]), phase, abort_p));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t stage = tiles + s * Cfg::STAGE_BYTES;
@@ -196,15 +204,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
           const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
           const uint64_t koff = (uint64_t)((k * TC_UMMA_K * 2) >> 4);   // 32 bytes per k-step
-          umma_f16(tmem_base, wdesc + koff, adesc + koff, idesc, acc);
+          umma_f16_by(issue, tmem_base, wdesc + koff, adesc + koff, idesc, acc);
           if (NACC == 2) {
             const uint64_t w2 = umma_desc_k_sw128(stage + Cfg::W_BYTES);
-            umma_f16(tmem_base + BT, w2 + koff, adesc + koff, idesc, acc);
+            umma_f16_by(issue, tmem_base + BT, w2 + koff, adesc + koff, idesc, acc);
           }
         }
-        umma_commit(smem_u32(&empty_bar[s]));     // frees the stage once these MMAs are done
+        umma_commit_by(issue, smem_u32(&empty_bar[s]));     // frees the stage once these MMAs are done
       }
-      if (ok) umma_commit(smem_u32(&acc_bar));    // accumulators complete
+      if (ok) umma_commit_by(issue, smem_u32(&acc_bar));    // accumulators complete
     }
   } else {
     // ---------------- epilogue: TMEM -> registers -> global
@@ -466,20 +474,22 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar_cluster_addr)
       : "memory");
 }
-__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                               uint32_t idesc, uint32_t accumulate) {
+// The pair's product, issued like umma_f16_by (whole warp, one issuing lane).
+__device__ __forceinline__ void umma_f16_pair_by(uint32_t issue, uint32_t tmem_d, uint64_t adesc,
+                                                  uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      "{\n.reg .pred p, q;\nsetp.ne.b32 p, %4, 0;\nsetp.ne.b32 q, %5, 0;\n"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(issue)
       : "memory");
 }
 // arrives on the barrier at this offset in both blocks once the MMAs issued so far are done
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+__device__ __forceinline__ void umma_commit_pair_by(uint32_t issue, uint32_t bar) {
   asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
-      " [%0], %1;"
-      ::"r"(bar), "h"((uint16_t)3) : "memory");
+      "{\n.reg .pred q;\nsetp.ne.b32 q, %1, 0;\n"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+      " [%0], %2;\n}"
+      ::"r"(bar), "r"(issue), "h"((uint16_t)3) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];"
@@ -507,8 +517,9 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   __shared__ __align__(16) uint16_t rope_out[NACC == 1 ? 16 : 1][TC_BM + 8];   // a rotated chunk, token-major
   __shared__ int rope_row[NACC == 1 ? BT : 1], rope_where[NACC == 1 ? BT : 1];
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_rank();
+  // (broadcasts from lane 0: the compiler then knows these are the same in every lane)
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+  const uint32_t rank = __shfl_sync(0xffffffffu, cluster_rank(), 0);
   const bool leader = rank == 0;
   const uint32_t tiles_smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int n_out = mode == 2 ? N / 2 : N;
@@ -540,7 +551,7 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   __syncthreads();
   cluster_sync_all();                                        // both blocks' barriers exist
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_slot, 0);
   volatile int* abort_p = &abort_flag;
   pdl_launch_dependents();
 
@@ -603,21 +614,22 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer: one thread of the first block, for the pair
-    if (lane == 0 && leader && pair < n_tiles) {
+    // ---------------- MMA issuer: warp 1 of the first block runs the loop, its lane 0 issues for the pair
+    if (leader && pair < n_tiles) {
+      const uint32_t issue = lane == 0 ? 1u : 0u;
       const uint32_t idesc = umma_idesc(ab_dtype, BT, 2 * TC_BM);
       bool ok = true;
       int it = 0, part = 0;
       for (int t = pair; t < n_tiles && ok; t += n_pairs, ++part) {
         const int buf = part & 1;
-        ok = mbar_wait(smem_u32(&acc_empty[buf]), (((uint32_t)part >> 1) & 1u) ^ 1u, abort_p);
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_empty[buf]), (((uint32_t)part >> 1) & 1u) ^ 1u, abort_p));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc_addr = tmem_base + (uint32_t)(buf * Cfg::ACC_COLS);
         for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
           const int s = it % Cfg::STAGES;
           const uint32_t phase = (it / Cfg::STAGES) & 1;
-          ok = mbar_wait(smem_u32(&full_bar[s]), phase, abort_p);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s]), phase, abort_p));
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t stage = tiles_smem + s * Cfg::STAGE_BYTES;
@@ -627,15 +639,15 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
             const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
             const uint64_t koff = (uint64_t)((k * TC_UMMA_K * 2) >> 4);
-            umma_f16_pair(acc_addr, wdesc + koff, adesc + koff, idesc, acc);
+            umma_f16_pair_by(issue, acc_addr, wdesc + koff, adesc + koff, idesc, acc);
             if (NACC == 2) {
               const uint64_t w2 = umma_desc_k_sw128(stage + Cfg::W_BYTES);
-              umma_f16_pair(acc_addr + BT, w2 + koff, adesc + koff, idesc, acc);
+              umma_f16_pair_by(issue, acc_addr + BT, w2 + koff, adesc + koff, idesc, acc);
             }
           }
-          umma_commit_pair(smem_u32(&empty_bar[s]));           // frees the stage in both blocks
+          umma_commit_pair_by(issue, smem_u32(&empty_bar[s]));           // frees the stage in both blocks
         }
-        if (ok) umma_commit_pair(smem_u32(&acc_full[buf]));    // both blocks' epilogues may read
+        if (ok) umma_commit_pair_by(issue, smem_u32(&acc_full[buf]));    // both blocks' epilogues may read
       }
     }
   } else {
