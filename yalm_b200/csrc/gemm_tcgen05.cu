@@ -29,13 +29,22 @@ constexpr int TC_BK = 64;       // k per stage: 64 16-bit elements = one 128-byt
 constexpr int TC_UMMA_K = 16;
 constexpr int TC_THREADS = 192; // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
-                                            uint32_t bar) {
+// The producers, like the issuers below, run as whole warps with one lane (`issue` set)
+// executing the copy or the arrival, so that addresses and coordinates are uniform values.
+__device__ __forceinline__ void tma_load_2d_by(uint32_t issue, uint32_t dst, const CUtensorMap* map,
+                                               int x, int y, uint32_t bar) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      "{\n.reg .pred q;\nsetp.ne.b32 q, %5, 0;\n"
+      "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];\n}"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar), "r"(issue)
       : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_by(uint32_t issue, uint32_t bar, uint32_t bytes) {
+  asm volatile(
+      "{\n.reg .pred q;\nsetp.ne.b32 q, %2, 0;\n"
+      "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n}"
+      ::"r"(bar), "r"(bytes), "r"(issue) : "memory");
 }
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
 // (64 16-bit elements) with the 128-byte swizzle: 8-row groups 1024 bytes apart.
@@ -153,8 +162,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   pdl_launch_dependents();
 
   if (warp == 0) {
-    // ---------------- TMA producer
-    if (lane == 0 && nk > 0) {
+    // ---------------- TMA producer: the whole warp runs the loop, lane 0 issues
+    if (nk > 0) {
+      const uint32_t issue = lane == 0 ? 1u : 0u;
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
       // weights do not depend on the previous kernel: the first stages' weight
@@ -163,26 +173,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       for (int it = 0; it < pre; ++it) {
         const uint32_t stage = tiles + it * Cfg::STAGE_BYTES;
         const uint32_t bar = smem_u32(&full_bar[it]);
-        mbar_expect_tx(bar, Cfg::STAGE_BYTES);
+        mbar_expect_tx_by(issue, bar, Cfg::STAGE_BYTES);
         const int kx = (kb_lo + it) * TC_BK;
-        tma_load_2d(stage, &map_w, kx, feat0, bar);
-        if (NACC == 2) tma_load_2d(stage + Cfg::W_BYTES, &map_w, kx, n_out + feat0, bar);
+        tma_load_2d_by(issue, stage, &map_w, kx, feat0, bar);
+        if (NACC == 2) tma_load_2d_by(issue, stage + Cfg::W_BYTES, &map_w, kx, n_out + feat0, bar);
       }
       pdl_wait();
       for (int it = 0; it < pre; ++it)
-        tma_load_2d(tiles + it * Cfg::STAGE_BYTES + NACC * Cfg::W_BYTES, &map_a,
+        tma_load_2d_by(issue, tiles + it * Cfg::STAGE_BYTES + NACC * Cfg::W_BYTES, &map_a,
                     (kb_lo + it) * TC_BK, tok0, smem_u32(&full_bar[it]));
       for (int it = pre; it < nk; ++it) {
         const int s = it % Cfg::STAGES;
         const uint32_t phase = (it / Cfg::STAGES) & 1;
-        if (!mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u, abort_p)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u, abort_p))) break;
         const uint32_t stage = tiles + s * Cfg::STAGE_BYTES;
         const uint32_t bar = smem_u32(&full_bar[s]);
-        mbar_expect_tx(bar, Cfg::STAGE_BYTES);
+        mbar_expect_tx_by(issue, bar, Cfg::STAGE_BYTES);
         const int kx = (kb_lo + it) * TC_BK;
-        tma_load_2d(stage, &map_w, kx, feat0, bar);
-        if (NACC == 2) tma_load_2d(stage + Cfg::W_BYTES, &map_w, kx, n_out + feat0, bar);
-        tma_load_2d(stage + NACC * Cfg::W_BYTES, &map_a, kx, tok0, bar);
+        tma_load_2d_by(issue, stage, &map_w, kx, feat0, bar);
+        if (NACC == 2) tma_load_2d_by(issue, stage + Cfg::W_BYTES, &map_w, kx, n_out + feat0, bar);
+        tma_load_2d_by(issue, stage + NACC * Cfg::W_BYTES, &map_a, kx, tok0, bar);
       }
     }
   } else if (warp == 1) {
@@ -466,12 +476,13 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 // TMA load whose completion bytes are counted on a barrier that may live in the peer block
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
-                                                 uint32_t bar_cluster_addr) {
+__device__ __forceinline__ void tma_load_2d_pair_by(uint32_t issue, uint32_t dst, const CUtensorMap* map,
+                                                    int x, int y, uint32_t bar_cluster_addr) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar_cluster_addr)
+      "{\n.reg .pred q;\nsetp.ne.b32 q, %5, 0;\n"
+      "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];\n}"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar_cluster_addr), "r"(issue)
       : "memory");
 }
 // The pair's product, issued like umma_f16_by (whole warp, one issuing lane).
@@ -566,8 +577,9 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   };
 
   if (warp == 0) {
-    // ---------------- TMA producer (one thread in each block)
-    if (lane == 0 && pair < n_tiles) {
+    // ---------------- TMA producer (warp 0 of each block runs the loop, its lane 0 issues)
+    if (pair < n_tiles) {
+      const uint32_t issue = lane == 0 ? 1u : 0u;
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
       // weights do not depend on the previous kernel: the first tile's first stages of them
@@ -580,14 +592,14 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         for (int kb = 0; kb < pre; ++kb) {
           const uint32_t stage = tiles_smem + kb * Cfg::STAGE_BYTES;
           const uint32_t bar0 = map_to_rank(smem_u32(&full_bar[kb]), 0);
-          if (leader) mbar_expect_tx(smem_u32(&full_bar[kb]), 2 * Cfg::STAGE_BYTES);
-          tma_load_2d_pair(stage, &map_w, kb * TC_BK, my_feat, bar0);
-          if (NACC == 2) tma_load_2d_pair(stage + Cfg::W_BYTES, &map_w, kb * TC_BK, n_out + my_feat, bar0);
+          mbar_expect_tx_by(leader ? issue : 0u, smem_u32(&full_bar[kb]), 2 * Cfg::STAGE_BYTES);
+          tma_load_2d_pair_by(issue, stage, &map_w, kb * TC_BK, my_feat, bar0);
+          if (NACC == 2) tma_load_2d_pair_by(issue, stage + Cfg::W_BYTES, &map_w, kb * TC_BK, n_out + my_feat, bar0);
         }
         pdl_wait();
         const int my_tok = tok0 + (int)rank * (BT / 2);
         for (int kb = 0; kb < pre; ++kb)
-          tma_load_2d_pair(tiles_smem + kb * Cfg::STAGE_BYTES + NACC * Cfg::W_BYTES, &map_a, kb * TC_BK, my_tok,
+          tma_load_2d_pair_by(issue, tiles_smem + kb * Cfg::STAGE_BYTES + NACC * Cfg::W_BYTES, &map_a, kb * TC_BK, my_tok,
                            map_to_rank(smem_u32(&full_bar[kb]), 0));
       }
       int it = 0;
@@ -601,15 +613,15 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           if (it < pre) continue;                             // requested above
           const int s = it % Cfg::STAGES;
           const uint32_t phase = (it / Cfg::STAGES) & 1;
-          ok = mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u, abort_p);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u, abort_p));
           if (!ok) break;
           const uint32_t stage = tiles_smem + s * Cfg::STAGE_BYTES;
           const uint32_t bar0 = map_to_rank(smem_u32(&full_bar[s]), 0);   // the first block's
-          if (leader) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * Cfg::STAGE_BYTES);
+          mbar_expect_tx_by(leader ? issue : 0u, smem_u32(&full_bar[s]), 2 * Cfg::STAGE_BYTES);
           const int kx = kb * TC_BK;
-          tma_load_2d_pair(stage, &map_w, kx, my_feat, bar0);
-          if (NACC == 2) tma_load_2d_pair(stage + Cfg::W_BYTES, &map_w, kx, n_out + my_feat, bar0);
-          tma_load_2d_pair(stage + NACC * Cfg::W_BYTES, &map_a, kx, my_tok, bar0);
+          tma_load_2d_pair_by(issue, stage, &map_w, kx, my_feat, bar0);
+          if (NACC == 2) tma_load_2d_pair_by(issue, stage + Cfg::W_BYTES, &map_w, kx, n_out + my_feat, bar0);
+          tma_load_2d_pair_by(issue, stage + NACC * Cfg::W_BYTES, &map_a, kx, my_tok, bar0);
         }
       }
     }
