@@ -106,16 +106,54 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """SM clock and throttle reasons while the timed region runs: NVML from a thread of this
+    process every 10 ms (a timed region of 64 decode steps lasts 0.2 s), or `nvidia-smi -lms`
+    where the NVML binding is missing.  Only reads; nothing is set."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self):
         self.proc = None
+        self.thread = None
         self.lines = []
+        self.samples = []          # (sm MHz, reasons bit mask)
+        self.max_mhz = None
+        self.running = False
+
+    def _nvml(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            first = visible.split(",")[0].strip() if visible else "0"
+            h = (pynvml.nvmlDeviceGetHandleByUUID(first) if first.startswith("GPU-")
+                 else pynvml.nvmlDeviceGetHandleByIndex(int(first) if first.isdigit() else 0))
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+            return pynvml, h
+        except Exception:
+            return None, None
 
     def start(self):
+        nv, h = self._nvml()
+        if nv is not None:
+            self.running = True
+
+            def loop():
+                while self.running:
+                    try:
+                        self.samples.append((float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)),
+                                             int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+                                             if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons")
+                                             else int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))))
+                    except Exception:
+                        pass
+                    time.sleep(0.01)
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
@@ -129,6 +167,16 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.thread is not None:
+            self.running = False
+            self.thread.join(timeout=2)
+            mhz = sorted(m for m, _ in self.samples)
+            # NVML's reason bits: 0x8 hw slowdown, 0x40 hw thermal, 0x20 sw thermal, 0x4 sw power cap
+            bits = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                    "sw_power_cap": 0x4}
+            reasons = sorted(n for n, b in bits.items() if any(r & b for _, r in self.samples))
+            return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": self.max_mhz,
+                    "reasons": reasons, "samples": len(mhz), "source": "nvml, every 10 ms"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -137,7 +185,6 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         mhz, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for l in self.lines:
             p = [x.strip() for x in l.split(",")]
             if len(p) < 6:
@@ -147,12 +194,12 @@ class ClockSampler:
                 mx = float(p[1])
             except ValueError:
                 continue
-            for n, v in zip(names, p[2:6]):
+            for n, v in zip(self.NAMES, p[2:6]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         mhz.sort()
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx,
-                "reasons": sorted(reasons), "samples": len(mhz)}
+                "reasons": sorted(reasons), "samples": len(mhz), "source": "nvidia-smi -lms 100"}
 
 
 def prompt_lengths(n, lo, hi, seed):
@@ -422,6 +469,8 @@ def main():
         point("decode_b8", lm, 8, half, STEADY, 1, lo, hi)
         point("decode_b64", lm, 64, half, STEADY, 74, lo, hi)
         # what a short generate() call sees: the 32 steps right after a batch of long prompts
+        # (run once before, untimed, so that this shape's graph exists as it would in a server)
+        time_decode(lm, 8, 32, 0, seed=5, lo=2048, hi=2048)
         point("decode_b8_first32_after_2048_token_prompts", lm, 8, 32, 0, 5, 2048, 2048)
         # the reference's one published figure: 63.8 tokens/s at batch 1 on an RTX 4090
         # (its README; other hardware, so no vs_baseline for the headline metric)
