@@ -617,6 +617,55 @@ def test_tcgen05_prefill_attention(ops, H, G, hd, window, dt, eps):
             assert (got - ref).abs().max().item() <= 6.4 * eps, (rep, i)
 
 
+@pytest.mark.parametrize("paged", [False, True])
+@pytest.mark.parametrize("H, G, hd, cap, window", [(8, 2, 128, 1000, None), (4, 4, 64, 700, None),
+                                                   (6, 3, 128, 960, 100), (3, 1, 64, 1024, 37)])
+@pytest.mark.parametrize("dt, eps", HALF)
+def test_tcgen05_prefill_attention_over_the_cache(ops, H, G, hd, cap, window, dt, eps, paged):
+    """attention_prefill_tc_cache: prompts cut into three steps (the second and third read
+    earlier keys from the cache: one block per sequence, or pages in a shuffled pool) against
+    the plain attention over the whole sequences.  Lengths end inside a tile, at a tile, in a
+    second block of two tiles; one sequence joins at the second step (its past is 0 there).
+    The cache is filled with a large finite value first: a row beyond a sequence's end that
+    reached a product would show."""
+    inv = plain_inv_freq(hd, 10000.0, None).to(DEV)
+    n_slots, slots = 5, [2, 0, 3, 4]
+    slot_pos = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+    kc = torch.full((n_slots, G, cap, hd), 3.0, device=DEV, dtype=dt)
+    vc = torch.full_like(kc, 3.0)
+    table = None
+    if paged:
+        kc, vc, table = _paged(kc, vc, seed=hd + cap)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    hist = {s: [] for s in slots}
+    for lens in ([150, 1, 70, 0], [300, 130, 256, 65], [240, 64, 1, 200]):
+        live = [(n, s) for n, s in zip(lens, slots) if n > 0]
+        b = B([n for n, _ in live], [s for _, s in live])
+        N = b.n_tokens
+        qkv = torch.randn(N, (H + 2 * G) * hd, device=DEV)
+        q_out = torch.empty(N, H * hd, device=DEV, dtype=dt)
+        kv_step = torch.empty(N, 2, G, hd, device=DEV, dtype=dt)
+        ops.rope_store(qkv, 1, inv, b, q_out, kv_step, kc, vc, slot_pos, H, G, hd, cap, pages=table)
+        out = torch.full((N, H * hd), 9.0, device=DEV, dtype=dt)
+        ops.attention_prefill_tc_cache(q_out, kc, vc, b, slot_pos, out, H, G, hd, cap, window, status,
+                                       pages=table)
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        qs = b.q_start.tolist()
+        for i, (n, s) in enumerate(live):
+            hist[s].append(qkv[qs[i]:qs[i + 1]].cpu().view(-1, H + 2 * G, hd))
+            allt = torch.cat(hist[s])
+            T = allt.shape[0]
+            pos = torch.arange(T)
+            qq = plain_rope(allt[:, :H], pos, inv.cpu()).to(dt).float()
+            kk = plain_rope(allt[:, H:H + G], pos, inv.cpu()).to(dt).float()
+            vv = allt[:, H + G:].to(dt).float()
+            ref = plain_attention(qq, kk, vv, window)[T - n:]
+            got = out[qs[i]:qs[i + 1]].float().cpu().view(-1, H, hd)
+            assert (got - ref).abs().max().item() <= 6.4 * eps, (lens, i)
+        ops.advance(b, slot_pos)
+
+
 def _paged(kc, vc, seed):
     """The same cache as pages of 64 positions in a shuffled pool: (k pages, v pages, table)."""
     n_slots, G, cap, hd = kc.shape

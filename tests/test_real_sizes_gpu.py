@@ -108,3 +108,33 @@ def test_decode_path_with_graphs_and_dependent_launch(name, dtype):
     lm.engine.use_graphs = True
     forced_decode(lm, reqs, prompts, refs, TOL[dtype],
                   order=sorted(reqs, key=lambda r: -prompts[r]))
+
+
+@pytest.mark.parametrize("max_tokens", [None, 1024])
+@pytest.mark.parametrize("dtype", [d for d in DTYPES if d != "float32"])
+@pytest.mark.parametrize("name", ["mistral_7b", "llama_1b"])
+def test_prompts_cut_into_two_steps(name, dtype, max_tokens):
+    """A batch of three prompts whose second parts go on top of the cache in one step of many
+    tokens each (what perplexity over a long text and a cut prefill do): the tensor-memory
+    attention then reads every key from the cache (one block per sequence, or pages).  Cuts
+    inside a tile, past one, and past a block of two tiles."""
+    cfg, w, reqs, refs, _ = setup(name)
+    lm = make_lm(cfg, w, dtype, 3, max_tokens=max_tokens)
+    ids = list(reqs)
+    cuts = {r: c if c < len(reqs[r]) - 1 else len(reqs[r]) // 2 for r, c in zip(ids, (100, 257, 130))}
+    slots = lm.acquire(3)
+    try:
+        first = lm.step([reqs[r][:cuts[r]] for r in ids], slots, [list(range(cuts[r])) for r in ids])
+        second = lm.step([reqs[r][cuts[r]:] for r in ids], slots,
+                         [list(range(len(reqs[r]) - cuts[r])) for r in ids])
+    finally:
+        lm.release(slots)
+    a = b = 0
+    for r in ids:
+        n, c = len(reqs[r]), cuts[r]
+        scale = refs[r].abs().max()
+        got = torch.cat([first[a:a + c], second[b:b + n - c]]).cpu()
+        a, b = a + c, b + n - c
+        err = ((got - refs[r]).abs().max() / scale).item()
+        assert err <= TOL[dtype], (r, err)
+    assert int(lm.rt.status.item()) == 0

@@ -78,6 +78,14 @@ int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_
 int yalm_attention_prefill_tc(const void* q, const void* kv_step, const int* q_start, void* out,
                               int dtype, int n_tokens, int n_seqs, int max_q_len, int H, int G,
                               int hd, int window, int* status, cudaStream_t stream);
+// ... for sequences that go on from slot_pos, no one wrapping around its ring in this step:
+// every key (this step's too) from the layer's cache, paged or one block per sequence
+int yalm_attention_prefill_tc_cache(const void* q, const void* k_cache, const void* v_cache,
+                                    const int* q_start, const int* seq_slot, const int* slot_pos,
+                                    void* out, int dtype, int n_tokens, int n_seqs, int max_q_len,
+                                    int n_slots, int H, int G, int hd, int capacity, int window,
+                                    const int* page_table, int pages_per_slot, int n_pages, int* status,
+                                    cudaStream_t stream);
 
 int yalm_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* out,
                    int out_dtype, int M, int N, int K, int accumulate, cudaStream_t stream);

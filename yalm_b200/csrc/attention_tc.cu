@@ -178,9 +178,23 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// Where the keys and values come from.  `on` = 0: this step's own rows (every sequence starts
+// at its first token; map_k and map_v are one map over [tokens, 2 * G * HD]).  `on` = 1: the
+// cache, which already holds this step's rows as well (sequences that go on from `slot_pos`;
+// none of them wraps around its ring in this step): map_k and map_v cover the layer's K and V
+// as rows of HD elements, one block per sequence ((slot * G + g) * capacity + position) or,
+// with a page table, pages of 64 positions ((g * n_pages + page) * 64 + position % 64).
+struct ta_cache_args {
+  const int* seq_slot;
+  const int* slot_pos;
+  const int* page_table;
+  int pages_per_slot, n_pages, capacity, on;
+};
+
 template <int HD, typename T16>
 __global__ void __launch_bounds__(TA_THREADS)
-attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const ta_cache_args ca,
                        const int* __restrict__ q_start, T16* __restrict__ out, int H, int G,
                        int window, float scale_log2, int* __restrict__ status) {
   constexpr uint32_t FMT = std::is_same<T16, __nv_bfloat16>::value ? 1u : 0u;   // operand format
@@ -203,6 +217,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // (broadcast from lane 0: the same value in every lane, and known to be)
   const int qs = __shfl_sync(0xffffffffu, q_start[b], 0);      // written by a host copy: safe early
   const int q_len = __shfl_sync(0xffffffffu, q_start[b + 1], 0) - qs;
+  // Positions are written by the advance kernel alone, which lets nothing start before it
+  // has ended: they too may be read while the previous kernel still runs.
+  const int slot = ca.on ? __shfl_sync(0xffffffffu, ca.seq_slot[b], 0) : 0;
+  const int past = ca.on ? __shfl_sync(0xffffffffu, ca.slot_pos[slot], 0) : 0;
   const int n_blocks = (q_len + 2 * TA_BM - 1) / (2 * TA_BM);
   if ((int)blockIdx.z >= n_blocks) return;
   const int m0 = (n_blocks - 1 - (int)blockIdx.z) * 2 * TA_BM;
@@ -212,8 +230,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   for (int x = 0; x < 2; ++x) {
     t_m0[x] = m0 + x * TA_BM;
     t_rows[x] = max(0, min(TA_BM, q_len - t_m0[x]));
-    const int k_end = t_m0[x] + t_rows[x];
-    const int k_begin = window > 0 ? max(0, t_m0[x] - window + 1) : 0;
+    const int k_end = past + t_m0[x] + t_rows[x];
+    const int k_begin = window > 0 ? max(0, past + t_m0[x] - window + 1) : 0;
     t_kb0[x] = k_begin / TA_BN;
     t_kb1[x] = t_rows[x] > 0 ? (k_end + TA_BN - 1) / TA_BN : t_kb0[x];
   }
@@ -268,7 +286,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // ---------------- TMA producer
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
       pdl_wait();
       const int n_tiles = t_rows[1] > 0 ? 2 : 1;
       mbar_expect_tx(smem_u32(&q_full), n_tiles * Q_BYTES);
@@ -278,7 +297,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ta_tma_load_2d(q_s + x * Q_BYTES + sub * (TA_BM * 128), &map_q, h * HD + sub * 64,
                          qs + t_m0[x], smem_u32(&q_full));
       for (int it = 0; it < n_it; ++it) {
-        const int row = qs + (kb_lo + it) * TA_BN;
+        // the block's first row in the maps, and the columns of K and of V
+        const int kb = kb_lo + it;
+        int row = qs + kb * TA_BN, col_k = g * HD, col_v = (G + g) * HD;
+        if (ca.on) {
+          col_k = col_v = 0;
+          if (ca.page_table != nullptr)
+            row = (g * ca.n_pages + ca.page_table[(size_t)slot * ca.pages_per_slot + kb]) * KV_PAGE;
+          else
+            row = (slot * G + g) * ca.capacity + kb * TA_BN;
+        }
         {
           const int s = it % TA_KSTAGES;
           if (!mbar_wait(smem_u32(&k_empty[s]), ((it / TA_KSTAGES) & 1) ^ 1u, abort_p)) break;
@@ -286,7 +314,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mbar_expect_tx(bar, KV_BYTES);
 #pragma unroll
           for (int sub = 0; sub < SUB; ++sub)
-            ta_tma_load_2d(k_s + s * KV_BYTES + sub * (TA_BN * 128), &map_kv, g * HD + sub * 64,
+            ta_tma_load_2d(k_s + s * KV_BYTES + sub * (TA_BN * 128), &map_k, col_k + sub * 64,
                            row, bar);
         }
         {
@@ -296,8 +324,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mbar_expect_tx(bar, KV_BYTES);
 #pragma unroll
           for (int sub = 0; sub < SUB; ++sub)
-            ta_tma_load_2d(v_s + s * KV_BYTES + sub * (TA_BN * 128), &map_kv,
-                           (G + g) * HD + sub * 64, row, bar);
+            ta_tma_load_2d(v_s + s * KV_BYTES + sub * (TA_BN * 128), &map_v, col_v + sub * 64,
+                           row, bar);
         }
       }
     }
@@ -390,8 +418,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int row = quarter * 32 + lane;
     const int my_m0 = x ? t_m0[1] : t_m0[0], my_rows = x ? t_rows[1] : t_rows[0];
     const int my_kb0 = x ? t_kb0[1] : t_kb0[0], my_kb1 = x ? t_kb1[1] : t_kb1[0];
-    const int p = my_m0 + row;                                // this row's position
-    const int p_hi = my_m0 + TA_BM - 1;
+    const int p = past + my_m0 + row;                         // this row's position
+    const int p_hi = past + my_m0 + TA_BM - 1;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t my_s = (x ? tmem_s[1] : tmem_s[0]) + lane_addr;
     const uint32_t my_o = (x ? tmem_o[1] : tmem_o[0]) + lane_addr;
@@ -420,7 +448,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int i = 0; i < TA_BN; ++i) s[i] = __uint_as_float(raw[i]);
       }
       // every row of the tile sees every key of the block?
-      const bool inside = j0 + TA_BN - 1 <= my_m0 && (window <= 0 || j0 > p_hi - window);
+      const bool inside = j0 + TA_BN - 1 <= past + my_m0 && (window <= 0 || j0 > p_hi - window);
       if (!inside) {
 #pragma unroll
         for (int i = 0; i < TA_BN; ++i) {
@@ -548,14 +576,17 @@ static int ta_make_map(CUtensorMap* map, const void* ptr, long long rows, long l
 }
 
 template <int HD, typename T16>
-static int launch_prefill_tc(const void* q, const void* kv_step, const int* q_start, void* out,
+static int launch_prefill_tc(const void* q, const void* k_rows, const void* v_rows, long long kv_n_rows,
+                             long long kv_cols, const ta_cache_args& ca, const int* q_start, void* out,
                              int n_tokens, int n_seqs, int max_q_len, int H, int G, int window,
                              int* status, cudaStream_t stream) {
-  CUtensorMap mq, mkv;
+  CUtensorMap mq, mk, mv;
   constexpr bool half = std::is_same<T16, __half>::value;
   int rc = ta_make_map(&mq, q, n_tokens, (long long)H * HD, TA_BM, half);
   if (rc) return rc;
-  rc = ta_make_map(&mkv, kv_step, n_tokens, (long long)2 * G * HD, TA_BN, half);
+  rc = ta_make_map(&mk, k_rows, kv_n_rows, kv_cols, TA_BN, half);
+  if (rc) return rc;
+  rc = ta_make_map(&mv, v_rows, kv_n_rows, kv_cols, TA_BN, half);
   if (rc) return rc;
   // two query tiles, the K and V rings, slack to align to 1024
   const size_t smem = (size_t)2 * TA_BM * HD * 2 + (size_t)(TA_KSTAGES + TA_VSTAGES) * TA_BN * HD * 2 + 1024;
@@ -568,10 +599,32 @@ static int launch_prefill_tc(const void* q, const void* kv_step, const int* q_st
   }
   const dim3 grid(H, n_seqs, (max_q_len + 2 * TA_BM - 1) / (2 * TA_BM));
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
-  launch_pdl(attn_prefill_tc_kernel<HD, T16>, grid, dim3(TA_THREADS), smem, stream, mq, mkv, q_start,
+  launch_pdl(attn_prefill_tc_kernel<HD, T16>, grid, dim3(TA_THREADS), smem, stream, mq, mk, mv, ca, q_start,
              (T16*)out, H, G, window, scale_log2, status);
   YALM_LAUNCH_CHECK();
   return 0;
+}
+
+static int ta_dispatch(const void* q, const void* k_rows, const void* v_rows, long long kv_n_rows,
+                       long long kv_cols, const ta_cache_args& ca, const int* q_start, void* out, int dtype,
+                       int n_tokens, int n_seqs, int max_q_len, int H, int G, int hd, int window,
+                       int* status, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0 || n_tokens <= 0) return 0;
+  if (dtype != DT_BF16 && dtype != DT_F16) return -3;
+  if (hd != 64 && hd != 128) return -2;
+  if (G <= 0 || H % G != 0) return -3;
+  if (n_seqs > 65535 || (max_q_len + 2 * TA_BM - 1) / (2 * TA_BM) > 65535) return -4;
+  if (((uintptr_t)q | (uintptr_t)k_rows | (uintptr_t)v_rows | (uintptr_t)out) & 15) return -6;
+#define YALM_TA(HD, T) \
+  return launch_prefill_tc<HD, T>(q, k_rows, v_rows, kv_n_rows, kv_cols, ca, q_start, out, n_tokens, \
+                                  n_seqs, max_q_len, H, G, window, status, stream)
+  if (dtype == DT_F16) {
+    if (hd == 64) YALM_TA(64, __half);
+    YALM_TA(128, __half);
+  }
+  if (hd == 64) YALM_TA(64, __nv_bfloat16);
+  YALM_TA(128, __nv_bfloat16);
+#undef YALM_TA
 }
 
 }  // namespace yalm
@@ -586,20 +639,30 @@ extern "C" int yalm_attention_prefill_tc(const void* q, const void* kv_step, con
                                          void* out, int dtype, int n_tokens, int n_seqs,
                                          int max_q_len, int H, int G, int hd, int window,
                                          int* status, cudaStream_t stream) {
-  if (n_seqs <= 0 || max_q_len <= 0 || n_tokens <= 0) return 0;
-  if (dtype != DT_BF16 && dtype != DT_F16) return -3;
-  if (hd != 64 && hd != 128) return -2;
-  if (G <= 0 || H % G != 0) return -3;
-  if (n_seqs > 65535 || (max_q_len + 2 * TA_BM - 1) / (2 * TA_BM) > 65535) return -4;
-  if (((uintptr_t)q | (uintptr_t)kv_step | (uintptr_t)out) & 15) return -6;
-#define YALM_TA(HD, T) \
-  return launch_prefill_tc<HD, T>(q, kv_step, q_start, out, n_tokens, n_seqs, max_q_len, H, G, \
-                                  window, status, stream)
-  if (dtype == DT_F16) {
-    if (hd == 64) YALM_TA(64, __half);
-    YALM_TA(128, __half);
-  }
-  if (hd == 64) YALM_TA(64, __nv_bfloat16);
-  YALM_TA(128, __nv_bfloat16);
-#undef YALM_TA
+  const ta_cache_args ca = {nullptr, nullptr, nullptr, 0, 0, 0, 0};
+  return ta_dispatch(q, kv_step, kv_step, n_tokens, (long long)2 * G * hd, ca, q_start, out, dtype, n_tokens,
+                     n_seqs, max_q_len, H, G, hd, window, status, stream);
+}
+
+// The same for sequences that go on from the positions in slot_pos (prompts cut into steps):
+// every key, this step's included, is read from the cache, which the step has written
+// before this launch.  k_cache / v_cache: the layer's [slots, G, capacity, hd], or with a
+// page table [G, n_pages, 64, hd] and page_table [slots, pages_per_slot].  No sequence may
+// wrap around its ring in this step (slot_pos + its tokens <= capacity): the caller checks.
+// seq_slot, slot_pos and the page table are read before the wait on the previous kernel.
+extern "C" int yalm_attention_prefill_tc_cache(const void* q, const void* k_cache, const void* v_cache,
+                                               const int* q_start, const int* seq_slot,
+                                               const int* slot_pos, void* out, int dtype, int n_tokens,
+                                               int n_seqs, int max_q_len, int n_slots, int H, int G,
+                                               int hd, int capacity, int window, const int* page_table,
+                                               int pages_per_slot, int n_pages, int* status,
+                                               cudaStream_t stream) {
+  if (capacity <= 0 || n_slots <= 0 || (page_table != nullptr && (pages_per_slot <= 0 || n_pages <= 0)))
+    return -4;
+  const ta_cache_args ca = {seq_slot, slot_pos, page_table, pages_per_slot, n_pages, capacity, 1};
+  const long long rows = page_table != nullptr ? (long long)G * n_pages * KV_PAGE
+                                               : (long long)n_slots * G * capacity;
+  if (rows > 0x7fffffffLL) return -4;
+  return ta_dispatch(q, k_cache, v_cache, rows, hd, ca, q_start, out, dtype, n_tokens, n_seqs, max_q_len,
+                     H, G, hd, window, status, stream);
 }

@@ -64,6 +64,8 @@ _SIGNATURES = {
     "yalm_attention_prefill_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                    _i, _i, _vp, _i, _i, _vp],
     "yalm_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "yalm_attention_prefill_tc_cache": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i,
+                                        _i, _vp, _i, _i, _vp, _vp],
     "yalm_attention_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
@@ -313,10 +315,16 @@ def attention_prefill_mma(q: torch.Tensor, kv_step: torch.Tensor, k_cache: torch
            "attention_prefill_mma")
 
 
-def tc_attention_usable(dtype: torch.dtype, hd: int, past) -> bool:
-    """The tcgen05 prefill attention takes bfloat16 or float16, head size 64 or 128, and
-    sequences that start at their first token (every key is one of this step's)."""
-    return dtype in HALF_TYPES and hd in (64, 128) and all(p == 0 for p in past)
+def tc_attention_usable(dtype: torch.dtype, hd: int, past, q_lens=None, capacity=None) -> bool:
+    """The tcgen05 prefill attention takes bfloat16 or float16 and head size 64 or 128;
+    sequences that start at their first token (every key is one of this step's), or, read
+    from the cache, sequences that go on without wrapping around their ring in this step."""
+    if dtype not in HALF_TYPES or hd not in (64, 128):
+        return False
+    if all(p == 0 for p in past):
+        return True
+    return (q_lens is not None and capacity is not None
+            and all(p + n <= capacity for p, n in zip(past, q_lens)))
 
 
 def attention_prefill_tc(q: torch.Tensor, kv_step: torch.Tensor, batch, out: torch.Tensor,
@@ -329,6 +337,28 @@ def attention_prefill_tc(q: torch.Tensor, kv_step: torch.Tensor, batch, out: tor
                                            dtype_code(q.dtype), q.shape[0], batch.n_seqs, max(batch.q_lens), H, G, hd,
                                            int(window or 0), _p(status), _stream()),
            "attention_prefill_tc")
+
+
+def attention_prefill_tc_cache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch,
+                               slot_pos: torch.Tensor, out: torch.Tensor, H: int, G: int, hd: int,
+                               capacity: int, window: Optional[int], status: torch.Tensor,
+                               pages=None) -> None:
+    """attention_prefill_tc with every key (this step's too) read from the cache, which the
+    step wrote before this call; for sequences that go on and do not wrap in this step."""
+    pt, pps, npg = _pages(pages, k_cache, G, hd)
+    _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype and q.dtype in HALF_TYPES
+          and q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
+          and out.is_contiguous(), "attention_prefill_tc_cache: one 16-bit type throughout")
+    n_slots = slot_pos.numel() if pt is not None else k_cache.shape[0]
+    if pt is None:
+        _need(tuple(k_cache.shape[1:]) == (G, capacity, hd),
+              f"attention_prefill_tc_cache: a cache of one block per sequence is [slots, {G}, {capacity}, {hd}]")
+    _check(lib().yalm_attention_prefill_tc_cache(_p(q), _p(k_cache), _p(v_cache), _p(batch.q_start),
+                                                 _p(batch.seq_slot), _p(slot_pos), _p(out),
+                                                 dtype_code(q.dtype), q.shape[0], batch.n_seqs,
+                                                 max(batch.q_lens), n_slots, H, G, hd, capacity,
+                                                 int(window or 0), pt, pps, npg, _p(status), _stream()),
+           "attention_prefill_tc_cache")
 
 
 def decode_mma_parts(max_context: int, window: Optional[int], chunks_per_block: int) -> int:

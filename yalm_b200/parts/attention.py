@@ -152,11 +152,18 @@ class GQAAttention:
                 ops.attention_decode(q, view.k, view.v, batch.seq_slot, view.slot_pos, o, part_o,
                                      part_ml, counters, rt.status, H, G, hd, view.capacity,
                                      self.window, chunk, bound, pages=view.pages)
-        elif rt.attention in ("auto", "tcgen05") and ops.tc_attention_usable(rt.dtype, hd, batch.past):
-            # whole prompts: S and O in tensor memory, two query tiles per block in
-            # ping-pong (99 us against 357 us for the mma.sync kernel per layer at
-            # 2,048 tokens of 32 heads of 128)
-            ops.attention_prefill_tc(q, kv_step, batch, o, H, G, hd, self.window, rt.status)
+        elif rt.attention in ("auto", "tcgen05") and ops.tc_attention_usable(
+                rt.dtype, hd, batch.past, batch.q_lens, view.capacity):
+            # S, P and O in tensor memory, two query tiles per block in ping-pong (41 us
+            # against 357 us for the mma.sync kernel per layer at 2,048 tokens of 32 heads
+            # of 128).  Whole prompts read this step's own keys; prompts that go on (and do
+            # not wrap around their ring in this step) read every key from the cache, which
+            # holds this step's rows by now.
+            if all(p == 0 for p in batch.past):
+                ops.attention_prefill_tc(q, kv_step, batch, o, H, G, hd, self.window, rt.status)
+            else:
+                ops.attention_prefill_tc_cache(q, view.k, view.v, batch, view.slot_pos, o, H, G, hd,
+                                               view.capacity, self.window, rt.status, pages=view.pages)
         elif tensor_cores:
             ops.attention_prefill_mma(q, kv_step, view.k, view.v, batch, view.slot_pos, o, H, G,
                                       hd, view.capacity, self.window, pages=view.pages)
