@@ -29,9 +29,11 @@
 // result is the plain softmax.
 //
 // Same mathematics as the reference's attn_dot / attn_softmax / att_mix
-// (infer.cu:339-523) and as attention.cu.  Takes the case "all keys are this step's
-// own" (prompts from their first token); head sizes 64 and 128.  Every wait on a
-// barrier is bounded.
+// (infer.cu:339-523) and as attention.cu.  Keys and values are this step's own rows
+// (prompts from their first token) or, for prompts that go on from earlier steps and do
+// not wrap around their ring in this step, the cache's rows, this step's included (a block
+// of 64 keys is then one page, or 64 rows of the sequence's block); head sizes 64 and 128.
+// Every wait on a barrier is bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
