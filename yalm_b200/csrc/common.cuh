@@ -55,6 +55,47 @@ __device__ __forceinline__ void store16_rt(int dtype, void* base, size_t index, 
   else reinterpret_cast<__nv_bfloat16*>(base)[index] = __float2bfloat16_rn(v);
 }
 
+// silu(g) * u where the result is rounded to a 16-bit type: 2^x and the division are the
+// special-function unit's approximations (relative error about 2^-22, far below that
+// rounding); the float32 path keeps expf and the IEEE division.
+__device__ __forceinline__ float silu_times_fast(float g, float u) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
+  return __fdividef(g * u, 1.0f + e);
+}
+// The SiLU.up epilogue of a product whose weight rows come as 16 gate rows followed by the
+// 16 up rows of the same features: of an accumulator chunk of 16 token columns, lane l < 16
+// holds the gate and lane l + 16 the up value of feature l.  The halves swap eight columns
+// each, so that every lane computes eight results: r[j] is token column j (lanes 0-15) or
+// 8 + j (lanes 16-31) of feature lane & 15.
+__device__ __forceinline__ void silu_pairs_of_chunk(const float* v, int lane, float* r) {
+  const bool lo = lane < 16;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float got = __shfl_xor_sync(0xffffffffu, lo ? v[8 + j] : v[j], 16);
+    r[j] = silu_times_fast(lo ? v[j] : got, lo ? got : v[8 + j]);
+  }
+}
+// ... and its store: eight tokens from tok_first on (those below M) of feature f, row pitch n_out
+__device__ __forceinline__ void store_eight_tokens(int out_dtype, void* __restrict__ out, const float* r,
+                                                   int f, int tok_first, int M, int n_out) {
+  if (out_dtype == DT_F32) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (tok_first + j < M) reinterpret_cast<float*>(out)[(size_t)(tok_first + j) * n_out + f] = r[j];
+  } else if (out_dtype == DT_F16) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (tok_first + j < M)
+        reinterpret_cast<__half*>(out)[(size_t)(tok_first + j) * n_out + f] = __float2half_rn(r[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (tok_first + j < M)
+        reinterpret_cast<__nv_bfloat16*>(out)[(size_t)(tok_first + j) * n_out + f] = __float2bfloat16_rn(r[j]);
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -7,6 +7,8 @@
 // fused_rope_and_cache_update infer.cu:660-705, act<SILU> infer.cu:601-604.
 // Here every kernel takes a ragged batch of tokens and reads each sequence's
 // position from the cache's per-slot state on the device.
+#include <type_traits>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -172,7 +174,9 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, int n_partials,
       g += p[gc];
       u += p[uc];
     }
-    out[idx] = from_float<TO>(g / (1.0f + expf(-g)) * u);
+    // the 16-bit paths round the result anyway: the same approximations as the products' epilogues
+    if (std::is_same<TO, float>::value) out[idx] = from_float<TO>(g / (1.0f + expf(-g)) * u);
+    else out[idx] = from_float<TO>(silu_times_fast(g, u));
   }
 }
 

@@ -249,27 +249,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           float u[16];
           tmem_ld16(taddr + BT + c0, u);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + expf(-v[j])) * u[j];
+          for (int j = 0; j < 16; ++j) v[j] = silu_times_fast(v[j], u[j]);
         }
         if (mode == 4) {
-          // weight rows come as 16 gate rows followed by the 16 up rows of the same
-          // features: lane l < 16 holds the gate, lane l + 16 the up value
-          const int fo = (feat0 >> 1) + quarter * 16 + lane;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float u = __shfl_down_sync(0xffffffffu, v[j], 16);
-            v[j] = v[j] / (1.0f + expf(-v[j])) * u;
-          }
-          if (lane < 16 && fo < (N >> 1)) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int tok = tok0 + c0 + j;
-              if (tok < M) {
-                if (out_dtype == DT_F32) outf[(size_t)tok * (N >> 1) + fo] = v[j];
-                else store16_rt(out_dtype, out, (size_t)tok * (N >> 1) + fo, v[j]);
-              }
-            }
-          }
+          // weight rows come as 16 gate rows followed by the 16 up rows of the same features
+          float r[8];
+          silu_pairs_of_chunk(v, lane, r);
+          const int fo = (feat0 >> 1) + quarter * 16 + (lane & 15);
+          if (fo < (N >> 1))
+            store_eight_tokens(out_dtype, out, r, fo, tok0 + c0 + (lane < 16 ? 0 : 8), M, N >> 1);
           continue;
         }
         if (f < n_out && mode == 1) {
@@ -773,17 +761,15 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           float g2[16];
           tmem_ld16(taddr + BT + c0, g2);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + expf(-v[j])) * g2[j];
+          for (int j = 0; j < 16; ++j) v[j] = silu_times_fast(v[j], g2[j]);
         }
         if (mode == 4) {
-          // rows interleaved in groups of 16: lane l < 16 the gate, lane l + 16 the up value
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float u = __shfl_down_sync(0xffffffffu, v[j], 16);
-            v[j] = v[j] / (1.0f + expf(-v[j])) * u;
-          }
-          const int fo = ((feat0 + (int)rank * TC_BM) >> 1) + quarter * 16 + lane;
-          sk_store_chunk(0, out_dtype, out, v, lane < 16 ? fo : (N >> 1), tok0 + c0, M, N >> 1);
+          // rows interleaved in groups of 16: gate and up of a feature in lanes l and l + 16
+          float r[8];
+          silu_pairs_of_chunk(v, lane, r);
+          const int fo = ((feat0 + (int)rank * TC_BM) >> 1) + quarter * 16 + (lane & 15);
+          if (fo < (N >> 1))
+            store_eight_tokens(out_dtype, out, r, fo, tok0 + c0 + (lane < 16 ? 0 : 8), M, N >> 1);
         } else {
           sk_store_chunk(mode, out_dtype, out, v, f, tok0 + c0, M, n_out);
         }
