@@ -444,9 +444,10 @@ template <int BT, int NACC> struct G2Cfg {
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
   static constexpr int ACC_COLS = NACC * BT;
+  static constexpr int ACC_STRIDE = (ACC_COLS + 63) / 64 * 64;  // the second buffer's first column
   static constexpr int TMEM_COLS = 512;
-  static_assert(2 * ACC_COLS <= 512, "two accumulator buffers must fit into TMEM");
-  static_assert(BT % 32 == 0 && BT <= 256, "token tile of the pair");
+  static_assert(2 * ACC_STRIDE <= 512, "two accumulator buffers must fit into TMEM");
+  static_assert(BT % 16 == 0 && BT <= 256 && STAGE_BYTES % 1024 == 0, "token tile of the pair");
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -625,7 +626,7 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_empty[buf]), (((uint32_t)part >> 1) & 1u) ^ 1u, abort_p));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t acc_addr = tmem_base + (uint32_t)(buf * Cfg::ACC_COLS);
+        const uint32_t acc_addr = tmem_base + (uint32_t)(buf * Cfg::ACC_STRIDE);
         for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
           const int s = it % Cfg::STAGES;
           const uint32_t phase = (it / Cfg::STAGES) & 1;
@@ -667,7 +668,7 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       if (*abort_p) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
-                             (uint32_t)(buf * Cfg::ACC_COLS);
+                             (uint32_t)(buf * Cfg::ACC_STRIDE);
       const int ncols = min(BT, M - tok0);
       if (NACC == 1 && mode == 5) {
         // ---- rotary encoding and cache write on the way out (rows are q, k, v heads)
@@ -825,6 +826,26 @@ static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, in
   return 0;
 }
 
+// The pair's token tile, 256 or 240: the one whose waves of tiles over the SM pairs cost
+// less (waves x tile width).  At 2,048 tokens a 4,096-feature product is 128 tiles of 256
+// tokens on 74 pairs (two waves, the second 73 % full) or 144 tiles of 240 (two fuller,
+// shorter waves: 6 % less time); a 28,672-feature product stays with 256.
+static int two_sm_token_tile(int M, int n_out) {
+  const long long pairs = sm_count() / 2 > 0 ? sm_count() / 2 : 1;
+  const long long feats = (n_out + 2 * TC_BM - 1) / (2 * TC_BM);
+  long long best = 0;
+  int best_bt = 256;
+  for (int bt : {256, 240}) {
+    const long long tiles = feats * ((M + bt - 1) / bt);
+    const long long cost = ((tiles + pairs - 1) / pairs) * bt;
+    if (best == 0 || cost < best) {
+      best = cost;
+      best_bt = bt;
+    }
+  }
+  return best_bt;
+}
+
 }  // namespace yalm
 
 using namespace yalm;
@@ -886,6 +907,8 @@ extern "C" int yalm_gemm_2sm(const void* A, const void* W, int ab_dtype, void* o
   yalm_rope_args none = {};
   if (mode == 2)
     return launch_2sm<128, 2>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, status, stream, none);
+  if (two_sm_token_tile(M, N) == 240)
+    return launch_2sm<240, 1>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, status, stream, none);
   return launch_2sm<256, 1>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, status, stream, none);
 }
 
@@ -905,5 +928,7 @@ extern "C" int yalm_gemm_2sm_rope(const void* A, const void* W, int ab_dtype, in
   if (!rope->cos_sin || !rope->token_seq || !rope->q_start || !rope->seq_slot || !rope->slot_pos ||
       !rope->q_out || !rope->kv_step || !rope->k_cache || !rope->v_cache)
     return -3;
+  if (two_sm_token_tile(M, N) == 240)
+    return launch_2sm<240, 1>(A, W, nullptr, ab_dtype, ab_dtype, M, N, K, 5, status, stream, *rope);
   return launch_2sm<256, 1>(A, W, nullptr, ab_dtype, ab_dtype, M, N, K, 5, status, stream, *rope);
 }
