@@ -538,11 +538,15 @@ def test_tensor_core_decode_attention(ops, H, G, hd, cap, window, dt, eps):
 
 
 @pytest.mark.parametrize("shape", [(1, 128, 64), (130, 300, 88), (256, 256, 64), (300, 512, 128),
-                                   (700, 640, 448), (1500, 1152, 320), (2048, 1024, 1024)])
+                                   (700, 640, 448), (1500, 1152, 320), (2048, 1024, 1024),
+                                   (512, 9472, 64)])
 @pytest.mark.parametrize("dt, eps", HALF)
 def test_two_sm_matrix_product(ops, shape, dt, eps):
     """gemm_2sm: a cluster of two blocks per 256-feature tile (tcgen05.mma.cta_group::2),
-    every epilogue, sizes that leave the second block of a pair partly or wholly empty."""
+    every epilogue, sizes that leave the second block of a pair partly or wholly empty.
+    The token tile is 240 wherever its waves over the 74 pairs cost no more than those of
+    256 (all shapes but the last: 37 feature tiles x 2 token tiles of 256 are one wave,
+    x 3 of 240 would be two)."""
     M, N, K = shape
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     a = (torch.randn(M, K, device=DEV) * 0.5).to(dt)
