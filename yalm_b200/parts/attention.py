@@ -17,6 +17,7 @@ from ..cache import CacheNeed
 from ..csrc import ops
 from ..weights import TensorNeed
 from .base import POSITIONS, make_part, register_mixer
+from . import linear
 from .linear import matmul_partials
 
 
@@ -103,7 +104,7 @@ class GQAAttention:
         q = rt.buffer("q_rot", (n, H * hd), rt.dtype)
         # many tokens: the q/k/v product rotates and stores in its own epilogue
         table = getattr(self.position, "step_table", None)
-        fused = (not shared and n > 128 and table is not None and rt.gemm != "simt"
+        fused = (not shared and n > linear.MANY_TOKENS and table is not None and rt.gemm != "simt"
                  and ops.gemm_2sm_rope_usable(h, self.w_qkv, hd))
         if not fused:
             qkv, S = matmul_partials(rt, h, self.w_qkv, "qkv")
