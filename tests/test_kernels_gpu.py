@@ -572,6 +572,18 @@ def test_two_sm_matrix_product(ops, shape, dt, eps):
             o4 = torch.full((M, N // 2), 9.0, device=DEV, dtype=dt)
             ops.gemm_2sm(a, w, o4, ops.GEMM_SILU_PAIRED, status)
             assert (o4.double() - r4).abs().max() <= eps * max(1.0, r4.abs().max())
+        # slices of K as 32-bit partial sums (what fills the idle pairs at a few hundred tokens)
+        nkb = -(-K // 64)
+        for S in (2, 3, 5):
+            per = -(-nkb // S)
+            if S > nkb or (S - 1) * per >= nkb:
+                continue
+            parts = torch.full((S, M, N), 7.0, device=DEV)
+            ops.gemm_2sm(a, w, parts, ops.GEMM_SPLIT, status, splits=S)
+            assert (parts.double().sum(0) - ref).abs().max() <= tol, S
+            if S == 2:          # each slice is its own part of the sum
+                first = a[:, :per * 64].double() @ w[:, :per * 64].double().T
+                assert (parts[0].double() - first).abs().max() <= tol
         torch.cuda.synchronize()
         assert status.item() == 0
 

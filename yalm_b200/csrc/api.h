@@ -133,9 +133,12 @@ typedef struct yalm_rope_args {
   int H, G, hd, capacity, write_cache;
 } yalm_rope_args;
 
-// Two-SM (cta_group::2) variant for many tokens: mode 0 store, 1 add, 2 silu(gate)*up.
+// Two-SM (cta_group::2) variant for many tokens: mode 0 store, 1 add, 2 silu(gate)*up, 4 the
+// same with interleaved rows, 3 `splits` slices of K as 32-bit partial sums [splits, M, N].
 int yalm_gemm_2sm(const void* A, const void* W, int ab_dtype, void* out, int out_dtype, int M,
-                  int N, int K, int mode, int* status, cudaStream_t stream);
+                  int N, int K, int mode, int splits, int* status, cudaStream_t stream);
+// the token tile (256 or 240) it takes for these sizes
+int yalm_gemm_2sm_token_tile(int M, int N, int splits);
 
 // The q/k/v product of many tokens with rotary encoding and cache write in its epilogue
 // (head sizes that divide 128).

@@ -514,11 +514,11 @@ static void launch_rmsnorm(float* x, const float* partials, int n_partials,
                      ((uintptr_t)out)) & 15) == 0;
   const int nvec = dim / 4;
   if (vec && nvec <= 8 * 512) {
-    // A few rows (a decode step): few vectors per thread, because the kernel is then a
-    // chain of memory round trips.  Many rows (a prompt): blocks of 256 threads with the
+    // A few rows (a decode step; up to 256, which is one wave of such blocks): few vectors
+    // per thread, because the kernel is then a chain of memory round trips.  Many rows (a prompt): blocks of 256 threads with the
     // row in four vectors per thread stream at the memory's rate.
     int threads;
-    if (n_rows <= 512) threads = nvec <= 1024 ? (nvec + 31) / 32 * 32 : (nvec <= 2048 ? 1024 : 512);
+    if (n_rows <= 256) threads = nvec <= 1024 ? (nvec + 31) / 32 * 32 : (nvec <= 2048 ? 1024 : 512);
     else threads = nvec <= 128 ? 128 : (nvec <= 1024 ? 256 : 512);
     const int vpt = (nvec + threads - 1) / threads;
 #define YALM_RMS(V)                                                                          \

@@ -498,11 +498,11 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
 
 // mode 0: store, 1: add into float32 out, 2: silu(gate)*up (NACC == 2), 4: silu(gate)*up
 // with gate and up rows interleaved in groups of 16
-template <int BT, int NACC>
+template <int BT, int NACC, bool SPLIT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS)
 gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                 void* __restrict__ out, int out_dtype, int ab_dtype, int M, int N, int K, int mode,
-                int* __restrict__ status, const yalm_rope_args rope) {
+                int splits, int* __restrict__ status, const yalm_rope_args rope) {
   using Cfg = G2Cfg<BT, NACC>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[Cfg::STAGES];
@@ -527,6 +527,9 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   const int n_tok_tiles = (M + BT - 1) / BT;
   const int n_tiles = n_feat_tiles * n_tok_tiles;
   const int nkb = (K + TC_BK - 1) / TC_BK;
+  // work items: (tile, slice of K); compiled without slices (every mode but 3) an item is a tile
+  const int n_items = SPLIT ? n_tiles * splits : n_tiles;
+  const int k_per = SPLIT ? (nkb + splits - 1) / splits : nkb;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
@@ -565,40 +568,51 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     tok0 = (in_band / band_w) * BT;
   };
 
+  // item -> its tile's place and its k-blocks [kb_lo, kb_hi): slices of one tile lie n_tiles apart
+  auto item_of = [&](int t, int& feat0, int& tok0, int& kb_lo, int& kb_hi) {
+    const int slice = SPLIT ? t / n_tiles : 0;
+    tile_of(t - slice * n_tiles, feat0, tok0);
+    kb_lo = slice * k_per;
+    kb_hi = SPLIT ? min(nkb, kb_lo + k_per) : nkb;
+    return slice;
+  };
+
   if (warp == 0) {
     // ---------------- TMA producer (warp 0 of each block runs the loop, its lane 0 issues)
-    if (pair < n_tiles) {
+    if (pair < n_items) {
       const uint32_t issue = lane == 0 ? 1u : 0u;
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
       // weights do not depend on the previous kernel: the first tile's first stages of them
       // are requested before the wait, the tokens of those stages after it
-      const int pre = nkb < Cfg::STAGES ? nkb : Cfg::STAGES;
+      int pre;
       {
-        int feat0, tok0;
-        tile_of(pair, feat0, tok0);
+        int feat0, tok0, kb_lo, kb_hi;
+        item_of(pair, feat0, tok0, kb_lo, kb_hi);
+        pre = kb_hi - kb_lo < Cfg::STAGES ? kb_hi - kb_lo : Cfg::STAGES;
         const int my_feat = feat0 + (int)rank * TC_BM;
-        for (int kb = 0; kb < pre; ++kb) {
-          const uint32_t stage = tiles_smem + kb * Cfg::STAGE_BYTES;
-          const uint32_t bar0 = map_to_rank(smem_u32(&full_bar[kb]), 0);
-          mbar_expect_tx_by(leader ? issue : 0u, smem_u32(&full_bar[kb]), 2 * Cfg::STAGE_BYTES);
-          tma_load_2d_pair_by(issue, stage, &map_w, kb * TC_BK, my_feat, bar0);
-          if (NACC == 2) tma_load_2d_pair_by(issue, stage + Cfg::W_BYTES, &map_w, kb * TC_BK, n_out + my_feat, bar0);
+        for (int i = 0; i < pre; ++i) {
+          const uint32_t stage = tiles_smem + i * Cfg::STAGE_BYTES;
+          const uint32_t bar0 = map_to_rank(smem_u32(&full_bar[i]), 0);
+          mbar_expect_tx_by(leader ? issue : 0u, smem_u32(&full_bar[i]), 2 * Cfg::STAGE_BYTES);
+          tma_load_2d_pair_by(issue, stage, &map_w, (kb_lo + i) * TC_BK, my_feat, bar0);
+          if (NACC == 2)
+            tma_load_2d_pair_by(issue, stage + Cfg::W_BYTES, &map_w, (kb_lo + i) * TC_BK, n_out + my_feat, bar0);
         }
         pdl_wait();
         const int my_tok = tok0 + (int)rank * (BT / 2);
-        for (int kb = 0; kb < pre; ++kb)
-          tma_load_2d_pair_by(issue, tiles_smem + kb * Cfg::STAGE_BYTES + NACC * Cfg::W_BYTES, &map_a, kb * TC_BK, my_tok,
-                           map_to_rank(smem_u32(&full_bar[kb]), 0));
+        for (int i = 0; i < pre; ++i)
+          tma_load_2d_pair_by(issue, tiles_smem + i * Cfg::STAGE_BYTES + NACC * Cfg::W_BYTES, &map_a,
+                              (kb_lo + i) * TC_BK, my_tok, map_to_rank(smem_u32(&full_bar[i]), 0));
       }
       int it = 0;
       bool ok = true;
-      for (int t = pair; t < n_tiles && ok; t += n_pairs) {
-        int feat0, tok0;
-        tile_of(t, feat0, tok0);
+      for (int t = pair; t < n_items && ok; t += n_pairs) {
+        int feat0, tok0, kb_lo, kb_hi;
+        item_of(t, feat0, tok0, kb_lo, kb_hi);
         const int my_feat = feat0 + (int)rank * TC_BM;
         const int my_tok = tok0 + (int)rank * (BT / 2);
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           if (it < pre) continue;                             // requested above
           const int s = it % Cfg::STAGES;
           const uint32_t phase = (it / Cfg::STAGES) & 1;
@@ -616,18 +630,19 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer: warp 1 of the first block runs the loop, its lane 0 issues for the pair
-    if (leader && pair < n_tiles) {
+    if (leader && pair < n_items) {
       const uint32_t issue = lane == 0 ? 1u : 0u;
       const uint32_t idesc = umma_idesc(ab_dtype, BT, 2 * TC_BM);
       bool ok = true;
       int it = 0, part = 0;
-      for (int t = pair; t < n_tiles && ok; t += n_pairs, ++part) {
+      for (int t = pair; t < n_items && ok; t += n_pairs, ++part) {
         const int buf = part & 1;
+        const int k_lo = SPLIT ? (t / n_tiles) * k_per : 0, k_hi = SPLIT ? min(nkb, k_lo + k_per) : nkb;
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_empty[buf]), (((uint32_t)part >> 1) & 1u) ^ 1u, abort_p));
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t acc_addr = tmem_base + (uint32_t)(buf * Cfg::ACC_STRIDE);
-        for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+        for (int kb = k_lo; kb < k_hi && ok; ++kb, ++it) {
           const int s = it % Cfg::STAGES;
           const uint32_t phase = (it / Cfg::STAGES) & 1;
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s]), phase, abort_p));
@@ -638,7 +653,7 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           const uint64_t adesc = umma_desc_k_sw128(stage + NACC * Cfg::W_BYTES);
 #pragma unroll
           for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
-            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+            const uint32_t acc = (kb > k_lo || k > 0) ? 1u : 0u;
             const uint64_t koff = (uint64_t)((k * TC_UMMA_K * 2) >> 4);
             umma_f16_pair_by(issue, acc_addr, wdesc + koff, adesc + koff, idesc, acc);
             if (NACC == 2) {
@@ -658,10 +673,10 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     bool ok = true;
     int part = 0;
     pdl_wait();
-    for (int t = pair; t < n_tiles && ok; t += n_pairs, ++part) {
+    for (int t = pair; t < n_items && ok; t += n_pairs, ++part) {
       const int buf = part & 1;
-      int feat0, tok0;
-      tile_of(t, feat0, tok0);
+      int feat0, tok0, kb_lo, kb_hi;
+      const int slice = item_of(t, feat0, tok0, kb_lo, kb_hi);
       const int f = feat0 + (int)rank * TC_BM + row;
       mbar_wait(smem_u32(&acc_full[buf]), ((uint32_t)part >> 1) & 1u, abort_p);
       asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
@@ -771,6 +786,10 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           const int fo = ((feat0 + (int)rank * TC_BM) >> 1) + quarter * 16 + (lane & 15);
           if (fo < (N >> 1))
             store_eight_tokens(out_dtype, out, r, fo, tok0 + c0 + (lane < 16 ? 0 : 8), M, N >> 1);
+        } else if (SPLIT && mode == 3) {
+          // this slice's 32-bit partial sums, [slice, M, N]
+          sk_store_chunk(0, DT_F32, reinterpret_cast<float*>(out) + (size_t)slice * M * n_out, v, f,
+                         tok0 + c0, M, n_out);
         } else {
           sk_store_chunk(mode, out_dtype, out, v, f, tok0 + c0, M, n_out);
         }
@@ -797,9 +816,9 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   }
 }
 
-template <int BT, int NACC>
+template <int BT, int NACC, bool SPLIT = false>
 static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, int ab_dtype, int M,
-                      int N, int K, int mode, int* status, cudaStream_t stream,
+                      int N, int K, int mode, int splits, int* status, cudaStream_t stream,
                       const yalm_rope_args& rope) {
   using Cfg = G2Cfg<BT, NACC>;
   static_assert(Cfg::STAGES >= 3, "pipeline depth");
@@ -810,7 +829,7 @@ static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, in
   if (rc) return rc;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_2sm_kernel<BT, NACC>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_2sm_kernel<BT, NACC, SPLIT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
@@ -818,10 +837,10 @@ static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, in
   const int n_out = mode == 2 ? N / 2 : N;
   const long long tiles = (long long)((n_out + 2 * TC_BM - 1) / (2 * TC_BM)) * ((M + BT - 1) / BT);
   long long pairs = sm_count() / 2;
-  if (pairs > tiles) pairs = tiles;
+  if (pairs > tiles * splits) pairs = tiles * splits;
   if (pairs < 1) return -4;
-  launch_pdl(gemm_2sm_kernel<BT, NACC>, dim3((unsigned)(2 * pairs)), dim3(TC_THREADS), Cfg::SMEM,
-             stream, mw, ma, out, out_dtype, ab_dtype, M, N, K, mode, status, rope);
+  launch_pdl(gemm_2sm_kernel<BT, NACC, SPLIT>, dim3((unsigned)(2 * pairs)), dim3(TC_THREADS), Cfg::SMEM,
+             stream, mw, ma, out, out_dtype, ab_dtype, M, N, K, mode, splits, status, rope);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -830,13 +849,13 @@ static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, in
 // less (waves x tile width).  At 2,048 tokens a 4,096-feature product is 128 tiles of 256
 // tokens on 74 pairs (two waves, the second 73 % full) or 144 tiles of 240 (two fuller,
 // shorter waves: 6 % less time); a 28,672-feature product stays with 256.
-static int two_sm_token_tile(int M, int n_out) {
+static int two_sm_token_tile(int M, int n_out, int splits) {
   const long long pairs = sm_count() / 2 > 0 ? sm_count() / 2 : 1;
   const long long feats = (n_out + 2 * TC_BM - 1) / (2 * TC_BM);
   long long best = 0;
   int best_bt = 256;
   for (int bt : {256, 240}) {
-    const long long tiles = feats * ((M + bt - 1) / bt);
+    const long long tiles = feats * ((M + bt - 1) / bt) * splits;
     const long long cost = ((tiles + pairs - 1) / pairs) * bt;
     if (best == 0 || cost < best) {
       best = cost;
@@ -892,24 +911,44 @@ extern "C" int yalm_gemm_tc(const void* A, const void* W, int ab_dtype, void* ou
 }
 
 // Two-SM variant for many tokens (see gemm_2sm_kernel): mode 0 store, 1 add into
-// float32 out, 2 silu(gate)*up, 4 the same with interleaved rows.
+// float32 out, 2 silu(gate)*up, 4 the same with interleaved rows, 3 `splits` slices of K as
+// 32-bit partial sums [splits, M, N] (for token counts whose tiles leave SM pairs idle).
 extern "C" int yalm_gemm_2sm(const void* A, const void* W, int ab_dtype, void* out, int out_dtype,
-                             int M, int N, int K, int mode, int* status, cudaStream_t stream) {
+                             int M, int N, int K, int mode, int splits, int* status,
+                             cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (ab_dtype != DT_BF16 && ab_dtype != DT_F16) return -3;
   if (out_dtype != DT_F32 && out_dtype != ab_dtype) return -3;
   if (K <= 0 || K % 8 != 0) return -2;
   if (((uintptr_t)A | (uintptr_t)W) & 15) return -6;
-  if (mode < 0 || mode == 3 || mode > 4) return -3;
+  if (mode < 0 || mode > 4) return -3;
   if (mode == 2 && (N % 2 != 0)) return -3;
   if (mode == 4 && (N % 32 != 0)) return -3;
-  if (mode == 1 && out_dtype != DT_F32) return -3;
+  if ((mode == 1 || mode == 3) && out_dtype != DT_F32) return -3;
+  if (mode != 3) splits = 1;
+  {
+    const int nkb = (K + TC_BK - 1) / TC_BK;
+    if (splits < 1 || splits > nkb) return -5;
+    const int per = (nkb + splits - 1) / splits;
+    if ((splits - 1) * per >= nkb) return -5;        // no empty slice of K
+  }
   yalm_rope_args none = {};
   if (mode == 2)
-    return launch_2sm<128, 2>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, status, stream, none);
-  if (two_sm_token_tile(M, N) == 240)
-    return launch_2sm<240, 1>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, status, stream, none);
-  return launch_2sm<256, 1>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, status, stream, none);
+    return launch_2sm<128, 2>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, 1, status, stream, none);
+  if (mode == 3) {
+    if (two_sm_token_tile(M, N, splits) == 240)
+      return launch_2sm<240, 1, true>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, splits, status, stream, none);
+    return launch_2sm<256, 1, true>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, splits, status, stream, none);
+  }
+  if (two_sm_token_tile(M, N, 1) == 240)
+    return launch_2sm<240, 1>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, 1, status, stream, none);
+  return launch_2sm<256, 1>(A, W, out, out_dtype, ab_dtype, M, N, K, mode, 1, status, stream, none);
+}
+
+// The token tile that yalm_gemm_2sm takes for these sizes (256 or 240): callers that plan a
+// split of K weigh it against the tiles this gives.
+extern "C" int yalm_gemm_2sm_token_tile(int M, int N, int splits) {
+  return two_sm_token_tile(M, N, splits < 1 ? 1 : splits);
 }
 
 // The q/k/v product of a prompt with the rotary encoding and the cache write in its
@@ -928,7 +967,7 @@ extern "C" int yalm_gemm_2sm_rope(const void* A, const void* W, int ab_dtype, in
   if (!rope->cos_sin || !rope->token_seq || !rope->q_start || !rope->seq_slot || !rope->slot_pos ||
       !rope->q_out || !rope->kv_step || !rope->k_cache || !rope->v_cache)
     return -3;
-  if (two_sm_token_tile(M, N) == 240)
-    return launch_2sm<240, 1>(A, W, nullptr, ab_dtype, ab_dtype, M, N, K, 5, status, stream, *rope);
-  return launch_2sm<256, 1>(A, W, nullptr, ab_dtype, ab_dtype, M, N, K, 5, status, stream, *rope);
+  if (two_sm_token_tile(M, N, 1) == 240)
+    return launch_2sm<240, 1>(A, W, nullptr, ab_dtype, ab_dtype, M, N, K, 5, 1, status, stream, *rope);
+  return launch_2sm<256, 1>(A, W, nullptr, ab_dtype, ab_dtype, M, N, K, 5, 1, status, stream, *rope);
 }

@@ -72,7 +72,8 @@ _SIGNATURES = {
     "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp, _vp],
     "yalm_gemm_tc": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "yalm_gemm_tc_available": [],
-    "yalm_gemm_2sm": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "yalm_gemm_2sm": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "yalm_gemm_2sm_token_tile": [_i, _i, _i],
     "yalm_gemm_2sm_rope": [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "yalm_rope_table": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
 }
@@ -427,16 +428,26 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, stat
 
 
 def gemm_2sm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
-             status: torch.Tensor) -> None:
-    """Two-SM tcgen05 product (pairs of blocks on one 256-feature tile) with a fused epilogue."""
+             status: torch.Tensor, splits: int = 1) -> None:
+    """Two-SM tcgen05 product (pairs of blocks on one 256-feature tile) with a fused epilogue;
+    with GEMM_SPLIT, ``splits`` slices of K as 32-bit partial sums in out [splits, M, N]."""
     M, K = a.shape
     N = w.shape[0]
     _need(a.dtype == w.dtype and a.dtype in HALF_TYPES and w.shape[1] == K
           and a.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "gemm_2sm: operands")
-    _need(tuple(out.shape) == ((M, N // 2) if mode in (GEMM_SILU_MUL, GEMM_SILU_PAIRED) else (M, N)),
-          "gemm_2sm: out shape")
+    if mode == GEMM_SPLIT:
+        _need(out.dtype == torch.float32 and tuple(out.shape) == (splits, M, N),
+              "gemm_2sm: split-K partials are float32 [splits, M, N]")
+    else:
+        _need(tuple(out.shape) == ((M, N // 2) if mode in (GEMM_SILU_MUL, GEMM_SILU_PAIRED) else (M, N)),
+              "gemm_2sm: out shape")
     _check(lib().yalm_gemm_2sm(_p(a), _p(w), dtype_code(a.dtype), _p(out), dtype_code(out.dtype), M,
-                               N, K, mode, _p(status), _stream()), "gemm_2sm")
+                               N, K, mode, splits, _p(status), _stream()), "gemm_2sm")
+
+
+def gemm_2sm_token_tile(M: int, N: int, splits: int = 1) -> int:
+    """The token tile (256 or 240) that gemm_2sm takes for these sizes."""
+    return lib().yalm_gemm_2sm_token_tile(M, N, splits)
 
 
 class _RopeArgs(ctypes.Structure):

@@ -19,9 +19,10 @@ from ..csrc import ops
 
 
 # Up to this many tokens a product runs on the single-SM kernel (split over K where its tiles
-# are few); above it on the two-SM kernel (measured at 7B sizes: 129 tokens 1.70 against 1.82 ms
-# per 8 layers, 256 tokens 2.02 against 2.06, 384 tokens 2.72 against 2.31).
-MANY_TOKENS = 256
+# are few); above it on the two-SM kernel, which splits over K too where its tiles leave pairs
+# idle (measured at 7B sizes, ms per 8 layers, single-SM against two-SM: 129 tokens 1.70 / 1.45,
+# 256 tokens 2.02 / 1.63).
+MANY_TOKENS = 128
 
 
 def _token_tile(M: int) -> int:
@@ -71,6 +72,36 @@ def plan_splits(M: int, N: int, K: int, sm_count: int = 148) -> int:
 
 def _use_tc(rt, a: torch.Tensor, w: torch.Tensor) -> bool:
     return rt.gemm != "simt" and ops.gemm_tc_usable(a, w)
+
+
+def plan_splits_many(M: int, N: int, K: int, sm_count: int = 148) -> int:
+    """Number of K slices for a product of many tokens on the two-SM kernel.
+
+    That kernel gives every pair of SMs whole 256-feature x 256- (or 240-)token tiles; a few
+    hundred tokens make fewer tiles than there are pairs (512 tokens x 4,096 features: 32 or
+    48 tiles on 74 pairs).  Slices of K then fill the idle pairs; their 32-bit partial sums are
+    added by the consumer, as in decode.  Cost of a plan: waves of work items over the pairs
+    x (the tile's tokens / slices + a work item's fixed cost of about 24 tokens' worth);
+    a split must win by 20 % and its partial sums, written and read once, may come to at
+    most twice the weights' bytes.  (Measured at 7B sizes, 512 tokens: down projection 88
+    -> 50 us, o-proj 38 -> 25 us.)"""
+    pairs = max(1, sm_count // 2)
+    nkb = -(-K // 64)
+    feats = -(-N // 256)
+
+    def cost(S):
+        return min(-(-feats * -(-M // bt) * S // pairs) * (bt / S + 24.0) for bt in (256, 240))
+
+    best, best_cost = 1, cost(1)
+    for S in (2, 3, 4, 6, 8):
+        if not _valid_splits(nkb, S) or nkb // S < 16:
+            continue
+        if 2.0 * S * M * N * 4.0 > 2.0 * (2.0 * N * K):
+            continue
+        c = cost(S)
+        if c < 0.8 * cost(1) and c < best_cost:
+            best, best_cost = S, c
+    return best
 
 
 def _small(rt, M: int, N: int) -> bool:
@@ -125,7 +156,13 @@ def matmul_into_stream(rt, a: torch.Tensor, w: torch.Tensor, stream) -> None:
             ops.gemm_tc(a, w, buf, ops.GEMM_SPLIT, rt.status, splits=S)
             stream.pending, stream.n_pending = buf, S
         elif M > MANY_TOKENS:
-            _many_tokens(rt, a, w, stream.x, ops.GEMM_ADD)
+            S = plan_splits_many(M, N, K, rt.sm_count)
+            if S > 1:
+                buf = rt.buffer("stream_partials", (S, M, N), torch.float32)
+                ops.gemm_2sm(a, w, buf, ops.GEMM_SPLIT, rt.status, splits=S)
+                stream.pending, stream.n_pending = buf, S
+            else:
+                _many_tokens(rt, a, w, stream.x, ops.GEMM_ADD)
         else:
             ops.gemm_tc(a, w, stream.x, ops.GEMM_ADD, rt.status)
     else:
