@@ -485,7 +485,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const float neg = m_ref > -INFINITY ? -m_ref : 0.f;
       float2 ls[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       const float2 scale2 = make_float2(scale_log2, scale_log2), neg2 = make_float2(neg, neg);
-#pragma unroll
       float pk[TA_BN / 2];                                    // P, two keys per 32-bit column
 #pragma unroll
       for (int j = 0; j < TA_BN / 2; ++j) {                   // pairs of keys, in packed arithmetic
