@@ -182,7 +182,11 @@ def matmul_silu_mul(rt, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Ten
             if M > MANY_TOKENS:
                 ops.gemm_2sm(a, w_gate_up, out, ops.GEMM_SILU_PAIRED, rt.status)
                 return
-            if not _small(rt, M, N2) or plan_splits(M, N2, K, rt.sm_count) == 1:
+            # nearly as many tiles as SMs: one fused launch beats two slices of K plus a
+            # SiLU kernel (Llama-3.2-1B sizes, 128 tiles: 3-5 % of a decode step at batch 1 to 64)
+            tiles = -(-N2 // 128) * -(-M // _token_tile(M))
+            if (not _small(rt, M, N2) or plan_splits(M, N2, K, rt.sm_count) == 1
+                    or 5 * tiles >= 4 * rt.sm_count):
                 ops.gemm_tc(a, w_gate_up, out, ops.GEMM_SILU_PAIRED, rt.status)
                 return
         elif not _small(rt, M, N2 // 2):
