@@ -699,16 +699,23 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // cosine and sine of (token, pair) come from a table made once per step for all layers
         const float2* cs_col = reinterpret_cast<const float2*>(rope.cos_sin) + (upper ? i - half : i);
         asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
-#pragma unroll 1
-        for (int c0 = 0; c0 < ncols; c0 += 16) {
-          float v[16];
-          tmem_ld16(taddr + c0, v);
-          // the chunk's cosines and sines: sixteen loads in flight across the barrier
-          float2 cs[16];
+        // A chunk's cosines and sines are asked for one chunk ahead: their round trip to L2
+        // then runs under the previous chunk's exchange and stores (asked for in the chunk
+        // itself, fifteen such round trips per tile made this epilogue longer than the next
+        // tile's main loop).
+        auto load_cs = [&](int c0, float2* cs) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             cs[j] = (live && rotates && c0 + j < ncols)
                         ? __ldg(cs_col + (size_t)(tok0 + c0 + j) * half) : make_float2(1.f, 0.f);
+        };
+        float2 cs[16], cs_next[16];
+        load_cs(0, cs);
+#pragma unroll 1
+        for (int c0 = 0; c0 < ncols; c0 += 16) {
+          float v[16];
+          tmem_ld16(taddr + c0, v);
+          load_cs(c0 + 16, cs_next);                          // nothing is loaded past the tile's last column
 #pragma unroll
           for (int j = 0; j < 16; ++j) rope_ex[row][j] = v[j];
           asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
@@ -757,6 +764,8 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
               reinterpret_cast<uint4*>(dst)[1] = hi;
             }
           }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) cs[j] = cs_next[j];
           asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
         }
       } else
