@@ -337,6 +337,25 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
   return r == CUDA_SUCCESS ? 0 : -11;
 }
 
+// out [rows, cols] of float32 or a 16-bit type, row-major; box = 16 rows x box_cols columns,
+// no swizzle: what the two-SM kernel's epilogue stages token-major in shared memory
+static int make_out_map(CUtensorMap* map, void* ptr, int rows, int cols, int dtype, int box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -10;
+  const int esz = dtype == DT_F32 ? 4 : 2;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * esz};
+  const cuuint32_t box[2] = {(cuuint32_t)box_cols, 16};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType t = dtype == DT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                : dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                  : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult r = fn(map, t, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -11;
+}
+
 template <int BT, int NACC>
 static int launch_tc(const CUtensorMap& mw, const void* A, void* out, int out_dtype, int ab_dtype,
                      int M, int N, int K, int mode, int splits, int* status, cudaStream_t stream) {
@@ -492,6 +511,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
 template <int BT, int NACC, bool SPLIT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS)
 gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                const __grid_constant__ CUtensorMap map_out, int out_tma,
                 void* __restrict__ out, int out_dtype, int ab_dtype, int M, int N, int K, int mode,
                 int splits, int* __restrict__ status, const yalm_rope_args rope) {
   using Cfg = G2Cfg<BT, NACC>;
@@ -504,8 +524,15 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   __shared__ int abort_flag;
   // mode 5 (rotary epilogue): a 16-token chunk of the block's 128 features, so that a
   // feature finds its rotation partner, and each token's position and cache row
-  __shared__ float rope_ex[NACC == 1 ? TC_BM : 1][17];
-  __shared__ __align__(16) uint16_t rope_out[NACC == 1 ? 16 : 1][TC_BM + 8];   // a rotated chunk, token-major
+  // The epilogues' staging area: for mode 5 rope_ex [128][17] floats and rope_out [16][136]
+  // 16-bit (a rotated chunk, token-major); for stores through TMA two buffers of a 16-token
+  // chunk of the block's 128 features, token-major ([16][128] of the output type).
+  constexpr int EPI_BYTES = NACC == 1 ? 16384 : 16;
+  constexpr int ROPE_OUT_AT = TC_BM * 17 * 4;
+  static_assert(NACC != 1 || ROPE_OUT_AT + 16 * (TC_BM + 8) * 2 <= EPI_BYTES, "staging area");
+  __shared__ __align__(128) uint8_t epi_smem[EPI_BYTES];
+  float (*rope_ex)[17] = reinterpret_cast<float(*)[17]>(epi_smem);
+  uint16_t (*rope_out)[TC_BM + 8] = reinterpret_cast<uint16_t(*)[TC_BM + 8]>(epi_smem + (NACC == 1 ? ROPE_OUT_AT : 0));
   __shared__ int rope_row[NACC == 1 ? BT : 1], rope_where[NACC == 1 ? BT : 1];
 
   // (broadcasts from lane 0: the compiler then knows these are the same in every lane)
@@ -662,7 +689,7 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     bool ok = true;
-    int part = 0;
+    int part = 0, stage_it = 0;
     pdl_wait();
     for (int t = pair; t < n_items && ok; t += n_pairs, ++part) {
       const int buf = part & 1;
@@ -768,6 +795,73 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           for (int j = 0; j < 16; ++j) cs[j] = cs_next[j];
           asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
         }
+      } else if (NACC == 1 && out_tma && mode == 4) {
+        // ---- SiLU(gate).up of interleaved rows, stored through TMA: the block's 128 rows are
+        // 64 output features; a chunk goes token-major ([16][64] of the 16-bit type) into one
+        // of two staging buffers (see the store below)
+        const int x = (feat0 + (int)rank * TC_BM) >> 1;
+        const bool issuer = row == 0 && x < (N >> 1);
+#pragma unroll 1
+        for (int c0 = 0; c0 < ncols; c0 += 16, ++stage_it) {
+          float v[16];
+          tmem_ld16(taddr + c0, v);
+          float r[8];
+          silu_pairs_of_chunk(v, lane, r);
+          const uint32_t st = smem_u32(epi_smem) + (uint32_t)((stage_it & 1) * 16 * 64 * 2);
+          if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
+          const uint32_t mine = st + (uint32_t)(((lane < 16 ? 0 : 8) * 64 + quarter * 16 + (lane & 15)) * 2);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(mine + (uint32_t)(j * 64 * 2)),
+                         "h"(bits16_rt(out_dtype, r[j])) : "memory");
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
+          if (issuer) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(reinterpret_cast<uint64_t>(&map_out)), "r"(st), "r"(x), "r"(tok0 + c0) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+      } else if (NACC == 1 && out_tma && mode <= 1) {
+        // ---- store (mode 0) or add into float32 out (mode 1) through TMA: a chunk of 16
+        // tokens goes token-major into one of two staging buffers and one thread hands it
+        // to the copy engine (one store per thread and column instead, 64-128 bytes per
+        // warp instruction, kept a tile's last epilogue 5-6 us long; tokens beyond M are
+        // clipped by the tensor map)
+        const int x = feat0 + (int)rank * TC_BM;
+        const bool issuer = row == 0 && x < n_out;           // (a block whose features lie beyond N copies nothing)
+        const int esz = out_dtype == DT_F32 ? 4 : 2;
+#pragma unroll 1
+        for (int c0 = 0; c0 < ncols; c0 += 16, ++stage_it) {
+          float v[16];
+          tmem_ld16(taddr + c0, v);
+          const uint32_t st = smem_u32(epi_smem) + (uint32_t)((stage_it & 1) * 16 * TC_BM * esz);
+          // the copy that read this buffer two chunks ago has read it
+          if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
+          if (out_dtype == DT_F32) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              asm volatile("st.shared.f32 [%0], %1;" ::"r"(st + (uint32_t)((j * TC_BM + row) * 4)), "f"(v[j]) : "memory");
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(st + (uint32_t)((j * TC_BM + row) * 2)),
+                           "h"(bits16_rt(out_dtype, v[j])) : "memory");
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(SK_EPI_THREADS) : "memory");
+          if (issuer) {
+            if (mode == 1)
+              asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(reinterpret_cast<uint64_t>(&map_out)), "r"(st), "r"(x), "r"(tok0 + c0) : "memory");
+            else
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(reinterpret_cast<uint64_t>(&map_out)), "r"(st), "r"(x), "r"(tok0 + c0) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
       } else
 #pragma unroll 1
       for (int c0 = 0; c0 < ncols; c0 += 16) {
@@ -798,6 +892,8 @@ gemm_2sm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty[buf]), 0));
     }
+    // the copies this thread handed to the copy engine are done before the block ends
+    if (row == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -822,11 +918,25 @@ static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, in
                       const yalm_rope_args& rope) {
   using Cfg = G2Cfg<BT, NACC>;
   static_assert(Cfg::STAGES >= 3, "pipeline depth");
-  CUtensorMap mw, ma;
+  CUtensorMap mw, ma, mo;
   int rc = make_map(&mw, W, N, K, TC_BM, ab_dtype);
   if (rc) return rc;
   rc = make_map(&ma, A, M, K, BT / 2, ab_dtype);
   if (rc) return rc;
+  // stores and residual adds of whole rows go through TMA where its rules allow (a 16-byte
+  // aligned base and row pitch); else, and for the other epilogues, threads store
+  int out_tma = 0;
+  mo = ma;
+  if (NACC == 1 && mode <= 1 && out != nullptr) {
+    const int esz = out_dtype == DT_F32 ? 4 : 2;
+    if (((uintptr_t)out & 15) == 0 && ((long long)N * esz) % 16 == 0 &&
+        make_out_map(&mo, out, M, N, out_dtype, TC_BM) == 0)
+      out_tma = 1;
+  } else if (NACC == 1 && mode == 4 && out != nullptr && out_dtype != DT_F32) {
+    if (((uintptr_t)out & 15) == 0 && ((long long)(N / 2) * 2) % 16 == 0 &&
+        make_out_map(&mo, out, M, N / 2, out_dtype, TC_BM / 2) == 0)
+      out_tma = 1;
+  }
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_2sm_kernel<BT, NACC, SPLIT>,
@@ -840,7 +950,7 @@ static int launch_2sm(const void* A, const void* W, void* out, int out_dtype, in
   if (pairs > tiles * splits) pairs = tiles * splits;
   if (pairs < 1) return -4;
   launch_pdl(gemm_2sm_kernel<BT, NACC, SPLIT>, dim3((unsigned)(2 * pairs)), dim3(TC_THREADS), Cfg::SMEM,
-             stream, mw, ma, out, out_dtype, ab_dtype, M, N, K, mode, splits, status, rope);
+             stream, mw, ma, mo, out_tma, out, out_dtype, ab_dtype, M, N, K, mode, splits, status, rope);
   YALM_LAUNCH_CHECK();
   return 0;
 }
