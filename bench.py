@@ -386,6 +386,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (profiling)")
     ap.add_argument("--prefill-only", action="store_true",
                     help="only the 2,048-token prefill, once (profiling); prints its record alone")
+    ap.add_argument("--prefill-tokens", type=int, default=2048,
+                    help="with --prefill-only: the prompt's length (the context grows to hold it)")
     ap.add_argument("--no-graphs", action="store_true",
                     help="launch decode kernels one by one instead of replaying a CUDA graph")
     ap.add_argument("--max-tokens", type=int, default=None,
@@ -421,9 +423,12 @@ def main():
             lm.engine.use_graphs = False
         return lm
 
-    lm = build(cfg, context, max(64, args.batch) if points_wanted else args.batch)
     if args.prefill_only:
-        print(json.dumps({"prefill": time_prefill(lm, 2048, 1, pk), "layers": args.layers}))
+        context = max(context, args.prefill_tokens)
+        cfg = dict(cfg, max_position_embeddings=max(cfg.get("max_position_embeddings", 0), context))
+    lm = build(cfg, context, max(64, args.batch) if points_wanted else (1 if args.prefill_only else args.batch))
+    if args.prefill_only:
+        print(json.dumps({"prefill": time_prefill(lm, args.prefill_tokens, 1, pk), "layers": args.layers}))
         return 0
     W = max(3, args.warmup)
     main_run = time_decode(lm, args.batch, args.steps, W, seed=1, sampler=ClockSampler(), lo=lo, hi=hi)
