@@ -537,6 +537,65 @@ def test_tensor_core_decode_attention(ops, H, G, hd, cap, window, dt, eps):
             assert (got - ref).abs().max().item() <= 6.4 * eps, (rep, b, n)
 
 
+@pytest.mark.parametrize("paged", [False, True])
+@pytest.mark.parametrize("H, G, hd, cap, window, S", [
+    (32, 8, 128, 700, None, 6),
+    (6, 3, 48, 40, 40, 1),
+    (40, 2, 64, 300, 100, 3),     # 20 query heads per kv head: two head groups write the same new row
+    (3, 1, 32, 1000, None, 9),
+    (24, 2, 80, 200, None, 2),
+])
+@pytest.mark.parametrize("dt, eps", HALF)
+def test_decode_attention_with_the_rotary_work_inside(ops, H, G, hd, cap, window, S, dt, eps, paged):
+    """attention_decode_mma_fused against rope_store followed by attention_decode_mma, bit for
+    bit: outputs and both caches.  Sequences whose new key opens a unit, ends one, lies in a
+    unit that the block has staged before its wait or asks for later, and (windowed) lands on
+    a ring row that holds an old key; few and many slices of the product; pages."""
+    g = torch.Generator(device=DEV).manual_seed(hd + cap + S)
+    lens = [1, 37, cap - 1, cap, 3 * cap + 5] if window else [1, 129, 200, cap - 1, cap, 33, 64, 65]
+    Bn, n_slots = len(lens), len(lens) + 3
+    slots = [5, 0, 3, 7, 2, 9, 1, 4][:Bn]
+    inv = plain_inv_freq(hd, 10000.0, None).to(DEV)
+    kc0 = torch.randn(n_slots, G, cap, hd, device=DEV, generator=g).to(dt)
+    vc0 = torch.randn(n_slots, G, cap, hd, device=DEV, generator=g).to(dt)
+    table = None
+    if paged:
+        kc0, vc0, table = _paged(kc0, vc0, seed=7)
+    parts = torch.randn(S, Bn, (H + 2 * G) * hd, device=DEV, generator=g)
+    slot_pos = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+    for s_, n in zip(slots, lens):
+        slot_pos[s_] = n - 1                                    # the new token's position
+    b = B([1] * Bn, slots)
+    bound = max(lens)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    cs = torch.empty(Bn, hd // 2, 2, device=DEV)
+    ops.rope_table(inv, b, slot_pos, cs)
+    for cpc in (1, 3, 1000):
+        mc = ops.decode_mma_parts(bound, window, cpc)
+        res = []
+        for fused in (False, True):
+            kc, vc = kc0.clone(), vc0.clone()
+            counters = torch.zeros(Bn * G * -(-(H // G) // 16), dtype=torch.int32, device=DEV)
+            part_o = torch.empty(Bn * H * mc * hd, device=DEV)
+            part_ml = torch.empty(Bn * H * mc * 2, device=DEV)
+            out = torch.zeros(Bn, H * hd, device=DEV, dtype=dt)
+            if fused:
+                ops.attention_decode_mma_fused(parts, S, cs, kc, vc, b.seq_slot, slot_pos, out, part_o,
+                                               part_ml, counters, status, H, G, hd, cap, window, bound,
+                                               cpc, pages=table)
+            else:
+                q = torch.empty(Bn, H * hd, device=DEV, dtype=dt)
+                kv_step = torch.empty(Bn, 2, G, hd, device=DEV, dtype=dt)
+                ops.rope_store(parts, S, inv, b, q, kv_step, kc, vc, slot_pos, H, G, hd, cap, pages=table)
+                ops.attention_decode_mma(q, kc, vc, b.seq_slot, slot_pos, out, part_o, part_ml, counters,
+                                         status, H, G, hd, cap, window, bound, cpc, pages=table)
+            torch.cuda.synchronize()
+            assert status.item() == 0 and int(counters.abs().sum()) == 0
+            res.append((out, kc, vc))
+        for name, x, y in zip(("out", "k cache", "v cache"), res[0], res[1]):
+            assert torch.equal(x, y), (name, cpc)
+
+
 @pytest.mark.parametrize("shape", [(1, 128, 64), (130, 300, 88), (256, 256, 64), (300, 512, 128),
                                    (700, 640, 448), (1500, 1152, 320), (2048, 1024, 1024),
                                    (512, 9472, 64)])

@@ -407,7 +407,21 @@ __device__ __noinline__ void warp_load_rows(uint32_t base, int n, int hd, const 
   }
 }
 
-template <int HDP, int NT, typename T16, bool PAGED>
+// The fused form's inputs: the q/k/v product of this step as n_partials 32-bit slices
+// [slice][token][(H + 2 G) hd] (partial_stride elements apart) and the step's cosines and
+// sines [token][hd / 2].  The kernel then does what rope_store_kernel would have done for its
+// own heads: it sums the slices (in the same order), rotates q and the new k, rounds to the
+// 16-bit type, keeps q in its shared-memory tile and writes the new k and v into the cache row
+// (and into the staged unit, where that is already on the chip).  One kernel and one
+// hand-over less per layer; bit for bit the two-kernel result.
+struct fd_fused_args {
+  const float* qkv;
+  const float2* cos_sin;
+  long long partial_stride;
+  int n_partials;
+};
+
+template <int HDP, int NT, typename T16, bool PAGED, bool FUSED>
 __global__ void __launch_bounds__(FA_THREADS)
 attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cache,
                        const T16* __restrict__ v_cache, const int* __restrict__ seq_slot,
@@ -415,7 +429,8 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
                        float* __restrict__ part_o, float* __restrict__ part_ml,
                        int* __restrict__ counters, int* __restrict__ status, int H, int G, int hd,
                        int capacity, int window, int cpc, int max_parts, float scale_log2,
-                       const int* __restrict__ page_table, int pps, int n_pages) {
+                       const int* __restrict__ page_table, int pps, int n_pages,
+                       const fd_fused_args fz) {
   constexpr int NKS = HDP / 16;                              // 16-wide steps over the head size
   constexpr int TILE = FD_UNIT * HDP * 2;                    // K (or V) of one unit, bytes
   constexpr int WARP_RING = FD_STAGES * 2 * TILE;
@@ -458,6 +473,12 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
     for (int i = threadIdx.x; i < WORDS; i += FA_THREADS)
       reinterpret_cast<uint4*>(fa_smem)[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
+  }
+  if (FUSED) {
+    // the query tile's rows beyond this block's heads stay zero (the copies of the unfused
+    // form zero-fill them); the rows of its heads are written after the dependency wait
+    for (int i = threadIdx.x; i < FD_ROWS * HDP * 2 / 16; i += FA_THREADS)
+      reinterpret_cast<uint4*>(fa_smem)[i] = make_uint4(0u, 0u, 0u, 0u);
   }
   // The page table is written by host copies before the step's first kernel, like the
   // batch's index arrays: it may be read before the dependency wait too.
@@ -503,21 +524,119 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
 #pragma unroll
   for (int i = 0; i < FD_STAGES - 1; ++i) {
     const int u = u0 + warp + i * FA_WARPS;
-    if (u < u1 && u != u_new) load_unit(u, i, row_first[i], page_first[i]);
+    // (fused: the newest key's unit comes now as well; its row for this step's position
+    // holds an old key, which is written over below)
+    if (u < u1 && (FUSED || u != u_new)) load_unit(u, i, row_first[i], page_first[i]);
     cp_async_commit();
   }
   pdl_wait();
-  load_tile<HDP>(q_s, FD_ROWS, hd, q, [&](int r) -> const T16* {
-    return r < nh ? q + ((size_t)t * H + h0 + r) * hd : nullptr;
-  });
+  if (!FUSED) {
+    load_tile<HDP>(q_s, FD_ROWS, hd, q, [&](int r) -> const T16* {
+      return r < nh ? q + ((size_t)t * H + h0 + r) * hd : nullptr;
+    });
 #pragma unroll
-  for (int i = 0; i < FD_STAGES - 1; ++i) {
-    const int u = u0 + warp + i * FA_WARPS;
-    if (u < u1 && u == u_new) load_unit(u, i, row_first[i], page_first[i]);
+    for (int i = 0; i < FD_STAGES - 1; ++i) {
+      const int u = u0 + warp + i * FA_WARPS;
+      if (u < u1 && u == u_new) load_unit(u, i, row_first[i], page_first[i]);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();                                      // this thread's share of Q and of the first units
+    __syncthreads();                                         // everybody's
+  } else {
+    // ---- what the rotary kernel would have done for this block's heads.  Work items of four
+    // pairs (q and k: elements i..i+3 and i+half..) or four elements (v); a thread's slices are
+    // all asked for before the first is added.
+    const int half = hd >> 1;
+    const int per_q = half >> 2, per_v = hd >> 2;            // items per query head, of v
+    const bool newest_here = u_new >= u0 && u_new < u1;      // this block sees this step's key
+    const int n_items = nh * per_q + (newest_here ? per_q + per_v : 0);
+    const int row_elems = (H + 2 * G) * hd;
+    const float* tok_row = fz.qkv + (size_t)t * row_elems;
+    const int r_new = (nkeys - 1) - u_new * FD_UNIT;         // the new key's row in its unit
+    const int new_at = u_new - u0;                           // its unit: warp new_at % 4, stage new_at / 4
+    const bool staged = newest_here && new_at < (FD_STAGES - 1) * FA_WARPS;
+    const uint32_t new_tile = q_s + FD_ROWS * HDP * 2 + (new_at % FA_WARPS) * WARP_RING +
+                              (new_at / FA_WARPS) * 2 * TILE;
+    const size_t new_row = newest_here
+        ? kv_row_offset(page_table, pps, n_pages, slot, g, G, capacity, pos % capacity, hd) : 0;
+    cp_async_wait<0>();                                      // this thread's share of the first units
+    __syncthreads();                                         // everybody's: their rows may be written over
+#pragma unroll 1
+    for (int item = threadIdx.x; item < n_items; item += FA_THREADS) {
+      int col, i, kind;                                      // kind 0: q, 1: k, 2: v
+      int r = 0;
+      if (item < nh * per_q) {
+        r = item / per_q;
+        i = (item - r * per_q) * 4;
+        col = (h0 + r) * hd + i;
+        kind = 0;
+      } else if (item < nh * per_q + per_q) {
+        i = (item - nh * per_q) * 4;
+        col = (H + g) * hd + i;
+        kind = 1;
+      } else {
+        i = (item - nh * per_q - per_q) * 4;
+        col = (H + G + g) * hd + i;
+        kind = 2;
+      }
+      const float* sp = tok_row + col;
+      const int second = kind == 2 ? 0 : half;               // v has no partner
+      float a[4] = {0.f, 0.f, 0.f, 0.f}, bb[4] = {0.f, 0.f, 0.f, 0.f};
+      constexpr int SB = 8;
+      for (int p0 = 0; p0 < fz.n_partials; p0 += SB) {
+        float4 x[SB], y[SB];
+#pragma unroll
+        for (int j = 0; j < SB; ++j) {
+          const float* pp = sp + (size_t)(p0 + j) * fz.partial_stride;
+          const bool live = p0 + j < fz.n_partials;
+          x[j] = live ? *reinterpret_cast<const float4*>(pp) : make_float4(0.f, 0.f, 0.f, 0.f);
+          y[j] = (live && kind != 2) ? *reinterpret_cast<const float4*>(pp + second)
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < SB; ++j) {
+          a[0] += x[j].x; a[1] += x[j].y; a[2] += x[j].z; a[3] += x[j].w;
+          bb[0] += y[j].x; bb[1] += y[j].y; bb[2] += y[j].z; bb[3] += y[j].w;
+        }
+      }
+      if (kind != 2) {
+        const float4* cs = reinterpret_cast<const float4*>(fz.cos_sin + (size_t)t * half + i);
+        const float4 c01 = cs[0], c23 = cs[1];               // (cos, sin) of pairs i, i+1 and i+2, i+3
+        const float cc[4] = {c01.x, c01.z, c23.x, c23.z}, ss[4] = {c01.y, c01.w, c23.y, c23.w};
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const float r0 = rotate_lo(a[v], bb[v], cc[v], ss[v]), r1 = rotate_hi(a[v], bb[v], cc[v], ss[v]);
+          a[v] = r0;
+          bb[v] = r1;
+        }
+      }
+      const uint2 lo4 = make_uint2(pack2<T16>(a[0], a[1]), pack2<T16>(a[2], a[3]));
+      const uint2 hi4 = make_uint2(pack2<T16>(bb[0], bb[1]), pack2<T16>(bb[2], bb[3]));
+      if (kind == 0) {
+        asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(tile_addr<HDP>(q_s, r, i >> 3) + (i & 4) * 2),
+                     "r"(lo4.x), "r"(lo4.y) : "memory");
+        asm volatile("st.shared.v2.b32 [%0], {%1, %2};"
+                     ::"r"(tile_addr<HDP>(q_s, r, (i + half) >> 3) + ((i + half) & 4) * 2), "r"(hi4.x), "r"(hi4.y)
+                     : "memory");
+      } else {
+        T16* crow = const_cast<T16*>(kind == 1 ? k_cache : v_cache) + new_row + i;
+        *reinterpret_cast<uint2*>(crow) = lo4;
+        if (kind == 1) *reinterpret_cast<uint2*>(crow + half) = hi4;
+        if (staged) {
+          const uint32_t tile = new_tile + (kind == 2 ? TILE : 0);
+          asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(tile_addr<HDP>(tile, r_new, i >> 3) + (i & 4) * 2),
+                       "r"(lo4.x), "r"(lo4.y) : "memory");
+          if (kind == 1)
+            asm volatile("st.shared.v2.b32 [%0], {%1, %2};"
+                         ::"r"(tile_addr<HDP>(tile, r_new, (i + half) >> 3) + ((i + half) & 4) * 2),
+                           "r"(hi4.x), "r"(hi4.y) : "memory");
+        }
+      }
+    }
+    // q and the new row are in place for every warp; a unit with the new key that is asked
+    // for later in the loop finds the row in the cache (a write of this block, before this barrier)
+    __syncthreads();
   }
-  cp_async_commit();
-  cp_async_wait<0>();                                        // this thread's share of Q and of the first units
-  __syncthreads();                                           // everybody's
   // Q^T as the B operand: per 16-wide step two registers for heads 0-7, two for 8-15
   uint32_t qf[NKS][4];
 #pragma unroll
@@ -757,19 +876,20 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   }
 }
 
-template <int HDP, int NT, typename T16, bool PAGED>
+template <int HDP, int NT, typename T16, bool PAGED, bool FUSED>
 static int launch_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                              const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                              float* part_ml, int* counters, int* status, int n_seqs, int H, int G,
                              int hd, int capacity, int window, int cpc, int max_parts,
-                             const int* page_table, int pps, int n_pages, cudaStream_t stream) {
+                             const int* page_table, int pps, int n_pages, const fd_fused_args& fz,
+                             cudaStream_t stream) {
   // Q, then every warp's ring of (K, V) stages; the merge buffer lies over them
   size_t smem = (size_t)(FD_ROWS + FA_WARPS * FD_STAGES * 2 * FD_UNIT) * HDP * 2;
   const size_t merge = (size_t)FA_WARPS * hd * FD_OPAD * 4;
   if (smem < merge) smem = merge;
   static size_t attr_smem = 0;
   if (smem > attr_smem) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HDP, NT, T16, PAGED>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HDP, NT, T16, PAGED, FUSED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_smem = smem;
@@ -777,10 +897,10 @@ static int launch_decode_mma(const void* q, const void* k_cache, const void* v_c
   const int nhc = (H / G + FD_ROWS - 1) / FD_ROWS;
   const dim3 grid(max_parts, G * nhc, n_seqs);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
-  launch_pdl(attn_decode_mma_kernel<HDP, NT, T16, PAGED>, grid, dim3(FA_THREADS), smem, stream,
+  launch_pdl(attn_decode_mma_kernel<HDP, NT, T16, PAGED, FUSED>, grid, dim3(FA_THREADS), smem, stream,
              (const T16*)q, (const T16*)k_cache, (const T16*)v_cache,
              seq_slot, slot_pos, (T16*)out, part_o, part_ml, counters, status, H, G, hd,
-             capacity, window, cpc, max_parts, scale_log2, page_table, pps, n_pages);
+             capacity, window, cpc, max_parts, scale_log2, page_table, pps, n_pages, fz);
   YALM_LAUNCH_CHECK();
   return 0;
 }
@@ -850,13 +970,12 @@ extern "C" int yalm_attention_prefill_mma(const void* q, const void* kv_step, co
 // visible = min(max_context, window).  part_o [n, H, parts, hd] and part_ml
 // [n, H, parts, 2] floats; counters: n * G * ceil((H/G)/16) ints, zero before the
 // first launch.  Head sizes: multiples of 16 up to 128.
-extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
-                                         const int* seq_slot, const int* slot_pos, void* out,
-                                         float* part_o, float* part_ml, int* counters, int* status,
-                                         int dtype, int n_seqs, int H, int G, int hd, int capacity,
-                                         int window, int max_context, int chunks_per_block,
-                                         const int* page_table, int pages_per_slot, int n_pages,
-                                         cudaStream_t stream) {
+static int decode_mma_dispatch(const void* q, const void* k_cache, const void* v_cache,
+                               const int* seq_slot, const int* slot_pos, void* out, float* part_o,
+                               float* part_ml, int* counters, int* status, int dtype, int n_seqs, int H,
+                               int G, int hd, int capacity, int window, int max_context,
+                               int chunks_per_block, const int* page_table, int pages_per_slot,
+                               int n_pages, const fd_fused_args* fused, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (dtype != DT_BF16 && dtype != DT_F16) return -3;
   if (hd % 16 != 0 || hd > 128 || hd <= 0) return -2;
@@ -867,12 +986,16 @@ extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, con
   const int max_parts = (max_chunks + chunks_per_block - 1) / chunks_per_block;
   if ((size_t)G * ((H / G + FD_ROWS - 1) / FD_ROWS) > 65535) return -4;
   const bool two = H / G > 8;                                 // a second tile of 8 heads
-#define YALM_FD_(HDP, NT, T, PAGED)                                                              \
-  launch_decode_mma<HDP, NT, T, PAGED>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o,     \
-                                       part_ml, counters, status, n_seqs, H, G, hd, capacity,    \
-                                       window, chunks_per_block, max_parts, page_table,          \
-                                       pages_per_slot, n_pages, stream)
-#define YALM_FD(HDP, NT, T) (page_table ? YALM_FD_(HDP, NT, T, true) : YALM_FD_(HDP, NT, T, false))
+  const fd_fused_args none = {nullptr, nullptr, 0, 0};
+  const fd_fused_args& fz = fused ? *fused : none;
+#define YALM_FD_(HDP, NT, T, PAGED, FUSED)                                                       \
+  launch_decode_mma<HDP, NT, T, PAGED, FUSED>(q, k_cache, v_cache, seq_slot, slot_pos, out,      \
+                                              part_o, part_ml, counters, status, n_seqs, H, G,   \
+                                              hd, capacity, window, chunks_per_block, max_parts, \
+                                              page_table, pages_per_slot, n_pages, fz, stream)
+#define YALM_FD(HDP, NT, T)                                                                      \
+  (fused ? (page_table ? YALM_FD_(HDP, NT, T, true, true) : YALM_FD_(HDP, NT, T, false, true))   \
+         : (page_table ? YALM_FD_(HDP, NT, T, true, false) : YALM_FD_(HDP, NT, T, false, false)))
   if (dtype == DT_F16) {
     if (hd <= 64) return two ? YALM_FD(64, 2, __half) : YALM_FD(64, 1, __half);
     return two ? YALM_FD(128, 2, __half) : YALM_FD(128, 1, __half);
@@ -881,4 +1004,36 @@ extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, con
   return two ? YALM_FD(128, 2, __nv_bfloat16) : YALM_FD(128, 1, __nv_bfloat16);
 #undef YALM_FD
 #undef YALM_FD_
+}
+
+extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
+                                         const int* seq_slot, const int* slot_pos, void* out,
+                                         float* part_o, float* part_ml, int* counters, int* status,
+                                         int dtype, int n_seqs, int H, int G, int hd, int capacity,
+                                         int window, int max_context, int chunks_per_block,
+                                         const int* page_table, int pages_per_slot, int n_pages,
+                                         cudaStream_t stream) {
+  return decode_mma_dispatch(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml, counters,
+                             status, dtype, n_seqs, H, G, hd, capacity, window, max_context,
+                             chunks_per_block, page_table, pages_per_slot, n_pages, nullptr, stream);
+}
+
+// The same with the rotary kernel's work done inside: instead of rotated queries and a cache
+// that already holds this step's row, it takes the q/k/v product of this step (n_partials
+// 32-bit slices [slice][n_seqs][(H + 2 G) hd], partial_stride elements apart) and the step's
+// cosines and sines cos_sin [n_seqs][hd / 2][2], and writes the new cache rows itself.
+extern "C" int yalm_attention_decode_mma_fused(const float* qkv, int n_partials, long long partial_stride,
+                                               const float* cos_sin, void* k_cache, void* v_cache,
+                                               const int* seq_slot, const int* slot_pos, void* out,
+                                               float* part_o, float* part_ml, int* counters,
+                                               int* status, int dtype, int n_seqs, int H, int G, int hd,
+                                               int capacity, int window, int max_context,
+                                               int chunks_per_block, const int* page_table,
+                                               int pages_per_slot, int n_pages, cudaStream_t stream) {
+  if (qkv == nullptr || cos_sin == nullptr || n_partials < 1) return -3;
+  if (((uintptr_t)qkv | (uintptr_t)cos_sin) & 15 || (partial_stride & 3)) return -6;
+  const fd_fused_args fz = {qkv, reinterpret_cast<const float2*>(cos_sin), partial_stride, n_partials};
+  return decode_mma_dispatch(nullptr, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,
+                             counters, status, dtype, n_seqs, H, G, hd, capacity, window, max_context,
+                             chunks_per_block, page_table, pages_per_slot, n_pages, &fz, stream);
 }

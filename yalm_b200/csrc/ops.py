@@ -68,6 +68,8 @@ _SIGNATURES = {
                                         _i, _vp, _i, _i, _vp, _vp],
     "yalm_attention_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                   _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
+    "yalm_attention_decode_mma_fused": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i,
+                                        _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "yalm_sample": [_vp, _i, _i, _f, _ull, _vp, _vp, _vp, _vp, _vp, _vp],
     "yalm_gemm_tc": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
@@ -390,6 +392,39 @@ def attention_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                                            chunks_per_block, pt, pps, npg,
                                            _stream()),
            "attention_decode_mma")
+
+
+def attention_decode_mma_fused(qkv: torch.Tensor, n_partials: int, cos_sin: torch.Tensor,
+                               k_cache: torch.Tensor, v_cache: torch.Tensor, seq_slot: torch.Tensor,
+                               slot_pos: torch.Tensor, out: torch.Tensor, part_o: torch.Tensor,
+                               part_ml: torch.Tensor, counters: torch.Tensor, status: torch.Tensor,
+                               H: int, G: int, hd: int, capacity: int, window: Optional[int],
+                               max_context: int, chunks_per_block: int, pages=None) -> None:
+    """attention_decode_mma with the rotary kernel's work inside: ``qkv`` is this step's q/k/v
+    product as float32 slices [n_partials, n, (H + 2 G) hd] (or [n, ...] for one), ``cos_sin`` the
+    step's table of ``rope_table`` [n, hd / 2, 2]; q is rotated in the kernel and the new k and v
+    rows are written into the cache by it."""
+    n = out.shape[0]
+    pt, pps, npg = _pages(pages, k_cache, G, hd)
+    row = (H + 2 * G) * hd
+    _need(qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.numel() == n_partials * n * row,
+          "attention_decode_mma_fused: qkv is float32 [n_partials, n, (H + 2 G) hd]")
+    _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+          and tuple(cos_sin.shape) == (n, hd // 2, 2), "attention_decode_mma_fused: cos_sin [n, hd/2, 2]")
+    _need(k_cache.dtype == v_cache.dtype == out.dtype and out.dtype in HALF_TYPES,
+          "attention_decode_mma_fused: one 16-bit type throughout")
+    parts = decode_mma_parts(max_context, window, chunks_per_block)
+    hc = -(-(H // G) // 16)
+    _need(part_o.numel() >= n * H * parts * hd and part_ml.numel() >= n * H * parts * 2
+          and counters.numel() >= n * G * hc and counters.dtype == torch.int32,
+          "attention_decode_mma_fused: workspace")
+    _check(lib().yalm_attention_decode_mma_fused(_p(qkv), n_partials, n * row, _p(cos_sin), _p(k_cache),
+                                                 _p(v_cache), _p(seq_slot), _p(slot_pos), _p(out),
+                                                 _p(part_o), _p(part_ml), _p(counters), _p(status),
+                                                 dtype_code(out.dtype), n, H, G, hd, capacity,
+                                                 int(window or 0), max_context, chunks_per_block, pt, pps,
+                                                 npg, _stream()),
+           "attention_decode_mma_fused")
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

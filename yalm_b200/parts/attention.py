@@ -108,6 +108,14 @@ class GQAAttention:
                  and ops.gemm_2sm_rope_usable(h, self.w_qkv, hd))
         if not fused:
             qkv, S = matmul_partials(rt, h, self.w_qkv, "qkv")
+        tensor_cores = ops.mma_attention_usable(rt.dtype, hd) and rt.attention != "simt"
+        # one token per sequence on the tensor-core kernel, a small batch: that kernel sums the
+        # product's slices, rotates and writes the cache row itself (no rotary kernel, one
+        # hand-over less: 2-3 % of a step at batch 1, 0.5 % at 8 to 16; from 32 sequences on the
+        # rotary kernel's many small blocks are the faster way, by 1-2 %)
+        in_attention = (batch.is_decode and n <= 16 and tensor_cores and not shared and not fused
+                        and table is not None and getattr(view, "kv_step", None) is None
+                        and getattr(rt, "decode_rope_in_attention", True))
         # a layer whose cache another run entry reads keeps its step keys apart
         kv_step = view.kv_step if getattr(view, "kv_step", None) is not None else \
             rt.buffer("kv_step", (n, 2, G, hd), rt.dtype)
@@ -122,6 +130,8 @@ class GQAAttention:
                               view.v, view.slot_pos,
                               H, G, hd, view.capacity, rt.status, write_cache=not late_write,
                               pages=view.pages)
+        elif in_attention:
+            pass
         elif shared:
             # this run reads the owner's keys and values: rotate q only
             scratch = rt.buffer("kv_step_unused", (n, 2, G, hd), rt.dtype)
@@ -131,7 +141,6 @@ class GQAAttention:
             self.position.rotate_and_store(qkv, S, batch, view, q, kv_step, H, G,
                                            write_cache=not late_write)
         o = rt.buffer("attn_out", (n, H * hd), rt.dtype)
-        tensor_cores = ops.mma_attention_usable(rt.dtype, hd) and rt.attention != "simt"
         if batch.is_decode:
             # one query per sequence, every key already in the cache
             bound = max(1, batch.ctx_bound)
@@ -145,7 +154,12 @@ class GQAAttention:
             part_o = rt.buffer("attn_part_o", (n, H, parts, hd), torch.float32)
             part_ml = rt.buffer("attn_part_ml", (n, H, parts, 2), torch.float32)
             counters = rt.zeros("attn_counters", n * G * -(-(H // G) // 4))
-            if tensor_cores:
+            if in_attention:
+                ops.attention_decode_mma_fused(qkv, S, table(batch, view.slot_pos), view.k, view.v,
+                                               batch.seq_slot, view.slot_pos, o, part_o, part_ml,
+                                               counters, rt.status, H, G, hd, view.capacity,
+                                               self.window, bound, cpc, pages=view.pages)
+            elif tensor_cores:
                 ops.attention_decode_mma(q, view.k, view.v, batch.seq_slot, view.slot_pos, o,
                                          part_o, part_ml, counters, rt.status, H, G, hd,
                                          view.capacity, self.window, bound, cpc, pages=view.pages)

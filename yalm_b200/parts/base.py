@@ -87,6 +87,8 @@ class Runtime:
         ops.lib()   # builds/loads the kernels now: a missing library fails here, loudly
         self.gemm = gemm                      # "auto" | "simt" (debugging aid: no tensor cores)
         self.attention = attention            # "auto" | "mma" (no tcgen05 prefill attention) | "simt"
+        # small decode batches: the attention kernel does the rotary kernel's work (False: never)
+        self.decode_rope_in_attention = True
         # a matrix stored in 32 bits under 16-bit compute: "keep" it (it is then multiplied by
         # the FMA kernel, without tensor cores) or "round" it to the compute type
         self.float32_matrices = float32_matrices
