@@ -23,9 +23,10 @@ import time
 from typing import List, Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["elementwise.cu", "attention.cu", "attention_mma.cu", "attention_tc.cu", "gemm_simt.cu",
+SOURCES = ["elementwise.cu", "attention.cu", "attention_mma.cu", "attention_mma_fused.cu", "attention_tc.cu",
+           "gemm_simt.cu",
            "gemm_tcgen05.cu", "sampling.cu"]
-HEADERS = ["api.h", "common.cuh", "no_alloc.h"]
+HEADERS = ["api.h", "common.cuh", "attention_mma.cuh", "no_alloc.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 
