@@ -338,7 +338,8 @@ def test_sampling_greedy_and_temperature(ops):
     one = out[0].item()
     ops.sample(logits, 1.0, 2, keys, seq_slot, slot_pos, out)
     assert out[3].item() == one
-    us = [ops.uniform01(9, 1, i) for i in range(2000)]
+    from yalm_b200 import sampling
+    us = [sampling.uniform01(9, 1, i) for i in range(2000)]
     assert 0.45 < sum(us) / len(us) < 0.55 and len(set(us)) > 1990
     # seed and temperature read from device memory (what a captured step does) give the
     # same tokens as the same values passed as arguments

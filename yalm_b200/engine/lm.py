@@ -18,6 +18,7 @@ from typing import Any, Dict, List, Optional, Sequence, Union
 import torch
 
 from ..config import config_from_dict, load_config
+from .. import sampling
 from ..csrc import ops
 from ..parts import Model, Runtime
 from ..weights import load_checkpoint, load_packed, random_tensors, write_model_dir
@@ -209,7 +210,7 @@ class _DeviceBackend:
             d = eng._decode_buffers()
             # sample the first token of every sequence into the decode token buffer
             eng.set_decode_batch([0] * B, slots, [keys[i] for i in order])
-            ops.sample(logits, self.temperature, self.seed, d["row_key"][:B], d["seq_slot"][:B],
+            sampling.sample(logits, self.temperature, self.seed, d["row_key"][:B], d["seq_slot"][:B],
                        eng.cache.slot_pos, d["tokens"][:B])
             sampled = eng.read_decode_tokens(B)
             self.prefill_seconds += time.perf_counter() - t0

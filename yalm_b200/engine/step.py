@@ -21,6 +21,7 @@ import numpy as np
 import torch
 
 from ..cache import Cache, CacheFull
+from .. import sampling
 from ..csrc import ops
 from ..parts import Model
 from .batch import StepBatch, build_batch
@@ -176,7 +177,7 @@ class Engine:
         if self._sampling == (temperature, seed):
             return
         d = self._decode_buffers()
-        d["host_params"][0], d["host_params"][1] = ops.sampling_params(temperature, seed)
+        d["host_params"][0], d["host_params"][1] = sampling.device_params(temperature, seed)
         ops.copy_async(d["ptr"]["sample_params"], d["ptr"]["host_params"], 16, True)
         ops.stream_wait()                     # the pinned words may change again right away
         self._sampling = (temperature, seed)
@@ -193,7 +194,7 @@ class Engine:
         logits = self.model.forward(batch, self.cache, batch.want_rows, B, logits_out=d["logits"][:B])
         ops.advance(batch, self.cache.slot_pos)
         # the new token goes where the next step's embedding reads it
-        ops.sample(logits, 0.0, 0, d["row_key"][:B], batch.seq_slot, self.cache.slot_pos,
+        sampling.sample(logits, 0.0, 0, d["row_key"][:B], batch.seq_slot, self.cache.slot_pos,
                    d["tokens"][:B], params=d["sample_params"])
 
     def decode_step(self, B: int, temperature: float, seed: int) -> None:
