@@ -501,8 +501,9 @@ def test_tensor_core_prefill_attention(ops, H, G, hd, cap, window, dt, eps):
     (3, 1, 32, 1000, None),
     (24, 2, 80, 200, None),     # 12 query heads per kv head: both 8-head tiles, one partly empty
 ])
+@pytest.mark.parametrize("warps", [4, 2])
 @pytest.mark.parametrize("dt, eps", HALF)
-def test_tensor_core_decode_attention(ops, H, G, hd, cap, window, dt, eps):
+def test_tensor_core_decode_attention(ops, H, G, hd, cap, window, dt, eps, warps):
     g = torch.Generator(device=DEV).manual_seed(hd + cap)
     lens = [1, 37, cap - 1, cap, 3 * cap + 5] if window else [1, 129, 200, cap - 1, cap]
     Bn, n_slots = len(lens), len(lens) + 3
@@ -523,7 +524,7 @@ def test_tensor_core_decode_attention(ops, H, G, hd, cap, window, dt, eps):
         part_ml = torch.empty(Bn * H * mc * 2, device=DEV)
         out = torch.zeros(Bn, H * hd, device=DEV, dtype=dt)
         ops.attention_decode_mma(q, kc, vc, seq_slot, slot_pos, out, part_o, part_ml, counters,
-                                 status, H, G, hd, cap, window, bound, cpc)
+                                 status, H, G, hd, cap, window, bound, cpc, warps=warps)
         torch.cuda.synchronize()
         assert status.item() == 0 and int(counters.abs().sum()) == 0
         for b, (s, n) in enumerate(zip(slots, lens)):
@@ -824,13 +825,13 @@ def test_every_cache_kernel_reads_and_writes_pages_like_rows(ops, dt, H, G, hd, 
                              H, G, hd, cap, window, chunk, bound, pages=pg)
         res.append(od)
         if ops.mma_attention_usable(dt, hd):
-            for cpc in (1, 1000):
+            for cpc, warps in ((1, 4), (1000, 4), (1, 2), (1000, 2)):
                 mp = ops.decode_mma_parts(bound, window, cpc)
                 om = torch.empty(3, H * hd, device=DEV, dtype=dt)
                 ops.attention_decode_mma(qd, K2, V2, bd.seq_slot, sp, om, torch.empty(3 * H * mp * hd, device=DEV),
                                          torch.empty(3 * H * mp * 2, device=DEV),
                                          torch.zeros(3 * G * -(-(H // G) // 16), dtype=torch.int32, device=DEV),
-                                         status, H, G, hd, cap, window, bound, cpc, pages=pg)
+                                         status, H, G, hd, cap, window, bound, cpc, pages=pg, warps=warps)
                 res.append(om)
         torch.cuda.synchronize()
         assert status.item() == 0

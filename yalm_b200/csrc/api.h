@@ -70,8 +70,8 @@ int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_
                               const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                               float* part_ml, int* counters, int* status, int dtype, int n_seqs,
                               int H, int G, int hd, int capacity, int window, int max_context,
-                              int chunks_per_block, const int* page_table, int pages_per_slot, int n_pages,
-                              cudaStream_t stream);
+                              int chunks_per_block, int warps, const int* page_table, int pages_per_slot,
+                              int n_pages, cudaStream_t stream);
 // ... with the rotary kernel's work inside (attention_mma.cu): takes this step's q/k/v product
 // as n_partials 32-bit slices and the step's cosines and sines, writes the new cache rows
 int yalm_attention_decode_mma_fused(const float* qkv, int n_partials, long long partial_stride,

@@ -344,6 +344,7 @@ constexpr int FD_MT = FD_UNIT / 16;
 constexpr int FD_ROWS = 16;        // query heads per block
 constexpr int FD_STAGES = 3;       // units in flight or in use per warp
 constexpr int FD_OPAD = 20;        // row length of the merge buffer [warp][feature][head]
+constexpr int FD_WARPS_MAX = 4;    // warps of a block (4, or 2 with two blocks to an SM): each has a ring of its own
 
 __device__ __forceinline__ uint32_t movmatrix_t(uint32_t a) {
   uint32_t d;
@@ -422,8 +423,8 @@ struct fd_fused_args {
   int n_partials;
 };
 
-template <int HDP, int NT, typename T16, bool PAGED, bool FUSED>
-__global__ void __launch_bounds__(FA_THREADS)
+template <int HDP, int NT, typename T16, bool PAGED, bool FUSED, int NW>
+__global__ void __launch_bounds__(NW * 32, FD_WARPS_MAX / NW)
 attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cache,
                        const T16* __restrict__ v_cache, const int* __restrict__ seq_slot,
                        const int* __restrict__ slot_pos, T16* __restrict__ out,
@@ -436,9 +437,10 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   constexpr int TILE = FD_UNIT * HDP * 2;                    // K (or V) of one unit, bytes
   constexpr int WARP_RING = FD_STAGES * 2 * TILE;
   constexpr uint32_t FULL = 0xffffffffu;
+  constexpr int FD_THREADS = NW * 32;
   extern __shared__ __align__(128) uint8_t fa_smem[];
-  __shared__ float wm_s[FA_WARPS][FD_ROWS];                  // per warp: row max, row sum
-  __shared__ float wl_s[FA_WARPS][FD_ROWS];
+  __shared__ float wm_s[NW][FD_ROWS];                  // per warp: row max, row sum
+  __shared__ float wl_s[NW][FD_ROWS];
   __shared__ float row_m[FD_ROWS], row_l[FD_ROWS];
   __shared__ int last_flag;
   pdl_launch_dependents();
@@ -470,15 +472,15 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   // A head size below HDP: the tiles' columns from hd on are zeroed once (no copy ever writes
   // them), and the products below run over all HDP columns without a test per step.
   if (hd < HDP) {
-    constexpr int WORDS = (FD_ROWS * HDP * 2 + FA_WARPS * WARP_RING) / 16;
-    for (int i = threadIdx.x; i < WORDS; i += FA_THREADS)
+    constexpr int WORDS = (FD_ROWS * HDP * 2 + NW * WARP_RING) / 16;
+    for (int i = threadIdx.x; i < WORDS; i += FD_THREADS)
       reinterpret_cast<uint4*>(fa_smem)[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
   }
   if (FUSED) {
     // the query tile's rows beyond this block's heads stay zero (the copies of the unfused
     // form zero-fill them); the rows of its heads are written after the dependency wait
-    for (int i = threadIdx.x; i < FD_ROWS * HDP * 2 / 16; i += FA_THREADS)
+    for (int i = threadIdx.x; i < FD_ROWS * HDP * 2 / 16; i += FD_THREADS)
       reinterpret_cast<uint4*>(fa_smem)[i] = make_uint4(0u, 0u, 0u, 0u);
   }
   // The page table is written by host copies before the step's first kernel, like the
@@ -490,7 +492,7 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   const T16* vc = v_cache + head_off;
   // A unit's place in the ring is carried from unit to unit (no division in the loop), and
   // the page that holds its first row is asked for one unit ahead of its use.
-  const int ring_step = (FA_WARPS * FD_UNIT) % capacity;
+  const int ring_step = (NW * FD_UNIT) % capacity;
   auto page_of = [&](int u, int row) { return (PAGED && u < u1) ? my_pages[row / KV_PAGE] : 0; };
   auto load_unit = [&](int u, int stage, int first, int page) {
     const int n = min(FD_UNIT, pos + 1 - (lo + u * FD_UNIT));
@@ -517,14 +519,14 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   for (int i = 0; i < FD_STAGES - 1; ++i) {
     row_first[i] = row_next;
     page_first[i] = page_of(u_next, row_next);
-    u_next += FA_WARPS;
+    u_next += NW;
     row_next += ring_step;
     if (row_next >= capacity) row_next -= capacity;
   }
   int page_next = page_of(u_next, row_next);
 #pragma unroll
   for (int i = 0; i < FD_STAGES - 1; ++i) {
-    const int u = u0 + warp + i * FA_WARPS;
+    const int u = u0 + warp + i * NW;
     // (fused: the newest key's unit comes now as well; its row for this step's position
     // holds an old key, which is written over below)
     if (u < u1 && (FUSED || u != u_new)) load_unit(u, i, row_first[i], page_first[i]);
@@ -532,12 +534,12 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   }
   pdl_wait();
   if (!FUSED) {
-    load_tile<HDP>(q_s, FD_ROWS, hd, q, [&](int r) -> const T16* {
+    load_tile<HDP, FD_THREADS>(q_s, FD_ROWS, hd, q, [&](int r) -> const T16* {
       return r < nh ? q + ((size_t)t * H + h0 + r) * hd : nullptr;
     });
 #pragma unroll
     for (int i = 0; i < FD_STAGES - 1; ++i) {
-      const int u = u0 + warp + i * FA_WARPS;
+      const int u = u0 + warp + i * NW;
       if (u < u1 && u == u_new) load_unit(u, i, row_first[i], page_first[i]);
     }
     cp_async_commit();
@@ -555,15 +557,15 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
     const float* tok_row = fz.qkv + (size_t)t * row_elems;
     const int r_new = (nkeys - 1) - u_new * FD_UNIT;         // the new key's row in its unit
     const int new_at = u_new - u0;                           // its unit: warp new_at % 4, stage new_at / 4
-    const bool staged = newest_here && new_at < (FD_STAGES - 1) * FA_WARPS;
-    const uint32_t new_tile = q_s + FD_ROWS * HDP * 2 + (new_at % FA_WARPS) * WARP_RING +
-                              (new_at / FA_WARPS) * 2 * TILE;
+    const bool staged = newest_here && new_at < (FD_STAGES - 1) * NW;
+    const uint32_t new_tile = q_s + FD_ROWS * HDP * 2 + (new_at % NW) * WARP_RING +
+                              (new_at / NW) * 2 * TILE;
     const size_t new_row = newest_here
         ? kv_row_offset(page_table, pps, n_pages, slot, g, G, capacity, pos % capacity, hd) : 0;
     cp_async_wait<0>();                                      // this thread's share of the first units
     __syncthreads();                                         // everybody's: their rows may be written over
 #pragma unroll 1
-    for (int item = threadIdx.x; item < n_items; item += FA_THREADS) {
+    for (int item = threadIdx.x; item < n_items; item += FD_THREADS) {
       int col, i, kind;                                      // kind 0: q, 1: k, 2: v
       int r = 0;
       if (item < nh * per_q) {
@@ -663,12 +665,12 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   const uint32_t v_lane = ((lane & 7) + ((lane >> 4) << 3)) * (HDP * 2),
                  v_x = (uint32_t)(((lane >> 3) & 1) ^ (lane & 7)) << 4;
   int it = 0;
-  for (int u = u0 + warp; u < u1; u += FA_WARPS, ++it) {
+  for (int u = u0 + warp; u < u1; u += NW, ++it) {
     const int stage = it % FD_STAGES;
     cp_async_wait<FD_STAGES - 2>();                          // unit u has landed (this lane's share)
     __syncwarp();                                            // ... every lane's; unit u-1 is read out
     if (u_next < u1) load_unit(u_next, (it + FD_STAGES - 1) % FD_STAGES, row_next, page_next);
-    u_next += FA_WARPS;
+    u_next += NW;
     row_next += ring_step;
     if (row_next >= capacity) row_next -= capacity;
     page_next = page_of(u_next, row_next);
@@ -800,10 +802,10 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
     const int r = threadIdx.x;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < FA_WARPS; ++w) M = fmaxf(M, wm_s[w][r]);
+    for (int w = 0; w < NW; ++w) M = fmaxf(M, wm_s[w][r]);
     float L = 0.f;
 #pragma unroll
-    for (int w = 0; w < FA_WARPS; ++w) {
+    for (int w = 0; w < NW; ++w) {
       const float f = wm_s[w][r] > -INFINITY ? exp2f(wm_s[w][r] - M) : 0.f;
       wm_s[w][r] = f;                                         // now the warp's weight
       L += wl_s[w][r] * f;
@@ -813,11 +815,11 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   }
   __syncthreads();
   const size_t qh = (size_t)t * H + h0;
-  for (int idx = threadIdx.x; idx < nh * hd; idx += FA_THREADS) {
+  for (int idx = threadIdx.x; idx < nh * hd; idx += FD_THREADS) {
     const int d = idx / nh, r = idx - d * nh;
     float O = 0.f;
 #pragma unroll
-    for (int w = 0; w < FA_WARPS; ++w) O += o_s[((size_t)w * hd + d) * FD_OPAD + r] * wm_s[w][r];
+    for (int w = 0; w < NW; ++w) O += o_s[((size_t)w * hd + d) * FD_OPAD + r] * wm_s[w][r];
     if (n_parts == 1) {
       out[(qh + r) * hd + d] = from_float<T16>(O / row_l[r]);
     } else {
@@ -838,8 +840,8 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   __threadfence();
   if (threadIdx.x == 0) *counter = 0;
   float* w_s = reinterpret_cast<float*>(fa_smem);            // [n_parts][16 rows]
-  {
-    const int r = threadIdx.x >> 3, sub = threadIdx.x & 7;   // 16 rows x 8 threads
+  for (int r = threadIdx.x >> 3; r < FD_ROWS; r += FD_THREADS / 8) {   // rows x 8 threads
+    const int sub = threadIdx.x & 7;
     float M = -INFINITY;
     if (r < nh)
       for (int s2 = sub; s2 < n_parts; s2 += 8)
@@ -860,7 +862,7 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
     if (sub == 0 && r < nh) row_l[r] = L;
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < nh * hd; idx += FA_THREADS) {
+  for (int idx = threadIdx.x; idx < nh * hd; idx += FD_THREADS) {
     const int r = idx / hd, d = idx - r * hd;
     const float* po = part_o + (qh + r) * max_parts * hd + d;
     float O = 0.f;
@@ -877,7 +879,7 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   }
 }
 
-template <int HDP, int NT, typename T16, bool PAGED, bool FUSED>
+template <int HDP, int NT, typename T16, bool PAGED, bool FUSED, int NW>
 static int launch_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                              const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                              float* part_ml, int* counters, int* status, int n_seqs, int H, int G,
@@ -885,12 +887,12 @@ static int launch_decode_mma(const void* q, const void* k_cache, const void* v_c
                              const int* page_table, int pps, int n_pages, const fd_fused_args& fz,
                              cudaStream_t stream) {
   // Q, then every warp's ring of (K, V) stages; the merge buffer lies over them
-  size_t smem = (size_t)(FD_ROWS + FA_WARPS * FD_STAGES * 2 * FD_UNIT) * HDP * 2;
-  const size_t merge = (size_t)FA_WARPS * hd * FD_OPAD * 4;
+  size_t smem = (size_t)(FD_ROWS + NW * FD_STAGES * 2 * FD_UNIT) * HDP * 2;
+  const size_t merge = (size_t)NW * hd * FD_OPAD * 4;
   if (smem < merge) smem = merge;
   static size_t attr_smem = 0;
   if (smem > attr_smem) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HDP, NT, T16, PAGED, FUSED>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HDP, NT, T16, PAGED, FUSED, NW>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_smem = smem;
@@ -898,7 +900,7 @@ static int launch_decode_mma(const void* q, const void* k_cache, const void* v_c
   const int nhc = (H / G + FD_ROWS - 1) / FD_ROWS;
   const dim3 grid(max_parts, G * nhc, n_seqs);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
-  launch_pdl(attn_decode_mma_kernel<HDP, NT, T16, PAGED, FUSED>, grid, dim3(FA_THREADS), smem, stream,
+  launch_pdl(attn_decode_mma_kernel<HDP, NT, T16, PAGED, FUSED, NW>, grid, dim3(NW * 32), smem, stream,
              (const T16*)q, (const T16*)k_cache, (const T16*)v_cache,
              seq_slot, slot_pos, (T16*)out, part_o, part_ml, counters, status, H, G, hd,
              capacity, window, cpc, max_parts, scale_log2, page_table, pps, n_pages, fz);
@@ -940,9 +942,11 @@ static int decode_mma_dispatch(const void* q, const void* k_cache, const void* v
                                const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                                float* part_ml, int* counters, int* status, int dtype, int n_seqs, int H,
                                int G, int hd, int capacity, int window, int max_context,
-                               int chunks_per_block, const int* page_table, int pages_per_slot,
-                               int n_pages, const fd_fused_args* fused, cudaStream_t stream) {
+                               int chunks_per_block, int warps, const int* page_table,
+                               int pages_per_slot, int n_pages, const fd_fused_args* fused,
+                               cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
+  if (warps != FD_WARPS_MAX && (FUSED || warps != 2)) return -4;
   if (dtype != DT_BF16 && dtype != DT_F16) return -3;
   if (hd % 16 != 0 || hd > 128 || hd <= 0) return -2;
   if (G <= 0 || H % G != 0) return -3;
@@ -954,13 +958,16 @@ static int decode_mma_dispatch(const void* q, const void* k_cache, const void* v
   const bool two = H / G > 8;                                 // a second tile of 8 heads
   const fd_fused_args none = {nullptr, nullptr, 0, 0};
   const fd_fused_args& fz = fused ? *fused : none;
-#define YALM_FD_(HDP, NT, T, PAGED, FUSED)                                                       \
-  launch_decode_mma<HDP, NT, T, PAGED, FUSED>(q, k_cache, v_cache, seq_slot, slot_pos, out,      \
-                                              part_o, part_ml, counters, status, n_seqs, H, G,   \
-                                              hd, capacity, window, chunks_per_block, max_parts, \
-                                              page_table, pages_per_slot, n_pages, fz, stream)
-#define YALM_FD(HDP, NT, T) \
-  (page_table ? YALM_FD_(HDP, NT, T, true, FUSED) : YALM_FD_(HDP, NT, T, false, FUSED))
+#define YALM_FD__(HDP, NT, T, PAGED, NW)                                                         \
+  launch_decode_mma<HDP, NT, T, PAGED, FUSED, NW>(q, k_cache, v_cache, seq_slot, slot_pos, out,  \
+                                                  part_o, part_ml, counters, status, n_seqs, H,  \
+                                                  G, hd, capacity, window, chunks_per_block,     \
+                                                  max_parts, page_table, pages_per_slot,         \
+                                                  n_pages, fz, stream)
+#define YALM_FD_(HDP, NT, T, PAGED)                                                              \
+  ((!FUSED && warps == 2) ? YALM_FD__(HDP, NT, T, PAGED, (FUSED ? FD_WARPS_MAX : 2))             \
+                          : YALM_FD__(HDP, NT, T, PAGED, FD_WARPS_MAX))
+#define YALM_FD(HDP, NT, T) (page_table ? YALM_FD_(HDP, NT, T, true) : YALM_FD_(HDP, NT, T, false))
   if (dtype == DT_F16) {
     if (hd <= 64) return two ? YALM_FD(64, 2, __half) : YALM_FD(64, 1, __half);
     return two ? YALM_FD(128, 2, __half) : YALM_FD(128, 1, __half);
@@ -969,6 +976,7 @@ static int decode_mma_dispatch(const void* q, const void* k_cache, const void* v
   return two ? YALM_FD(128, 2, __nv_bfloat16) : YALM_FD(128, 1, __nv_bfloat16);
 #undef YALM_FD
 #undef YALM_FD_
+#undef YALM_FD__
 }
 
 }  // namespace yalm

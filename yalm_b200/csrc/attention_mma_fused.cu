@@ -21,5 +21,6 @@ extern "C" int yalm_attention_decode_mma_fused(const float* qkv, int n_partials,
   const fd_fused_args fz = {qkv, reinterpret_cast<const float2*>(cos_sin), partial_stride, n_partials};
   return decode_mma_dispatch<true>(nullptr, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,
                              counters, status, dtype, n_seqs, H, G, hd, capacity, window, max_context,
-                             chunks_per_block, page_table, pages_per_slot, n_pages, &fz, stream);
+                             chunks_per_block, FD_WARPS_MAX, page_table, pages_per_slot, n_pages, &fz,
+                             stream);
 }

@@ -67,7 +67,7 @@ _SIGNATURES = {
     "yalm_attention_prefill_tc_cache": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i,
                                         _i, _vp, _i, _i, _vp, _vp],
     "yalm_attention_decode_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
-                                  _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
+                                  _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_attention_decode_mma_fused": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i,
                                         _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "yalm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
@@ -375,7 +375,8 @@ def attention_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          part_o: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
                          status: torch.Tensor, H: int, G: int, hd: int, capacity: int,
                          window: Optional[int], max_context: int, chunks_per_block: int,
-                         pages=None) -> None:
+                         pages=None, warps: int = 4) -> None:
+    """``warps``: 4 (one block to an SM) or 2 (two blocks of two warps to an SM)."""
     n = q.shape[0]
     pt, pps, npg = _pages(pages, k_cache, G, hd)
     _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype and q.dtype in HALF_TYPES,
@@ -389,7 +390,7 @@ def attention_decode_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                                            _p(slot_pos), _p(out), _p(part_o), _p(part_ml),
                                            _p(counters), _p(status), dtype_code(q.dtype), n, H, G,
                                            hd, capacity, int(window or 0), max_context,
-                                           chunks_per_block, pt, pps, npg,
+                                           chunks_per_block, warps, pt, pps, npg,
                                            _stream()),
            "attention_decode_mma")
 

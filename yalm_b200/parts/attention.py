@@ -73,10 +73,29 @@ class GQAAttention:
                   for p in batch.past]
         resident = self.rt.sm_count
         most = max(1, -(-visible // 64))
+        if self.rt.decode_attention_chunks:
+            return min(most, int(self.rt.decode_attention_chunks))
         cpc = max(1, min(most, -(-groups * sum(chunks) // resident)))
         while cpc < most and groups * sum(-(-c // cpc) for c in chunks) > resident:
             cpc += 1
         return cpc
+
+    def decode_warps(self, batch, visible: int, cpc: int) -> int:
+        """Warps per block of the tensor-core decode kernel.  Four, one block to an SM, unless
+        the blocks take whole sequences and come in three waves or more: then two blocks of
+        two warps share an SM, and one block's start (positions, pages, first copies) and end
+        (the warps' merge, the output) run under the other's copies.  Measured at 7B sizes,
+        contexts 64 to 2,048, ms per step with four and with two warps: 48 sequences 4.52 /
+        4.55, 56: 4.75 / 4.65, 64: 4.99 / 4.83, 128: 7.42 / 7.18.  With fewer blocks each
+        block's length decides and four warps are faster (32 sequences: 3.60 / 3.90).  Head
+        sizes up to 64 already have two four-warp blocks to an SM; there the two-warp form
+        wins from six waves on (Llama-3.2-1B sizes, 128 sequences: 1.80 / 1.73)."""
+        if self.rt.decode_attention_warps:
+            return int(self.rt.decode_attention_warps)
+        groups = self.G * -(-(self.H // self.G) // 16)
+        whole = cpc >= max(1, -(-visible // 64))
+        waves = 3 if self.hd > 64 else 6
+        return 2 if whole and groups * batch.n_seqs >= waves * self.rt.sm_count else 4
 
     # The decode kernel's grid takes sequences in row order, and long blocks that start
     # last leave the SMs idle at the end: the generation loop orders a batch by this.
@@ -147,6 +166,7 @@ class GQAAttention:
             visible = min(bound, self.window) if self.window else bound
             if tensor_cores:
                 cpc = self.decode_chunks_per_block(batch, visible)
+                warps = 4 if in_attention else self.decode_warps(batch, visible, cpc)
                 parts = ops.decode_mma_parts(bound, self.window, cpc)
             else:
                 chunk = self.decode_chunk(batch)
@@ -162,7 +182,8 @@ class GQAAttention:
             elif tensor_cores:
                 ops.attention_decode_mma(q, view.k, view.v, batch.seq_slot, view.slot_pos, o,
                                          part_o, part_ml, counters, rt.status, H, G, hd,
-                                         view.capacity, self.window, bound, cpc, pages=view.pages)
+                                         view.capacity, self.window, bound, cpc, pages=view.pages,
+                                         warps=warps)
             else:
                 ops.attention_decode(q, view.k, view.v, batch.seq_slot, view.slot_pos, o, part_o,
                                      part_ml, counters, rt.status, H, G, hd, view.capacity,

@@ -89,6 +89,10 @@ class Runtime:
         self.attention = attention            # "auto" | "mma" (no tcgen05 prefill attention) | "simt"
         # small decode batches: the attention kernel does the rotary kernel's work (False: never)
         self.decode_rope_in_attention = True
+        # the tensor-core decode attention's plan, for measurements: warps per block (4 or 2) and
+        # 64-key chunks per block; None: the part decides
+        self.decode_attention_warps = None
+        self.decode_attention_chunks = None
         # a matrix stored in 32 bits under 16-bit compute: "keep" it (it is then multiplied by
         # the FMA kernel, without tensor cores) or "round" it to the compute type
         self.float32_matrices = float32_matrices
