@@ -393,6 +393,9 @@ def main():
     ap.add_argument("--max-tokens", type=int, default=None,
                     help="a cache pool of this many tokens in pages of 64 behind a page table, "
                          "instead of one block of the context length per sequence")
+    ap.add_argument("--decode-warps", type=int, default=None, choices=[2, 4],
+                    help="warps per block of the tensor-core decode attention (default: the "
+                         "attention part decides by the batch)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -421,6 +424,7 @@ def main():
               file=sys.stderr, flush=True)
         if args.no_graphs:
             lm.engine.use_graphs = False
+        lm.rt.decode_attention_warps = args.decode_warps
         return lm
 
     if args.prefill_only:
