@@ -17,7 +17,7 @@ from ..cache import CacheNeed
 from ..csrc import ops
 from ..weights import TensorNeed
 from .base import POSITIONS, make_part, register_mixer
-from . import linear
+from . import decode_plan, linear
 from .linear import matmul_partials
 
 
@@ -81,21 +81,19 @@ class GQAAttention:
         return cpc
 
     def decode_warps(self, batch, visible: int, cpc: int) -> int:
-        """Warps per block of the tensor-core decode kernel.  Four, one block to an SM, unless
-        the blocks take whole sequences and come in three waves or more: then two blocks of
-        two warps share an SM, and one block's start (positions, pages, first copies) and end
-        (the warps' merge, the output) run under the other's copies.  Measured at 7B sizes,
-        contexts 64 to 2,048, ms per step with four and with two warps: 48 sequences 4.52 /
-        4.55, 56: 4.75 / 4.65, 64: 4.99 / 4.83, 128: 7.42 / 7.18.  With fewer blocks each
-        block's length decides and four warps are faster (32 sequences: 3.60 / 3.90).  Head
-        sizes up to 64 already have two four-warp blocks to an SM; there the two-warp form
-        wins from six waves on (Llama-3.2-1B sizes, 128 sequences: 1.80 / 1.73)."""
+        """Warps per block of the tensor-core decode kernel: four, unless the blocks take
+        whole sequences, outnumber the SMs' block slots, and the estimate of
+        ``decode_plan`` says that two blocks of two warps per SM get through the grid
+        sooner (few long blocks of equal length; many waves)."""
         if self.rt.decode_attention_warps:
             return int(self.rt.decode_attention_warps)
+        if cpc < max(1, -(-visible // 64)):
+            return 4
+        chunks = tuple(-(-(min(p + 1, self.window) if self.window else p + 1) // 64)
+                       for p in batch.past)
         groups = self.G * -(-(self.H // self.G) // 16)
-        whole = cpc >= max(1, -(-visible // 64))
-        waves = 3 if self.hd > 64 else 6
-        return 2 if whole and groups * batch.n_seqs >= waves * self.rt.sm_count else 4
+        return decode_plan.decode_warps(decode_plan.rounded(chunks), groups, self.hd,
+                                        self.rt.sm_count)
 
     # The decode kernel's grid takes sequences in row order, and long blocks that start
     # last leave the SMs idle at the end: the generation loop orders a batch by this.
