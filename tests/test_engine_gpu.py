@@ -190,6 +190,29 @@ def test_decode_fast_path_logits_across_graph_keys(name, dtype, monkeypatch):
     assert lm.engine.cache.slots.free_count == lm.max_batch
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_e"])
+def test_decode_with_two_warp_attention_blocks(name, dtype):
+    """The decode attention's second block shape (two warps; the engine takes it by itself only
+    for grids of several waves) forced on the trace's batch, with the rotary kernel apart:
+    logits against the plain model at every step, with and without graphs."""
+    from yalm_b200 import LM
+    from yalm_b200.config import config_from_dict
+    cfg, w, reqs, refs, _ = setup(name)
+    prompts = dict(REQUESTS[name]["prompts"])
+    ids = REQUESTS[name]["batches"][0]
+    sub = {r: reqs[r] for r in ids}
+    lm = LM(config_from_dict(cfg), dict(w), dtype=dtype, max_batch=len(ids))
+    lm.rt.decode_attention_warps = 2
+    lm.rt.decode_rope_in_attention = False
+    fast = forced_decode(lm, sub, prompts, refs, TOL[dtype])
+    lm.engine.use_graphs = False
+    assert torch.equal(fast, forced_decode(lm, sub, prompts, refs, TOL[dtype]))
+    lm.rt.decode_attention_warps = 4
+    four = forced_decode(lm, sub, prompts, refs, TOL[dtype])
+    assert (fast - four).abs().max().item() <= TOL[dtype] * max(1.0, four.abs().max().item())
+
+
 def test_temperature_sampling_is_per_request_and_reproducible():
     from yalm_b200 import LM
     from yalm_b200.config import config_from_dict
