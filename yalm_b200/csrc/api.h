@@ -59,7 +59,7 @@ int yalm_attention_decode(const void* q, const void* k_cache, const void* v_cach
                           int G, int hd, int capacity, int window, int chunk, int max_context,
                           const int* page_table, int pages_per_slot, int n_pages, cudaStream_t stream);
 
-// 16-bit attention on tensor cores (attention_mma.cu; dtype 1 or 2): head sizes in steps of
+// 16-bit attention on tensor cores (attention_mma_prefill.cu, attention_mma.cu; dtype 1 or 2): head sizes in steps of
 // 16 up to 128
 int yalm_attention_prefill_mma(const void* q, const void* kv_step, const void* k_cache,
                                const void* v_cache, const int* q_start, const int* seq_slot,
@@ -72,7 +72,15 @@ int yalm_attention_decode_mma(const void* q, const void* k_cache, const void* v_
                               int H, int G, int hd, int capacity, int window, int max_context,
                               int chunks_per_block, int warps, const int* page_table, int pages_per_slot,
                               int n_pages, cudaStream_t stream);
-// ... with the rotary kernel's work inside (attention_mma.cu): takes this step's q/k/v product
+// ... compiled with two warps per block (attention_mma_two_warps.cu); yalm_attention_decode_mma
+// calls it for warps = 2
+int yalm_attention_decode_mma_two_warps(const void* q, const void* k_cache, const void* v_cache,
+                                        const int* seq_slot, const int* slot_pos, void* out, float* part_o,
+                                        float* part_ml, int* counters, int* status, int dtype, int n_seqs,
+                                        int H, int G, int hd, int capacity, int window, int max_context,
+                                        int chunks_per_block, const int* page_table, int pages_per_slot,
+                                        int n_pages, cudaStream_t stream);
+// ... with the rotary kernel's work inside (attention_mma_fused.cu): takes this step's q/k/v product
 // as n_partials 32-bit slices and the step's cosines and sines, writes the new cache rows
 int yalm_attention_decode_mma_fused(const float* qkv, int n_partials, long long partial_stride,
                                     const float* cos_sin, void* k_cache, void* v_cache,

@@ -1,35 +1,8 @@
-// Attention on mma.sync tensor-core tiles: the entry points of the prefill kernel and of the
-// decode kernel (the kernels themselves: attention_mma.cuh).
+// Attention on mma.sync tensor-core tiles: the entry point of the decode kernel (the kernels
+// themselves: attention_mma.cuh; the prefill kernel's entry: attention_mma_prefill.cu).
 #include "attention_mma.cuh"
 
 using namespace yalm;
-
-// Prefill attention on tensor cores (dtype: bfloat16 or float16).  Sequences are given by q_start
-// [n_seqs + 1]; max_q_len is the longest of them (it sizes the grid).  Head sizes:
-// multiples of 16 up to 128 (others: use yalm_attention).
-extern "C" int yalm_attention_prefill_mma(const void* q, const void* kv_step, const void* k_cache,
-                                          const void* v_cache, const int* q_start,
-                                          const int* seq_slot, const int* slot_pos, void* out,
-                                          int dtype, int n_seqs, int max_q_len, int H, int G,
-                                          int hd, int capacity, int window, const int* page_table,
-                                          int pages_per_slot, int n_pages, cudaStream_t stream) {
-  if (n_seqs <= 0 || max_q_len <= 0) return 0;
-  if (dtype != DT_BF16 && dtype != DT_F16) return -3;
-  if (hd % 16 != 0 || hd > 128 || hd <= 0) return -2;
-  if (G <= 0 || H % G != 0) return -3;
-  if (H > 65535 || n_seqs > 65535) return -4;
-#define YALM_FP(HDP, T)                                                                          \
-  return launch_prefill<HDP, T>(q, kv_step, k_cache, v_cache, q_start, seq_slot, slot_pos, out,  \
-                                n_seqs, max_q_len, H, G, hd, capacity, window, page_table,        \
-                                pages_per_slot, n_pages, stream)
-  if (dtype == DT_F16) {
-    if (hd <= 64) YALM_FP(64, __half);
-    YALM_FP(128, __half);
-  }
-  if (hd <= 64) YALM_FP(64, __nv_bfloat16);
-  YALM_FP(128, __nv_bfloat16);
-#undef YALM_FP
-}
 
 // Decode attention on tensor cores (dtype: bfloat16 or float16): one query per sequence over the
 // cache.  A block walks through `chunks_per_block` chunks of 64 positions; a
@@ -47,8 +20,14 @@ extern "C" int yalm_attention_decode_mma(const void* q, const void* k_cache, con
                                          int window, int max_context, int chunks_per_block,
                                          int warps, const int* page_table, int pages_per_slot,
                                          int n_pages, cudaStream_t stream) {
-  return decode_mma_dispatch<false>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml, counters,
-                             status, dtype, n_seqs, H, G, hd, capacity, window, max_context,
-                             chunks_per_block, warps, page_table, pages_per_slot, n_pages, nullptr,
-                             stream);
+  if (warps == 2)                     // compiled in a translation unit of its own
+    return yalm_attention_decode_mma_two_warps(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o,
+                                               part_ml, counters, status, dtype, n_seqs, H, G, hd,
+                                               capacity, window, max_context, chunks_per_block,
+                                               page_table, pages_per_slot, n_pages, stream);
+  if (warps != FD_WARPS_MAX) return -4;
+  return decode_mma_dispatch<false, FD_WARPS_MAX>(q, k_cache, v_cache, seq_slot, slot_pos, out, part_o,
+                                                  part_ml, counters, status, dtype, n_seqs, H, G, hd,
+                                                  capacity, window, max_context, chunks_per_block,
+                                                  page_table, pages_per_slot, n_pages, nullptr, stream);
 }

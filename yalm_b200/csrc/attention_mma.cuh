@@ -937,16 +937,16 @@ static int launch_prefill(const void* q, const void* kv_step, const void* k_cach
 }
 
 // host side of the decode kernel: argument checks and the choice of the instantiation
-template <bool FUSED>
+template <bool FUSED, int NW>
 static int decode_mma_dispatch(const void* q, const void* k_cache, const void* v_cache,
                                const int* seq_slot, const int* slot_pos, void* out, float* part_o,
                                float* part_ml, int* counters, int* status, int dtype, int n_seqs, int H,
                                int G, int hd, int capacity, int window, int max_context,
-                               int chunks_per_block, int warps, const int* page_table,
+                               int chunks_per_block, const int* page_table,
                                int pages_per_slot, int n_pages, const fd_fused_args* fused,
                                cudaStream_t stream) {
+  static_assert(NW == FD_WARPS_MAX || NW == 2, "blocks of four warps, or of two");
   if (n_seqs <= 0) return 0;
-  if (warps != FD_WARPS_MAX && (FUSED || warps != 2)) return -4;
   if (dtype != DT_BF16 && dtype != DT_F16) return -3;
   if (hd % 16 != 0 || hd > 128 || hd <= 0) return -2;
   if (G <= 0 || H % G != 0) return -3;
@@ -958,15 +958,12 @@ static int decode_mma_dispatch(const void* q, const void* k_cache, const void* v
   const bool two = H / G > 8;                                 // a second tile of 8 heads
   const fd_fused_args none = {nullptr, nullptr, 0, 0};
   const fd_fused_args& fz = fused ? *fused : none;
-#define YALM_FD__(HDP, NT, T, PAGED, NW)                                                         \
+#define YALM_FD_(HDP, NT, T, PAGED)                                                              \
   launch_decode_mma<HDP, NT, T, PAGED, FUSED, NW>(q, k_cache, v_cache, seq_slot, slot_pos, out,  \
                                                   part_o, part_ml, counters, status, n_seqs, H,  \
                                                   G, hd, capacity, window, chunks_per_block,     \
                                                   max_parts, page_table, pages_per_slot,         \
                                                   n_pages, fz, stream)
-#define YALM_FD_(HDP, NT, T, PAGED)                                                              \
-  ((!FUSED && warps == 2) ? YALM_FD__(HDP, NT, T, PAGED, (FUSED ? FD_WARPS_MAX : 2))             \
-                          : YALM_FD__(HDP, NT, T, PAGED, FD_WARPS_MAX))
 #define YALM_FD(HDP, NT, T) (page_table ? YALM_FD_(HDP, NT, T, true) : YALM_FD_(HDP, NT, T, false))
   if (dtype == DT_F16) {
     if (hd <= 64) return two ? YALM_FD(64, 2, __half) : YALM_FD(64, 1, __half);
@@ -976,7 +973,6 @@ static int decode_mma_dispatch(const void* q, const void* k_cache, const void* v
   return two ? YALM_FD(128, 2, __nv_bfloat16) : YALM_FD(128, 1, __nv_bfloat16);
 #undef YALM_FD
 #undef YALM_FD_
-#undef YALM_FD__
 }
 
 }  // namespace yalm

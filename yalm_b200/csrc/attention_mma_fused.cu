@@ -19,8 +19,8 @@ extern "C" int yalm_attention_decode_mma_fused(const float* qkv, int n_partials,
   if (qkv == nullptr || cos_sin == nullptr || n_partials < 1) return -3;
   if (((uintptr_t)qkv | (uintptr_t)cos_sin) & 15 || (partial_stride & 3)) return -6;
   const fd_fused_args fz = {qkv, reinterpret_cast<const float2*>(cos_sin), partial_stride, n_partials};
-  return decode_mma_dispatch<true>(nullptr, k_cache, v_cache, seq_slot, slot_pos, out, part_o, part_ml,
-                             counters, status, dtype, n_seqs, H, G, hd, capacity, window, max_context,
-                             chunks_per_block, FD_WARPS_MAX, page_table, pages_per_slot, n_pages, &fz,
-                             stream);
+  return decode_mma_dispatch<true, FD_WARPS_MAX>(nullptr, k_cache, v_cache, seq_slot, slot_pos, out, part_o,
+                                                 part_ml, counters, status, dtype, n_seqs, H, G, hd, capacity,
+                                                 window, max_context, chunks_per_block, page_table,
+                                                 pages_per_slot, n_pages, &fz, stream);
 }

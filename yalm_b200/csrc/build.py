@@ -23,9 +23,8 @@ import time
 from typing import List, Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["elementwise.cu", "attention.cu", "attention_mma.cu", "attention_mma_fused.cu", "attention_tc.cu",
-           "gemm_simt.cu",
-           "gemm_tcgen05.cu", "sampling.cu"]
+SOURCES = ["elementwise.cu", "attention.cu", "attention_mma.cu", "attention_mma_prefill.cu",
+           "attention_mma_fused.cu", "attention_mma_two_warps.cu", "attention_tc.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "sampling.cu"]
 HEADERS = ["api.h", "common.cuh", "attention_mma.cuh", "no_alloc.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
@@ -100,7 +99,7 @@ def build(verbose_ptxas: bool = False, force: bool = False) -> str:
     _say(f"building the sm_100a kernel library ({len(SOURCES)} files) into {out_dir}")
     t0 = time.time()
     objs = [os.path.join(out_dir, f"{os.path.splitext(s)[0]}_{tag}_{os.getpid()}.o") for s in SOURCES]
-    with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as pool:
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(10, len(SOURCES))) as pool:
         futs = {pool.submit(_compile_one, nvcc, s, o, extra): s for s, o in zip(SOURCES, objs)}
         pending = set(futs)
         while pending:
