@@ -500,6 +500,7 @@ def test_tensor_core_prefill_attention(ops, H, G, hd, cap, window, dt, eps):
     (40, 2, 64, 300, 100),      # 20 query heads per kv head: two head groups of the tile
     (3, 1, 32, 1000, None),
     (24, 2, 80, 200, None),     # 12 query heads per kv head: both 8-head tiles, one partly empty
+    (4, 2, 64, 1700, None),     # 27 parts at one chunk per block
 ])
 @pytest.mark.parametrize("warps", [4, 2])
 @pytest.mark.parametrize("dt, eps", HALF)

@@ -839,6 +839,42 @@ attn_decode_mma_kernel(const T16* __restrict__ q, const T16* __restrict__ k_cach
   if (!last_flag) return;
   __threadfence();
   if (threadIdx.x == 0) *counter = 0;
+  // Up to 8 parts: every thread asks for its features' partial sums and its row's maxima and
+  // sums at once (one trip to L2, no barrier) and adds them in the order of the parts: 1.5 us
+  // less per layer than the two rounds below (7B sizes, 2 to 12 sequences: 1.2-1.6 % of a
+  // step).  With 9 to 24 parts at once it is slower than the two rounds (one sequence: +1 %).
+  auto merge_at_once = [&](auto width) {
+    constexpr int MP = decltype(width)::value;
+    for (int idx = threadIdx.x; idx < nh * hd; idx += FD_THREADS) {
+      const int r = idx / hd, d = idx - r * hd;
+      const float* po = part_o + (qh + r) * max_parts * hd + d;
+      const float2* ml = reinterpret_cast<const float2*>(part_ml + (qh + r) * max_parts * 2);
+      float v[MP], ms[MP], ls[MP];
+#pragma unroll
+      for (int j = 0; j < MP; ++j) {
+        const bool live = j < n_parts;
+        v[j] = live ? __ldcg(po + (size_t)j * hd) : 0.f;
+        const float2 x = live ? __ldcg(ml + j) : make_float2(-INFINITY, 0.f);
+        ms[j] = x.x;
+        ls[j] = x.y;
+      }
+      float M = ms[0];
+#pragma unroll
+      for (int j = 1; j < MP; ++j) M = fmaxf(M, ms[j]);
+      float O = 0.f, L = 0.f;
+#pragma unroll
+      for (int j = 0; j < MP; ++j) {
+        const float f = ms[j] > -INFINITY ? exp2f(ms[j] - M) : 0.f;
+        O = fmaf(v[j], f, O);
+        L = fmaf(ls[j], f, L);
+      }
+      out[(qh + r) * hd + d] = from_float<T16>(O / L);
+    }
+  };
+  if (n_parts <= 8) {
+    merge_at_once(std::integral_constant<int, 8>());
+    return;
+  }
   float* w_s = reinterpret_cast<float*>(fa_smem);            // [n_parts][16 rows]
   for (int r = threadIdx.x >> 3; r < FD_ROWS; r += FD_THREADS / 8) {   // rows x 8 threads
     const int sub = threadIdx.x & 7;
