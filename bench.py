@@ -327,6 +327,8 @@ def reference_arm(args):
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
     import run_reference
     base_cfg, context, default_batch, lo, hi = WORKLOADS[args.workload]
+    if args.prompt_lengths:
+        lo, hi = args.prompt_lengths
     batch = args.batch or default_batch
     layers = args.layers or base_cfg["num_hidden_layers"]
     cfg = dict(base_cfg, num_hidden_layers=layers)
@@ -393,6 +395,11 @@ def main():
     ap.add_argument("--max-tokens", type=int, default=None,
                     help="a cache pool of this many tokens in pages of 64 behind a page table, "
                          "instead of one block of the context length per sequence")
+    ap.add_argument("--prompt-lengths", type=int, nargs=2, default=None, metavar=("LO", "HI"),
+                    help="prompt lengths are drawn from U[LO, HI] instead of the workload's range")
+    ap.add_argument("--decode-chunks", type=int, default=None,
+                    help="64-key chunks per block of the tensor-core decode attention (default: "
+                         "the attention part decides by the batch)")
     ap.add_argument("--decode-warps", type=int, default=None, choices=[2, 4],
                     help="warps per block of the tensor-core decode attention (default: the "
                          "attention part decides by the batch)")
@@ -425,6 +432,7 @@ def main():
         if args.no_graphs:
             lm.engine.use_graphs = False
         lm.rt.decode_attention_warps = args.decode_warps
+        lm.rt.decode_attention_chunks = args.decode_chunks
         return lm
 
     if args.prefill_only:
