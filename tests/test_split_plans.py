@@ -67,3 +67,52 @@ def test_decode_attention_block_shape_follows_the_measurements():
     assert pick(ragged(32, 16, 1024), 64) == 4    # head size 64: two four-warp blocks share an SM anyway
     assert pick(ragged(128, 16, 1024), 64) == 2
     assert decode_plan.rounded((3, 16, 17, 33, 61)) == (3, 16, 18, 36, 64)
+
+
+class _Lengths:
+    def __init__(self, past, bound):
+        self.past, self.ctx_bound, self.n_seqs = list(past), bound, len(past)
+
+
+def _attention(window=None):
+    from yalm_b200.config import config_from_dict
+    from yalm_b200.parts import Model, Runtime
+    cfg = {"architectures": ["MistralForCausalLM"], "model_type": "mistral", "hidden_size": 4096,
+           "intermediate_size": 14336, "num_hidden_layers": 1, "num_attention_heads": 32,
+           "num_key_value_heads": 8, "vocab_size": 32000, "rms_norm_eps": 1e-5, "rope_theta": 1e6,
+           "max_position_embeddings": 32768, "sliding_window": window, "hidden_act": "silu",
+           "tie_word_embeddings": False}
+    model = Model(config_from_dict(cfg).to_spec(), Runtime.shapes_only())
+    return next(iter(model.layers[0].mixers().values()))
+
+
+def test_chunks_per_block_of_the_decode_attention():
+    att = _attention()
+    plan = lambda past, bound: att.decode_chunks_per_block(_Lengths(past, bound), bound)
+    # one long sequence: about six parts, not the sixteen that would give every block an SM
+    assert plan([959], 1024) == 3 and plan([1899], 2048) == 6 and plan([3899], 4096) == 11
+    # up to eight chunks at the step's bound: one part
+    assert plan([299], 512) == 8 and plan([299] * 8, 512) == 8
+    # many sequences: whole sequences, nothing to merge
+    assert plan([700] * 20, 1024) == 16 and plan([100, 2000] * 32, 2048) == 32
+    # counted at the lengths the sequences have when the longest reaches the bound: sixteen of
+    # 700 keys fit 148 SMs in runs of 11 chunks today and of 16 (whole) at 1,024
+    assert plan([699] * 16, 1024) == 16
+    # eight ragged sequences at batch 8: every block resident at the bound, and no sequence
+    # in more than six parts
+    past = [1032, 955, 930, 798, 737, 634, 503, 207]
+    cpc = plan(past, 1536)
+    at_bound = [-(-(p + 1 + 1536 - 1033) // 64) for p in past]
+    assert 8 * sum(-(-c // cpc) for c in at_bound) <= 148 < 8 * sum(-(-c // (cpc - 1)) for c in at_bound)
+    assert max(-(-c // cpc) for c in at_bound) <= 6
+    # a window bounds what a query sees, and so the chunks
+    win = _attention(window=256)
+    assert win.decode_chunks_per_block(_Lengths([5000], 5120), 256) == 4
+    # the block shape: four warps while every block has an SM, two where many whole sequences
+    # come in waves; forced figures pass through
+    assert att.decode_warps(_Lengths([700] * 16, 1024), 1024, 16) == 4
+    assert att.decode_warps(_Lengths([2040] * 20, 2048), 2048, 32) == 2
+    assert att.decode_warps(_Lengths([700] * 16, 1024), 1024, 8) == 4       # blocks are parts: four warps
+    att.rt.decode_attention_warps, att.rt.decode_attention_chunks = 2, 5
+    assert att.decode_warps(_Lengths([700] * 16, 1024), 1024, 16) == 2
+    assert plan([959], 1024) == 5

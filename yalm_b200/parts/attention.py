@@ -77,9 +77,10 @@ class GQAAttention:
         """How many 64-key chunks one block of the tensor-core decode kernel walks
         through: the fewest with which all blocks are resident at once (one per
         SM; its four warps take the chunks' halves in turn), but no fewer than
-        leave a sequence about six parts, and a whole sequence of up to six
-        chunks.  A few sequences then get several blocks each and a merge; with
-        many sequences a block takes its whole sequence and nothing is merged.
+        leave a sequence about six parts, and a whole sequence of up to eight
+        chunks (lengths as they are when the longest reaches the step's bound).
+        A few sequences then get several blocks each and a merge; with many
+        sequences a block takes its whole sequence and nothing is merged.
         (Merging costs about 2 us and 0.3 to 0.4 us per part, a further unit of 32
         keys per warp about 1 us: one or two sequences of 1,000 to 4,000 keys in
         16 parts each, as the first rule alone has it, take 2.5 to 4 % longer per
@@ -95,7 +96,7 @@ class GQAAttention:
         while cpc < most and groups * sum(-(-c // cpc) for c in chunks) > resident:
             cpc += 1
         longest = max(chunks)
-        return max(cpc, most if longest <= 6 else min(most, -(-most // 6)))
+        return max(cpc, most if longest <= 8 else min(most, -(-most // 6)))
 
     def decode_warps(self, batch, visible: int, cpc: int) -> int:
         """Warps per block of the tensor-core decode kernel: four, unless the blocks take

@@ -113,6 +113,8 @@ class Runtime:
         rt.float32_matrices, rt.kept_float32 = "keep", 0
         rt.status, rt._buffers, rt._shared = None, {}, []
         rt.frozen, rt.sm_count, rt.buffer_generation = True, 148, 0
+        rt.decode_rope_in_attention = True
+        rt.decode_attention_warps = rt.decode_attention_chunks = None
         return rt
 
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
